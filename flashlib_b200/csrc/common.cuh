@@ -1,0 +1,143 @@
+// Shared helpers for the flashlib_b200 kernels: error plumbing for the C ABI and the
+// warp-level sorting network used by every top-k pool in this library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <math.h>
+
+#include "../../include/flashlib_b200.h"
+
+namespace fl {
+
+// ---- host-side error plumbing ------------------------------------------------------
+void set_error(const char* fmt, ...);
+
+#define FL_CHECK_ARG(cond, ...)                                                         \
+    do {                                                                                \
+        if (!(cond)) {                                                                  \
+            ::fl::set_error(__VA_ARGS__);                                               \
+            return FL_EINVAL;                                                           \
+        }                                                                               \
+    } while (0)
+
+#define FL_CHECK_CUDA(expr)                                                             \
+    do {                                                                                \
+        cudaError_t e__ = (expr);                                                       \
+        if (e__ != cudaSuccess) {                                                       \
+            ::fl::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__),    \
+                            __FILE__, __LINE__);                                        \
+            return FL_ECUDA;                                                            \
+        }                                                                               \
+    } while (0)
+
+#define FL_CHECK_LAUNCH()  FL_CHECK_CUDA(cudaGetLastError())
+
+static inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline int pow2_ceil(int v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+// Opt-in dynamic shared memory limit of the current device in bytes.
+int smem_optin_bytes();
+
+// ---- device-side helpers -----------------------------------------------------------
+constexpr unsigned FULL_MASK = 0xffffffffu;
+constexpr uint32_t INVALID_ID = 0xffffffffu;
+
+#if defined(__CUDACC__)
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+__device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
+
+// Bitonic sorting network over NPL*32 (key, id) pairs held NPL per lane; the element at
+// register r of lane l has position r*32 + l.  Sorts by DESCENDING key.  With TIEBREAK,
+// equal keys are ordered by ascending id, which makes the order total and the result
+// independent of where the elements started.
+template <int NPL, bool TIEBREAK>
+__device__ __forceinline__ void warp_sort_desc(float (&key)[NPL], uint32_t (&id)[NPL]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int k = 2; k <= NPL * 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j >= 32) {
+                const int jr = j >> 5;
+#pragma unroll
+                for (int r = 0; r < NPL; ++r) {
+                    const int pr = r ^ jr;
+                    if (pr > r) {
+                        const bool desc_block = (((r << 5) & k) == 0);
+                        const float a = key[r], b = key[pr];
+                        const uint32_t ia = id[r], ib = id[pr];
+                        // "a should come after b" in a descending block
+                        bool a_lt_b = a < b;
+                        bool a_gt_b = a > b;
+                        if (TIEBREAK) {
+                            a_lt_b = a_lt_b || (a == b && ia > ib);
+                            a_gt_b = a_gt_b || (a == b && ia < ib);
+                        }
+                        const bool sw = desc_block ? a_lt_b : a_gt_b;
+                        if (sw) {
+                            key[r] = b; key[pr] = a;
+                            id[r] = ib; id[pr] = ia;
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < NPL; ++r) {
+                    const int p = (r << 5) | lane;
+                    const float ok = __shfl_xor_sync(FULL_MASK, key[r], j);
+                    const uint32_t oi = __shfl_xor_sync(FULL_MASK, id[r], j);
+                    const bool lower = (lane & j) == 0;
+                    const bool desc_block = ((p & k) == 0);
+                    const bool take_max = (lower == desc_block);
+                    bool o_gt = ok > key[r];
+                    bool o_lt = ok < key[r];
+                    if (TIEBREAK) {
+                        o_gt = o_gt || (ok == key[r] && oi < id[r]);
+                        o_lt = o_lt || (ok == key[r] && oi > id[r]);
+                    }
+                    const bool take = take_max ? o_gt : o_lt;
+                    if (take) { key[r] = ok; id[r] = oi; }
+                }
+            }
+        }
+    }
+}
+
+// Compacts one row's candidate pool: reads `cnt` (score, id) entries from sc/idv (any
+// address space), keeps the K1 best (largest score) at positions [0, K1) in descending
+// order and returns the new threshold: the K1-th best score, or -inf while fewer than
+// K1 entries exist.  NPL*32 must be >= the pool capacity.  All 32 lanes must call it.
+template <int NPL>
+__device__ __forceinline__ float warp_pool_compact(float* sc, uint32_t* idv, int cnt, int K1) {
+    const int lane = threadIdx.x & 31;
+    float key[NPL];
+    uint32_t id[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const int e = (r << 5) | lane;
+        const bool ok = e < cnt;
+        key[r] = ok ? sc[e] : neg_inf();
+        id[r] = ok ? idv[e] : INVALID_ID;
+    }
+    warp_sort_desc<NPL, false>(key, id);
+    float thr = neg_inf();
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const int e = (r << 5) | lane;
+        if (e < K1) { sc[e] = key[r]; idv[e] = id[r]; }
+        if (((K1 - 1) >> 5) == r) thr = __shfl_sync(FULL_MASK, key[r], (K1 - 1) & 31);
+    }
+    __syncwarp();
+    return thr;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace fl

@@ -1,0 +1,199 @@
+// IVF-Flat fine scan: groups the (query, probe) pairs by inverted list on the device,
+// scans every probed list once per group of queries with the exact CUDA-core scoring
+// kernel and merges each query's per-probe pools with an exact fp32 re-rank.
+#include "knn_internal.h"
+#include "pool.cuh"
+
+namespace fl {
+
+__global__ void ivf_count_kernel(const int32_t* __restrict__ probed, int64_t npairs, int nlist,
+                                 int* __restrict__ cnt) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= npairs) return;
+    const int c = probed[i];
+    if (c >= 0 && c < nlist) atomicAdd(cnt + c, 1);
+}
+
+// Single block: exclusive scans of the per-list pair counts and group counts.
+__global__ void __launch_bounds__(1024) ivf_scan_kernel(const int* __restrict__ cnt, int nlist, int bq,
+                                                        const int64_t* __restrict__ list_offsets,
+                                                        int* __restrict__ pair_off,
+                                                        int* __restrict__ item_off, int* __restrict__ cursor) {
+    __shared__ int s_pair[1024];
+    __shared__ int s_item[1024];
+    __shared__ int carry_pair, carry_item;
+    const int t = threadIdx.x;
+    if (t == 0) { carry_pair = 0; carry_item = 0; }
+    __syncthreads();
+    for (int base = 0; base < nlist; base += 1024) {
+        const int c = base + t;
+        int np = 0, ni = 0;
+        if (c < nlist) {
+            np = cnt[c];
+            // a list without rows contributes no work item; its pairs keep empty pools
+            const bool has_rows = list_offsets[c + 1] > list_offsets[c];
+            ni = has_rows ? (np + bq - 1) / bq : 0;
+        }
+        s_pair[t] = np;
+        s_item[t] = ni;
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {
+            const int a = t >= o ? s_pair[t - o] : 0;
+            const int b = t >= o ? s_item[t - o] : 0;
+            __syncthreads();
+            s_pair[t] += a;
+            s_item[t] += b;
+            __syncthreads();
+        }
+        if (c < nlist) {
+            pair_off[c] = carry_pair + s_pair[t] - np;
+            item_off[c] = carry_item + s_item[t] - ni;
+            cursor[c] = 0;
+        }
+        __syncthreads();
+        if (t == 1023) { carry_pair += s_pair[t]; carry_item += s_item[t]; }
+        __syncthreads();
+    }
+    if (t == 0) { pair_off[nlist] = carry_pair; item_off[nlist] = carry_item; }
+}
+
+__global__ void ivf_scatter_kernel(const int32_t* __restrict__ probed, int64_t npairs, int nlist,
+                                   const int* __restrict__ pair_off, int* __restrict__ cursor,
+                                   int* __restrict__ sorted_pair) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= npairs) return;
+    const int c = probed[i];
+    if (c < 0 || c >= nlist) return;
+    const int pos = pair_off[c] + atomicAdd(cursor + c, 1);
+    sorted_pair[pos] = (int)i;
+}
+
+__global__ void ivf_fill_kernel(float* sc, uint32_t* id, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { sc[i] = neg_inf(); id[i] = INVALID_ID; }
+}
+
+__global__ void ivf_halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, int64_t ld,
+                                    float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const float* p = x + row * ld;
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if (lane == 0) out[row] = 0.5f * s;
+}
+
+struct IvfWs {
+    int K1, bq;
+    int64_t max_items;
+    int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_part_sc, off_part_id,
+        off_hnorm, bytes;
+};
+
+static int64_t take(int64_t& cur, int64_t bytes) {
+    const int64_t o = cur;
+    cur += round_up(bytes > 0 ? bytes : 1, 1024);
+    return o;
+}
+
+static IvfWs ivf_ws_plan(int64_t nq, int nprobe, int nlist, int64_t m, int k) {
+    IvfWs w{};
+    w.K1 = simt_pool_size(k);
+    w.bq = simt_block_queries(w.K1);
+    const int64_t npairs = nq * nprobe;
+    w.max_items = ceil_div(npairs, w.bq > 0 ? w.bq : 16) + nlist;
+    int64_t cur = 0;
+    w.off_cnt = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_pair_off = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_item_off = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_cursor = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_sorted = take(cur, npairs * 4);
+    w.off_part_sc = take(cur, npairs * w.K1 * 4);
+    w.off_part_id = take(cur, npairs * w.K1 * 4);
+    w.off_hnorm = take(cur, m * 4);
+    w.bytes = cur;
+    return w;
+}
+
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int64_t fl_ivf_fine_scan_workspace_bytes(int64_t nq, int nprobe, int nlist, int64_t m, int d,
+                                                    int k) {
+    (void)d;
+    if (nq < 1 || nprobe < 1 || nlist < 1 || k < 1 || m < 1) return 0;
+    return ivf_ws_plan(nq, nprobe, nlist, m, k).bytes;
+}
+
+extern "C" int fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq, const float* data, int64_t m,
+                                    int64_t ldd, int d, const int64_t* list_offsets, int nlist,
+                                    const int32_t* probed, int nprobe, int k, const float* data_hnorm,
+                                    float* out_dist, int32_t* out_pos, void* ws, int64_t ws_bytes,
+                                    void* stream) {
+    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1 && nlist >= 1 && nprobe >= 1 && k >= 1,
+                 "fl_ivf_fine_scan_f32: bad shape");
+    FL_CHECK_ARG(ldq >= d && ldd >= d, "fl_ivf_fine_scan_f32: leading dimensions smaller than d");
+    FL_CHECK_ARG(m < (1ll << 31) && nq * (int64_t)nprobe < (1ll << 31), "fl_ivf_fine_scan_f32: too many rows or pairs");
+    if (k > 512) { set_error("fl_ivf_fine_scan_f32: k=%d > 512 is not supported", k); return FL_EUNSUPPORTED; }
+    if (nq == 0) return FL_OK;
+    FL_CHECK_ARG(q && data && list_offsets && probed && out_dist && out_pos && ws, "fl_ivf_fine_scan_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0, "fl_ivf_fine_scan_f32: workspace must be 256-byte aligned");
+    const IvfWs w = ivf_ws_plan(nq, nprobe, nlist, m, k);
+    if (w.bq == 0) { set_error("fl_ivf_fine_scan_f32: pool does not fit shared memory"); return FL_EUNSUPPORTED; }
+    if (ws_bytes < w.bytes) {
+        set_error("fl_ivf_fine_scan_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
+        return FL_EWORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(ws);
+    int* cnt = reinterpret_cast<int*>(base + w.off_cnt);
+    int* pair_off = reinterpret_cast<int*>(base + w.off_pair_off);
+    int* item_off = reinterpret_cast<int*>(base + w.off_item_off);
+    int* cursor = reinterpret_cast<int*>(base + w.off_cursor);
+    int* sorted_pair = reinterpret_cast<int*>(base + w.off_sorted);
+    float* part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    uint32_t* part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    const int64_t npairs = nq * nprobe;
+
+    const float* hnorm = data_hnorm;
+    if (!hnorm) {
+        float* h = reinterpret_cast<float*>(base + w.off_hnorm);
+        ivf_halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(data, m, d, ldd, h);
+        FL_CHECK_LAUNCH();
+        hnorm = h;
+    }
+    FL_CHECK_CUDA(cudaMemsetAsync(cnt, 0, (size_t)(nlist + 1) * 4, st));
+    ivf_count_kernel<<<(unsigned)ceil_div(npairs, 256), 256, 0, st>>>(probed, npairs, nlist, cnt);
+    FL_CHECK_LAUNCH();
+    ivf_scan_kernel<<<1, 1024, 0, st>>>(cnt, nlist, w.bq, list_offsets, pair_off, item_off, cursor);
+    FL_CHECK_LAUNCH();
+    ivf_scatter_kernel<<<(unsigned)ceil_div(npairs, 256), 256, 0, st>>>(probed, npairs, nlist, pair_off, cursor,
+                                                                        sorted_pair);
+    FL_CHECK_LAUNCH();
+    ivf_fill_kernel<<<(unsigned)ceil_div(npairs * w.K1, 256), 256, 0, st>>>(part_sc, part_id, npairs * w.K1);
+    FL_CHECK_LAUNCH();
+
+    SimtKnnParams sp{};
+    sp.q = q; sp.ldq = ldq; sp.db = data; sp.m = m; sp.ldb = ldd; sp.d = d; sp.hnorm = hnorm;
+    sp.K1 = w.K1; sp.cap = 2 * w.K1; sp.npl = sp.cap / 32; sp.nsplit = 1; sp.rows_per_split = m;
+    sp.part_sc = part_sc; sp.part_id = part_id;
+    sp.vecq = (ldq % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
+    sp.vecd = (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(data) & 15) == 0);
+    sp.ivf = 1; sp.nlist = nlist; sp.nprobe = nprobe; sp.bq_items = w.bq;
+    sp.item_off = item_off; sp.pair_off = pair_off; sp.sorted_pair = sorted_pair;
+    sp.list_offsets = list_offsets;
+    int rc = launch_knn_simt(sp, w.max_items, st);
+    if (rc != FL_OK) return rc;
+
+    FinalizeParams fp{};
+    fp.q = q; fp.ldq = ldq; fp.count = nq; fp.db = data; fp.m = m; fp.ldb = ldd; fp.d = d;
+    fp.vec = sp.vecq && sp.vecd && (d % 4 == 0);
+    fp.part_sc = part_sc; fp.part_id = part_id; fp.nsplit = nprobe; fp.K1 = w.K1;
+    fp.k = k; fp.rerank = (k + 8 < w.K1) ? k + 8 : w.K1; fp.row_offset = 0;
+    fp.out_dist = out_dist; fp.out_idx = out_pos; fp.verify = 0;
+    return launch_knn_finalize(fp, nq, st);
+}

@@ -1,0 +1,226 @@
+// k-means device work: nearest-centroid assignment, per-cluster sums/counts and the
+// centroid finalisation with per-centroid shift.
+#include "common.cuh"
+#include "simt_tile.cuh"
+
+namespace fl {
+
+__global__ void kmeans_halfnorm_kernel(const float* __restrict__ x, int n, int d, int64_t ld,
+                                       float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const float* p = x + (int64_t)row * ld;
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if (lane == 0) out[row] = 0.5f * s;
+}
+
+// Exact fp32 assignment: 64 points per block against all centroids in tiles of 128.
+// The winner maximises <x,c> - ||c||^2/2, i.e. minimises ||x - c||^2; on exact ties the
+// lowest centroid index wins.
+template <int TQ>
+__global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
+    const float* __restrict__ x, int64_t n, int64_t ldx, const float* __restrict__ c, int K, int64_t ldc,
+    int d, const float* __restrict__ hnorm, int32_t* __restrict__ labels, int vecx, int vecc) {
+    using T = SimtTile<TQ>;
+    constexpr int BQ = T::BQ;
+    extern __shared__ __align__(16) float smem[];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t row0 = (int64_t)blockIdx.x * BQ;
+
+    const float* qrow[T::QL];
+#pragma unroll
+    for (int i = 0; i < T::QL; ++i) {
+        const int r = (i * 256 + tid) >> 3;
+        qrow[i] = (r < BQ && row0 + r < n) ? x + (row0 + r) * ldx : nullptr;
+    }
+    float best[TQ];
+    int bidx[TQ];
+#pragma unroll
+    for (int i = 0; i < TQ; ++i) { best[i] = neg_inf(); bidx[i] = 0x7fffffff; }
+
+    for (int tile = 0; tile < K; tile += 128) {
+        const float* drow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int gr = tile + ((i * 256 + tid) >> 3);
+            drow[i] = gr < K ? c + (int64_t)gr * ldc : nullptr;
+        }
+        float acc[TQ][8];
+        simt_cross_tile<TQ>(qrow, drow, d, vecx != 0, vecc != 0, smem, acc);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = tile + ((j < 4) ? (tx * 4 + j) : (64 + tx * 4 + (j - 4)));
+            if (col < K) {
+                const float hv = __ldg(hnorm + col);
+#pragma unroll
+                for (int i = 0; i < TQ; ++i) {
+                    const float s = acc[i][j] - hv;
+                    if (s > best[i] || (s == best[i] && col < bidx[i])) { best[i] = s; bidx[i] = col; }
+                }
+            }
+        }
+    }
+    // the 16 threads sharing a point row sit in one half warp
+#pragma unroll
+    for (int i = 0; i < TQ; ++i) {
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(FULL_MASK, best[i], o);
+            const int oi = __shfl_xor_sync(FULL_MASK, bidx[i], o);
+            if (ob > best[i] || (ob == best[i] && oi < bidx[i])) { best[i] = ob; bidx[i] = oi; }
+        }
+        const int64_t r = row0 + ty * TQ + i;
+        if (tx == 0 && r < n) labels[r] = bidx[i];
+    }
+}
+
+// One warp per chunk of rows; consecutive rows with the same label are summed in
+// registers and flushed with one atomic add per feature per run.
+template <int DPL>
+__global__ void kmeans_update_kernel(const float* __restrict__ x, int64_t n, int64_t ldx, int d,
+                                     const int32_t* __restrict__ labels, int K, float* __restrict__ sums,
+                                     int32_t* __restrict__ cnts, int rows_per_warp, int dbase) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t r0 = w * rows_per_warp;
+    if (r0 >= n) return;
+    const int64_t r1 = min(n, r0 + (int64_t)rows_per_warp);
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    int cur = -1, run = 0;
+    for (int64_t r = r0; r < r1; ++r) {
+        const int lab = __ldg(labels + r);
+        if (lab != cur) {
+            if (cur >= 0 && cur < K) {
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    const int cidx = dbase + i * 32 + lane;
+                    if (cidx < d) atomicAdd(sums + (int64_t)cur * d + cidx, acc[i]);
+                }
+                if (lane == 0 && dbase == 0) atomicAdd(cnts + cur, run);
+            }
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+            cur = lab;
+            run = 0;
+        }
+        const float* p = x + r * ldx;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int cidx = dbase + i * 32 + lane;
+            if (cidx < d) acc[i] += __ldg(p + cidx);
+        }
+        ++run;
+    }
+    if (cur >= 0 && cur < K) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int cidx = dbase + i * 32 + lane;
+            if (cidx < d) atomicAdd(sums + (int64_t)cur * d + cidx, acc[i]);
+        }
+        if (lane == 0 && dbase == 0) atomicAdd(cnts + cur, run);
+    }
+}
+
+// One block per centroid.
+__global__ void __launch_bounds__(128) kmeans_finalize_kernel(const float* __restrict__ sums,
+                                                              const int32_t* __restrict__ cnts,
+                                                              const float* __restrict__ old_c,
+                                                              float* __restrict__ new_c,
+                                                              float* __restrict__ shift, int K, int d) {
+    const int j = blockIdx.x;
+    const int cnt = cnts[j];
+    const float fc = (float)cnt;
+    float s = 0.f;
+    for (int t = threadIdx.x; t < d; t += blockDim.x) {
+        const float o = old_c[(int64_t)j * d + t];
+        const float v = cnt > 0 ? sums[(int64_t)j * d + t] / fc : o;
+        new_c[(int64_t)j * d + t] = v;
+        const float df = v - o;
+        s += df * df;
+    }
+    __shared__ float red[4];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) shift[j] = sqrtf(red[0] + red[1] + red[2] + red[3]);
+}
+
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int64_t fl_kmeans_assign_workspace_bytes(int64_t n, int K, int d) {
+    (void)n; (void)d;
+    if (K < 1) return 0;
+    return round_up((int64_t)K * 4, 1024);
+}
+
+extern "C" int fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx, const float* c, int K,
+                                    int64_t ldc, int d, int32_t* labels, void* ws, int64_t ws_bytes,
+                                    void* stream) {
+    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d && ldc >= d, "fl_kmeans_assign_f32: bad shape");
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && c && labels && ws, "fl_kmeans_assign_f32: null pointer");
+    if (ws_bytes < fl_kmeans_assign_workspace_bytes(n, K, d)) {
+        set_error("fl_kmeans_assign_f32: workspace too small");
+        return FL_EWORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* hnorm = static_cast<float*>(ws);
+    kmeans_halfnorm_kernel<<<(unsigned)ceil_div(K, 8), 256, 0, st>>>(c, K, d, ldc, hnorm);
+    FL_CHECK_LAUNCH();
+    const int vecx = (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int vecc = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    constexpr int TQ = 4;
+    const size_t smem = sizeof(float) * SimtTile<TQ>::SLAB_FLOATS;
+    FL_CHECK_CUDA(cudaFuncSetAttribute(kmeans_assign_simt_kernel<TQ>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kmeans_assign_simt_kernel<TQ><<<(unsigned)ceil_div(n, SimtTile<TQ>::BQ), 256, smem, st>>>(
+        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels,
+                                    int K, float* sums, int32_t* cnts, void* stream) {
+    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_f32: bad shape");
+    FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_f32: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    FL_CHECK_CUDA(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)K * d, st));
+    FL_CHECK_CUDA(cudaMemsetAsync(cnts, 0, sizeof(int32_t) * (size_t)K, st));
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && labels, "fl_kmeans_update_f32: null pointer");
+    const int rows_per_warp = 16;
+    const int64_t warps = ceil_div(n, rows_per_warp);
+    const unsigned grid = (unsigned)ceil_div(warps, 8);
+    for (int dbase = 0; dbase < d; dbase += 256) {
+        const int rem = d - dbase;
+        if (rem <= 32)
+            kmeans_update_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+        else if (rem <= 64)
+            kmeans_update_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+        else if (rem <= 128)
+            kmeans_update_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+        else
+            kmeans_update_kernel<8><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+        FL_CHECK_LAUNCH();
+    }
+    return FL_OK;
+}
+
+extern "C" int fl_kmeans_finalize_f32(const float* sums, const int32_t* cnts, const float* old_c,
+                                      float* new_c, float* shift, int K, int d, void* stream) {
+    FL_CHECK_ARG(K >= 1 && d >= 1, "fl_kmeans_finalize_f32: bad shape");
+    FL_CHECK_ARG(sums && cnts && old_c && new_c && shift, "fl_kmeans_finalize_f32: null pointer");
+    kmeans_finalize_kernel<<<(unsigned)K, 128, 0, (cudaStream_t)stream>>>(sums, cnts, old_c, new_c, shift, K, d);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}

@@ -1,0 +1,375 @@
+// Host orchestration of fl_knn_f32 plus the small helper kernels around it (half norms,
+// bf16 query plane, fallback bookkeeping), the shard merge and the exact gather.
+#include "knn_internal.h"
+#include "pool.cuh"
+#include <cuda_bf16.h>
+
+namespace fl {
+
+// out[i] = ||x_i||^2 / 2
+__global__ void halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, int64_t ld,
+                                float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const float* p = x + row * ld;
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if (lane == 0) out[row] = 0.5f * s;
+}
+
+__global__ void query_plane_kernel(const float* __restrict__ q, int64_t nq, int64_t ldq, int d,
+                                   __nv_bfloat16* __restrict__ out, int64_t nq_pad, int d_pad) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total = nq_pad * d_pad;
+    if (i >= total) return;
+    const int64_t r = i / d_pad;
+    const int c = (int)(i - r * d_pad);
+    const float v = (r < nq && c < d) ? __ldg(q + r * ldq + c) : 0.f;
+    out[i] = __float2bfloat16_rn(v);
+}
+
+int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
+                       int d_pad, cudaStream_t st) {
+    const int64_t total = nq_pad * d_pad;
+    query_plane_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
+        q, nq, ldq, d, reinterpret_cast<__nv_bfloat16*>(qplane), nq_pad, d_pad);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+__global__ void fill_f32_kernel(float* p, int64_t n, float v) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// Clamps the fallback count to the list capacity and publishes it in the status words.
+__global__ void fallback_fixup_kernel(int* fb_count, int fb_cap, int32_t* status, int K1) {
+    int c = *fb_count;
+    if (status) {
+        status[FL_STATUS_FALLBACK] = c;
+        status[FL_STATUS_POOL] = K1;
+        if (c > fb_cap && status[FL_STATUS_ERROR] == 0) status[FL_STATUS_ERROR] = FL_EWORKSPACE;
+    }
+    if (c > fb_cap) *fb_count = fb_cap;
+}
+
+// ---- workspace layout -----------------------------------------------------------------
+struct KnnWs {
+    int mode, K1, K1f;
+    int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
+    int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
+    int64_t nq_pad; int d_pad; int fb_cap;
+    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_tau, off_cnt, off_fblist,
+        off_fbpart_sc, off_fbpart_id, bytes;
+};
+
+static int64_t take(int64_t& cur, int64_t bytes) {
+    const int64_t o = cur;
+    cur += round_up(bytes > 0 ? bytes : 1, 1024);
+    return o;
+}
+
+static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
+    KnnWs w{};
+    w.mode = mode;
+    int64_t cur = 0;
+    if (mode == FL_KNN_BF16_RERANK) {
+        w.K1 = tc_pool_size(k);
+        w.K1f = simt_pool_size(k);
+        w.nq_pad = round_up(nq, 128);
+        w.d_pad = (int)round_up(d, 64);
+        const int64_t m_pad = round_up(m, 256);
+        tc_split_plan(w.nq_pad, m_pad, &w.nsplit, &w.rows_per_split);
+        w.fb_cap = (int)(nq < 4096 ? nq : (nq / 4 > 4096 ? nq / 4 : 4096));
+        // fallback splits: bounded partial storage (<= 128 MB), at least 4 tiles per split
+        int64_t s = (int64_t)(128ll << 20) / ((int64_t)w.fb_cap * w.K1f * 8);
+        const int64_t tiles = ceil_div(m, 128);
+        if (s > tiles / 4) s = tiles / 4;
+        if (s > 128) s = 128;
+        if (s < 1) s = 1;
+        w.rows_per_split_fb = round_up(ceil_div(m, s), 128);
+        w.nsplit_fb = (int)ceil_div(m, w.rows_per_split_fb);
+        w.off_hnorm = -1;
+        w.off_qplane = take(cur, w.nq_pad * w.d_pad * 2);
+        w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
+        w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
+        w.off_tau = take(cur, w.nq_pad * 4);
+        w.off_cnt = take(cur, 1024);
+        w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
+        w.off_fbpart_sc = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * w.K1f * 4);
+        w.off_fbpart_id = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * w.K1f * 4);
+    } else {
+        w.K1 = simt_pool_size(k);
+        w.K1f = w.K1;
+        simt_split_plan(nq, m, w.K1, d, &w.nsplit, &w.rows_per_split);
+        w.off_hnorm = take(cur, m * 4);
+        w.off_part_sc = take(cur, nq * w.nsplit * (int64_t)w.K1 * 4);
+        w.off_part_id = take(cur, nq * w.nsplit * (int64_t)w.K1 * 4);
+        w.off_cnt = take(cur, 1024);
+    }
+    w.bytes = cur;
+    return w;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int resolve_mode(int64_t nq, int64_t m, int d, int k, int mode) {
+    if (mode == FL_KNN_AUTO) return tc_knn_supported(nq, m, d, k) == FL_OK ? FL_KNN_BF16_RERANK
+                                                                             : FL_KNN_EXACT_SIMT;
+    return mode;
+}
+
+// ---- shard merge ------------------------------------------------------------------------
+// One warp per row: streams the candidates in chunks of 32, keeps the k best (dist, idx).
+template <int NPL1>
+__global__ void __launch_bounds__(128) topk_merge_kernel(const float* __restrict__ cd,
+                                                         const int32_t* __restrict__ ci, int64_t nq,
+                                                         int ncand, int k, float* __restrict__ od,
+                                                         int32_t* __restrict__ oi) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (row >= nq) return;
+    constexpr int N2 = 2 * NPL1;
+    float key[N2];
+    uint32_t id[N2];
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
+    const float* d = cd + row * ncand;
+    const int32_t* ix = ci + row * ncand;
+    for (int base = 0; base < ncand; base += NPL1 * 32) {
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            const int e = base + ((r << 5) | lane);
+            const bool ok = e < ncand && ix[e] >= 0;
+            key[NPL1 + r] = ok ? -d[e] : neg_inf();
+            id[NPL1 + r] = ok ? (uint32_t)ix[e] : INVALID_ID;
+        }
+        warp_sort_desc<N2, true>(key, id);
+    }
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) {
+        const int e = (r << 5) | lane;
+        if (e < k) {
+            const bool ok = id[r] != INVALID_ID;
+            od[row * k + e] = ok ? -key[r] : pos_inf();
+            oi[row * k + e] = ok ? (int32_t)id[r] : -1;
+        }
+    }
+}
+
+// ---- exact gather ---------------------------------------------------------------------
+template <typename IdxT>
+__global__ void gather_l2sq_kernel(const float* __restrict__ x, int64_t n, int64_t ldx,
+                                   const float* __restrict__ c, int64_t m, int64_t ldc, int d,
+                                   const IdxT* __restrict__ idx, int k, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= n * k) return;
+    const int64_t i = pair / k;
+    const int64_t j = (int64_t)idx[pair];
+    if (j < 0 || j >= m) {
+        if (lane == 0) out[pair] = pos_inf();
+        return;
+    }
+    const float* xp = x + i * ldx;
+    const float* cp = c + j * ldc;
+    float s = 0.f;
+    for (int t = lane; t < d; t += 32) { const float df = __ldg(xp + t) - __ldg(cp + t); s += df * df; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if (lane == 0) out[pair] = s;
+}
+
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int fl_knn_resolve_mode(int64_t nq, int64_t m, int d, int k) {
+    return resolve_mode(nq, m, d, k, FL_KNN_AUTO);
+}
+
+extern "C" int64_t fl_knn_workspace_bytes(int64_t nq, int64_t m, int d, int k, int mode) {
+    if (nq < 1 || m < 1 || d < 1 || k < 1) return 0;
+    mode = resolve_mode(nq, m, d, k, mode);
+    return knn_ws_plan(nq, m, d, k, mode).bytes;
+}
+
+extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
+                          int64_t ldb, int d, int k, int mode, const void* plane, int64_t row_offset,
+                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes,
+                          int32_t* status, void* stream) {
+    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1, "fl_knn_f32: bad shape nq=%lld m=%lld d=%d", (long long)nq,
+                 (long long)m, d);
+    FL_CHECK_ARG(k >= 1 && k <= m, "fl_knn_f32: k must be in [1, m=%lld] (got %d)", (long long)m, k);
+    FL_CHECK_ARG(ldq >= d && ldb >= d, "fl_knn_f32: leading dimensions smaller than d");
+    FL_CHECK_ARG(m < (1ll << 31) && nq < (1ll << 31), "fl_knn_f32: more than 2^31 rows");
+    FL_CHECK_ARG(row_offset >= 0 && row_offset + m <= (1ll << 31),
+                 "fl_knn_f32: row_offset + m exceeds int32 index range");
+    if (k > 512) {
+        set_error("fl_knn_f32: k=%d > 512 is not supported", k);
+        return FL_EUNSUPPORTED;
+    }
+    if (nq == 0) return FL_OK;
+    FL_CHECK_ARG(q && db && out_dist && out_idx && ws, "fl_knn_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0, "fl_knn_f32: workspace must be 256-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+
+    if (mode == FL_KNN_BF16_RERANK && tc_knn_supported(nq, m, d, k) != FL_OK) {
+        set_error("fl_knn_f32: shape (nq=%lld m=%lld d=%d k=%d) outside the tensor-core kernel's range",
+                  (long long)nq, (long long)m, d, k);
+        return FL_EUNSUPPORTED;
+    }
+    mode = resolve_mode(nq, m, d, k, mode);
+    if (mode == FL_KNN_BF16_RERANK && plane == nullptr) {
+        FL_CHECK_ARG(false, "fl_knn_f32: the tensor-core mode needs the plane built by fl_knn_prepare_db_f32");
+    }
+    FL_CHECK_ARG(mode == FL_KNN_EXACT_SIMT || mode == FL_KNN_BF16_RERANK, "fl_knn_f32: unknown mode %d", mode);
+
+    const KnnWs w = knn_ws_plan(nq, m, d, k, mode);
+    if (ws_bytes < w.bytes) {
+        set_error("fl_knn_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
+        return FL_EWORKSPACE;
+    }
+    char* base = static_cast<char*>(ws);
+    const int vecq = (ldq % 4 == 0) && aligned16(q);
+    const int vecd = (ldb % 4 == 0) && aligned16(db);
+    const int vec = vecq && vecd && (d % 4 == 0);
+    if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
+
+    if (mode == FL_KNN_EXACT_SIMT) {
+        FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
+        const float* hnorm;
+        if (plane) {
+            const PlaneLayout L = plane_layout(m, d);
+            hnorm = reinterpret_cast<const float*>(static_cast<const char*>(plane) + L.off_hnorm);
+        } else {
+            float* h = reinterpret_cast<float*>(base + w.off_hnorm);
+            halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h);
+            FL_CHECK_LAUNCH();
+            hnorm = h;
+        }
+        SimtKnnParams sp{};
+        sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
+        sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
+        sp.K1 = w.K1; sp.cap = 2 * w.K1; sp.npl = sp.cap / 32;
+        sp.nsplit = w.nsplit; sp.rows_per_split = w.rows_per_split;
+        sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+        sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+        sp.vecq = vecq; sp.vecd = vecd;
+        int rc = launch_knn_simt(sp, nq, st);
+        if (rc != FL_OK) return rc;
+
+        FinalizeParams fp{};
+        fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
+        fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
+        fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
+        fp.k = k; fp.rerank = (k + 8 < w.K1) ? k + 8 : w.K1; fp.row_offset = row_offset;
+        fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 0;
+        rc = launch_knn_finalize(fp, nq, st);
+        if (rc != FL_OK) return rc;
+        if (status) {
+            fallback_fixup_kernel<<<1, 1, 0, st>>>(reinterpret_cast<int*>(base + w.off_cnt), 1 << 30,
+                                                   status, w.K1);
+            FL_CHECK_LAUNCH();
+        }
+        return FL_OK;
+    }
+
+    // ---- tensor-core candidates + exact re-rank + verified fallback ---------------------
+    const PlaneLayout L = plane_layout(m, d);
+    const char* pl = static_cast<const char*>(plane);
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0, "fl_knn_f32: plane must be 256-byte aligned");
+    int* fb_count = reinterpret_cast<int*>(base + w.off_cnt);
+    int* fb_list = reinterpret_cast<int*>(base + w.off_fblist);
+    float* tau = reinterpret_cast<float*>(base + w.off_tau);
+    FL_CHECK_CUDA(cudaMemsetAsync(fb_count, 0, 1024, st));
+    fill_f32_kernel<<<(unsigned)ceil_div(w.nq_pad, 256), 256, 0, st>>>(tau, w.nq_pad, -INFINITY);
+    FL_CHECK_LAUNCH();
+    int rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st);
+    if (rc != FL_OK) return rc;
+
+    TcKnnParams tp{};
+    tp.qplane = base + w.off_qplane; tp.nq = nq; tp.nq_pad = w.nq_pad;
+    tp.dbrows = pl + L.off_rows; tp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
+    tp.m = m; tp.m_pad = L.m_pad; tp.d_pad = L.d_pad; tp.K1 = w.K1;
+    tp.nsplit = w.nsplit; tp.tiles_per_split = w.rows_per_split;
+    tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    tp.tau = tau; tp.status = status;
+    rc = launch_knn_tc(tp, st);
+    if (rc != FL_OK) return rc;
+
+    FinalizeParams fp{};
+    fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
+    fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
+    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
+    fp.k = k; fp.rerank = w.K1; fp.row_offset = row_offset;
+    fp.out_dist = out_dist; fp.out_idx = out_idx;
+    fp.verify = 1; fp.eps_rel = 0.004f;  // 2^-8 operand rounding of both bf16 factors, rounded up
+    fp.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
+    fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = w.fb_cap;
+    rc = launch_knn_finalize(fp, nq, st);
+    if (rc != FL_OK) return rc;
+    fallback_fixup_kernel<<<1, 1, 0, st>>>(fb_count, w.fb_cap, status, w.K1);
+    FL_CHECK_LAUNCH();
+
+    // Rows whose pool could not be proven complete: exact CUDA-core pass over the list.
+    SimtKnnParams sp{};
+    sp.q = q; sp.ldq = ldq; sp.qlist = fb_list; sp.count_dev = fb_count; sp.count = 0;
+    sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d;
+    sp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
+    sp.K1 = w.K1f; sp.cap = 2 * w.K1f; sp.npl = sp.cap / 32;
+    sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
+    sp.part_sc = reinterpret_cast<float*>(base + w.off_fbpart_sc);
+    sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_fbpart_id);
+    sp.vecq = vecq; sp.vecd = vecd;
+    rc = launch_knn_simt(sp, w.fb_cap, st);
+    if (rc != FL_OK) return rc;
+    FinalizeParams ff = fp;
+    ff.qlist = fb_list; ff.count_dev = fb_count; ff.count = 0;
+    ff.part_sc = sp.part_sc; ff.part_id = sp.part_id; ff.nsplit = w.nsplit_fb; ff.K1 = w.K1f;
+    ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0;
+    rc = launch_knn_finalize(ff, w.fb_cap, st);
+    return rc;
+}
+
+extern "C" int fl_topk_merge_f32(const float* cand_dist, const int32_t* cand_idx, int64_t nq, int ncand,
+                                 int k, float* out_dist, int32_t* out_idx, void* stream) {
+    FL_CHECK_ARG(nq >= 0 && ncand >= 1 && k >= 1, "fl_topk_merge_f32: bad shape");
+    if (k > 512) { set_error("fl_topk_merge_f32: k=%d > 512 is not supported", k); return FL_EUNSUPPORTED; }
+    if (nq == 0) return FL_OK;
+    FL_CHECK_ARG(cand_dist && cand_idx && out_dist && out_idx, "fl_topk_merge_f32: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)ceil_div(nq, 4);
+    const int K1 = simt_pool_size(k);
+    switch (K1 / 32) {
+        case 1: topk_merge_kernel<1><<<grid, 128, 0, st>>>(cand_dist, cand_idx, nq, ncand, k, out_dist, out_idx); break;
+        case 2: topk_merge_kernel<2><<<grid, 128, 0, st>>>(cand_dist, cand_idx, nq, ncand, k, out_dist, out_idx); break;
+        case 4: topk_merge_kernel<4><<<grid, 128, 0, st>>>(cand_dist, cand_idx, nq, ncand, k, out_dist, out_idx); break;
+        case 8: topk_merge_kernel<8><<<grid, 128, 0, st>>>(cand_dist, cand_idx, nq, ncand, k, out_dist, out_idx); break;
+        default: topk_merge_kernel<16><<<grid, 128, 0, st>>>(cand_dist, cand_idx, nq, ncand, k, out_dist, out_idx); break;
+    }
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+extern "C" int fl_gather_l2sq_f32(const float* x, int64_t n, int64_t ldx, const float* c, int64_t m,
+                                  int64_t ldc, int d, const void* idx, int idx_is_i64, int k, float* out,
+                                  void* stream) {
+    FL_CHECK_ARG(n >= 0 && m >= 1 && d >= 1 && k >= 1 && ldx >= d && ldc >= d, "fl_gather_l2sq_f32: bad shape");
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && c && idx && out, "fl_gather_l2sq_f32: null pointer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)ceil_div(n * k, 8);
+    if (idx_is_i64)
+        gather_l2sq_kernel<int64_t><<<grid, 256, 0, st>>>(x, n, ldx, c, m, ldc, d,
+                                                          static_cast<const int64_t*>(idx), k, out);
+    else
+        gather_l2sq_kernel<int32_t><<<grid, 256, 0, st>>>(x, n, ldx, c, m, ldc, d,
+                                                          static_cast<const int32_t*>(idx), k, out);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}

@@ -1,0 +1,73 @@
+// Internal launch interfaces shared by the kNN translation units.
+#pragma once
+#include "common.cuh"
+#include "plane.h"
+
+namespace fl {
+
+// Exact CUDA-core scoring pass: every (slot, split) pair gets a descending pool of K1
+// (score, row) entries at part[(slot*nsplit + split)*K1].
+struct SimtKnnParams {
+    const float* q; int64_t ldq;
+    const int* qlist;       // optional slot -> query row map
+    const int* count_dev;   // optional device-resident slot count
+    int64_t count;          // slot count when count_dev is null
+    const float* db; int64_t m; int64_t ldb; int d;
+    const float* hnorm;     // ||x||^2 / 2 per database row
+    int K1, cap, npl;
+    int nsplit; int64_t rows_per_split;
+    float* part_sc; uint32_t* part_id;
+    int vecq, vecd;
+    // Inverted-file mode (ivf != 0): block b is work item b = (list c, group g of up to BQ
+    // of the (query, probe) pairs that name list c).  item_off/pair_off are exclusive scans
+    // over lists (nlist+1 entries), sorted_pair lists the pair ids grouped by list, and the
+    // block scans rows list_offsets[c] .. list_offsets[c+1] of db.  Pools are written at
+    // part[pair_id * K1]; bq_items is the group size the item table was built for.
+    int ivf; int nlist; int nprobe; int bq_items;
+    const int* item_off; const int* pair_off; const int* sorted_pair;
+    const int64_t* list_offsets;
+};
+int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st);
+// Split count / rows per split the CUDA-core pass uses for a problem.
+void simt_split_plan(int64_t slots, int64_t m, int K1, int d, int* nsplit, int64_t* rows_per_split);
+// Queries per block the CUDA-core pass uses for a pool of K1 entries (0: does not fit).
+int simt_block_queries(int K1);
+
+// Merge of the per-split pools, exact fp32 re-rank, top-k selection and (optionally)
+// verification of the candidate pool against the scoring error bound.
+struct FinalizeParams {
+    const float* q; int64_t ldq;
+    const int* qlist; const int* count_dev; int64_t count;
+    const float* db; int64_t m; int64_t ldb; int d; int vec;
+    const float* part_sc; const uint32_t* part_id; int nsplit; int K1;
+    int k; int rerank; int64_t row_offset;
+    float* out_dist; int32_t* out_idx;
+    int verify; float eps_rel; const float* maxnorm;
+    int* fb_count; int* fb_list; int fb_cap;
+};
+int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);
+
+// Tensor-core (tcgen05) candidate pass over the bf16 plane.
+struct TcKnnParams {
+    const void* qplane;      // bf16 [nq_pad][d_pad], zero padded
+    int64_t nq, nq_pad;
+    const void* dbrows;      // bf16 [m_pad][d_pad]
+    const float* hnorm;      // f32 [m_pad]
+    int64_t m, m_pad; int d_pad;
+    int K1;                  // pool size (32)
+    int nsplit; int64_t tiles_per_split;   // database tiles of 256 rows per split
+    float* part_sc; uint32_t* part_id;     // [nq_pad][nsplit][K1]
+    float* tau;              // f32 [nq_pad], running per-query thresholds, -inf initialised
+    int32_t* status;
+};
+// Returns FL_EUNSUPPORTED when the shape is outside the tensor-core kernel's range.
+int tc_knn_supported(int64_t nq, int64_t m, int d, int k);
+int tc_pool_size(int k);
+void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_per_split);
+int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
+
+// bf16 query plane [nq_pad][d_pad] (zero padded) from fp32 queries.
+int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
+                       int d_pad, cudaStream_t st);
+
+}  // namespace fl

@@ -1,0 +1,364 @@
+// Exact CUDA-core kNN scoring pass and the pool finalisation (merge + exact re-rank +
+// top-k + verification) shared by both kNN modes.
+#include "knn_internal.h"
+#include "pool.cuh"
+#include "simt_tile.cuh"
+
+namespace fl {
+
+// ------------------------------------------------------------------------------------
+// Scoring pass.  grid = (ceil(slots / BQ), nsplit).  Each block keeps BQ query rows,
+// streams its split of the database in tiles of 128 rows, scores every pair with
+// score = <q,x> - ||x||^2/2 in fp32 FFMA and feeds the per-row pools.
+// ------------------------------------------------------------------------------------
+template <int TQ>
+__global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
+    using T = SimtTile<TQ>;
+    constexpr int BQ = T::BQ;
+    constexpr int SSTR = 129;
+    extern __shared__ __align__(16) float smem[];
+    float* slab = smem;
+    float* pool_sc = smem + T::SLAB_FLOATS;
+    uint32_t* pool_id = reinterpret_cast<uint32_t*>(pool_sc + BQ * p.cap);
+    float* tau = reinterpret_cast<float*>(pool_id + BQ * p.cap);
+    int* cnt = reinterpret_cast<int*>(tau + BQ);
+    int* qmap = cnt + BQ;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int tx = tid & 15, ty = tid >> 4;
+    int* pslot = qmap + BQ;
+    int64_t slot0, row_begin, row_end;
+    int split;
+    if (p.ivf) {
+        const int b = blockIdx.x;
+        if (b >= p.item_off[p.nlist]) return;
+        int lo = 0, hi = p.nlist;  // largest c with item_off[c] <= b
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (p.item_off[mid] <= b) lo = mid; else hi = mid;
+        }
+        const int c = lo;
+        const int s0 = p.pair_off[c] + (b - p.item_off[c]) * BQ;
+        const int s1 = min(s0 + BQ, p.pair_off[c + 1]);
+        row_begin = p.list_offsets[c];
+        row_end = p.list_offsets[c + 1];
+        slot0 = 0;
+        split = 0;
+        for (int i = tid; i < BQ; i += 256) {
+            const int pr = (s0 + i < s1) ? p.sorted_pair[s0 + i] : -1;
+            pslot[i] = pr;
+            qmap[i] = pr >= 0 ? pr / p.nprobe : -1;
+            tau[i] = neg_inf();
+            cnt[i] = 0;
+        }
+    } else {
+        const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
+        slot0 = (int64_t)blockIdx.x * BQ;
+        if (slot0 >= count) return;
+        split = blockIdx.y;
+        row_begin = (int64_t)split * p.rows_per_split;
+        row_end = min(p.m, row_begin + p.rows_per_split);
+        for (int i = tid; i < BQ; i += 256) {
+            const int64_t slot = slot0 + i;
+            qmap[i] = slot < count ? (p.qlist ? p.qlist[slot] : (int)slot) : -1;
+            pslot[i] = 0;
+            tau[i] = neg_inf();
+            cnt[i] = 0;
+        }
+    }
+    __syncthreads();
+
+    const float* qrow[T::QL];
+#pragma unroll
+    for (int i = 0; i < T::QL; ++i) {
+        const int r = (i * 256 + tid) >> 3;
+        qrow[i] = (r < BQ && qmap[r] >= 0) ? p.q + (int64_t)qmap[r] * p.ldq : nullptr;
+    }
+
+    constexpr int RPW = BQ / 8;  // rows per warp in the pool phase
+    for (int64_t tile_row = row_begin; tile_row < row_end; tile_row += 128) {
+        const float* drow[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t gr = tile_row + ((i * 256 + tid) >> 3);
+            drow[i] = gr < row_end ? p.db + gr * p.ldb : nullptr;
+        }
+        float acc[TQ][8];
+        simt_cross_tile<TQ>(qrow, drow, p.d, p.vecq != 0, p.vecd != 0, slab, acc);
+
+        // Scores into the tile buffer (it aliases the operand slabs, which are idle now).
+        float* S = slab;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = (j < 4) ? (tx * 4 + j) : (64 + tx * 4 + (j - 4));
+            const int64_t gr = tile_row + col;
+            const float hv = gr < row_end ? __ldg(p.hnorm + gr) : pos_inf();
+#pragma unroll
+            for (int i = 0; i < TQ; ++i) S[(ty * TQ + i) * SSTR + col] = acc[i][j] - hv;
+        }
+        __syncthreads();
+
+#pragma unroll 1
+        for (int rr = 0; rr < RPW; ++rr) {
+            const int row = warp * RPW + rr;
+            if (qmap[row] < 0) continue;
+            float t = tau[row];
+            int c = cnt[row];
+            float* sc = pool_sc + row * p.cap;
+            uint32_t* idp = pool_id + row * p.cap;
+#pragma unroll
+            for (int sub = 0; sub < 4; ++sub) {
+                const float s = S[row * SSTR + sub * 32 + lane];
+                const bool pass = s > t;
+                const unsigned mask = __ballot_sync(FULL_MASK, pass);
+                if (mask) {
+                    if (pass) {
+                        const int pos = c + __popc(mask & ((1u << lane) - 1u));
+                        sc[pos] = s;
+                        idp[pos] = (uint32_t)(tile_row + sub * 32 + lane);
+                    }
+                    c += __popc(mask);
+                    if (c > p.cap - 32) {
+                        __syncwarp();
+                        t = pool_compact_dyn(sc, idp, c, p.K1, p.npl);
+                        c = min(c, p.K1);
+                    }
+                }
+            }
+            if (lane == 0) { tau[row] = t; cnt[row] = c; }
+        }
+        __syncthreads();
+    }
+
+#pragma unroll 1
+    for (int rr = 0; rr < RPW; ++rr) {
+        const int row = warp * RPW + rr;
+        if (qmap[row] < 0) continue;
+        float* sc = pool_sc + row * p.cap;
+        uint32_t* idp = pool_id + row * p.cap;
+        __syncwarp();
+        pool_compact_dyn(sc, idp, cnt[row], p.K1, p.npl);
+        const int64_t o = p.ivf ? (int64_t)pslot[row] * p.K1
+                                : ((slot0 + row) * p.nsplit + split) * (int64_t)p.K1;
+        for (int e = lane; e < p.K1; e += 32) {
+            p.part_sc[o + e] = sc[e];
+            p.part_id[o + e] = idp[e];
+        }
+    }
+}
+
+template <int TQ>
+static size_t simt_smem_bytes(int cap) {
+    using T = SimtTile<TQ>;
+    return sizeof(float) * ((size_t)T::SLAB_FLOATS + (size_t)T::BQ * cap * 2 + (size_t)T::BQ * 4);
+}
+
+static int simt_pick_tq(int cap) {
+    const size_t lim = (size_t)smem_optin_bytes() - 1024;
+    if (simt_smem_bytes<4>(cap) <= lim) return 4;
+    if (simt_smem_bytes<2>(cap) <= lim) return 2;
+    if (simt_smem_bytes<1>(cap) <= lim) return 1;
+    return 0;
+}
+
+int simt_block_queries(int K1) { return 16 * simt_pick_tq(2 * K1); }
+
+void simt_split_plan(int64_t slots, int64_t m, int K1, int d, int* nsplit, int64_t* rows_per_split) {
+    (void)d;
+    const int tq = simt_pick_tq(2 * K1);
+    const int bq = 16 * (tq > 0 ? tq : 1);
+    const int64_t qblocks = ceil_div(slots > 0 ? slots : 1, bq);
+    const int64_t tiles = ceil_div(m, 128);
+    int64_t want = ceil_div(2 * (int64_t)sm_count(), qblocks);
+    int64_t max_split = tiles / 4 > 0 ? tiles / 4 : 1;
+    if (want > max_split) want = max_split;
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    int64_t rps = round_up(ceil_div(m, want), 128);
+    *rows_per_split = rps;
+    *nsplit = (int)ceil_div(m, rps);
+}
+
+template <int TQ>
+static int launch_simt_t(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) {
+    const size_t smem = simt_smem_bytes<TQ>(p.cap);
+    FL_CHECK_CUDA(cudaFuncSetAttribute(knn_simt_kernel<TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    dim3 grid(p.ivf ? (unsigned)max_slots : (unsigned)ceil_div(max_slots, SimtTile<TQ>::BQ),
+              (unsigned)p.nsplit);
+    knn_simt_kernel<TQ><<<grid, 256, smem, st>>>(p);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) {
+    if (max_slots <= 0) return FL_OK;
+    const int tq = simt_pick_tq(p.cap);
+    if (tq == 0) {
+        set_error("kNN pool of %d entries per row does not fit shared memory", p.cap);
+        return FL_EUNSUPPORTED;
+    }
+    if (p.ivf && p.bq_items != 16 * tq) {
+        set_error("inverted-file item table built for %d queries per block, kernel uses %d", p.bq_items, 16 * tq);
+        return FL_EINVAL;
+    }
+    if (tq == 4) return launch_simt_t<4>(p, max_slots, st);
+    if (tq == 2) return launch_simt_t<2>(p, max_slots, st);
+    return launch_simt_t<1>(p, max_slots, st);
+}
+
+// ------------------------------------------------------------------------------------
+// Finalisation: one warp per query slot.
+// ------------------------------------------------------------------------------------
+template <int NPL1>
+__global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
+    const int lane = threadIdx.x & 31;
+    const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
+    if (slot >= count) return;
+    const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
+    constexpr int N2 = 2 * NPL1;
+    const int K1 = p.K1;
+
+    // 1. merge the split pools: keep the K1 best scores.
+    float key[N2];
+    uint32_t id[N2];
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
+    const float* psc = p.part_sc + slot * p.nsplit * (int64_t)K1;
+    const uint32_t* pid = p.part_id + slot * p.nsplit * (int64_t)K1;
+    for (int s = 0; s < p.nsplit; ++s) {
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            const int e = (r << 5) | lane;
+            key[NPL1 + r] = psc[(int64_t)s * K1 + e];
+            id[NPL1 + r] = pid[(int64_t)s * K1 + e];
+        }
+        warp_sort_desc<N2, false>(key, id);
+    }
+    const float T = __shfl_sync(FULL_MASK, key[NPL1 - 1], 31);
+    const bool pool_full = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID;
+
+    // 2. exact fp32 distances of the first `rerank` pool entries.
+    const float* qp = p.q + qi * p.ldq;
+    float qsq = 0.f;
+    if (p.vec) {
+        for (int c = lane * 4; c < p.d; c += 128) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(qp + c));
+            qsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int c = lane; c < p.d; c += 32) { const float v = __ldg(qp + c); qsq += v * v; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
+
+    float dist[NPL1];
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) {
+        dist[r] = pos_inf();
+        for (int l0 = 0; l0 < 32; l0 += 4) {
+            if ((r << 5) + l0 >= p.rerank) break;
+            uint32_t cid[4];
+            float a[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                cid[u] = __shfl_sync(FULL_MASK, id[r], l0 + u);
+                if ((r << 5) + l0 + u >= p.rerank) cid[u] = INVALID_ID;
+                a[u] = 0.f;
+            }
+            if (p.vec) {
+                for (int c = lane * 4; c < p.d; c += 128) {
+                    const float4 qv = __ldg(reinterpret_cast<const float4*>(qp + c));
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (cid[u] != INVALID_ID) {
+                            const float4 xv = __ldg(
+                                reinterpret_cast<const float4*>(p.db + (int64_t)cid[u] * p.ldb + c));
+                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z,
+                                        d3 = qv.w - xv.w;
+                            a[u] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                        }
+                    }
+                }
+            } else {
+                for (int c = lane; c < p.d; c += 32) {
+                    const float qv = __ldg(qp + c);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (cid[u] != INVALID_ID) {
+                            const float df = qv - __ldg(p.db + (int64_t)cid[u] * p.ldb + c);
+                            a[u] += df * df;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) a[u] += __shfl_xor_sync(FULL_MASK, a[u], o);
+                if (lane == l0 + u && cid[u] != INVALID_ID) dist[r] = a[u];
+            }
+        }
+    }
+
+    // 3. order by (exact distance, row) ascending and write the first k.
+    float k2[NPL1];
+    uint32_t id2[NPL1];
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) {
+        const bool ok = dist[r] < pos_inf();
+        k2[r] = ok ? -dist[r] : neg_inf();
+        id2[r] = ok ? id[r] : INVALID_ID;
+    }
+    warp_sort_desc<NPL1, true>(k2, id2);
+    float dk = pos_inf();
+#pragma unroll
+    for (int r = 0; r < NPL1; ++r) {
+        const int e = (r << 5) | lane;
+        if (e < p.k) {
+            const bool ok = id2[r] != INVALID_ID;
+            p.out_dist[qi * p.k + e] = ok ? -k2[r] : pos_inf();
+            p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)id2[r] + p.row_offset) : -1;
+        }
+        if (((p.k - 1) >> 5) == r) {
+            const float v = __shfl_sync(FULL_MASK, k2[r], (p.k - 1) & 31);
+            dk = (v > neg_inf()) ? -v : pos_inf();
+        }
+    }
+
+    // 4. verification: every row outside the pool scored <= T, so its exact distance is
+    //    at least qsq - 2 (T + eps).  The result is proven when the k-th exact distance
+    //    is below that bound; otherwise the row is queued for the exact path.
+    if (p.verify && pool_full) {
+        const float mn = __ldg(p.maxnorm);
+        const float eps = p.eps_rel * sqrtf(qsq) * mn;
+        const float lb = qsq - 2.f * (T + eps);
+        const float slack = 1e-5f * (qsq + mn * mn);
+        const bool ok = dk < lb - slack;
+        if (!ok && lane == 0) {
+            const int i = atomicAdd(p.fb_count, 1);
+            if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+        }
+    }
+}
+
+int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
+    if (max_slots <= 0) return FL_OK;
+    const unsigned grid = (unsigned)ceil_div(max_slots, 4);
+    switch (p.K1 / 32) {
+        case 1: knn_finalize_kernel<1><<<grid, 128, 0, st>>>(p); break;
+        case 2: knn_finalize_kernel<2><<<grid, 128, 0, st>>>(p); break;
+        case 4: knn_finalize_kernel<4><<<grid, 128, 0, st>>>(p); break;
+        case 8: knn_finalize_kernel<8><<<grid, 128, 0, st>>>(p); break;
+        case 16: knn_finalize_kernel<16><<<grid, 128, 0, st>>>(p); break;
+        default:
+            set_error("unsupported pool size %d", p.K1);
+            return FL_EUNSUPPORTED;
+    }
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+}  // namespace fl

@@ -1,0 +1,29 @@
+// Per-row candidate pools: an append buffer of `cap` (score, id) entries with a
+// threshold.  A row accepts a candidate only when its score beats the threshold; when
+// the buffer is nearly full a warp sorts it, keeps the K1 best and raises the threshold
+// to the K1-th best score.  Larger score = closer neighbour (score = <q,x> - ||x||^2/2).
+#pragma once
+#include "common.cuh"
+
+namespace fl {
+
+// Runtime-sized front end of warp_pool_compact: `npl` = capacity / 32 in {2,4,8,16,32}.
+// Kept out of line: compaction is rare and the sorting networks are large.
+static __device__ __noinline__ float pool_compact_dyn(float* sc, uint32_t* idv, int cnt, int K1,
+                                                      int npl) {
+    switch (npl) {
+        case 2: return warp_pool_compact<2>(sc, idv, cnt, K1);
+        case 4: return warp_pool_compact<4>(sc, idv, cnt, K1);
+        case 8: return warp_pool_compact<8>(sc, idv, cnt, K1);
+        case 16: return warp_pool_compact<16>(sc, idv, cnt, K1);
+        default: return warp_pool_compact<32>(sc, idv, cnt, K1);
+    }
+}
+
+// Pool size (a power of two >= 32) used for k neighbours on the exact CUDA-core path.
+static inline int simt_pool_size(int k) {
+    int p = pow2_ceil(k);
+    return p < 32 ? 32 : p;
+}
+
+}  // namespace fl

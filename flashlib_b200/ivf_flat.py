@@ -1,0 +1,178 @@
+"""IVF-Flat index build and search behind flashlib's ``flash_ivf_flat_*`` API.
+
+Mirrors ``flashlib/primitives/ivf_flat/impl.py:69-159``, the container of
+``ivf_flat/index.py:27-78``, the build of ``ivf_flat/triton/build.py:34-95`` and the search
+of ``ivf_flat/triton/search.py:52-108``.  The fine scan (grouping of (query, probe) pairs by
+list, list scan, per-query merge, exact re-rank) runs in one C-ABI call; nothing on the
+search path synchronises the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .kmeans import euclid_assign_triton, flash_kmeans
+from .knn import _as_f32_rows, _stream_ptr, flash_knn, row_sqnorm
+
+
+@dataclass
+class IvfFlatIndex:
+    """A built IVF-Flat index; field for field the reference's ``IvfFlatIndex``.
+
+    ``data`` holds the database rows cell-contiguously: list ``c`` owns rows
+    ``list_offsets[c] .. list_offsets[c+1]``; ``ids[p]`` is the caller's row id of stored
+    row ``p``.
+    """
+
+    centroids: torch.Tensor
+    data: torch.Tensor
+    ids: torch.Tensor
+    list_offsets: torch.Tensor
+    metric: str
+    D: int
+    Dp: int
+    nlist: int
+    nprobe: int
+    max_list_len: int = 0
+    _hnorm: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
+
+    @property
+    def M(self) -> int:
+        return int(self.data.shape[0])
+
+    @property
+    def device(self) -> torch.device:
+        return self.data.device
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.data.dtype
+
+    def list_lengths(self) -> torch.Tensor:
+        return self.list_offsets[1:] - self.list_offsets[:-1]
+
+    def half_norms(self) -> torch.Tensor:
+        """fp32 ``||row||^2 / 2`` of the stored rows, computed once per index."""
+        if self._hnorm is None or self._hnorm.device != self.data.device:
+            self._hnorm = row_sqnorm(self.data).mul_(0.5)
+        return self._hnorm
+
+
+def _pad_features(x: torch.Tensor, Dp: int) -> torch.Tensor:
+    D = x.shape[-1]
+    if D >= Dp:
+        return x
+    pad = torch.zeros((*x.shape[:-1], Dp - D), device=x.device, dtype=x.dtype)
+    return torch.cat([x, pad], dim=-1)
+
+
+def flash_ivf_flat_build(X: torch.Tensor, nlist: int, *, metric: str = "l2", nprobe: int = 8,
+                         niter: int = 20, train_size: Optional[int] = None, seed: int = 0,
+                         backend: Optional[str] = None) -> IvfFlatIndex:
+    """Train the coarse quantiser on a sample and lay the rows out cell-contiguously.
+
+    Same steps and the same torch random draws as ``ivf_flat/triton/build.py:34-95``:
+    ``randperm`` from a device generator seeded with ``seed`` picks the sample,
+    ``flash_kmeans`` (global-generator ``randint`` init) trains ``nlist`` centroids, one
+    assignment pass labels every row, and ``bincount`` / ``cumsum`` / stable ``argsort`` build
+    the CSR layout.
+    """
+    if metric != "l2":
+        raise NotImplementedError(f"ivf_flat currently supports metric='l2' only (got {metric!r})")
+    if not X.is_cuda or X.ndim != 2:
+        raise ValueError("flash_ivf_flat_build requires a 2D CUDA tensor")
+    M, D = X.shape
+    nlist = int(min(nlist, M))
+    if nlist < 1:
+        raise ValueError("nlist must be >= 1")
+    Dp = max(int(D), 16)
+    Xp = _pad_features(X, Dp).contiguous()
+
+    train_size = int(train_size or min(M, nlist * 256))
+    train_size = max(min(train_size, M), nlist)
+    g = torch.Generator(device=X.device).manual_seed(seed)
+    sample_idx = torch.randperm(M, generator=g, device=X.device)[:train_size]
+    sample = Xp.index_select(0, sample_idx)
+
+    _, centroids, _ = flash_kmeans(sample, nlist, max_iters=niter, metric="euclidean")
+    centroids = centroids.contiguous()
+    return index_from_centroids(Xp, centroids, D=int(D), nprobe=nprobe, metric=metric)
+
+
+def index_from_centroids(Xp: torch.Tensor, centroids: torch.Tensor, *, D: int, nprobe: int,
+                         metric: str = "l2") -> IvfFlatIndex:
+    """Assign every (padded) row to its nearest centroid and build the CSR layout."""
+    nlist = centroids.shape[0]
+    assign = euclid_assign_triton(Xp.unsqueeze(0), centroids.unsqueeze(0)).squeeze(0).to(torch.int64)
+    counts = torch.bincount(assign, minlength=nlist)
+    offsets = torch.zeros(nlist + 1, dtype=torch.int64, device=Xp.device)
+    offsets[1:] = counts.cumsum(0)
+    order = torch.argsort(assign, stable=True)
+    data_sorted = Xp.index_select(0, order).contiguous()
+    max_list_len = int(counts.max().item())
+    return IvfFlatIndex(centroids=centroids, data=data_sorted, ids=order.to(torch.int64),
+                        list_offsets=offsets, metric=metric, D=int(D), Dp=int(Xp.shape[1]),
+                        nlist=int(nlist), nprobe=int(nprobe), max_list_len=max_list_len)
+
+
+def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k: int):
+    """Fine scan of the probed lists: ``(vals fp32 (nq,k), pos int32 (nq,k))``, ``+inf`` / ``-1``
+    padded when a query's lists hold fewer than ``k`` rows."""
+    lib = _lib.load()
+    _lib.require_device()
+    q = _as_f32_rows(Qp)
+    data = _as_f32_rows(index.data)
+    nq, d = q.shape
+    m = data.shape[0]
+    probed = probed.to(torch.int32).contiguous()
+    nprobe = probed.shape[1]
+    offs = index.list_offsets.to(torch.int64).contiguous()
+    vals = torch.empty((nq, k), dtype=torch.float32, device=q.device)
+    pos = torch.empty((nq, k), dtype=torch.int32, device=q.device)
+    ws_bytes = lib.fl_ivf_fine_scan_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
+    hn = index.half_norms() if data.data_ptr() == index.data.data_ptr() else None
+    with torch.cuda.device(q.device):
+        _lib.check(lib.fl_ivf_fine_scan_f32(q.data_ptr(), nq, q.stride(0) if nq else d, data.data_ptr(), m,
+                                            data.stride(0), d, offs.data_ptr(), index.nlist,
+                                            probed.data_ptr(), nprobe, k,
+                                            hn.data_ptr() if hn is not None else None,
+                                            vals.data_ptr(), pos.data_ptr(), ws.data_ptr(), ws_bytes,
+                                            _stream_ptr(q.device)))
+    return vals, pos
+
+
+def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprobe: Optional[int] = None,
+                          backend: Optional[str] = None, variant: str = "auto"):
+    """``(vals fp32, ids int64)`` of the ``k`` nearest probed rows per query, ``-1`` / ``+inf``
+    padded (``ivf_flat/triton/search.py:52-108``).  ``variant`` is validated like the
+    reference's and otherwise ignored: one fine-scan kernel serves every batch size."""
+    if variant not in ("auto", "gemm", "elementwise"):
+        raise ValueError(f"unknown variant {variant!r} (auto|gemm|elementwise)")
+    if not Q.is_cuda or Q.ndim != 2:
+        raise ValueError("flash_ivf_flat_search requires a 2D CUDA tensor")
+    nprobe = int(nprobe or index.nprobe)
+    nprobe = max(1, min(nprobe, index.nlist))
+    if not (1 <= k <= index.M):
+        raise ValueError(f"k must be in [1, M={index.M}] (got {k})")
+    Qp = _pad_features(Q.to(index.data.dtype), index.Dp).contiguous()
+    # coarse probe in the exact-rank mode: near-tied centroids must rank as in fp32
+    probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
+                       return_distances=False, mode="exact")[0]
+    vals, pos = ivf_fine_scan(Qp, index, probed, k)
+    valid = pos >= 0
+    pos_safe = pos.clamp_min(0).to(torch.int64)
+    ids = torch.where(valid, index.ids[pos_safe], torch.full_like(pos_safe, -1))
+    return vals, ids
+
+
+def flash_ivf_flat(X: torch.Tensor, Q: torch.Tensor, k: int, *, nlist: int = 1024, nprobe: int = 8,
+                   metric: str = "l2", niter: int = 20, train_size: Optional[int] = None, seed: int = 0,
+                   backend: Optional[str] = None):
+    """One-shot build + search (``ivf_flat/impl.py:132-150``)."""
+    index = flash_ivf_flat_build(X, nlist, metric=metric, nprobe=nprobe, niter=niter,
+                                 train_size=train_size, seed=seed, backend=backend)
+    return flash_ivf_flat_search(index, Q, k, nprobe=nprobe, backend=backend)

@@ -1,0 +1,233 @@
+"""Fused exact brute-force kNN behind flashlib's ``flash_knn`` signature.
+
+Mirrors ``flashlib/primitives/knn/impl.py:199-287`` (``flash_knn_dispatch``): same
+arguments, same return dtypes on CUDA (``vals`` fp32 true squared L2, ``idxs`` int32),
+same error behaviour for unknown backends.  The reference's multi-backend routing is
+gone: every call goes through the C ABI into the sm_100a kernels, and CPU tensors are
+rejected because this library has no CPU path.
+"""
+from __future__ import annotations
+
+import os
+from collections import OrderedDict
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_VALID_BACKENDS = ("triton", "cutedsl", "torch")
+_MODES = {None: _lib.FL_KNN_AUTO, "auto": _lib.FL_KNN_AUTO, "exact": _lib.FL_KNN_EXACT_SIMT,
+          "simt": _lib.FL_KNN_EXACT_SIMT, "bf16": _lib.FL_KNN_BF16_RERANK,
+          "tc": _lib.FL_KNN_BF16_RERANK}
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _as_f32_rows(t: torch.Tensor) -> torch.Tensor:
+    """fp32 tensor whose last dimension is contiguous (rows may be strided)."""
+    if t.dtype != torch.float32:
+        t = t.float()
+    if t.stride(-1) != 1 or (t.dim() == 2 and t.stride(0) < t.shape[1]):
+        t = t.contiguous()
+    return t
+
+
+def _mode_from(mode: Optional[str]) -> int:
+    if mode is None:
+        mode = os.environ.get("FLASHLIB_B200_KNN_MODE") or None
+    if mode not in _MODES:
+        raise ValueError(f"mode must be one of {sorted(k for k in _MODES if k)} or None, got {mode!r}")
+    return _MODES[mode]
+
+
+class DbPlane:
+    """The bf16 operand plane (+ half norms) of one fp32 database, built once per database.
+
+    The reference caches ``||c||^2`` per ``data_ptr`` in the same spirit
+    (``flashlib/primitives/knn/triton/_row_norm.py:82-93``).
+    """
+
+    def __init__(self, db: torch.Tensor):
+        lib = _lib.load()
+        m, d = db.shape
+        nbytes = lib.fl_knn_plane_bytes(m, d)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=db.device)
+        _lib.check(lib.fl_knn_prepare_db_f32(db.data_ptr(), m, d, db.stride(0), self.buf.data_ptr(),
+                                             nbytes, _stream_ptr(db.device)))
+        self.key = _plane_key(db)
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
+def _plane_key(db: torch.Tensor):
+    return (db.data_ptr(), tuple(db.shape), db.stride(0), db._version, db.device.index)
+
+
+_PLANE_CACHE: "OrderedDict[tuple, DbPlane]" = OrderedDict()
+_PLANE_CACHE_SIZE = 4
+
+
+def get_plane(db: torch.Tensor) -> DbPlane:
+    key = _plane_key(db)
+    hit = _PLANE_CACHE.get(key)
+    if hit is not None:
+        _PLANE_CACHE.move_to_end(key)
+        return hit
+    plane = DbPlane(db)
+    _PLANE_CACHE[key] = plane
+    while len(_PLANE_CACHE) > _PLANE_CACHE_SIZE:
+        _PLANE_CACHE.popitem(last=False)
+    return plane
+
+
+def clear_plane_cache() -> None:
+    _PLANE_CACHE.clear()
+
+
+def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KNN_AUTO,
+            row_offset: int = 0, plane: Optional[DbPlane] = None, check_status: bool = True):
+    """One 2-D problem through ``fl_knn_f32``: returns ``(dist fp32 (nq,k), idx int32 (nq,k), info)``."""
+    lib = _lib.load()
+    _lib.require_device()
+    nq, d = q.shape
+    m = db.shape[0]
+    dev = q.device
+    resolved = lib.fl_knn_resolve_mode(nq, m, d, k) if mode == _lib.FL_KNN_AUTO else mode
+    if resolved == _lib.FL_KNN_BF16_RERANK and plane is None:
+        plane = get_plane(db)
+    out_d = torch.empty((nq, k), dtype=torch.float32, device=dev)
+    out_i = torch.empty((nq, k), dtype=torch.int32, device=dev)
+    ws_bytes = lib.fl_knn_workspace_bytes(max(nq, 1), m, d, k, resolved)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    status = torch.zeros(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=dev)
+    rc = lib.fl_knn_f32(q.data_ptr(), nq, q.stride(0) if nq else d, db.data_ptr(), m, db.stride(0), d, k,
+                        resolved, plane.ptr if plane is not None else None, row_offset,
+                        out_d.data_ptr(), out_i.data_ptr(), ws.data_ptr(), ws_bytes,
+                        status.data_ptr(), _stream_ptr(dev))
+    _lib.check(rc)
+    info = {"mode": resolved, "status": status}
+    if check_status and resolved == _lib.FL_KNN_BF16_RERANK:
+        st = status.tolist()
+        info["fallback_rows"] = st[_lib.FL_STATUS_FALLBACK]
+        if st[_lib.FL_STATUS_ERROR] != 0:
+            raise _lib.FlashlibError(
+                f"tensor-core kNN kernel reported status {st[_lib.FL_STATUS_ERROR]} "
+                f"(where={st[_lib.FL_STATUS_WHERE]:#x})")
+    return out_d, out_i, info
+
+
+def flash_knn_dispatch(x: torch.Tensor, c: torch.Tensor, k: int, *, tol: Optional[float] = None,
+                       backend: Optional[str] = None, return_distances: bool = True,
+                       mode: Optional[str] = None, **kwargs):
+    """Exact k nearest rows of ``c`` for every row of ``x`` by squared L2.
+
+    Parameters follow ``flashlib/primitives/knn/impl.py:199-247``: ``x`` is ``(B, N, D)`` or
+    ``(N, D)``, ``c`` has the same rank and dtype, ``backend`` may be ``None`` or one of the
+    reference's names (validated, then ignored: there is one implementation), ``tol`` is
+    accepted for compatibility (fp32 is kept: results are exact either way).  ``mode``
+    (``"exact"`` | ``"bf16"`` | ``None`` = auto) picks the scoring kernel.
+
+    Returns ``(vals, idxs)`` -- fp32 true squared distances ascending and int32 indices --
+    or just ``idxs`` with ``return_distances=False``.
+    """
+    if backend is not None and backend not in _VALID_BACKENDS:
+        raise ValueError(f"backend must be one of {_VALID_BACKENDS} or None, got {backend!r}")
+    if x.dim() not in (2, 3) or c.dim() != x.dim():
+        raise ValueError("flash_knn expects x and c of the same rank: (N, D)/(M, D) or (B, N, D)/(B, M, D)")
+    if x.dtype != c.dtype:
+        raise AssertionError("x and c must share a dtype")
+    if not (x.is_cuda and c.is_cuda):
+        raise RuntimeError("flashlib_b200.flash_knn needs CUDA tensors (no CPU fallback)")
+    squeeze = x.dim() == 2
+    if squeeze:
+        x = x.unsqueeze(0)
+        c = c.unsqueeze(0)
+    B, N, D = x.shape
+    Bc, M, Dc = c.shape
+    if Bc != B or Dc != D:
+        raise AssertionError("x and c must agree on batch and feature dimensions")
+    if not (1 <= int(k) <= M):
+        raise AssertionError(f"k must be in [1, M={M}] (got {k})")
+    k = int(k)
+    m = _mode_from(mode)
+    vals = torch.empty((B, N, k), dtype=torch.float32, device=x.device)
+    idxs = torch.empty((B, N, k), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        for b in range(B):
+            qb = _as_f32_rows(x[b])
+            cb = _as_f32_rows(c[b])
+            d_b, i_b, _ = knn_f32(qb, cb, k, mode=m)
+            vals[b] = d_b
+            idxs[b] = i_b
+    if not return_distances:
+        return idxs[0] if squeeze else idxs
+    if squeeze:
+        return vals[0], idxs[0]
+    return vals, idxs
+
+
+flash_knn = flash_knn_dispatch
+flash_knn_triton = flash_knn_dispatch  # name kept for callers of the reference's Triton entry
+
+
+def triton_knn_gather_sqdist(x: torch.Tensor, c: torch.Tensor, idx: torch.Tensor,
+                             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[b,n,j] = sum_d (x[b,n,d] - c[b,idx[b,n,j],d])^2`` in fp32.
+
+    Same contract as ``flashlib/kernels/distance/triton/knn_gather_l2sq.py:173-229``
+    (3-D inputs, int32 or int64 indices).
+    """
+    assert x.is_cuda and c.is_cuda and idx.is_cuda
+    assert x.dim() == 3 and c.dim() == 3 and idx.dim() == 3
+    B, N, D = x.shape
+    Bc, M, Dc = c.shape
+    Bi, Ni, K = idx.shape
+    assert B == Bc == Bi and N == Ni and D == Dc
+    assert idx.dtype in (torch.int32, torch.int64)
+    lib = _lib.load()
+    _lib.require_device()
+    if out is None:
+        out = torch.empty((B, N, K), dtype=torch.float32, device=x.device)
+    else:
+        assert out.shape == (B, N, K) and out.dtype == torch.float32 and out.is_contiguous()
+    with torch.cuda.device(x.device):
+        for b in range(B):
+            xb = _as_f32_rows(x[b])
+            cb = _as_f32_rows(c[b])
+            ib = idx[b].contiguous()
+            _lib.check(lib.fl_gather_l2sq_f32(xb.data_ptr(), N, xb.stride(0), cb.data_ptr(), M, cb.stride(0), D,
+                                              ib.data_ptr(), 1 if ib.dtype == torch.int64 else 0, K,
+                                              out[b].data_ptr(), _stream_ptr(x.device)))
+    return out
+
+
+def row_sqnorm(x: torch.Tensor) -> torch.Tensor:
+    """fp32 ``||row||^2`` of a 2-D CUDA tensor (``knn/triton/_row_norm.py:59-93``)."""
+    lib = _lib.load()
+    _lib.require_device()
+    xb = _as_f32_rows(x)
+    out = torch.empty(xb.shape[0], dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.fl_rownorm_f32(xb.data_ptr(), xb.shape[0], xb.shape[1], xb.stride(0), out.data_ptr(),
+                                      _stream_ptr(x.device)))
+    return out
+
+
+def topk_merge(cand_dist: torch.Tensor, cand_idx: torch.Tensor, k: int):
+    """k smallest ``(dist, idx)`` per row of ``(nq, ncand)`` candidates (idx < 0 ignored)."""
+    lib = _lib.load()
+    _lib.require_device()
+    cand_dist = cand_dist.contiguous().float()
+    cand_idx = cand_idx.contiguous().to(torch.int32)
+    nq, ncand = cand_dist.shape
+    out_d = torch.empty((nq, k), dtype=torch.float32, device=cand_dist.device)
+    out_i = torch.empty((nq, k), dtype=torch.int32, device=cand_dist.device)
+    with torch.cuda.device(cand_dist.device):
+        _lib.check(lib.fl_topk_merge_f32(cand_dist.data_ptr(), cand_idx.data_ptr(), nq, ncand, k,
+                                         out_d.data_ptr(), out_i.data_ptr(), _stream_ptr(cand_dist.device)))
+    return out_d, out_i

@@ -1,0 +1,152 @@
+/*
+ * flashlib_b200 -- C ABI of the B200 (sm_100a) fused squared-L2 distance + top-k path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*).  Nothing here allocates device memory unless the
+ * comment on the entry point says otherwise: the caller passes outputs and a
+ * workspace sized by the matching *_workspace_bytes() query.  All launches are
+ * stream-ordered and never synchronise the host.
+ *
+ * The reference project (FlashML-org/flashlib) is pure Python; it has no FFI layer.
+ * Each declaration therefore cites the Python function (path:line inside the reference
+ * tree) whose device work it replaces.
+ *
+ * Return value: 0 on success, a negative FL_E* code otherwise; fl_last_error() returns
+ * a thread-local human-readable message for the last failure.
+ */
+#ifndef FLASHLIB_B200_H_
+#define FLASHLIB_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FL_OK            0
+#define FL_EINVAL       -1   /* bad argument (maps to ValueError / AssertionError)      */
+#define FL_EUNSUPPORTED -2   /* shape or mode outside what this build implements         */
+#define FL_ECUDA        -3   /* a CUDA runtime / driver call failed                      */
+#define FL_ETIMEOUT     -4   /* a bounded device-side wait gave up (see status words)    */
+#define FL_EWORKSPACE   -5   /* workspace or plane buffer too small                      */
+
+/* kNN modes (argument `mode` of fl_knn_f32 / fl_knn_workspace_bytes). */
+#define FL_KNN_AUTO        -1  /* tensor-core path when supported, else CUDA-core path   */
+#define FL_KNN_EXACT_SIMT   0  /* fp32 CUDA-core scoring + exact re-rank                 */
+#define FL_KNN_BF16_RERANK  1  /* tcgen05 bf16 candidates, exact fp32 re-rank, verified  */
+
+/* Device status words (int32[FL_STATUS_WORDS]) written by the kNN / assign kernels.     */
+#define FL_STATUS_WORDS     8
+#define FL_STATUS_ERROR     0  /* 0, or FL_ETIMEOUT when a bounded wait expired          */
+#define FL_STATUS_WHERE     1  /* which wait expired (role << 16 | barrier index)        */
+#define FL_STATUS_FALLBACK  2  /* rows whose candidate pool failed verification and were
+                                  recomputed on the exact CUDA-core path                 */
+#define FL_STATUS_POOL      3  /* candidate-pool size per row used by the last call      */
+
+int         fl_version(void);
+const char* fl_last_error(void);
+
+/* 1 when the running process can see an sm_100 device, 0 otherwise (never fails). */
+int         fl_device_ok(void);
+
+/* ---------------------------------------------------------------------------------- */
+/* Row norms.  Replaces flashlib/primitives/knn/triton/_row_norm.py:59-93               */
+/* (_fast_row_sq) and knn/cutedsl/blackwell_impl.py:114-124 (_row_sqnorm).              */
+/* out[i] = sum_j x[i*ld + j]^2 in fp32.                                               */
+int fl_rownorm_f32(const float* x, int64_t n, int d, int64_t ld, float* out, void* stream);
+
+/* ---------------------------------------------------------------------------------- */
+/* Database operand plane for the tensor-core path (index-build-time work; the          */
+/* reference caches the equivalent c_sq per data_ptr: knn/triton/_row_norm.py:82-93,    */
+/* and casts storage per knn/impl.py:257-261).                                          */
+/* Layout of `plane` (all offsets 1024-byte aligned, see fl_knn_plane_bytes):           */
+/*   bf16 [m_pad][d_pad]  row-major, zero padded (m_pad % 256 == 0, d_pad % 64 == 0)    */
+/*   f32  [m_pad]         half squared norms ||x||^2/2 of the fp32 rows, +inf padding   */
+/*   f32  [4]             [0] = max row norm ||x|| over the plane                        */
+int64_t fl_knn_plane_bytes(int64_t m, int d);
+int     fl_knn_prepare_db_f32(const float* db, int64_t m, int d, int64_t ld,
+                              void* plane, int64_t plane_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------- */
+/* Fused exact kNN.  Replaces flash_knn_triton/_run/_try_launch                         */
+/* (knn/triton/dispatch.py:934-1178), the insert kernel (knn/triton/insert.py:30-204),  */
+/* the split merge (dispatch.py:987-994), the Blackwell CuTe-DSL kernels                */
+/* (knn/cutedsl/blackwell_impl.py:152-1225) and the exact distance gather               */
+/* (kernels/distance/triton/knn_gather_l2sq.py:173-229) behind                          */
+/* flash_knn_dispatch (knn/impl.py:199-282).                                            */
+/*                                                                                      */
+/* q [nq][ldq], db [m][ldb] fp32 row-major on the device.  out_dist [nq][k] fp32 true   */
+/* squared L2, ascending; out_idx [nq][k] int32 = database row + row_offset (row_offset */
+/* lets a row shard report global ids); ties keep the lower row.  `plane` is the buffer */
+/* filled by fl_knn_prepare_db_f32 for the same db (may be NULL for FL_KNN_EXACT_SIMT). */
+/* `status` is int32[FL_STATUS_WORDS] on the device (may be NULL).                      */
+int64_t fl_knn_workspace_bytes(int64_t nq, int64_t m, int d, int k, int mode);
+int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
+                   const float* db, int64_t m, int64_t ldb, int d, int k, int mode,
+                   const void* plane, int64_t row_offset,
+                   float* out_dist, int32_t* out_idx,
+                   void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
+/* Which mode FL_KNN_AUTO resolves to for a shape (no device work). */
+int     fl_knn_resolve_mode(int64_t nq, int64_t m, int d, int k);
+
+/* ---------------------------------------------------------------------------------- */
+/* k-way merge of per-shard candidates (the reference has no sharded kNN; within one    */
+/* GPU its split merge is torch.topk, knn/triton/dispatch.py:987-994).                  */
+/* cand_dist/cand_idx [nq][ncand]; picks the k smallest (dist, idx) per row, ascending. */
+/* Entries with idx < 0 are ignored.                                                    */
+int fl_topk_merge_f32(const float* cand_dist, const int32_t* cand_idx, int64_t nq, int ncand,
+                      int k, float* out_dist, int32_t* out_idx, void* stream);
+
+/* ---------------------------------------------------------------------------------- */
+/* Exact gather distances.  Replaces triton_knn_gather_sqdist                           */
+/* (kernels/distance/triton/knn_gather_l2sq.py:173-229):                                */
+/* out[i][j] = sum_d (x[i][d] - c[idx[i][j]][d])^2 ; idx < 0 gives +inf.               */
+/* idx_is_i64 selects int64 or int32 index elements.                                    */
+int fl_gather_l2sq_f32(const float* x, int64_t n, int64_t ldx,
+                       const float* c, int64_t m, int64_t ldc, int d,
+                       const void* idx, int idx_is_i64, int k, float* out, void* stream);
+
+/* ---------------------------------------------------------------------------------- */
+/* k-means.  Replaces euclid_assign_triton (kmeans/triton/assign.py:1439-1596),         */
+/* triton_centroid_update_sorted_euclid / _centroid_update_chunk_kernel                 */
+/* (kmeans/triton/update.py:179-259,313-384), triton_centroid_finalize                  */
+/* (update.py:406-554) and the Blackwell assign kernels                                 */
+/* (kmeans/cutedsl/blackwell_assign.py:77-2289).                                        */
+/*                                                                                      */
+/* labels[i] = argmin_j ||x_i - c_j||^2 (lowest j on exact ties), int32.                */
+int64_t fl_kmeans_assign_workspace_bytes(int64_t n, int K, int d);
+int     fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx,
+                             const float* c, int K, int64_t ldc, int d,
+                             int32_t* labels, void* ws, int64_t ws_bytes, void* stream);
+/* sums [K][d] fp32 and cnts [K] int32 are overwritten with the per-cluster sums/counts. */
+int     fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d,
+                             const int32_t* labels, int K,
+                             float* sums, int32_t* cnts, void* stream);
+/* new_c = cnt ? sums/cnt : old_c ; shift[j] = ||new_c[j] - old_c[j]||_2.               */
+int     fl_kmeans_finalize_f32(const float* sums, const int32_t* cnts, const float* old_c,
+                               float* new_c, float* shift, int K, int d, void* stream);
+
+/* ---------------------------------------------------------------------------------- */
+/* IVF-Flat fine scan.  Replaces ivf_fine_scan_gemm + _ivf_fine_gemm_kernel             */
+/* (ivf_flat/triton/fine_scan_gemm.py:41-272) and ivf_fine_scan                         */
+/* (ivf_flat/triton/fine_scan.py:44-235).                                               */
+/* data [m][ldd] is cell-contiguous; list c owns rows list_offsets[c]..list_offsets[c+1]*/
+/* (int64[nlist+1]).  probed [nq][nprobe] int32 list ids.  out_dist [nq][k] exact       */
+/* squared L2 ascending, out_pos [nq][k] int32 stored-row positions; rows with fewer    */
+/* than k candidates are padded with +inf / -1.  data_hnorm is ||row||^2/2 per stored    */
+/* row (fp32 [m]; what fl_rownorm_f32 returns, halved) or NULL to have it computed in    */
+/* the workspace on every call.                                                         */
+int64_t fl_ivf_fine_scan_workspace_bytes(int64_t nq, int nprobe, int nlist, int64_t m, int d, int k);
+int     fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq,
+                             const float* data, int64_t m, int64_t ldd, int d,
+                             const int64_t* list_offsets, int nlist,
+                             const int32_t* probed, int nprobe, int k,
+                             const float* data_hnorm,
+                             float* out_dist, int32_t* out_pos,
+                             void* ws, int64_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHLIB_B200_H_ */
