@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the fused exact-kNN hot path: queries/s on the 1,000,000 x 128 fp32, k=10
+configuration, database row-sharded over the GPUs of one box.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # CPU restatement of the reference's torch path
+
+A step is one batch of queries through the hot path.  Scaling is weak: every rank brings
+10,000 queries per step (global batch 10,000 x N) and holds 1/N of the database rows; the
+per-rank candidates are all-gathered (NCCL) and merged on every rank.  One JSON line is
+printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+K_NEIGHBOURS = 10
+DB_ROWS = 1_000_000
+DIM = 128
+QUERIES_PER_GPU = 10_000
+N_COMP = 4096
+SEED = 2
+METRIC = "exact_knn_queries_per_sec"
+UNIT = "queries/s"
+
+
+def workload_name(n_gpus: int) -> str:
+    return (f"knn_1m: exact kNN, database {DB_ROWS}x{DIM} fp32 (4096-component gaussian mixture, "
+            f"clamped >= 0, seed {SEED}), {QUERIES_PER_GPU} queries per GPU per step, k={K_NEIGHBOURS}, squared L2")
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"source": "measured", "hbm_gbs": p.get("hbm_gbs"), "bf16_tflops": p.get("bf16_tflops"),
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained")}
+    return {"source": "fallback", "hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.out.close()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as f:
+            for line in f:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1]))
+                    smax.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_workload(rank: int, world: int):
+    from flashlib_b200 import synthetic
+    from flashlib_b200.sharded import shard_bounds
+    X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU * world, clamp=True)
+    s, e = shard_bounds(DB_ROWS, world, rank)
+    return X, Q, s, e
+
+
+def cpu_baseline_run(X: torch.Tensor, Q: torch.Tensor, n_queries: int, repeats: int = 1):
+    """Times the numpy restatement of the reference's chunked torch path on `n_queries` queries
+    against the whole database; returns (queries/s, threads)."""
+    from oracle import oracle_torch
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle_torch.knn_chunked(Q[:n_queries], X, K_NEIGHBOURS, chunk_size=8192)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return n_queries / best, torch.get_num_threads()
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    from flashlib_b200 import synthetic
+    X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
+    from oracle import oracle_torch
+    sample = 1024
+    for _ in range(min(args.warmup, 1)):
+        oracle_torch.knn_chunked(Q[:64], X, K_NEIGHBOURS, chunk_size=8192)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        lo = (s * sample) % (QUERIES_PER_GPU - sample + 1)
+        oracle_torch.knn_chunked(Q[lo:lo + sample], X, K_NEIGHBOURS, chunk_size=8192)
+    dt = time.perf_counter() - t0
+    qps = args.steps * sample / dt
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.gpus), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS},
+        "cpu_baseline": {"value": qps, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{sample} queries per step against all {DB_ROWS} rows; torch-CPU "
+                                   "restatement of knn_torch_chunked, chunk 8192"},
+        "e2e": {"value": qps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from flashlib_b200 import _lib
+    from flashlib_b200.knn import _mode_from, flash_knn, get_plane
+    from flashlib_b200.sharded import sharded_knn
+    lib = _lib.load()
+    _lib.require_device()
+    mode = _mode_from(args.mode)
+
+    X, Q, s, e = make_workload(rank, world)
+    nq = Q.shape[0]
+    db = X[s:e].contiguous().to(dev)
+    q_host = Q.contiguous().pin_memory()
+    q_dev = q_host.to(dev)
+    resolved = lib.fl_knn_resolve_mode(nq, db.shape[0], DIM, K_NEIGHBOURS) if mode == _lib.FL_KNN_AUTO else mode
+    plane = get_plane(db) if resolved == _lib.FL_KNN_BF16_RERANK else None   # index-build-time work
+    torch.cuda.synchronize()
+
+    def step_device():
+        return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ----------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        out = step_device()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    lib.fl_profile_enable(1)
+    launches0 = lib.fl_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        out = step_device()
+    ev1.record()
+    barrier()
+    launches = lib.fl_launch_count() - launches0
+    ms_total = ev0.elapsed_time(ev1)
+    kernel_ms = []
+    tmp = ctypes.c_float()
+    for i in range(lib.fl_profile_count()):
+        if lib.fl_profile_read_ms(i, ctypes.byref(tmp)) == 0:
+            kernel_ms.append(tmp.value)
+    lib.fl_profile_enable(0)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    value = nq * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end: pinned host queries in, host results out, through the public API -----
+    out_d_host = torch.empty((nq, K_NEIGHBOURS), dtype=torch.float32).pin_memory()
+    out_i_host = torch.empty((nq, K_NEIGHBOURS), dtype=torch.int32).pin_memory()
+
+    def step_e2e():
+        qd = q_host.to(dev, non_blocking=True)
+        if world == 1:
+            d_, i_ = flash_knn(qd, db, K_NEIGHBOURS, mode=args.mode)
+        else:
+            d_, i_ = sharded_knn(qd, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane)
+        out_d_host.copy_(d_, non_blocking=True)
+        out_i_host.copy_(i_, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    e2e_value = nq * args.steps / e2e_s
+
+    if rank == 0:
+        peaks = load_peaks()
+        rows_local = e - s
+        flop_per_launch = 2.0 * nq * rows_local * DIM
+        k_ms = statistics.mean(kernel_ms) if kernel_ms else None
+        achieved = flop_per_launch / (k_ms * 1e-3) / 1e12 if k_ms else None
+        peak = peaks["bf16_tflops"]
+        roofline = {
+            "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": (achieved / peak) if achieved else None, "traffic": None,
+            "kernel": "knn_tc_kernel" if resolved == _lib.FL_KNN_BF16_RERANK else "knn_simt_kernel",
+            "kernel_ms": k_ms, "launches_timed": len(kernel_ms),
+            "algorithmic_flop_per_launch": flop_per_launch,
+            "peak_source": f"{peaks['source']} bf16 burst (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
+            else "fallback 1.59 PFLOP/s",
+        }
+        cpu_base = None
+        if not args.no_cpu_baseline and world == 1:
+            n_cpu_q = 2048
+            v, cores = cpu_baseline_run(X, Q, n_cpu_q)
+            cpu_base = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                        "sample": f"{n_cpu_q} of the {QUERIES_PER_GPU} queries against all {DB_ROWS} rows; "
+                                  "torch-CPU restatement of knn_torch_chunked, chunk 8192"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
+            "data": "synthetic",
+            "config": {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,
+                       "queries_per_step": nq, "sharding": f"database rows over {world} rank(s); candidates "
+                       "all-gathered and merged on every rank" if world > 1 else "single GPU",
+                       "mode": {_lib.FL_KNN_EXACT_SIMT: "exact fp32 CUDA-core scoring + exact re-rank",
+                                _lib.FL_KNN_BF16_RERANK: "tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback"}[resolved],
+                       "l2": "no flush needed: each step streams the database operand (>= 256 MB), larger than the 126 MB L2"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 4),
+                    "d2h_bytes_per_step": int(out_d_host.numel() * 4 + out_i_host.numel() * 4),
+                    "note": "queries from pinned host memory, results to pinned host memory; the database is the fitted index and stays resident"},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "cpu_baseline": cpu_base,
+            "clocks": clocks,
+            "tensor_tflops_algorithmic": 2.0 * nq * DB_ROWS * DIM * args.steps / (ms_total * 1e-3) / 1e12 / world,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,10 @@ SIGNATURES = {
     "fl_version": (c_int, []),
     "fl_last_error": (c_char_p, []),
     "fl_device_ok": (c_int, []),
+    "fl_launch_count": (ctypes.c_ulonglong, []),
+    "fl_profile_enable": (c_int, [c_int]),
+    "fl_profile_count": (c_int, []),
+    "fl_profile_read_ms": (c_int, [c_int, c_void_p]),
     "fl_rownorm_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p]),
     "fl_knn_plane_bytes": (c_int64, [c_int64, c_int]),
     "fl_knn_prepare_db_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),

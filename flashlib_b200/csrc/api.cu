@@ -12,6 +12,27 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_add_fetch(&g_launches, 1ull, __ATOMIC_RELAXED); }
+
+// Ring of event pairs around the dominant kernel of the profiled entry points.
+constexpr int PROFILE_SLOTS = 256;
+static int g_profile_on = 0;
+static int g_profile_n = 0;
+static cudaEvent_t g_ev_begin[PROFILE_SLOTS];
+static cudaEvent_t g_ev_end[PROFILE_SLOTS];
+static bool g_ev_made = false;
+
+void profile_begin(cudaStream_t st) {
+    if (!g_profile_on || g_profile_n >= PROFILE_SLOTS) return;
+    cudaEventRecord(g_ev_begin[g_profile_n], st);
+}
+void profile_end(cudaStream_t st) {
+    if (!g_profile_on || g_profile_n >= PROFILE_SLOTS) return;
+    cudaEventRecord(g_ev_end[g_profile_n], st);
+    ++g_profile_n;
+}
+
 int sm_count() {
     static int cached[64];
     int dev = 0;
@@ -55,4 +76,30 @@ extern "C" int fl_device_ok(void) {
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
     return major == 10 ? 1 : 0;
+}
+
+extern "C" unsigned long long fl_launch_count(void) { return __atomic_load_n(&fl::g_launches, __ATOMIC_RELAXED); }
+
+extern "C" int fl_profile_enable(int on) {
+    using namespace fl;
+    if (on && !g_ev_made) {
+        for (int i = 0; i < PROFILE_SLOTS; ++i) {
+            FL_CHECK_CUDA(cudaEventCreate(&g_ev_begin[i]));
+            FL_CHECK_CUDA(cudaEventCreate(&g_ev_end[i]));
+        }
+        g_ev_made = true;
+    }
+    g_profile_on = on ? 1 : 0;
+    g_profile_n = 0;
+    return FL_OK;
+}
+
+extern "C" int fl_profile_count(void) { return fl::g_profile_n; }
+
+extern "C" int fl_profile_read_ms(int i, float* ms) {
+    using namespace fl;
+    FL_CHECK_ARG(ms && i >= 0 && i < g_profile_n, "fl_profile_read_ms: no such sample %d", i);
+    FL_CHECK_CUDA(cudaEventSynchronize(g_ev_end[i]));
+    FL_CHECK_CUDA(cudaEventElapsedTime(ms, g_ev_begin[i], g_ev_end[i]));
+    return FL_OK;
 }

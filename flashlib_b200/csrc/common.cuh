@@ -14,6 +14,11 @@ namespace fl {
 
 // ---- host-side error plumbing ------------------------------------------------------
 void set_error(const char* fmt, ...);
+void count_launch();
+// Profiling hooks (no-ops unless fl_profile_enable(1) was called): bracket the dominant
+// kernel of an entry point with CUDA events recorded on the caller's stream.
+void profile_begin(cudaStream_t st);
+void profile_end(cudaStream_t st);
 
 #define FL_CHECK_ARG(cond, ...)                                                         \
     do {                                                                                \
@@ -33,7 +38,13 @@ void set_error(const char* fmt, ...);
         }                                                                               \
     } while (0)
 
-#define FL_CHECK_LAUNCH()  FL_CHECK_CUDA(cudaGetLastError())
+// Every kernel launch in the library goes through this macro: it counts the launch
+// (fl_launch_count) and surfaces launch-configuration errors.
+#define FL_CHECK_LAUNCH()                                                               \
+    do {                                                                                \
+        ::fl::count_launch();                                                           \
+        FL_CHECK_CUDA(cudaGetLastError());                                              \
+    } while (0)
 
 static inline int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

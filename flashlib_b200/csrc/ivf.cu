@@ -186,7 +186,9 @@ extern "C" int fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq, con
     sp.ivf = 1; sp.nlist = nlist; sp.nprobe = nprobe; sp.bq_items = w.bq;
     sp.item_off = item_off; sp.pair_off = pair_off; sp.sorted_pair = sorted_pair;
     sp.list_offsets = list_offsets;
+    profile_begin(st);
     int rc = launch_knn_simt(sp, w.max_items, st);
+    profile_end(st);
     if (rc != FL_OK) return rc;
 
     FinalizeParams fp{};

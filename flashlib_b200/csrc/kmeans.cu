@@ -183,8 +183,10 @@ extern "C" int fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx, cons
     const size_t smem = sizeof(float) * SimtTile<TQ>::SLAB_FLOATS;
     FL_CHECK_CUDA(cudaFuncSetAttribute(kmeans_assign_simt_kernel<TQ>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    profile_begin(st);
     kmeans_assign_simt_kernel<TQ><<<(unsigned)ceil_div(n, SimtTile<TQ>::BQ), 256, smem, st>>>(
         x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc);
+    profile_end(st);
     FL_CHECK_LAUNCH();
     return FL_OK;
 }

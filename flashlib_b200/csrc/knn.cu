@@ -259,7 +259,9 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
         sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
         sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
         sp.vecq = vecq; sp.vecd = vecd;
+        profile_begin(st);
         int rc = launch_knn_simt(sp, nq, st);
+        profile_end(st);
         if (rc != FL_OK) return rc;
 
         FinalizeParams fp{};
@@ -299,7 +301,9 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
     tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
     tp.tau = tau; tp.status = status;
+    profile_begin(st);
     rc = launch_knn_tc(tp, st);
+    profile_end(st);
     if (rc != FL_OK) return rc;
 
     FinalizeParams fp{};

@@ -1,0 +1,116 @@
+"""Row-sharded kNN and k-means over the GPUs of one box: one process per GPU,
+``torch.distributed`` (NCCL over NVLink) for the exchange step.
+
+The reference has no sharded kNN; its only multi-device code is the single-process k-means
+of ``flashlib/primitives/kmeans/large.py:35-280``, which copies per-GPU partial sums to GPU 0
+and adds them there.  Here every rank owns a contiguous row range of the database (or of the
+sample set), runs the single-GPU kernels on it and exchanges only what the algorithm needs:
+
+* kNN: the ``(nq, k)`` local candidates with global row ids are all-gathered and every rank
+  picks the k best of ``world * k`` per query with ``fl_topk_merge_f32``;
+* k-means: the per-cluster sums and counts are all-reduced, every rank finalises the same
+  centroids (no broadcast), labels stay sharded.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(m: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous row range ``[start, end)`` of ``rank``; the first ``m % world`` ranks hold
+    one extra row."""
+    base, rem = divmod(int(m), int(world))
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+def gather_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
+    """All-gathers ``(nq, k)`` candidates from every rank into ``(nq, world * k)`` tensors
+    (rank-major along the candidate axis)."""
+    world = dist.get_world_size(group)
+    nq, k = local_d.shape
+    gd = torch.empty((world, nq, k), dtype=local_d.dtype, device=local_d.device)
+    gi = torch.empty((world, nq, k), dtype=local_i.dtype, device=local_i.device)
+    dist.all_gather_into_tensor(gd, local_d.contiguous(), group=group)
+    dist.all_gather_into_tensor(gi, local_i.contiguous(), group=group)
+    cand_d = gd.permute(1, 0, 2).reshape(nq, world * k)
+    cand_i = gi.permute(1, 0, 2).reshape(nq, world * k)
+    return cand_d, cand_i
+
+
+def sharded_knn(q: torch.Tensor, db_shard: torch.Tensor, k: int, *, row_offset: int, group=None,
+                mode: Optional[str] = None, plane=None,
+                local_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
+    """Exact kNN of the replicated queries ``q`` against a row-sharded database.
+
+    ``db_shard`` is this rank's rows, ``row_offset`` its first global row id.  A shard with
+    fewer than ``k`` rows contributes ``+inf`` / ``-1`` padding.  Returns the same
+    ``(dist fp32 (nq,k), idx int32 (nq,k))`` on every rank.  ``local_fn`` / ``merge_fn``
+    replace the device kernels (used by the CPU tests of the exchange logic).
+    """
+    if local_fn is None:
+        from .knn import _mode_from, knn_f32
+
+        def local_fn(q_, db_, k_, off_):
+            d_, i_, _ = knn_f32(q_, db_, k_, mode=_mode_from(mode), row_offset=off_, plane=plane)
+            return d_, i_
+    if merge_fn is None:
+        from .knn import topk_merge as merge_fn
+    m_local = db_shard.shape[0]
+    k_local = min(k, m_local)
+    nq = q.shape[0]
+    if k_local > 0:
+        d_loc, i_loc = local_fn(q, db_shard, k_local, row_offset)
+    else:
+        d_loc = torch.empty((nq, 0), dtype=torch.float32, device=q.device)
+        i_loc = torch.empty((nq, 0), dtype=torch.int32, device=q.device)
+    if k_local < k:
+        pad_d = torch.full((nq, k - k_local), float("inf"), dtype=torch.float32, device=q.device)
+        pad_i = torch.full((nq, k - k_local), -1, dtype=torch.int32, device=q.device)
+        d_loc = torch.cat([d_loc, pad_d], 1)
+        i_loc = torch.cat([i_loc, pad_i], 1)
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return d_loc, i_loc
+    cand_d, cand_i = gather_candidates(d_loc, i_loc, group)
+    return merge_fn(cand_d, cand_i, k)
+
+
+def sharded_kmeans(x_shard: torch.Tensor, n_clusters: int, *, max_iters: int = 100, tol: float = 0.0,
+                   init_centroids: torch.Tensor, group=None,
+                   assign_fn: Optional[Callable] = None, update_fn: Optional[Callable] = None,
+                   finalize_fn: Optional[Callable] = None):
+    """Lloyd k-means over row-sharded samples.  ``init_centroids`` ``(K, D)`` must be identical
+    on every rank.  Per iteration: local assignment, local sums/counts, all-reduce of both,
+    identical finalisation on every rank.  Returns ``(labels of this shard int32, centroids,
+    iterations)``; the loop and its return convention follow
+    ``flashlib/primitives/kmeans/triton/kmeans.py:117-153``."""
+    from . import kmeans as km
+    if assign_fn is None:
+        assign_fn = lambda x, c: km.euclid_assign_triton(x[None], c[None])[0]  # noqa: E731
+    if update_fn is None:
+        def update_fn(x, lab, c):
+            s, n = km.triton_centroid_update_euclid(x[None], lab[None], c[None], calculate_new=False)
+            return s[0], n[0]
+    if finalize_fn is None:
+        def finalize_fn(s, n, c):
+            new, shift = km.triton_centroid_finalize(s[None], n[None], c[None])
+            return new[0], shift[0]
+    K = int(n_clusters)
+    cur = init_centroids.reshape(K, -1).float().contiguous().clone()
+    multi = dist.is_initialized() and dist.get_world_size(group) > 1
+    labels = None
+    it = 0
+    for it in range(max_iters):
+        labels = assign_fn(x_shard, cur)
+        sums, cnts = update_fn(x_shard, labels, cur)
+        if multi:
+            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+            dist.all_reduce(cnts, op=dist.ReduceOp.SUM, group=group)
+        new, shift = finalize_fn(sums, cnts, cur)
+        cur = new
+        if tol > 0.0 and float(shift.max()) < tol:
+            break
+    return labels, cur, it + 1

@@ -49,6 +49,17 @@ const char* fl_last_error(void);
 /* 1 when the running process can see an sm_100 device, 0 otherwise (never fails). */
 int         fl_device_ok(void);
 
+/* Measurement hooks; they have no counterpart in the reference (it times from Python,   */
+/* knn/triton/_common.py:32-44).  fl_launch_count: kernels launched by this library since */
+/* it was loaded.  fl_profile_enable(1) makes fl_knn_f32 / fl_kmeans_assign_f32 /        */
+/* fl_ivf_fine_scan_f32 bracket their dominant (scoring) kernel with CUDA events on the  */
+/* caller's stream, up to 256 samples; fl_profile_read_ms waits for sample i and returns */
+/* its duration.  Not thread-safe; meant for one benchmarking thread.                    */
+unsigned long long fl_launch_count(void);
+int         fl_profile_enable(int on);
+int         fl_profile_count(void);
+int         fl_profile_read_ms(int i, float* ms);
+
 /* ---------------------------------------------------------------------------------- */
 /* Row norms.  Replaces flashlib/primitives/knn/triton/_row_norm.py:59-93               */
 /* (_fast_row_sq) and knn/cutedsl/blackwell_impl.py:114-124 (_row_sqnorm).              */

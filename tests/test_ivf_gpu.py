@@ -1,0 +1,84 @@
+"""GPU parity of the IVF-Flat search against the reference fixture (same index on both
+sides, the protocol of the reference's tests/test_primitives_correctness.py:135-164)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flashlib_b200 as fl
+from flashlib_b200.ivf_flat import IvfFlatIndex
+from oracle import oracle
+from tests import parity
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def golden_index():
+    d = np.load(os.path.join(G, "ivf_small.npz"))
+    idx = IvfFlatIndex(centroids=torch.from_numpy(d["centroids"]).cuda(), data=torch.from_numpy(d["data"]).cuda(),
+                       ids=torch.from_numpy(d["ids"]).cuda(), list_offsets=torch.from_numpy(d["list_offsets"]).cuda(),
+                       metric="l2", D=d["x"].shape[1], Dp=d["data"].shape[1], nlist=int(d["nlist"]), nprobe=4)
+    return d, idx
+
+
+@pytest.mark.parametrize("k,nprobe", [(10, 4), (5, 32), (10, 1)])
+def test_search_matches_reference_on_same_index(k, nprobe):
+    d, index = golden_index()
+    vals, ids = fl.flash_ivf_flat_search(index, torch.from_numpy(d["q"]).cuda(), k, nprobe=nprobe)
+    assert vals.dtype == torch.float32 and ids.dtype == torch.int64
+    ref_v, ref_i = d[f"vals_k{k}_p{nprobe}"], d[f"ids_k{k}_p{nprobe}"]
+    v, i = vals.cpu().numpy(), ids.cpu().numpy()
+    finite = np.isfinite(ref_v)
+    assert np.array_equal(np.isfinite(v), finite)
+    assert np.all(i[~finite] == -1)
+    assert parity.rel_close(v[finite], ref_v[finite], rel=1e-4, atol=1e-4)
+    same = np.mean([set(a[f].tolist()) == set(b[f].tolist()) for a, b, f in zip(i, ref_i, finite)])
+    assert same >= 0.99, same
+
+
+def test_exhaustive_probe_equals_brute_force():
+    d, index = golden_index()
+    q = torch.from_numpy(d["q"]).cuda()
+    vals, ids = fl.flash_ivf_flat_search(index, q, 10, nprobe=index.nlist)
+    bv, bi = fl.flash_knn(q, torch.from_numpy(d["x"]).cuda(), 10)
+    assert torch.allclose(vals, bv, rtol=1e-5, atol=1e-5)
+    assert torch.equal(ids, bi.long())
+
+
+def test_build_and_recall():
+    g = torch.Generator().manual_seed(21)
+    means = 2 * torch.randn(50, 24, generator=g)
+    X = (means[torch.randint(0, 50, (20_000,), generator=g)] + torch.randn(20_000, 24, generator=g)).cuda()
+    Q = (means[torch.randint(0, 50, (300,), generator=g)] + torch.randn(300, 24, generator=g)).cuda()
+    ivf = fl.IVFFlat(nlist=64, nprobe=8, niter=8, seed=1).fit(X)
+    idx = ivf.index_
+    assert idx.list_offsets[-1].item() == 20_000 and idx.data.shape == (20_000, 24)
+    assert torch.equal(torch.sort(idx.ids).values, torch.arange(20_000, device="cuda"))
+    _, bi = fl.flash_knn(Q, X, 10)
+    recalls = []
+    for nprobe in (1, 8, 64):
+        vals, ids = ivf.kneighbors(Q, 10, nprobe=nprobe)
+        recalls.append(np.mean([len(set(a.tolist()) & set(b.tolist())) / 10 for a, b in zip(ids.cpu().numpy(), bi.cpu().numpy())]))
+    assert recalls[0] <= recalls[1] <= recalls[2] and recalls[2] == 1.0 and recalls[1] > 0.9, recalls
+    # same index through the oracle
+    ov, oi, _ = oracle.ivf_search(idx.centroids.cpu().numpy(), idx.data.cpu().numpy(), idx.ids.cpu().numpy(),
+                                  idx.list_offsets.cpu().numpy(), Q.cpu().numpy(), 10, 8)
+    vals, ids = ivf.kneighbors(Q, 10)
+    assert parity.rel_close(vals.cpu().numpy(), ov, rel=1e-4, atol=1e-4)
+    assert np.mean(np.sort(ids.cpu().numpy(), 1) == np.sort(oi, 1)) >= 0.99
+
+
+def test_small_dim_padding_and_short_lists():
+    g = torch.Generator().manual_seed(22)
+    X = torch.randn(200, 5, generator=g).cuda()            # D < 16 is zero padded to 16
+    ivf = fl.IVFFlat(nlist=40, nprobe=1, niter=3).fit(X)
+    assert ivf.index_.Dp == 16 and ivf.index_.D == 5
+    vals, ids = ivf.kneighbors(X[:20], 12)
+    assert vals.shape == (20, 12)
+    pad = ids < 0
+    assert torch.all(torch.isinf(vals[pad])) and torch.all(torch.isfinite(vals[~pad]))
+    assert torch.all(ids[:, 0] == torch.arange(20, device="cuda"))
+    with pytest.raises(ValueError):
+        ivf.kneighbors(X[:2], 201)

@@ -1,0 +1,94 @@
+"""GPU parity of the k-means path against the reference fixtures and the numpy oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import flashlib_b200 as fl
+from flashlib_b200 import synthetic
+from oracle import oracle
+from tests import parity
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_assign_update_golden():
+    d = np.load(os.path.join(G, "kmeans_small.npz"))
+    x = torch.from_numpy(d["x"]).cuda()
+    init = torch.from_numpy(d["init"]).cuda()
+    lab = fl.euclid_assign_triton(x[None], init[None])
+    assert lab.dtype == torch.int32 and lab.shape == (1, x.shape[0])
+    assert parity.label_parity(d["x"], d["init"], lab[0].cpu().numpy(), d["labels0"])["ok"]
+    ref_lab = torch.from_numpy(d["labels0"]).cuda()
+    new, ids, shift = fl.triton_lloyd_centroid_step_euclid(x[None], ref_lab[None], init[None])
+    assert parity.rel_close(new[0].cpu().numpy(), d["new0"], rel=1e-4, atol=1e-5)
+    ref_shift = np.sqrt(((d["new0"] - d["init"]) ** 2).sum(-1)).max()
+    assert abs(float(shift) - ref_shift) <= 1e-4 * ref_shift
+
+
+def test_loop_teacher_forced_and_end_to_end():
+    d = np.load(os.path.join(G, "kmeans_small.npz"))
+    x = torch.from_numpy(d["x"]).cuda()
+    hc, hl = d["hist_centroids"], d["hist_labels"]
+    for t in range(hl.shape[0]):
+        c = torch.from_numpy(hc[t]).cuda()
+        lab = fl.euclid_assign_triton(x[None], c[None])
+        assert parity.label_parity(d["x"], hc[t], lab[0].cpu().numpy(), hl[t])["ok"]
+        new, _, _ = fl.triton_lloyd_centroid_step_euclid(x[None], lab, c[None])
+        assert parity.rel_close(new[0].cpu().numpy(), hc[t + 1], rel=1e-4, atol=1e-5)
+    ids, cents, n_iter = fl.flash_kmeans(x, int(d["K"]), max_iters=6, init_centroids=torch.from_numpy(d["init"]).cuda())
+    assert n_iter == int(d["n_iter"]) and ids.dtype == torch.int32 and ids.shape == (x.shape[0],)
+    assert np.mean(ids.cpu().numpy() == d["final_labels"]) > 0.999
+    assert parity.rel_close(cents.cpu().numpy(), d["final_centroids"], rel=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("n,d,K", [(257, 32, 257), (1000, 128, 7), (4096, 768, 64), (5000, 3, 10), (300, 130, 300)])
+def test_assign_shapes_vs_oracle(n, d, K):
+    g = torch.Generator().manual_seed(n + K)
+    x = torch.randn(n, d, generator=g)
+    c = torch.randn(K, d, generator=g)
+    ref = oracle.kmeans_assign(x.numpy(), c.numpy())
+    lab = fl.euclid_assign_triton(x.cuda()[None], c.cuda()[None])[0]
+    assert parity.label_parity(x.numpy(), c.numpy(), lab.cpu().numpy(), ref)["ok"]
+    new_ref, sums_ref, cnts_ref = oracle.kmeans_update(x.numpy(), ref.astype(np.int64), c.numpy())
+    sums, cnts = fl.triton_centroid_update_euclid(x.cuda()[None], torch.from_numpy(ref).cuda()[None],
+                                                  c.cuda()[None], calculate_new=False)
+    assert np.array_equal(cnts[0].cpu().numpy(), cnts_ref)
+    assert parity.rel_close(sums[0].cpu().numpy(), sums_ref, rel=1e-4, atol=1e-4)
+
+
+def test_empty_cluster_batch_and_tolerance_break():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2, 400, 8, generator=g).cuda()
+    init = x[:, :5].clone()
+    init[:, 4] = 1000.0                           # never wins: stays empty, keeps its value
+    ids, cents, n_iter = fl.flash_kmeans(x, 5, max_iters=4, init_centroids=init)
+    assert ids.shape == (2, 400) and cents.shape == (2, 5, 8) and n_iter == 4
+    assert torch.all(cents[:, 4] == 1000.0)
+    assert not torch.any(ids == 4)
+    ids2, cents2, n2 = fl.flash_kmeans(x, 5, max_iters=100, tol=1e-6, init_centroids=init)
+    assert n2 < 100
+    km = fl.KMeans(d=8, k=5, niter=3, tol=0.0, seed=0)
+    lab = km.fit_predict(x[0])
+    assert lab.shape == (400,) and torch.equal(km.predict(x[0]).cpu() >= 0, torch.ones(400, dtype=torch.bool))
+
+
+def test_full_size_one_iteration():
+    """1M x 128 mixture, K = 1024, init = first K rows: one teacher-forced step against the
+    oracle plus conservation properties."""
+    cfg = synthetic.CONFIGS["kmeans_1m"]
+    X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
+    Xd = X.cuda()
+    init = Xd[:cfg["K"]].clone()
+    lab = fl.euclid_assign_triton(Xd[None], init[None])[0]
+    ref = oracle.kmeans_assign(X.numpy(), X[:cfg["K"]].numpy())
+    assert parity.label_parity(X.numpy(), X[:cfg["K"]].numpy(), lab.cpu().numpy(), ref)["ok"]
+    sums, cnts = fl.triton_centroid_update_euclid(Xd[None], lab[None], init[None], calculate_new=False)
+    assert int(cnts.sum()) == cfg["n"]
+    tot = X.double().sum(0)
+    assert torch.allclose(sums[0].double().sum(0).cpu(), tot, rtol=1e-5, atol=1e-2)
+    new_ref, _, _ = oracle.kmeans_update(X.numpy(), lab.cpu().numpy().astype(np.int64), X[:cfg["K"]].numpy())
+    new, _ = fl.triton_centroid_finalize(sums, cnts, init[None])
+    assert parity.rel_close(new[0].cpu().numpy(), new_ref, rel=1e-4, atol=1e-5)

@@ -117,3 +117,14 @@ def test_ivf_layout_matches_reference():
     assign, offsets, order = oracle.ivf_assign_lists(Xp, d["centroids"])
     assert np.array_equal(offsets, d["list_offsets"])
     assert np.mean(order == d["ids"]) > 0.999
+
+
+def test_torch_baseline_matches_oracle_and_reference():
+    import torch
+    from oracle import oracle_torch
+    d = load("knn_small.npz")
+    v, i = oracle_torch.knn_chunked(torch.from_numpy(d["q"]), torch.from_numpy(d["db"]), 10, chunk_size=512)
+    res = parity.knn_parity(d["q"], d["db"], v.numpy(), i.numpy(), d["idxs_chunked_k10"])
+    assert res["ok"], res
+    _, oi = oracle.knn_naive(d["q"], d["db"], 10)
+    assert parity.knn_parity(d["q"], d["db"], v.numpy(), i.numpy(), oi)["ok"]
