@@ -117,8 +117,7 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int resolve_mode(int64_t nq, int64_t m, int d, int k, int mode) {
-    if (mode == FL_KNN_AUTO) return tc_knn_supported(nq, m, d, k) == FL_OK ? FL_KNN_BF16_RERANK
-                                                                             : FL_KNN_EXACT_SIMT;
+    if (mode == FL_KNN_AUTO) return tc_knn_auto(nq, m, d, k) ? FL_KNN_BF16_RERANK : FL_KNN_EXACT_SIMT;
     return mode;
 }
 
@@ -376,4 +375,36 @@ extern "C" int fl_gather_l2sq_f32(const float* x, int64_t n, int64_t ldx, const 
                                                           static_cast<const int32_t*>(idx), k, out);
     FL_CHECK_LAUNCH();
     return FL_OK;
+}
+
+// Test hook: runs only the tensor-core scoring pass for up to 128 queries and writes the
+// scores s = <q,x> - ||x||^2/2 of every (query, database row) pair, so a test can compare
+// the MMA pipeline with a plain matrix product.
+extern "C" int fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, int d, const void* plane,
+                                      int64_t m, float* scores, int64_t ld_scores, void* ws, int64_t ws_bytes,
+                                      int32_t* status, void* stream) {
+    FL_CHECK_ARG(q && plane && scores && ws && nq >= 1 && nq <= 128 && m >= 1 && d >= 1, "fl_debug_knn_tc_scores: bad arguments");
+    if (tc_knn_supported(nq, m, d, 10) != FL_OK) { set_error("fl_debug_knn_tc_scores: unsupported shape"); return FL_EUNSUPPORTED; }
+    const KnnWs w = knn_ws_plan(nq, m, d, 10, FL_KNN_BF16_RERANK);
+    if (ws_bytes < w.bytes) { set_error("fl_debug_knn_tc_scores: workspace too small"); return FL_EWORKSPACE; }
+    const PlaneLayout L = plane_layout(m, d);
+    FL_CHECK_ARG(ld_scores >= L.m_pad, "fl_debug_knn_tc_scores: ld_scores must cover the padded row count %lld", (long long)L.m_pad);
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(ws);
+    const char* pl = static_cast<const char*>(plane);
+    float* tau = reinterpret_cast<float*>(base + w.off_tau);
+    if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
+    fill_f32_kernel<<<(unsigned)ceil_div(w.nq_pad, 256), 256, 0, st>>>(tau, w.nq_pad, -INFINITY);
+    FL_CHECK_LAUNCH();
+    int rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st);
+    if (rc != FL_OK) return rc;
+    TcKnnParams tp{};
+    tp.qplane = base + w.off_qplane; tp.nq = nq; tp.nq_pad = w.nq_pad;
+    tp.dbrows = pl + L.off_rows; tp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
+    tp.m = m; tp.m_pad = L.m_pad; tp.d_pad = L.d_pad; tp.K1 = w.K1;
+    tp.nsplit = w.nsplit; tp.tiles_per_split = w.rows_per_split;
+    tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    tp.tau = tau; tp.status = status;
+    return launch_knn_tc_debug(tp, scores, ld_scores, st);
 }

@@ -63,6 +63,10 @@ struct TcKnnParams {
 // Returns FL_EUNSUPPORTED when the shape is outside the tensor-core kernel's range.
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k);
 int tc_pool_size(int k);
+// 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
+int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
+// Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].
+int launch_knn_tc_debug(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st);
 void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_per_split);
 int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 
