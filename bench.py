@@ -165,8 +165,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="small case for profiler captures: 524,288 rows, 2,048 queries, no warm-up floor, "
+                         "no end-to-end or CPU legs (its numbers are not benchmark values)")
     args = ap.parse_args()
 
+    global DB_ROWS, QUERIES_PER_GPU
+    if args.profile_case:
+        DB_ROWS, QUERIES_PER_GPU = 524_288, 2_048
+        args.no_cpu_baseline = True
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -208,7 +215,8 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing ----------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
+    n_warm = args.warmup if args.profile_case else max(args.warmup, 3)
+    for _ in range(n_warm):
         out = step_device()
     barrier()
     sampler = ClockSampler(local_rank)
@@ -252,19 +260,20 @@ def main():
         out_i_host.copy_(i_, non_blocking=True)
         torch.cuda.synchronize()
 
-    for _ in range(2):
+    e2e_steps = 0 if args.profile_case else args.steps
+    for _ in range(2 if e2e_steps else 0):
         step_e2e()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(e2e_steps):
         step_e2e()
     barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = max(time.perf_counter() - t0, 1e-9)
     t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_s = float(t.item())
-    e2e_value = nq * args.steps / e2e_s
+    e2e_value = nq * e2e_steps / e2e_s
 
     if rank == 0:
         peaks = load_peaks()
@@ -291,7 +300,7 @@ def main():
                                   "torch-CPU restatement of knn_torch_chunked, chunk 8192"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "warmup": n_warm, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
             "data": "synthetic",
             "config": {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,

@@ -45,6 +45,8 @@ SIGNATURES = {
     "fl_knn_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_knn_resolve_mode": (c_int, [c_int64, c_int64, c_int, c_int]),
+    "fl_debug_knn_tc_scores": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                       c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_topk_merge_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fl_gather_l2sq_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p]),

@@ -98,6 +98,14 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
                    float* out_dist, int32_t* out_idx,
                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 
+/* Test hook without a counterpart in the reference: runs only the tensor-core scoring    */
+/* pass for nq <= 128 queries and writes scores[i][j] = <q_i, x_j> - ||x_j||^2/2 (bf16      */
+/* products, fp32 accumulation) for every database row j; ld_scores >= m rounded up to 256. */
+/* ws is sized by fl_knn_workspace_bytes(nq, m, d, 10, FL_KNN_BF16_RERANK).                 */
+int     fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, int d, const void* plane,
+                               int64_t m, float* scores, int64_t ld_scores,
+                               void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
 /* Which mode FL_KNN_AUTO resolves to for a shape (no device work). */
 int     fl_knn_resolve_mode(int64_t nq, int64_t m, int d, int k);
 
