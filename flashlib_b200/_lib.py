@@ -44,6 +44,7 @@ SIGNATURES = {
     "fl_knn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int, c_int]),
     "fl_knn_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_debug_tc_prof_read": (c_int, [c_void_p, c_int]),
     "fl_knn_resolve_mode": (c_int, [c_int64, c_int64, c_int, c_int]),
     "fl_debug_knn_tc_scores": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64,
                                        c_void_p, c_int64, c_void_p, c_void_p]),

@@ -20,20 +20,27 @@ __global__ void halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, i
     if (lane == 0) out[row] = 0.5f * s;
 }
 
+// bf16 query plane [nq_pad][d_pad + 16]: the features, zero padding, and ones in the three
+// columns that meet the database plane's split -||x||^2/2 terms.
 __global__ void query_plane_kernel(const float* __restrict__ q, int64_t nq, int64_t ldq, int d,
                                    __nv_bfloat16* __restrict__ out, int64_t nq_pad, int d_pad) {
+    const int pitch = d_pad + PLANE_AUG_COLS;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t total = nq_pad * d_pad;
+    const int64_t total = nq_pad * pitch;
     if (i >= total) return;
-    const int64_t r = i / d_pad;
-    const int c = (int)(i - r * d_pad);
-    const float v = (r < nq && c < d) ? __ldg(q + r * ldq + c) : 0.f;
+    const int64_t r = i / pitch;
+    const int c = (int)(i - r * pitch);
+    float v = 0.f;
+    if (r < nq) {
+        if (c < d) v = __ldg(q + r * ldq + c);
+        else if (c >= d_pad && c < d_pad + 3) v = 1.f;
+    }
     out[i] = __float2bfloat16_rn(v);
 }
 
 int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
                        int d_pad, cudaStream_t st) {
-    const int64_t total = nq_pad * d_pad;
+    const int64_t total = nq_pad * (d_pad + PLANE_AUG_COLS);
     query_plane_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
         q, nq, ldq, d, reinterpret_cast<__nv_bfloat16*>(qplane), nq_pad, d_pad);
     FL_CHECK_LAUNCH();
@@ -93,7 +100,7 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.rows_per_split_fb = round_up(ceil_div(m, s), 128);
         w.nsplit_fb = (int)ceil_div(m, w.rows_per_split_fb);
         w.off_hnorm = -1;
-        w.off_qplane = take(cur, w.nq_pad * w.d_pad * 2);
+        w.off_qplane = take(cur, w.nq_pad * (w.d_pad + PLANE_AUG_COLS) * 2);
         w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
         w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
         w.off_tau = take(cur, w.nq_pad * 4);
@@ -407,4 +414,11 @@ extern "C" int fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, i
     tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
     tp.tau = tau; tp.status = status;
     return launch_knn_tc_debug(tp, scores, ld_scores, st);
+}
+
+// Debug aid: copies the per-CTA cycle counters of the last tensor-core kNN launch on the
+// current device to host memory (16 counters for each of up to 160 CTAs; synchronises).
+extern "C" int fl_debug_tc_prof_read(unsigned long long* host_out, int words) {
+    FL_CHECK_ARG(host_out && words > 0, "fl_debug_tc_prof_read: bad arguments");
+    return tc_prof_read(host_out, words);
 }

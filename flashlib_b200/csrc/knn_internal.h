@@ -66,6 +66,7 @@ int tc_pool_size(int k);
 // 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
 int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
 // Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].
+int tc_prof_read(unsigned long long* host_out, int words);
 int launch_knn_tc_debug(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st);
 void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_per_split);
 int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);

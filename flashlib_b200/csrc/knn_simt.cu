@@ -232,8 +232,10 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
 #pragma unroll
         for (int r = 0; r < NPL1; ++r) {
             const int e = (r << 5) | lane;
-            key[NPL1 + r] = psc[(int64_t)s * K1 + e];
-            id[NPL1 + r] = pid[(int64_t)s * K1 + e];
+            const uint32_t cid = pid[(int64_t)s * K1 + e];
+            const bool real = cid < (uint32_t)p.m;   // padding rows of the operand plane never count
+            key[NPL1 + r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
+            id[NPL1 + r] = real ? cid : INVALID_ID;
         }
         warp_sort_desc<N2, false>(key, id);
     }

@@ -3,9 +3,12 @@
 // tiles) it keeps the bf16 query tile resident in shared memory, streams bf16 database
 // tiles of 256 rows through a TMA ring, multiplies them with tcgen05.mma into two
 // 128 x 256 fp32 accumulators in tensor memory (so the next tile's MMAs overlap the
-// current tile's epilogue) and, in the epilogue, turns every accumulator row into scores
+// current tile's epilogue).  The operand planes carry 16 extra columns (ones on the query
+// side, -||x||^2/2 split into three bf16 terms on the database side), so one extra K=16 MMA
+// step makes every accumulator element the score
 //     s = <q, x> - ||x||^2 / 2          (larger = closer)
-// that feed a per-query candidate pool in shared memory.  Nothing of the 128 x 256 score
+// and the epilogue only compares: scores above a row's threshold feed that query's
+// candidate pool in shared memory.  Nothing of the 128 x 256 score
 // tile ever reaches global memory; a pool of K1 = 32 (score, row) pairs per query and
 // range is all that is written.
 //
@@ -28,7 +31,11 @@ constexpr int TC_K1 = 32;             // pool size per query
 constexpr int TC_CAP = 64;            // pool capacity before compaction
 constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread)
 constexpr int TC_A_CHUNK = TC_BM * 128;   // bytes of one K-chunk of the query tile
-constexpr int TC_B_STAGE = TC_BN * 128;   // bytes of one K-chunk of a database tile
+constexpr int TC_A_AUG = TC_BM * 32;      // bytes of the query tile's 16 norm columns
+constexpr int TC_B_CHUNK = TC_BN * 128;   // bytes of one K-chunk of a database tile
+constexpr int TC_B_AUG = TC_BN * 32;      // bytes of a database tile's 16 norm columns
+constexpr int TC_B_STAGE = TC_B_CHUNK + TC_B_AUG;   // ring slot: a K-chunk, plus the norm
+                                                    // columns when it is the tile's last chunk
 constexpr int TC_MAX_STAGES = 6;
 constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // 2 s per wait
 
@@ -41,26 +48,33 @@ static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit) {
     TcSmemPlan s{};
     s.nkc = d_pad / TC_BK;
     int cur = 0;
-    s.off_a = cur; cur += s.nkc * TC_A_CHUNK;
+    s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
     const int pool = TC_BM * TC_PSTR * 4;
-    const int fixed = cur + 2 * pool + 4 * TC_BN * 4 + 256 + 1024 /* alignment slack */;
+    const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
     int ns = (smem_limit - fixed) / TC_B_STAGE;
     if (ns > TC_MAX_STAGES) ns = TC_MAX_STAGES;
     s.nstage = ns;
     s.off_b = cur; cur += (ns > 0 ? ns : 0) * TC_B_STAGE;
     s.off_pool_sc = cur; cur += pool;
     s.off_pool_id = cur; cur += pool;
-    s.off_hbuf = cur; cur += 4 * TC_BN * 4;
+    s.off_hbuf = cur;
     s.off_bar = cur; cur += 256;
     s.bytes = cur + 1024;
     return s;
 }
 
+// Per-CTA cycle counters of the last launch (debug aid, read by fl_debug_tc_prof_read):
+// [0] producer waiting for a free slot, [1] MMA waiting for operands, [2] MMA waiting for a
+// free accumulator, [3] epilogue waiting for an accumulator, [4] epilogue waiting for
+// tcgen05.ld, [5] epilogue slow sections entered, [6] pool compactions, [7] scores appended
+// (warp 0 / lane 0 views), [8] kernel cycles, [9] tiles.
+constexpr int TC_PROF_WORDS = 16;
+__device__ unsigned long long g_tc_prof[160 * TC_PROF_WORDS];
+
 struct TcKernelParams {
     int n_qtiles, n_tiles, nsplit, tiles_per_split, nkc, nstage;
-    int off_b, off_pool_sc, off_pool_id, off_hbuf, off_bar;
+    int off_b, off_pool_sc, off_pool_id, off_bar;
     int64_t nq_pad;
-    const float* hnorm;
     float* part_sc; uint32_t* part_id;
     float* tau;
     int32_t* status;
@@ -74,26 +88,12 @@ __device__ __forceinline__ void tc_report_timeout(int32_t* status, int role, int
     }
 }
 
-struct TcPoolState { int cnt; float tau; };
-
-// Slow path of the epilogue, entered by the whole warp when at least one lane holds a score
-// above its row's threshold: the hitting lanes append their passing scores to their rows'
-// pools, then the warp compacts every pool that is nearly full.  Kept out of line so the
-// streaming loop stays small.
-static __device__ __noinline__ TcPoolState tc_pool_update(bool hit, float s0, float s1, float s2, float s3,
-                                                          float s4, float s5, float s6, float s7, uint32_t cb,
-                                                          float* my_sc, uint32_t* my_id, float* warp_sc,
-                                                          uint32_t* warp_id, int cnt, float tau) {
+// Compacts the pools of the rows named in `need` (one bit per lane = row of this warp).
+// Kept out of line: compaction is rare and the sorting network is large.
+static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp_sc, uint32_t* warp_id, int cnt,
+                                                      float tau) {
     const int lane = threadIdx.x & 31;
-    if (hit) {
-        const float s[8] = {s0, s1, s2, s3, s4, s5, s6, s7};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (s[j] > tau) { my_sc[cnt] = s[j]; my_id[cnt] = cb + j; ++cnt; }
-        }
-    }
-    unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
-    if (need) __syncwarp();
+    __syncwarp();
     while (need) {
         const int src = __ffs(need) - 1;
         need &= need - 1;
@@ -101,24 +101,22 @@ static __device__ __noinline__ TcPoolState tc_pool_update(bool hit, float s0, fl
         const float thr = warp_pool_compact<TC_CAP / 32>(warp_sc + src * TC_PSTR, warp_id + src * TC_PSTR, n, TC_K1);
         if (lane == src) { cnt = min(n, TC_K1); tau = fmaxf(tau, thr); }
     }
-    TcPoolState r;
-    r.cnt = cnt;
-    r.tau = tau;
-    return r;
+    return make_float2(__int_as_float(cnt), tau);
 }
 
 __global__ void __launch_bounds__(192, 1)
-knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_db,
+knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
+              const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_db_aug,
               const TcKernelParams p) {
     extern __shared__ uint8_t smem_raw[];
     // the swizzled operand tiles need 1024-byte aligned shared memory
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t a_addr = sbase;                      // nkc chunks of 16 KB
-    const uint32_t b_addr = sbase + p.off_b;            // nstage stages of 32 KB
+    const uint32_t a_addr = sbase;                                // nkc chunks of 16 KB
+    const uint32_t a_aug_addr = sbase + p.nkc * TC_A_CHUNK;       // 4 KB: the query tile's norm columns
+    const uint32_t b_addr = sbase + p.off_b;                      // nstage slots of 40 KB
     float* pool_sc = reinterpret_cast<float*>(smem + p.off_pool_sc);
     uint32_t* pool_id = reinterpret_cast<uint32_t*>(smem + p.off_pool_id);
-    float* hbuf = reinterpret_cast<float*>(smem + p.off_hbuf);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
     // barrier slots: [0, 6) full, [6, 12) empty, 12 a_full, 13 a_empty, 14-15 tmem_full, 16-17 tmem_empty
     const uint32_t bar0 = smem_u32(bars);
@@ -138,7 +136,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 4 && lane == 0) { prefetch_tensormap(&map_q); prefetch_tensormap(&map_db); }
+    if (warp == 4 && lane == 0) {
+        prefetch_tensormap(&map_q); prefetch_tensormap(&map_q_aug);
+        prefetch_tensormap(&map_db); prefetch_tensormap(&map_db_aug);
+    }
     if (warp == 5) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
@@ -149,6 +150,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_items = p.n_qtiles * p.nsplit;
+    const int d_pad = p.nkc * TC_BK;
 
     if (warp == 4) {
         // ------------------------------ TMA producer --------------------------------------
@@ -156,6 +158,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t fill = 0;     // database chunks issued so far
             uint32_t item_no = 0;
             bool ok = true;
+            long long prof_a = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
                 const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
                 const int t0 = split * p.tiles_per_split;
@@ -163,21 +166,34 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
-                mbar_expect_tx(BAR(B_AFULL), p.nkc * TC_A_CHUNK);
+                mbar_expect_tx(BAR(B_AFULL), p.nkc * TC_A_CHUNK + TC_A_AUG);
                 for (int kc = 0; kc < p.nkc; ++kc)
                     tma_load_2d(a_addr + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, BAR(B_AFULL));
-                for (int t = t0; t < t1 && ok; ++t) {
+                tma_load_2d(a_aug_addr, &map_q_aug, d_pad, qt * TC_BM, BAR(B_AFULL));
+                const int nt = t1 - t0;
+                const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
+                for (int i = 0; i < nt && ok; ++i) {
+                    // Query tiles walk their range from different starting tiles, so the CTAs of a
+                    // wave do not all ask the L2 for the same lines at the same moment.
+                    const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                     for (int kc = 0; kc < p.nkc; ++kc, ++fill) {
                         const int s = fill % p.nstage;
                         const uint32_t ph = (fill / p.nstage) & 1;
+                        const long long c0 = clock64();
                         if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, TC_WAIT_NS)) {
                             tc_report_timeout(p.status, 4, B_EMPTY + s); ok = false; break;
                         }
-                        mbar_expect_tx(BAR(B_FULL + s), TC_B_STAGE);
+                        prof_a += clock64() - c0;
+                        const bool last = (kc == p.nkc - 1);
+                        mbar_expect_tx(BAR(B_FULL + s), last ? TC_B_STAGE : TC_B_CHUNK);
                         tma_load_2d(b_addr + s * TC_B_STAGE, &map_db, kc * TC_BK, t * TC_BN, BAR(B_FULL + s));
+                        if (last)
+                            tma_load_2d(b_addr + s * TC_B_STAGE + TC_B_CHUNK, &map_db_aug, d_pad, t * TC_BN,
+                                        BAR(B_FULL + s));
                     }
                 }
             }
+            if (blockIdx.x < 160) g_tc_prof[blockIdx.x * TC_PROF_WORDS + 0] = prof_a;
             if (!ok) {
                 // give copies already in flight a bounded time to land before the CTA exits
                 const uint64_t t_start = globaltimer_ns();
@@ -192,6 +208,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t tile_no = 0;  // tiles issued so far (accumulator ring position)
             uint32_t item_no = 0;
             bool ok = true;
+            long long prof_full = 0, prof_tempty = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
                 const int split = it / p.n_qtiles;
                 const int t0 = split * p.tiles_per_split;
@@ -201,17 +218,21 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
                 for (int t = t0; t < t1 && ok; ++t, ++tile_no) {
                     const int b = tile_no & 1;
+                    const long long c0 = clock64();
                     if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, TC_WAIT_NS)) {
                         tc_report_timeout(p.status, 5, B_TEMPTY + b); ok = false; break;
                     }
+                    prof_tempty += clock64() - c0;
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + b * TC_BN;
                     for (int kc = 0; kc < p.nkc; ++kc, ++use) {
                         const int s = use % p.nstage;
                         const uint32_t ph = (use / p.nstage) & 1;
+                        const long long c1 = clock64();
                         if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, TC_WAIT_NS)) {
                             tc_report_timeout(p.status, 5, B_FULL + s); ok = false; break;
                         }
+                        prof_full += clock64() - c1;
                         tc_fence_after_sync();
                         const uint64_t da = umma_desc(a_addr + kc * TC_A_CHUNK);
                         const uint64_t db = umma_desc(b_addr + s * TC_B_STAGE);
@@ -220,21 +241,34 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                             // +32 bytes per 16-feature step inside the 128-byte swizzled row
                             umma_bf16(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0 ? 1u : 0u);
                         }
-                        umma_commit(BAR(B_EMPTY + s));   // stage reusable once these MMAs retire
+                        if (kc == p.nkc - 1) {
+                            // norm columns: ones x split(-||x||^2/2), 32-byte rows, 32-byte swizzle
+                            umma_bf16(d_tmem, umma_desc_sw32(a_aug_addr),
+                                      umma_desc_sw32(b_addr + s * TC_B_STAGE + TC_B_CHUNK), idesc, 1u);
+                        }
+                        umma_commit(BAR(B_EMPTY + s));   // slot reusable once these MMAs retire
                     }
                     if (ok) umma_commit(BAR(B_TFULL + b));
                 }
                 if (ok) umma_commit(BAR(B_AEMPTY));       // query tile reusable
             }
+            if (blockIdx.x < 160) {
+                g_tc_prof[blockIdx.x * TC_PROF_WORDS + 1] = prof_full;
+                g_tc_prof[blockIdx.x * TC_PROF_WORDS + 2] = prof_tempty;
+            }
         }
     } else {
         // ------------------------------ epilogue warps --------------------------------------
-        float* my_sc = pool_sc + (warp * 32 + lane) * TC_PSTR;
-        uint32_t* my_id = pool_id + (warp * 32 + lane) * TC_PSTR;
-        float* hb = hbuf + warp * TC_BN;
+        float* warp_sc = pool_sc + warp * 32 * TC_PSTR;
+        uint32_t* warp_id = pool_id + warp * 32 * TC_PSTR;
+        float* my_sc = warp_sc + lane * TC_PSTR;
+        uint32_t* my_id = warp_id + lane * TC_PSTR;
         const uint32_t lane_taddr = tmem_base + (uint32_t(warp * 32) << 16);
         uint32_t tile_no = 0;
         bool ok = true;
+        long long prof_tfull = 0, prof_ld = 0, prof_slowcyc = 0, prof_compcyc = 0, prof_ldw = 0, prof_proc = 0;
+        unsigned prof_slow = 0, prof_compact = 0, prof_append = 0;
+        const long long prof_t0 = clock64();
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
             const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
             const int t0 = split * p.tiles_per_split;
@@ -243,71 +277,95 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const float tau_in = __ldcg(p.tau + qrow);
             float tau = tau_in;
             int cnt = 0;
-            // half norms of the first tile of the range
-            float4 h0 = __ldg(reinterpret_cast<const float4*>(p.hnorm + (int64_t)t0 * TC_BN + lane * 8));
-            float4 h1 = __ldg(reinterpret_cast<const float4*>(p.hnorm + (int64_t)t0 * TC_BN + lane * 8 + 4));
-            for (int t = t0; t < t1; ++t, ++tile_no) {
-                __syncwarp();
-                *reinterpret_cast<float4*>(hb + lane * 8) = h0;
-                *reinterpret_cast<float4*>(hb + lane * 8 + 4) = h1;
-                __syncwarp();
-                if (t + 1 < t1) {
-                    h0 = __ldg(reinterpret_cast<const float4*>(p.hnorm + (int64_t)(t + 1) * TC_BN + lane * 8));
-                    h1 = __ldg(reinterpret_cast<const float4*>(p.hnorm + (int64_t)(t + 1) * TC_BN + lane * 8 + 4));
-                }
+            const int nt = t1 - t0;
+            const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
+            for (int i = 0; i < nt; ++i, ++tile_no) {
+                const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = tile_no & 1;
+                const long long c0 = clock64();
                 if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
                     ok = false;
                     break;
                 }
+                prof_tfull += clock64() - c0;
                 tc_fence_after_sync();
                 const uint32_t tile_taddr = lane_taddr + b * TC_BN;
                 const uint32_t row_base = (uint32_t)t * TC_BN;
 
                 uint32_t va[32], vb[32];
+                // One slice = 32 score columns of this thread's query row.
                 auto process = [&](uint32_t (&v)[32], int slice) {
-                    const float* hs = hb + slice * 32;
+                    float m8[4];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const float4 ha = *reinterpret_cast<const float4*>(hs + g * 8);
-                        const float4 hc = *reinterpret_cast<const float4*>(hs + g * 8 + 4);
-                        float s[8];
-                        s[0] = __uint_as_float(v[g * 8 + 0]) - ha.x;
-                        s[1] = __uint_as_float(v[g * 8 + 1]) - ha.y;
-                        s[2] = __uint_as_float(v[g * 8 + 2]) - ha.z;
-                        s[3] = __uint_as_float(v[g * 8 + 3]) - ha.w;
-                        s[4] = __uint_as_float(v[g * 8 + 4]) - hc.x;
-                        s[5] = __uint_as_float(v[g * 8 + 5]) - hc.y;
-                        s[6] = __uint_as_float(v[g * 8 + 6]) - hc.z;
-                        s[7] = __uint_as_float(v[g * 8 + 7]) - hc.w;
-                        if (p.dbg_scores != nullptr && qt == 0) {
+                        const float x = fmax3(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]),
+                                              __uint_as_float(v[g * 8 + 2]));
+                        const float y = fmax3(__uint_as_float(v[g * 8 + 3]), __uint_as_float(v[g * 8 + 4]),
+                                              __uint_as_float(v[g * 8 + 5]));
+                        const float z = fmax3(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]), x);
+                        m8[g] = fmaxf(y, z);
+                    }
+                    if (p.dbg_scores != nullptr && qt == 0) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                p.dbg_scores[(int64_t)(warp * 32 + lane) * p.dbg_ld + row_base + slice * 32 + g * 8 + j] = s[j];
+                        for (int j = 0; j < 32; ++j)
+                            p.dbg_scores[(int64_t)(warp * 32 + lane) * p.dbg_ld + row_base + slice * 32 + j] =
+                                __uint_as_float(v[j]);
+                    }
+                    const float m32 = fmaxf(fmax3(m8[0], m8[1], m8[2]), m8[3]);
+                    if (__any_sync(FULL_MASK, m32 > tau)) {
+                        ++prof_slow;
+                        const long long cs0 = clock64();
+                        // Rare path.  Each lane appends the scores above its threshold group by
+                        // group; a lane whose pool is nearly full stops, the warp compacts the
+                        // pools of the stopped lanes (which raises their thresholds) and the
+                        // stopped lanes resume.
+                        unsigned todo = (m8[0] > tau ? 1u : 0u) | (m8[1] > tau ? 2u : 0u) | (m8[2] > tau ? 4u : 0u) |
+                                        (m8[3] > tau ? 8u : 0u);
+                        while (true) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                if (((todo >> g) & 1u) && cnt <= TC_CAP - 8) {
+                                    const uint32_t cb = row_base + slice * 32 + g * 8;
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        const float sv = __uint_as_float(v[g * 8 + j]);
+                                        if (sv > tau) { my_sc[cnt] = sv; my_id[cnt] = cb + j; ++cnt; ++prof_append; }
+                                    }
+                                    todo &= ~(1u << g);
+                                }
+                            }
+                            const unsigned need = __ballot_sync(FULL_MASK, todo != 0);
+                            if (!need) break;
+                            prof_compact += __popc(need);
+                            const long long cc0 = clock64();
+                            const float2 r = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                            prof_compcyc += clock64() - cc0;
+                            cnt = __float_as_int(r.x);
+                            tau = r.y;
+                            todo &= (m8[0] > tau ? 1u : 0u) | (m8[1] > tau ? 2u : 0u) | (m8[2] > tau ? 4u : 0u) |
+                                    (m8[3] > tau ? 8u : 0u);
                         }
-                        const float m = fmaxf(fmax3(s[0], s[1], s[2]), fmaxf(fmax3(s[3], s[4], s[5]), fmaxf(s[6], s[7])));
-                        const bool hit = m > tau;
-                        if (__any_sync(FULL_MASK, hit)) {
-                            const TcPoolState r = tc_pool_update(hit, s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7],
-                                                                 row_base + slice * 32 + g * 8, my_sc, my_id,
-                                                                 pool_sc + warp * 32 * TC_PSTR,
-                                                                 pool_id + warp * 32 * TC_PSTR, cnt, tau);
-                            cnt = r.cnt;
-                            tau = r.tau;
-                        }
+                        prof_slowcyc += clock64() - cs0;
                     }
                 };
 
+                const long long c2 = clock64();
                 tmem_ld_32x32b_x32(tile_taddr, va);
                 tmem_ld_wait();
                 reg_fence32(va);
+                prof_ld += clock64() - c2;
 #pragma unroll 1
                 for (int sp = 0; sp < TC_BN / 64; ++sp) {
                     tmem_ld_32x32b_x32(tile_taddr + (2 * sp + 1) * 32, vb);
+                    const long long cp0 = clock64();
                     process(va, 2 * sp);
+                    const long long cp1 = clock64();
                     tmem_ld_wait();
                     reg_fence32(vb);
+                    const long long cp2 = clock64();
+                    prof_proc += cp1 - cp0;
+                    prof_ldw += cp2 - cp1;
                     if (sp + 1 < TC_BN / 64) {
                         tmem_ld_32x32b_x32(tile_taddr + (2 * sp + 2) * 32, va);
                     } else {
@@ -329,8 +387,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll 1
             for (int src = 0; src < 32; ++src) {
                 const int n = __shfl_sync(FULL_MASK, cnt, src);
-                float* rsc = pool_sc + (warp * 32 + src) * TC_PSTR;
-                uint32_t* rid = pool_id + (warp * 32 + src) * TC_PSTR;
+                float* rsc = warp_sc + src * TC_PSTR;
+                uint32_t* rid = warp_id + src * TC_PSTR;
                 const float thr = warp_pool_compact<TC_CAP / 32>(rsc, rid, n, TC_K1);
                 if (lane == src) tau = fmaxf(tau, thr);
                 const int64_t q = (int64_t)qt * TC_BM + warp * 32 + src;
@@ -340,6 +398,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 __syncwarp();
             }
             if (tau > tau_in) __stcg(p.tau + qrow, tau);
+        }
+        if (warp == 0 && lane == 0 && blockIdx.x < 160) {
+            unsigned long long* pr = g_tc_prof + blockIdx.x * TC_PROF_WORDS;
+            pr[3] = prof_tfull; pr[4] = prof_ld; pr[5] = prof_slow; pr[6] = prof_compact; pr[7] = prof_append;
+            pr[8] = clock64() - prof_t0; pr[9] = tile_no;
+            pr[10] = prof_slowcyc; pr[11] = prof_compcyc; pr[12] = prof_ldw; pr[13] = prof_proc;
         }
     }
 
@@ -370,16 +434,19 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 2-D bf16 row-major tensor [rows][cols], box = 64 columns x box_rows rows, 128-byte swizzle.
-static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int cols, int box_rows) {
+// 2-D bf16 row-major tensor [rows][cols]; box = box_cols columns x box_rows rows.  box_cols is
+// 64 (128-byte rows in shared memory, 128-byte swizzle) or 16 (32-byte rows, 32-byte swizzle).
+static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int cols, int box_cols, int box_rows) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return FL_ECUDA; }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return FL_ECUDA; }
     return FL_OK;
@@ -425,10 +492,12 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_pe
 }
 
 static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
-    CUtensorMap map_q, map_db;
-    int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, p.d_pad, TC_BM);
-    if (rc != FL_OK) return rc;
-    rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, p.d_pad, TC_BN);
+    CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
+    const int pitch = p.d_pad + PLANE_AUG_COLS;
+    int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
+    if (rc == FL_OK) rc = make_map_bf16(&map_q_aug, p.qplane, p.nq_pad, pitch, PLANE_AUG_COLS, TC_BM);
+    if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
+    if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
     const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes());
     if (sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
@@ -439,14 +508,20 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.tiles_per_split = (int)p.tiles_per_split;
     kp.nkc = sp.nkc; kp.nstage = sp.nstage;
     kp.off_b = sp.off_b; kp.off_pool_sc = sp.off_pool_sc; kp.off_pool_id = sp.off_pool_id;
-    kp.off_hbuf = sp.off_hbuf; kp.off_bar = sp.off_bar;
-    kp.nq_pad = p.nq_pad; kp.hnorm = p.hnorm; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
+    kp.off_bar = sp.off_bar;
+    kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
     kp.tau = p.tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
     const int items = kp.n_qtiles * kp.nsplit;
     const int grid = items < sm_count() ? items : sm_count();
     FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-    knn_tc_kernel<<<grid, 192, sp.bytes, st>>>(map_q, map_db, kp);
+    knn_tc_kernel<<<grid, 192, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+int tc_prof_read(unsigned long long* host_out, int words) {
+    const size_t n = sizeof(unsigned long long) * (size_t)(words < 160 * TC_PROF_WORDS ? words : 160 * TC_PROF_WORDS);
+    FL_CHECK_CUDA(cudaMemcpyFromSymbol(host_out, g_tc_prof, n));
     return FL_OK;
 }
 

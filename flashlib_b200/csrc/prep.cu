@@ -34,15 +34,20 @@ __global__ void rownorm_kernel(const float* __restrict__ x, int64_t n, int d, in
 // One warp per plane row: converts the fp32 row to bf16 (round to nearest even), zero
 // pads columns [d, d_pad), writes ||x||^2/2 (+inf for padding rows) and folds the row's
 // norm into the plane-wide maximum (non-negative floats order like their bit patterns).
+// Columns [d_pad, d_pad+3) carry -||x||^2/2 split into three bf16 terms (their sum is exact
+// to 2^-24 relative); multiplied by the ones the query plane holds in the same columns they
+// make the tensor-core product come out as <q,x> - ||x||^2/2.  Padding rows carry a huge
+// negative value there so they can never rank.
 __global__ void plane_build_kernel(const float* __restrict__ db, int64_t m, int d, int64_t ld,
                                    __nv_bfloat16* __restrict__ rows, float* __restrict__ hnorm,
                                    unsigned int* __restrict__ maxnorm_bits, int64_t m_pad, int d_pad) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= m_pad) return;
-    __nv_bfloat16* o = rows + row * d_pad;
+    const int pitch = d_pad + PLANE_AUG_COLS;
+    __nv_bfloat16* o = rows + row * pitch;
     if (row >= m) {
-        for (int c = lane; c < d_pad; c += 32) o[c] = __float2bfloat16_rn(0.f);
+        for (int c = lane; c < pitch; c += 32) o[c] = __float2bfloat16_rn(c == d_pad ? -3.0e38f : 0.f);
         if (lane == 0) hnorm[row] = pos_inf();
         return;
     }
@@ -59,14 +64,24 @@ __global__ void plane_build_kernel(const float* __restrict__ db, int64_t m, int 
         hnorm[row] = 0.5f * s;
         atomicMax(maxnorm_bits, __float_as_uint(sqrtf(s)));
     }
+    if (lane < PLANE_AUG_COLS) {
+        const float nh = -0.5f * s;
+        const __nv_bfloat16 h1 = __float2bfloat16_rn(nh);
+        const float r1 = nh - __bfloat162float(h1);
+        const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+        const float r2 = r1 - __bfloat162float(h2);
+        const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
+        o[d_pad + lane] = lane == 0 ? h1 : lane == 1 ? h2 : lane == 2 ? h3 : __float2bfloat16_rn(0.f);
+    }
 }
 
 PlaneLayout plane_layout(int64_t m, int d) {
     PlaneLayout L;
     L.m_pad = round_up(m, 256);
     L.d_pad = (int)round_up(d, 64);
+    L.pitch = L.d_pad + PLANE_AUG_COLS;
     L.off_rows = 0;
-    L.off_hnorm = round_up(L.m_pad * (int64_t)L.d_pad * 2, 1024);
+    L.off_hnorm = round_up(L.m_pad * (int64_t)L.pitch * 2, 1024);
     L.off_meta = L.off_hnorm + round_up(L.m_pad * 4, 1024);
     L.bytes = L.off_meta + 1024;
     return L;

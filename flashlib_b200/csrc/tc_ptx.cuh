@@ -153,6 +153,12 @@ __host__ __device__ constexpr uint64_t umma_desc_base_sw128() {
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     return umma_desc_base_sw128() | uint64_t((smem_addr >> 4) & 0x3FFF);
 }
+// Same for a K-major tile stored as rows of 32 bytes (16 bf16) with the 32-byte swizzle:
+// 8-row groups are 256 bytes apart, layout type 6 (SWIZZLE_32B).
+__device__ __forceinline__ uint64_t umma_desc_sw32(uint32_t smem_addr) {
+    return (uint64_t(1) << 16) | (uint64_t(256 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(6) << 61) |
+           uint64_t((smem_addr >> 4) & 0x3FFF);
+}
 // Instruction descriptor: fp32 accumulator, bf16 A and B, both K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);

@@ -71,7 +71,8 @@ int fl_rownorm_f32(const float* x, int64_t n, int d, int64_t ld, float* out, voi
 /* reference caches the equivalent c_sq per data_ptr: knn/triton/_row_norm.py:82-93,    */
 /* and casts storage per knn/impl.py:257-261).                                          */
 /* Layout of `plane` (all offsets 1024-byte aligned, see fl_knn_plane_bytes):           */
-/*   bf16 [m_pad][d_pad]  row-major, zero padded (m_pad % 256 == 0, d_pad % 64 == 0)    */
+/*   bf16 [m_pad][d_pad+16] row-major, zero padded (m_pad % 256 == 0, d_pad % 64 == 0);   */
+/*                        columns d_pad..d_pad+2 hold -||x||^2/2 split into three bf16     */
 /*   f32  [m_pad]         half squared norms ||x||^2/2 of the fp32 rows, +inf padding   */
 /*   f32  [4]             [0] = max row norm ||x|| over the plane                        */
 int64_t fl_knn_plane_bytes(int64_t m, int d);
@@ -105,6 +106,11 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
 int     fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, int d, const void* plane,
                                int64_t m, float* scores, int64_t ld_scores,
                                void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
+/* Debug aid without a counterpart in the reference: per-CTA cycle counters of the last   */
+/* tensor-core kNN launch (16 x uint64 for each of up to 160 CTAs: waits of the producer, */
+/* MMA and epilogue roles, slow-path and compaction counts, kernel cycles, tiles).          */
+int     fl_debug_tc_prof_read(unsigned long long* host_out, int words);
 
 /* Which mode FL_KNN_AUTO resolves to for a shape (no device work). */
 int     fl_knn_resolve_mode(int64_t nq, int64_t m, int d, int k);

@@ -41,7 +41,7 @@ def test_mma_pipeline_scores(nq, m, d):
     ref = q.bfloat16().float() @ db.bfloat16().float().T - 0.5 * (db * db).sum(-1)[None, :]
     err = (got[:nq, :m] - ref).abs().max().item()
     assert err < 2e-3, err
-    assert torch.all(got[:nq, m:] == float("-inf"))          # padding rows can never be candidates
+    assert torch.all(got[:nq, m:] < -1e37)                    # padding rows can never be candidates
 
 
 SHAPES = [(1, 300, 16, 1), (129, 5000, 128, 10), (300, 40_000, 128, 16), (64, 9_000, 200, 10), (500, 100_000, 64, 10),
