@@ -191,6 +191,68 @@ extern "C" int fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx, cons
     return FL_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Assignment without a caller-provided workspace.
+//
+// Some hosts of this library may only launch work: a plugin that is handed a stream and its
+// input/output buffers but no allocator, a service that gave all device memory to its own
+// pool at start-up, a latency-critical loop that must not meet cudaMalloc's device-wide
+// synchronisation.  For them the per-centroid half norms, the one piece of scratch the
+// assignment needs, live in a fixed array that is part of the loaded library image.
+//
+// The array holds FL_KMEANS_NOALLOC_MAX_K floats (64 KiB) on every GPU that loads the library
+// and stays there until the process exits.  Every call on a device uses the same array and
+// leaves its half norms behind: each call overwrites the K entries it reads before reading
+// them, so nothing has to be cleared, but two calls that overlap on one GPU (different
+// streams, no ordering between them) race on it and must be serialised by the caller.
+static __device__ __align__(256) float g_kmeans_noalloc_hnorm[FL_KMEANS_NOALLOC_MAX_K];
+
+// Device address of the array for the current device.  Host code cannot use the symbol's
+// name as a pointer, so the address is looked up once per device (with that device current)
+// and cached.  The first call on a device does this look-up, which is why that call should
+// happen before any stream capture begins.
+static int kmeans_noalloc_scratch(float** out) {
+    static float* cached[64];
+    int dev = 0;
+    FL_CHECK_CUDA(cudaGetDevice(&dev));
+    FL_CHECK_ARG(dev >= 0 && dev < 64, "fl_kmeans_assign_noalloc_f32: device ordinal %d out of range", dev);
+    if (cached[dev] == nullptr) {
+        float* ptr = nullptr;
+        FL_CHECK_CUDA(cudaGetSymbolAddress((void**)&ptr, g_kmeans_noalloc_hnorm));
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return FL_OK;
+}
+
+extern "C" int fl_kmeans_assign_noalloc_f32(const float* x, int64_t n, int64_t ldx, const float* c, int K,
+                                            int64_t ldc, int d, int32_t* labels, void* stream) {
+    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d && ldc >= d, "fl_kmeans_assign_noalloc_f32: bad shape");
+    if (K > FL_KMEANS_NOALLOC_MAX_K) {
+        set_error("fl_kmeans_assign_noalloc_f32: K=%d exceeds the built-in scratch of %d centroids; "
+                  "use fl_kmeans_assign_f32 with a workspace", K, FL_KMEANS_NOALLOC_MAX_K);
+        return FL_EUNSUPPORTED;
+    }
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && c && labels, "fl_kmeans_assign_noalloc_f32: null pointer");
+    float* hnorm = nullptr;
+    const int rc = kmeans_noalloc_scratch(&hnorm);
+    if (rc != FL_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    kmeans_halfnorm_kernel<<<(unsigned)ceil_div(K, 8), 256, 0, st>>>(c, K, d, ldc, hnorm);
+    FL_CHECK_LAUNCH();
+    const int vecx = (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int vecc = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    constexpr int TQ = 4;
+    const size_t smem = sizeof(float) * SimtTile<TQ>::SLAB_FLOATS;
+    FL_CHECK_CUDA(cudaFuncSetAttribute(kmeans_assign_simt_kernel<TQ>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kmeans_assign_simt_kernel<TQ><<<(unsigned)ceil_div(n, SimtTile<TQ>::BQ), 256, smem, st>>>(
+        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels,
                                     int K, float* sums, int32_t* cnts, void* stream) {
     FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_f32: bad shape");

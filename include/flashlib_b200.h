@@ -144,6 +144,19 @@ int64_t fl_kmeans_assign_workspace_bytes(int64_t n, int K, int d);
 int     fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx,
                              const float* c, int K, int64_t ldc, int d,
                              int32_t* labels, void* ws, int64_t ws_bytes, void* stream);
+/* Same assignment for callers that cannot allocate device memory or pass a workspace (a  */
+/* plugin that only receives a stream and its buffers, a host whose memory pool owns the   */
+/* whole GPU, a loop that must avoid cudaMalloc's synchronisation).  It has no counterpart */
+/* in the reference.  The half norms go to a 64 KiB array built into the library image     */
+/* (resident on every GPU that loads the library until exit), so K is limited to           */
+/* FL_KMEANS_NOALLOC_MAX_K (larger K returns FL_EUNSUPPORTED) and the call never runs       */
+/* cudaMalloc/cudaFree.  The first call on a device looks the array's address up; make it  */
+/* before any stream capture.  All calls on a device share the array: calls that overlap   */
+/* on the GPU race and must be serialised by the caller.                                   */
+#define FL_KMEANS_NOALLOC_MAX_K 16384
+int     fl_kmeans_assign_noalloc_f32(const float* x, int64_t n, int64_t ldx,
+                                     const float* c, int K, int64_t ldc, int d,
+                                     int32_t* labels, void* stream);
 /* sums [K][d] fp32 and cnts [K] int32 are overwritten with the per-cluster sums/counts. */
 int     fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d,
                              const int32_t* labels, int K,
