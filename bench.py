@@ -165,6 +165,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--db-rows", type=int, default=None, help="with --profile-case: database rows")
+    ap.add_argument("--queries", type=int, default=None, help="with --profile-case: queries per GPU")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for profiler captures: 524,288 rows, 2,048 queries, no warm-up floor, "
                          "no end-to-end or CPU legs (its numbers are not benchmark values)")
@@ -172,7 +174,7 @@ def main():
 
     global DB_ROWS, QUERIES_PER_GPU
     if args.profile_case:
-        DB_ROWS, QUERIES_PER_GPU = 524_288, 2_048
+        DB_ROWS, QUERIES_PER_GPU = args.db_rows or 524_288, args.queries or 2_048
         args.no_cpu_baseline = True
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -54,6 +54,11 @@ SIGNATURES = {
     "fl_kmeans_assign_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),
     "fl_kmeans_assign_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int,
                                      c_void_p, c_void_p, c_int64, c_void_p]),
+    "fl_kmeans_xplane_bytes": (c_int64, [c_int64, c_int]),
+    "fl_kmeans_prepare_x_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
+    "fl_kmeans_assign_tc_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int]),
+    "fl_kmeans_assign_tc_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int64, c_int,
+                                        c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_kmeans_assign_noalloc_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int, c_int64, c_int,
                                              c_void_p, c_void_p]),
     "fl_kmeans_update_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int,

@@ -63,13 +63,24 @@ __global__ void fallback_fixup_kernel(int* fb_count, int fb_cap, int32_t* status
     if (c > fb_cap) *fb_count = fb_cap;
 }
 
+int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t st) {
+    fill_f32_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(p, n, v);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+int launch_fallback_fixup(int* fb_count, int fb_cap, int32_t* status, int K1, cudaStream_t st) {
+    fallback_fixup_kernel<<<1, 1, 0, st>>>(fb_count, fb_cap, status, K1);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 // ---- workspace layout -----------------------------------------------------------------
 struct KnnWs {
     int mode, K1, K1f;
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
     int64_t nq_pad; int d_pad; int fb_cap;
-    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_tau, off_cnt, off_fblist,
+    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_tau, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
 };
 
@@ -101,8 +112,9 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.nsplit_fb = (int)ceil_div(m, w.rows_per_split_fb);
         w.off_hnorm = -1;
         w.off_qplane = take(cur, w.nq_pad * (w.d_pad + PLANE_AUG_COLS) * 2);
-        w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
-        w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)w.K1 * 4);
+        w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
+        w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
+        w.off_part_tau = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_tau = take(cur, w.nq_pad * 4);
         w.off_cnt = take(cur, 1024);
         w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
@@ -307,6 +319,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
     tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
     tp.tau = tau; tp.status = status;
+    tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     profile_begin(st);
     rc = launch_knn_tc(tp, st);
     profile_end(st);
@@ -315,8 +328,11 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     FinalizeParams fp{};
     fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
     fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
-    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
-    fp.k = k; fp.rerank = w.K1; fp.row_offset = row_offset;
+    // Re-rank the tc_partial_len best scores of the union of the published pools; what the
+    // scoring pass left out is bounded by the thresholds it published.
+    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = w.nsplit; fp.K1 = tc_partial_len(k);
+    fp.k = k; fp.rerank = fp.K1; fp.row_offset = row_offset;
+    fp.part_tau = tp.part_tau; fp.ntau = w.nsplit * tc_taus_per_range();
     fp.out_dist = out_dist; fp.out_idx = out_idx;
     fp.verify = 1; fp.eps_rel = 0.004f;  // 2^-8 operand rounding of both bf16 factors, rounded up
     fp.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
@@ -341,7 +357,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     FinalizeParams ff = fp;
     ff.qlist = fb_list; ff.count_dev = fb_count; ff.count = 0;
     ff.part_sc = sp.part_sc; ff.part_id = sp.part_id; ff.nsplit = w.nsplit_fb; ff.K1 = w.K1f;
-    ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0;
+    ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0; ff.part_tau = nullptr; ff.ntau = 0;
     rc = launch_knn_finalize(ff, w.fb_cap, st);
     return rc;
 }
@@ -413,6 +429,7 @@ extern "C" int fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, i
     tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
     tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
     tp.tau = tau; tp.status = status;
+    tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     return launch_knn_tc_debug(tp, scores, ld_scores, st);
 }
 

@@ -43,6 +43,9 @@ struct FinalizeParams {
     int k; int rerank; int64_t row_offset;
     float* out_dist; int32_t* out_idx;
     int verify; float eps_rel; const float* maxnorm;
+    // thresholds the scoring pass published per (slot, range): every row it left out of its
+    // published pool scored at most this much (nullptr: none were left out below the pool)
+    const float* part_tau; int ntau;
     int* fb_count; int* fb_list; int fb_cap;
 };
 int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);
@@ -56,13 +59,18 @@ struct TcKnnParams {
     int64_t m, m_pad; int d_pad;
     int K1;                  // pool size (32)
     int nsplit; int64_t tiles_per_split;   // database tiles of 256 rows per split
-    float* part_sc; uint32_t* part_id;     // [nq_pad][nsplit][K1]
+    float* part_sc; uint32_t* part_id;     // [nq_pad][nsplit][tc_partial_len]
     float* tau;              // f32 [nq_pad], running per-query thresholds, -inf initialised
+    float* part_tau;         // f32 [nq_pad][nsplit][tc_taus_per_range]: thresholds each (query, range) ended with
     int32_t* status;
 };
 // Returns FL_EUNSUPPORTED when the shape is outside the tensor-core kernel's range.
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k);
 int tc_pool_size(int k);
+// Entries the tensor-core pass publishes per (query, range): a multiple of the pool size.
+int tc_partial_len(int k);
+// Thresholds the tensor-core pass publishes per (query, range).
+int tc_taus_per_range();
 // 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
 int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
 // Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].
@@ -74,5 +82,10 @@ int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 // bf16 query plane [nq_pad][d_pad] (zero padded) from fp32 queries.
 int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
                        int d_pad, cudaStream_t st);
+
+// Small helpers shared by the entry points.
+int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st);
+int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t st);
+int launch_fallback_fixup(int* fb_count, int fb_cap, int32_t* status, int K1, cudaStream_t st);
 
 }  // namespace fl

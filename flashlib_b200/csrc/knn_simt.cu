@@ -239,8 +239,18 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
         }
         warp_sort_desc<N2, false>(key, id);
     }
-    const float T = __shfl_sync(FULL_MASK, key[NPL1 - 1], 31);
-    const bool pool_full = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID;
+    // Upper bound on the score of every row that is not among the K1 entries kept here: the
+    // K1-th kept score covers what this merge dropped, the published thresholds cover what
+    // the scoring pass never published.
+    float bound = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID
+                      ? __shfl_sync(FULL_MASK, key[NPL1 - 1], 31) : neg_inf();
+    if (p.part_tau != nullptr) {
+        float u = neg_inf();
+        for (int i = lane; i < p.ntau; i += 32) u = fmaxf(u, p.part_tau[slot * p.ntau + i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
+        bound = fmaxf(bound, u);
+    }
 
     // 2. exact fp32 distances of the first `rerank` pool entries.
     const float* qp = p.q + qi * p.ldq;
@@ -330,13 +340,13 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
         }
     }
 
-    // 4. verification: every row outside the pool scored <= T, so its exact distance is
-    //    at least qsq - 2 (T + eps).  The result is proven when the k-th exact distance
+    // 4. verification: every row outside the pool scored <= bound, so its exact distance is
+    //    at least qsq - 2 (bound + eps).  The result is proven when the k-th exact distance
     //    is below that bound; otherwise the row is queued for the exact path.
-    if (p.verify && pool_full) {
+    if (p.verify && bound > neg_inf()) {
         const float mn = __ldg(p.maxnorm);
         const float eps = p.eps_rel * sqrtf(qsq) * mn;
-        const float lb = qsq - 2.f * (T + eps);
+        const float lb = qsq - 2.f * (bound + eps);
         const float slack = 1e-5f * (qsq + mn * mn);
         const bool ok = dk < lb - slack;
         if (!ok && lane == 0) {

@@ -10,15 +10,17 @@
 // and the epilogue only compares: scores above a row's threshold feed that query's
 // candidate pool in shared memory.  Nothing of the 128 x 256 score
 // tile ever reaches global memory; a pool of K1 = 32 (score, row) pairs per query and
-// range is all that is written.
+// range is all that is written (published unsorted, up to 64 entries per query and range).
 //
-// Warp roles (192 threads): warps 0-3 epilogue (warp w reads TMEM lanes 32w..32w+31, one
-// query row per thread), warp 4 TMA producer, warp 5 MMA issuer and TMEM owner.
+// Warp roles (320 threads): warps 0-7 epilogue in two warpgroups (group g takes accumulator
+// g, i.e. every other tile; warp w reads TMEM lanes 32(w%4)..32(w%4)+31, one query row per
+// thread, and keeps a pool per row), warp 8 TMA producer, warp 9 MMA issuer and TMEM owner.
 // Every wait is bounded; a wait that gives up raises a CTA-wide abort flag, records where
 // it happened in the status words and every role falls through to the common exit.
 #include "knn_internal.h"
 #include "pool.cuh"
 #include "tc_ptx.cuh"
+#include <stdlib.h>
 
 namespace fl {
 
@@ -27,9 +29,11 @@ using namespace tc;
 constexpr int TC_BM = 128;            // queries per tile (MMA M)
 constexpr int TC_BN = 256;            // database rows per tile (MMA N)
 constexpr int TC_BK = 64;             // bf16 features per shared-memory chunk (128 bytes)
-constexpr int TC_K1 = 32;             // pool size per query
-constexpr int TC_CAP = 64;            // pool capacity before compaction
-constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread)
+constexpr int TC_NWG = 2;             // epilogue warpgroups; group g owns accumulator g (every other tile)
+constexpr int TC_K1 = 16;             // entries a (query, warpgroup) pool keeps at compaction
+constexpr int TC_CAP = 32;            // pool capacity before compaction
+constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread); the extra slot is scratch
+constexpr int TC_THREADS = (4 * TC_NWG + 2) * 32;
 constexpr int TC_A_CHUNK = TC_BM * 128;   // bytes of one K-chunk of the query tile
 constexpr int TC_A_AUG = TC_BM * 32;      // bytes of the query tile's 16 norm columns
 constexpr int TC_B_CHUNK = TC_BN * 128;   // bytes of one K-chunk of a database tile
@@ -49,7 +53,7 @@ static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit) {
     s.nkc = d_pad / TC_BK;
     int cur = 0;
     s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
-    const int pool = TC_BM * TC_PSTR * 4;
+    const int pool = TC_NWG * TC_BM * TC_PSTR * 4;
     const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
     int ns = (smem_limit - fixed) / TC_B_STAGE;
     if (ns > TC_MAX_STAGES) ns = TC_MAX_STAGES;
@@ -65,8 +69,8 @@ static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit) {
 
 // Per-CTA cycle counters of the last launch (debug aid, read by fl_debug_tc_prof_read):
 // [0] producer waiting for a free slot, [1] MMA waiting for operands, [2] MMA waiting for a
-// free accumulator, [3] epilogue waiting for an accumulator, [4] epilogue waiting for
-// tcgen05.ld, [5] epilogue slow sections entered, [6] pool compactions, [7] scores appended
+// free accumulator, [3] epilogue waiting for an accumulator, [4] cycles in the epilogue's
+// second pass, [5] column groups revisited there, [6] pool compactions, [7] scores appended
 // (warp 0 / lane 0 views), [8] kernel cycles, [9] tiles.
 constexpr int TC_PROF_WORDS = 16;
 __device__ unsigned long long g_tc_prof[160 * TC_PROF_WORDS];
@@ -77,7 +81,10 @@ struct TcKernelParams {
     int64_t nq_pad;
     float* part_sc; uint32_t* part_id;
     float* tau;
+    float* part_tau;
     int32_t* status;
+    int dbg_flags;           // timing experiments (results invalid): 1 skip pass 2, 2 skip the
+                             // reductions of pass 1, 4 skip the tensor-memory loads too
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
     int64_t dbg_ld;
 };
@@ -104,7 +111,8 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
     return make_float2(__int_as_float(cnt), tau);
 }
 
-__global__ void __launch_bounds__(192, 1)
+template <bool DBG>
+__global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
               const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_db_aug,
               const TcKernelParams p) {
@@ -136,11 +144,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 4 && lane == 0) {
+    constexpr int W_PRODUCER = 4 * TC_NWG, W_MMA = 4 * TC_NWG + 1;
+    if (warp == W_PRODUCER && lane == 0) {
         prefetch_tensormap(&map_q); prefetch_tensormap(&map_q_aug);
         prefetch_tensormap(&map_db); prefetch_tensormap(&map_db_aug);
     }
-    if (warp == 5) {
+    if (warp == W_MMA) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
@@ -152,7 +161,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     const int n_items = p.n_qtiles * p.nsplit;
     const int d_pad = p.nkc * TC_BK;
 
-    if (warp == 4) {
+    if (warp == W_PRODUCER) {
         // ------------------------------ TMA producer --------------------------------------
         if (lane == 0) {
             uint32_t fill = 0;     // database chunks issued so far
@@ -200,7 +209,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 while (globaltimer_ns() - t_start < 2000000ull) { }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == W_MMA) {
         // ------------------------------ MMA issuer -----------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
@@ -259,29 +268,33 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
     } else {
         // ------------------------------ epilogue warps --------------------------------------
+        // warp = 4 * warpgroup + TMEM lane quarter; warpgroup g reads accumulator g, i.e. the
+        // tiles with tile_no % 2 == g, and keeps its own pool per query row.
+        const int wg = warp >> 2, quarter = warp & 3;
         float* warp_sc = pool_sc + warp * 32 * TC_PSTR;
         uint32_t* warp_id = pool_id + warp * 32 * TC_PSTR;
         float* my_sc = warp_sc + lane * TC_PSTR;
         uint32_t* my_id = warp_id + lane * TC_PSTR;
-        const uint32_t lane_taddr = tmem_base + (uint32_t(warp * 32) << 16);
+        const uint32_t lane_taddr = tmem_base + (uint32_t(quarter * 32) << 16);
         uint32_t tile_no = 0;
         bool ok = true;
-        long long prof_tfull = 0, prof_ld = 0, prof_slowcyc = 0, prof_compcyc = 0, prof_ldw = 0, prof_proc = 0;
-        unsigned prof_slow = 0, prof_compact = 0, prof_append = 0;
+        long long prof_tfull = 0, prof_rare = 0;
+        unsigned prof_groups = 0, prof_compact = 0, prof_append = 0;
         const long long prof_t0 = clock64();
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
             const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
             const int t0 = split * p.tiles_per_split;
             const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
-            const int64_t qrow = (int64_t)qt * TC_BM + warp * 32 + lane;
+            const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
             const float tau_in = __ldcg(p.tau + qrow);
             float tau = tau_in;
             int cnt = 0;
             const int nt = t1 - t0;
             const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
             for (int i = 0; i < nt; ++i, ++tile_no) {
+                if ((int)(tile_no & 1) != wg) continue;
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
-                const int b = tile_no & 1;
+                const int b = wg;
                 const long long c0 = clock64();
                 if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
@@ -293,10 +306,14 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const uint32_t tile_taddr = lane_taddr + b * TC_BN;
                 const uint32_t row_base = (uint32_t)t * TC_BN;
 
-                uint32_t va[32], vb[32];
-                // One slice = 32 score columns of this thread's query row.
-                auto process = [&](uint32_t (&v)[32], int slice) {
-                    float m8[4];
+                // Pass 1, branch free: stream the 256 scores of this thread's query row through
+                // registers, 64 columns per wait, and note which groups of 8 columns hold a score
+                // above the row's threshold (bit g of `hits` = columns 8g .. 8g+7).
+                // tcgen05.wait::ld waits for every load in flight, so while one batch of 64
+                // columns is reduced the next one is already on its way.
+                uint32_t va[32], vb[32], vc[32], vd[32];
+                unsigned hits = 0;
+                auto scan = [&](uint32_t (&v)[32], int slice) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const float x = fmax3(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]),
@@ -304,113 +321,138 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         const float y = fmax3(__uint_as_float(v[g * 8 + 3]), __uint_as_float(v[g * 8 + 4]),
                                               __uint_as_float(v[g * 8 + 5]));
                         const float z = fmax3(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]), x);
-                        m8[g] = fmaxf(y, z);
+                        hits |= (fmaxf(y, z) > tau) ? (1u << (slice * 4 + g)) : 0u;
                     }
-                    if (p.dbg_scores != nullptr && qt == 0) {
+                    if (DBG) {
+                        if (p.dbg_scores != nullptr && qt == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            p.dbg_scores[(int64_t)(warp * 32 + lane) * p.dbg_ld + row_base + slice * 32 + j] =
-                                __uint_as_float(v[j]);
-                    }
-                    const float m32 = fmaxf(fmax3(m8[0], m8[1], m8[2]), m8[3]);
-                    if (__any_sync(FULL_MASK, m32 > tau)) {
-                        ++prof_slow;
-                        const long long cs0 = clock64();
-                        // Rare path.  Each lane appends the scores above its threshold group by
-                        // group; a lane whose pool is nearly full stops, the warp compacts the
-                        // pools of the stopped lanes (which raises their thresholds) and the
-                        // stopped lanes resume.
-                        unsigned todo = (m8[0] > tau ? 1u : 0u) | (m8[1] > tau ? 2u : 0u) | (m8[2] > tau ? 4u : 0u) |
-                                        (m8[3] > tau ? 8u : 0u);
-                        while (true) {
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                if (((todo >> g) & 1u) && cnt <= TC_CAP - 8) {
-                                    const uint32_t cb = row_base + slice * 32 + g * 8;
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) {
-                                        const float sv = __uint_as_float(v[g * 8 + j]);
-                                        if (sv > tau) { my_sc[cnt] = sv; my_id[cnt] = cb + j; ++cnt; ++prof_append; }
-                                    }
-                                    todo &= ~(1u << g);
-                                }
-                            }
-                            const unsigned need = __ballot_sync(FULL_MASK, todo != 0);
-                            if (!need) break;
-                            prof_compact += __popc(need);
-                            const long long cc0 = clock64();
-                            const float2 r = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
-                            prof_compcyc += clock64() - cc0;
-                            cnt = __float_as_int(r.x);
-                            tau = r.y;
-                            todo &= (m8[0] > tau ? 1u : 0u) | (m8[1] > tau ? 2u : 0u) | (m8[2] > tau ? 4u : 0u) |
-                                    (m8[3] > tau ? 8u : 0u);
+                            for (int j = 0; j < 32; ++j)
+                                p.dbg_scores[(int64_t)(quarter * 32 + lane) * p.dbg_ld + row_base + slice * 32 + j] =
+                                    __uint_as_float(v[j]);
                         }
-                        prof_slowcyc += clock64() - cs0;
                     }
                 };
-
-                const long long c2 = clock64();
-                tmem_ld_32x32b_x32(tile_taddr, va);
-                tmem_ld_wait();
-                reg_fence32(va);
-                prof_ld += clock64() - c2;
-#pragma unroll 1
-                for (int sp = 0; sp < TC_BN / 64; ++sp) {
-                    tmem_ld_32x32b_x32(tile_taddr + (2 * sp + 1) * 32, vb);
-                    const long long cp0 = clock64();
-                    process(va, 2 * sp);
-                    const long long cp1 = clock64();
+                if (!DBG || !(p.dbg_flags & 4)) {
+                    tmem_ld_32x32b_x32(tile_taddr, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 32, vb);
                     tmem_ld_wait();
+                    reg_fence32(va);
                     reg_fence32(vb);
-                    const long long cp2 = clock64();
-                    prof_proc += cp1 - cp0;
-                    prof_ldw += cp2 - cp1;
-                    if (sp + 1 < TC_BN / 64) {
-                        tmem_ld_32x32b_x32(tile_taddr + (2 * sp + 2) * 32, va);
-                    } else {
-                        // every column of this accumulator is in registers: hand it back
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
-                    }
-                    process(vb, 2 * sp + 1);
-                    if (sp + 1 < TC_BN / 64) {
-                        tmem_ld_wait();
-                        reg_fence32(va);
-                    }
+                    tmem_ld_32x32b_x32(tile_taddr + 64, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 96, vd);
+                    scan(va, 0);
+                    scan(vb, 1);
+                    tmem_ld_wait();
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tmem_ld_32x32b_x32(tile_taddr + 128, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 160, vb);
+                    scan(vc, 2);
+                    scan(vd, 3);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 192, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 224, vd);
+                    scan(va, 4);
+                    scan(vb, 5);
+                    tmem_ld_wait();
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    scan(vc, 6);
+                    scan(vd, 7);
                 }
+                if (DBG && (p.dbg_flags & 1)) hits = 0;
+
+                // Pass 2, rare: the warp revisits every group some lane flagged, one group per trip
+                // through a small loop (a small body stays in the instruction cache; the load of
+                // the next group is in flight while the current one is handled).  Each lane tests
+                // its 8 scores of the group -- only flagged lanes can pass -- and stores the passing
+                // ones at slots computed from the bit mask; the others go to the row's scratch slot.
+                unsigned wm = __reduce_or_sync(FULL_MASK, hits);
+                if (wm) {
+                    const long long cr0 = clock64();
+                    uint32_t rn[8];
+                    int g = __ffs(wm) - 1;
+                    wm &= wm - 1;
+                    tmem_ld_32x32b_x8(tile_taddr + g * 8, rn);
+#pragma unroll 1
+                    while (true) {
+                        tmem_ld_wait();
+                        reg_fence8(rn);
+                        uint32_t r[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) r[j] = rn[j];
+                        const int gcur = g;
+                        const bool more = wm != 0;
+                        if (more) {
+                            g = __ffs(wm) - 1;
+                            wm &= wm - 1;
+                            tmem_ld_32x32b_x8(tile_taddr + g * 8, rn);
+                        }
+                        ++prof_groups;
+                        // make room first, so the append below never has to stop half way
+                        const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
+                        if (need) {
+                            prof_compact += __popc(need);
+                            const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                            cnt = __float_as_int(cr.x);
+                            tau = cr.y;
+                        }
+                        unsigned pm = 0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) pm |= (__uint_as_float(r[j]) > tau) ? (1u << j) : 0u;
+                        pm = ((hits >> gcur) & 1u) ? pm : 0u;
+                        const uint32_t cb = row_base + gcur * 8;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            my_sc[pos] = __uint_as_float(r[j]);     // slot TC_CAP is the row's scratch slot
+                            my_id[pos] = cb + j;
+                        }
+                        cnt += __popc(pm);
+                        prof_append += __popc(pm);
+                        if (!more) break;
+                    }
+                    prof_rare += clock64() - cr0;
+                }
+                // the accumulator is no longer needed: hand it back to the MMA warp
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
             }
             if (!ok) break;
-            // end of the item: sort every row's pool, publish it and the row's threshold
+            // end of the item: publish every row's pool as it stands (up to TC_CAP entries, the rest
+            // padded) and the row's threshold.  The pool is not sorted here: the finalize kernel
+            // merges the published entries anyway.
             __syncwarp();
 #pragma unroll 1
             for (int src = 0; src < 32; ++src) {
                 const int n = __shfl_sync(FULL_MASK, cnt, src);
-                float* rsc = warp_sc + src * TC_PSTR;
-                uint32_t* rid = warp_id + src * TC_PSTR;
-                const float thr = warp_pool_compact<TC_CAP / 32>(rsc, rid, n, TC_K1);
-                if (lane == src) tau = fmaxf(tau, thr);
-                const int64_t q = (int64_t)qt * TC_BM + warp * 32 + src;
-                const int64_t o = (q * p.nsplit + split) * TC_K1;
-                p.part_sc[o + lane] = rsc[lane];
-                p.part_id[o + lane] = rid[lane];
-                __syncwarp();
+                const float* rsc = warp_sc + src * TC_PSTR;
+                const uint32_t* rid = warp_id + src * TC_PSTR;
+                const int64_t q = (int64_t)qt * TC_BM + quarter * 32 + src;
+                const int64_t o = ((q * p.nsplit + split) * TC_NWG + wg) * TC_CAP;
+#pragma unroll
+                for (int e = lane; e < TC_CAP; e += 32) {
+                    p.part_sc[o + e] = e < n ? rsc[e] : neg_inf();
+                    p.part_id[o + e] = e < n ? rid[e] : INVALID_ID;
+                }
             }
+            p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
             if (tau > tau_in) __stcg(p.tau + qrow, tau);
         }
         if (warp == 0 && lane == 0 && blockIdx.x < 160) {
             unsigned long long* pr = g_tc_prof + blockIdx.x * TC_PROF_WORDS;
-            pr[3] = prof_tfull; pr[4] = prof_ld; pr[5] = prof_slow; pr[6] = prof_compact; pr[7] = prof_append;
+            pr[3] = prof_tfull; pr[4] = prof_rare; pr[5] = prof_groups; pr[6] = prof_compact; pr[7] = prof_append;
             pr[8] = clock64() - prof_t0; pr[9] = tile_no;
-            pr[10] = prof_slowcyc; pr[11] = prof_compcyc; pr[12] = prof_ldw; pr[13] = prof_proc;
         }
     }
 
     // ------------------------------ common exit ----------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == W_MMA) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
@@ -453,6 +495,8 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int c
 }
 
 int tc_pool_size(int k) { (void)k; return TC_K1; }
+int tc_partial_len(int k) { (void)k; return TC_NWG * TC_CAP; }
+int tc_taus_per_range() { return TC_NWG; }
 
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k) {
     if (nq < 1 || m < 1) return FL_EUNSUPPORTED;
@@ -492,6 +536,8 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_pe
 }
 
 static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
+    FL_CHECK_ARG(p.qplane && p.dbrows && p.part_sc && p.part_id && p.tau && p.part_tau,
+                 "tensor-core kNN launch with a null buffer");
     CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
     const int pitch = p.d_pad + PLANE_AUG_COLS;
     int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
@@ -510,11 +556,20 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.off_b = sp.off_b; kp.off_pool_sc = sp.off_pool_sc; kp.off_pool_id = sp.off_pool_id;
     kp.off_bar = sp.off_bar;
     kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
-    kp.tau = p.tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
+    kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
+    {
+        const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
+        kp.dbg_flags = e ? atoi(e) : 0;
+    }
     const int items = kp.n_qtiles * kp.nsplit;
     const int grid = items < sm_count() ? items : sm_count();
-    FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-    knn_tc_kernel<<<grid, 192, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    if (dbg != nullptr || kp.dbg_flags != 0) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<true><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    } else {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    }
     FL_CHECK_LAUNCH();
     return FL_OK;
 }

@@ -1,7 +1,7 @@
 // Row norms and the database operand plane (bf16 rows + half squared norms) that the
 // tensor-core kNN / assign kernels stream with TMA.
 #include "common.cuh"
-#include "plane.h"
+#include "knn_internal.h"
 #include <cuda_bf16.h>
 
 namespace fl {
@@ -87,6 +87,20 @@ PlaneLayout plane_layout(int64_t m, int d) {
     return L;
 }
 
+// Fills `plane` (layout plane_layout(m, d)) for the fp32 rows of db.
+int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st) {
+    const PlaneLayout L = plane_layout(m, d);
+    char* base = static_cast<char*>(plane);
+    FL_CHECK_CUDA(cudaMemsetAsync(base + L.off_meta, 0, 1024, st));
+    const int wpb = 8;
+    plane_build_kernel<<<(unsigned)ceil_div(L.m_pad, wpb), wpb * 32, 0, st>>>(
+        db, m, d, ld, reinterpret_cast<__nv_bfloat16*>(base + L.off_rows),
+        reinterpret_cast<float*>(base + L.off_hnorm), reinterpret_cast<unsigned int*>(base + L.off_meta),
+        L.m_pad, L.d_pad);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 }  // namespace fl
 
 using namespace fl;
@@ -120,14 +134,5 @@ extern "C" int fl_knn_prepare_db_f32(const float* db, int64_t m, int d, int64_t 
                   (long long)L.bytes);
         return FL_EWORKSPACE;
     }
-    char* base = static_cast<char*>(plane);
-    cudaStream_t st = (cudaStream_t)stream;
-    FL_CHECK_CUDA(cudaMemsetAsync(base + L.off_meta, 0, 1024, st));
-    const int wpb = 8;
-    plane_build_kernel<<<(unsigned)ceil_div(L.m_pad, wpb), wpb * 32, 0, st>>>(
-        db, m, d, ld, reinterpret_cast<__nv_bfloat16*>(base + L.off_rows),
-        reinterpret_cast<float*>(base + L.off_hnorm), reinterpret_cast<unsigned int*>(base + L.off_meta),
-        L.m_pad, L.d_pad);
-    FL_CHECK_LAUNCH();
-    return FL_OK;
+    return launch_plane_build(db, m, d, ld, plane, (cudaStream_t)stream);
 }

@@ -127,6 +127,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
         : "r"(taddr)
         : "memory");
 }
+// 8 consecutive fp32 columns of this thread's TMEM lane (warp-collective).
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void reg_fence8(uint32_t (&v)[8]) {
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
+                      "+r"(v[7])::"memory");
+}
 // Ties the registers written by an asynchronous tcgen05.ld to a point after the wait, so
 // the compiler cannot move their uses above it.
 __device__ __forceinline__ void reg_fence32(uint32_t (&v)[32]) {

@@ -8,6 +8,7 @@ imports; all of them run the sm_100a kernels behind the C ABI.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -16,10 +17,55 @@ from . import _lib
 from .knn import _as_f32_rows, _stream_ptr
 
 
-def _assign_2d(x: torch.Tensor, c: torch.Tensor, out: torch.Tensor) -> None:
+_XPLANE_CACHE = {}
+
+
+def _x_plane(x: torch.Tensor) -> torch.Tensor:
+    """bf16 operand plane of the sample rows for the tensor-core assignment, built once per
+    data set (keyed like the reference's per-``data_ptr`` norm cache,
+    ``flashlib/primitives/knn/triton/_row_norm.py:82-93``)."""
+    key = (x.data_ptr(), tuple(x.shape), x.stride(0), x._version, x.device.index)
+    hit = _XPLANE_CACHE.get(key)
+    if hit is not None:
+        return hit
+    lib = _lib.load()
+    n, d = x.shape
+    nbytes = lib.fl_kmeans_xplane_bytes(n, d)
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    _lib.check(lib.fl_kmeans_prepare_x_f32(x.data_ptr(), n, d, x.stride(0), buf.data_ptr(), nbytes,
+                                           _stream_ptr(x.device)))
+    if len(_XPLANE_CACHE) >= 2:
+        _XPLANE_CACHE.pop(next(iter(_XPLANE_CACHE)))
+    _XPLANE_CACHE[key] = buf
+    return buf
+
+
+def _use_tensor_cores(n: int, K: int, d: int, mode: Optional[str]) -> bool:
+    if mode in ("exact", "simt"):
+        return False
+    if d > 256:
+        if mode in ("bf16", "tc"):
+            raise NotImplementedError("tensor-core assignment supports d <= 256")
+        return False
+    if mode in ("bf16", "tc"):
+        return True
+    return n * K >= (1 << 24) and K >= 64
+
+
+def _assign_2d(x: torch.Tensor, c: torch.Tensor, out: torch.Tensor, mode: Optional[str] = None) -> None:
     lib = _lib.load()
     n, d = x.shape
     K = c.shape[0]
+    if mode is None:
+        mode = os.environ.get("FLASHLIB_B200_ASSIGN_MODE") or None
+    if _use_tensor_cores(n, K, d, mode):
+        xplane = _x_plane(x)
+        ws_bytes = lib.fl_kmeans_assign_tc_workspace_bytes(n, K, d, 1)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+        _lib.check(lib.fl_kmeans_assign_tc_f32(x.data_ptr(), n, x.stride(0), xplane.data_ptr(), c.data_ptr(), K,
+                                               c.stride(0), d, out.data_ptr(), ws.data_ptr(), ws_bytes, None,
+                                               _stream_ptr(x.device)))
+        return
     ws_bytes = lib.fl_kmeans_assign_workspace_bytes(n, K, d)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
     _lib.check(lib.fl_kmeans_assign_f32(x.data_ptr(), n, x.stride(0), c.data_ptr(), K, c.stride(0), d,
@@ -27,11 +73,14 @@ def _assign_2d(x: torch.Tensor, c: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def euclid_assign_triton(x: torch.Tensor, centroids: torch.Tensor, out: Optional[torch.Tensor] = None,
-                         c_sq: Optional[torch.Tensor] = None, **_ignored) -> torch.Tensor:
+                         c_sq: Optional[torch.Tensor] = None, *, mode: Optional[str] = None,
+                         **_ignored) -> torch.Tensor:
     """Nearest-centroid labels ``(B, N) int32`` (lowest index on exact ties).
 
     Same arguments as ``flashlib/primitives/kmeans/triton/assign.py:1439-1479``; ``c_sq`` and
     the tile-config keywords are accepted and ignored (norms are computed on the device).
+    ``mode`` (``"exact"`` | ``"bf16"`` | ``None`` = by size) picks the CUDA-core or the tensor-core kernel;
+    both return the same labels.
     """
     assert x.is_cuda and centroids.is_cuda, "All tensors must be on CUDA"
     assert centroids.dtype == x.dtype, "centroids dtype mismatch"
@@ -45,7 +94,7 @@ def euclid_assign_triton(x: torch.Tensor, centroids: torch.Tensor, out: Optional
         assert out.shape == (B, N) and out.dtype == torch.int32 and out.is_contiguous()
     with torch.cuda.device(x.device):
         for b in range(B):
-            _assign_2d(_as_f32_rows(x[b]), _as_f32_rows(centroids[b]), out[b])
+            _assign_2d(_as_f32_rows(x[b]), _as_f32_rows(centroids[b]), out[b], mode)
     return out
 
 

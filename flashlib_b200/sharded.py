@@ -34,8 +34,9 @@ def gather_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
     nq, k = local_d.shape
     gd = torch.empty((world, nq, k), dtype=local_d.dtype, device=local_d.device)
     gi = torch.empty((world, nq, k), dtype=local_i.dtype, device=local_i.device)
-    dist.all_gather_into_tensor(gd, local_d.contiguous(), group=group)
-    dist.all_gather_into_tensor(gi, local_i.contiguous(), group=group)
+    # list form: supported by both the nccl and the gloo backend
+    dist.all_gather(list(gd.unbind(0)), local_d.contiguous(), group=group)
+    dist.all_gather(list(gi.unbind(0)), local_i.contiguous(), group=group)
     cand_d = gd.permute(1, 0, 2).reshape(nq, world * k)
     cand_i = gi.permute(1, 0, 2).reshape(nq, world * k)
     return cand_d, cand_i

@@ -144,6 +144,18 @@ int64_t fl_kmeans_assign_workspace_bytes(int64_t n, int K, int d);
 int     fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx,
                              const float* c, int K, int64_t ldc, int d,
                              int32_t* labels, void* ws, int64_t ws_bytes, void* stream);
+/* Tensor-core assignment (tcgen05 bf16 candidates, exact fp32 re-score, proven or recomputed */
+/* on the exact path; d <= 256).  Replaces the Blackwell assign kernels of                    */
+/* kmeans/cutedsl/blackwell_assign.py:77-2289 for fp32 inputs.  `xplane` is the bf16 operand   */
+/* plane of the sample rows built once per data set by fl_kmeans_prepare_x_f32 (NULL: built   */
+/* in the workspace on every call).  Labels are identical to fl_kmeans_assign_f32's.          */
+int64_t fl_kmeans_xplane_bytes(int64_t n, int d);
+int     fl_kmeans_prepare_x_f32(const float* x, int64_t n, int d, int64_t ldx,
+                                void* xplane, int64_t xplane_bytes, void* stream);
+int64_t fl_kmeans_assign_tc_workspace_bytes(int64_t n, int K, int d, int have_xplane);
+int     fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, const void* xplane,
+                                const float* c, int K, int64_t ldc, int d, int32_t* labels,
+                                void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 /* Same assignment for callers that cannot allocate device memory or pass a workspace (a  */
 /* plugin that only receives a stream and its buffers, a host whose memory pool owns the   */
 /* whole GPU, a loop that must avoid cudaMalloc's synchronisation).  It has no counterpart */

@@ -92,3 +92,32 @@ def test_full_size_one_iteration():
     new_ref, _, _ = oracle.kmeans_update(X.numpy(), lab.cpu().numpy().astype(np.int64), X[:cfg["K"]].numpy())
     new, _ = fl.triton_centroid_finalize(sums, cnts, init[None])
     assert parity.rel_close(new[0].cpu().numpy(), new_ref, rel=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("n,d,K", [(300, 32, 40), (5000, 128, 1024), (20_000, 96, 300), (4097, 256, 257), (1000, 16, 3)])
+def test_tensor_core_assign_equals_exact_assign(n, d, K):
+    g = torch.Generator().manual_seed(n * 3 + K)
+    means = 2 * torch.randn(K, d, generator=g)
+    x = (means[torch.randint(0, K, (n,), generator=g)] + torch.randn(n, d, generator=g)).cuda()
+    c = (means + 0.3 * torch.randn(K, d, generator=g)).cuda()
+    ref = oracle.kmeans_assign(x.cpu().numpy(), c.cpu().numpy())
+    tc = fl.euclid_assign_triton(x[None], c[None], mode="bf16")[0]
+    ex = fl.euclid_assign_triton(x[None], c[None], mode="exact")[0]
+    assert parity.label_parity(x.cpu().numpy(), c.cpu().numpy(), tc.cpu().numpy(), ref)["ok"]
+    assert parity.label_parity(x.cpu().numpy(), c.cpu().numpy(), tc.cpu().numpy(), ex.cpu().numpy())["ok"]
+
+
+def test_tensor_core_assign_near_duplicate_centroids():
+    """Centroids that nearly coincide cannot be separated by bf16 scores: those points must come
+    back through the exact path with the exact winner (lowest index on exact ties)."""
+    g = torch.Generator().manual_seed(4)
+    base = torch.randn(64, 64, generator=g)
+    c = torch.cat([base, base + 1e-3 * torch.randn(64, 64, generator=g), base[:16]]).cuda()   # 144 centroids
+    x = (base[torch.randint(0, 64, (3000,), generator=g)] + 0.05 * torch.randn(3000, 64, generator=g)).cuda()
+    tc = fl.euclid_assign_triton(x[None], c[None], mode="bf16")[0]
+    xd, cd = x.double(), c.double()
+    d64 = (xd * xd).sum(-1, keepdim=True) + (cd * cd).sum(-1)[None] - 2 * xd @ cd.T
+    best = d64.min(1).values
+    got = d64[torch.arange(3000, device="cuda"), tc.long()]
+    assert torch.all((got - best).abs() <= 1e-5 * best + 1e-6)
+    assert not torch.any(tc >= 128)          # rows 128.. duplicate rows 0..15 exactly: lower index wins
