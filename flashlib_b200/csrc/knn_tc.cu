@@ -30,7 +30,7 @@ constexpr int TC_BM = 128;            // queries per tile (MMA M)
 constexpr int TC_BN = 256;            // database rows per tile (MMA N)
 constexpr int TC_BK = 64;             // bf16 features per shared-memory chunk (128 bytes)
 constexpr int TC_NWG = 2;             // epilogue warpgroups; group g owns accumulator g (every other tile)
-constexpr int TC_K1 = 16;             // entries a (query, warpgroup) pool keeps at compaction
+constexpr int TC_K1 = 12;             // entries a (query, warpgroup) pool keeps at compaction
 constexpr int TC_CAP = 32;            // pool capacity before compaction
 constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread); the extra slot is scratch
 constexpr int TC_THREADS = (4 * TC_NWG + 2) * 32;
@@ -278,7 +278,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const uint32_t lane_taddr = tmem_base + (uint32_t(quarter * 32) << 16);
         uint32_t tile_no = 0;
         bool ok = true;
-        long long prof_tfull = 0, prof_rare = 0;
+        long long prof_tfull = 0, prof_rare = 0, prof_cc = 0;
         unsigned prof_groups = 0, prof_compact = 0, prof_append = 0;
         const long long prof_t0 = clock64();
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
@@ -365,11 +365,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (DBG && (p.dbg_flags & 1)) hits = 0;
 
                 // Pass 2, rare: the warp revisits every group some lane flagged, one group per trip
-                // through a small loop (a small body stays in the instruction cache; the load of
-                // the next group is in flight while the current one is handled).  Each lane tests
-                // its 8 scores of the group -- only flagged lanes can pass -- and stores the passing
-                // ones at slots computed from the bit mask; the others go to the row's scratch slot.
+                // through a small loop; the copy of the next group is in flight while the current
+                // one is handled, and the accumulator is handed back to the MMA warp as soon as the
+                // last copy has arrived.  A lone warp runs at a few cycles per instruction, so the
+                // common case -- a single passing score per flagged lane -- is kept short: the
+                // passing score is the group's maximum and its column comes from the bit mask.
                 unsigned wm = __reduce_or_sync(FULL_MASK, hits);
+                bool released = false;
                 if (wm) {
                     const long long cr0 = clock64();
                     uint32_t rn[8];
@@ -380,46 +382,64 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     while (true) {
                         tmem_ld_wait();
                         reg_fence8(rn);
-                        uint32_t r[8];
+                        float r[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) r[j] = rn[j];
+                        for (int j = 0; j < 8; ++j) r[j] = __uint_as_float(rn[j]);
                         const int gcur = g;
                         const bool more = wm != 0;
                         if (more) {
                             g = __ffs(wm) - 1;
                             wm &= wm - 1;
                             tmem_ld_32x32b_x8(tile_taddr + g * 8, rn);
+                        } else {
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                            released = true;
                         }
                         ++prof_groups;
-                        // make room first, so the append below never has to stop half way
+                        // make room first, so the appends below never have to stop half way
                         const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
                         if (need) {
                             prof_compact += __popc(need);
+                            const long long cc0 = clock64();
                             const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                            prof_cc += clock64() - cc0;
                             cnt = __float_as_int(cr.x);
                             tau = cr.y;
                         }
                         unsigned pm = 0;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) pm |= (__uint_as_float(r[j]) > tau) ? (1u << j) : 0u;
+                        for (int j = 0; j < 8; ++j) pm |= (r[j] > tau) ? (1u << j) : 0u;
                         pm = ((hits >> gcur) & 1u) ? pm : 0u;
                         const uint32_t cb = row_base + gcur * 8;
+                        const int np = __popc(pm);
+                        if (!__any_sync(FULL_MASK, np > 1)) {
+                            // at most one passing score per lane: it is the maximum of the group
+                            const float mx = fmaxf(fmax3(r[0], r[1], r[2]), fmax3(fmax3(r[3], r[4], r[5]), r[6], r[7]));
+                            const int pos = np ? cnt : TC_CAP;          // slot TC_CAP is the row's scratch slot
+                            my_sc[pos] = mx;
+                            my_id[pos] = cb + (__ffs(pm) - 1);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
-                            my_sc[pos] = __uint_as_float(r[j]);     // slot TC_CAP is the row's scratch slot
-                            my_id[pos] = cb + j;
+                            for (int j = 0; j < 8; ++j) {
+                                const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                                my_sc[pos] = r[j];
+                                my_id[pos] = cb + j;
+                            }
                         }
-                        cnt += __popc(pm);
-                        prof_append += __popc(pm);
+                        cnt += np;
+                        prof_append += np;
                         if (!more) break;
                     }
                     prof_rare += clock64() - cr0;
                 }
-                // the accumulator is no longer needed: hand it back to the MMA warp
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                if (!released) {
+                    // nothing flagged: hand the accumulator back right away
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                }
             }
             if (!ok) break;
             // end of the item: publish every row's pool as it stands (up to TC_CAP entries, the rest
@@ -446,6 +466,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             unsigned long long* pr = g_tc_prof + blockIdx.x * TC_PROF_WORDS;
             pr[3] = prof_tfull; pr[4] = prof_rare; pr[5] = prof_groups; pr[6] = prof_compact; pr[7] = prof_append;
             pr[8] = clock64() - prof_t0; pr[9] = tile_no;
+            pr[10] = 0; pr[11] = prof_cc;
         }
     }
 
