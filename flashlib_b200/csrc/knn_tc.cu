@@ -83,6 +83,8 @@ struct TcKernelParams {
     float* tau;
     float* part_tau;
     int32_t* status;
+    uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
+    int tile_stride;         // database tile actually read for loop index t is t * tile_stride (1 outside seeding)
     int dbg_flags;           // timing experiments (results invalid): 1 skip pass 2, 2 skip the
                              // reductions of pass 1, 4 skip the tensor-memory loads too
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
@@ -111,7 +113,22 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
     return make_float2(__int_as_float(cnt), tau);
 }
 
-template <bool DBG>
+// Largest-value update of a float in global memory (compare-and-swap; a few writers at most).
+__device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
+    int* ai = reinterpret_cast<int*>(addr);
+    int old = *reinterpret_cast<volatile int*>(ai);
+    while (__int_as_float(old) < v) {
+        const int assumed = old;
+        old = atomicCAS(ai, assumed, __float_as_int(v));
+        if (old == assumed) break;
+    }
+}
+
+// SEED = true turns the kernel into the threshold-seeding pass: it scans a strided sample of
+// the database tiles and, instead of pools, keeps 16 running maxima per query row over
+// disjoint column classes; their minimum is a score that 16 distinct rows reach, i.e. a valid
+// starting threshold that spares the main pass most of its cold-start appends.
+template <bool DBG, bool SEED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
               const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_db_aug,
@@ -172,7 +189,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
                 const int t0 = split * p.tiles_per_split;
                 const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
-                if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS)) {
+                if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
                 mbar_expect_tx(BAR(B_AFULL), p.nkc * TC_A_CHUNK + TC_A_AUG);
@@ -189,16 +206,16 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         const int s = fill % p.nstage;
                         const uint32_t ph = (fill / p.nstage) & 1;
                         const long long c0 = clock64();
-                        if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, TC_WAIT_NS)) {
+                        if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 4, B_EMPTY + s); ok = false; break;
                         }
                         prof_a += clock64() - c0;
                         const bool last = (kc == p.nkc - 1);
                         mbar_expect_tx(BAR(B_FULL + s), last ? TC_B_STAGE : TC_B_CHUNK);
-                        tma_load_2d(b_addr + s * TC_B_STAGE, &map_db, kc * TC_BK, t * TC_BN, BAR(B_FULL + s));
+                        tma_load_2d(b_addr + s * TC_B_STAGE, &map_db, kc * TC_BK, t * p.tile_stride * TC_BN, BAR(B_FULL + s));
                         if (last)
-                            tma_load_2d(b_addr + s * TC_B_STAGE + TC_B_CHUNK, &map_db_aug, d_pad, t * TC_BN,
-                                        BAR(B_FULL + s));
+                            tma_load_2d(b_addr + s * TC_B_STAGE + TC_B_CHUNK, &map_db_aug, d_pad,
+                                        t * p.tile_stride * TC_BN, BAR(B_FULL + s));
                     }
                 }
             }
@@ -222,13 +239,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int split = it / p.n_qtiles;
                 const int t0 = split * p.tiles_per_split;
                 const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
-                if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS)) {
+                if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 5, B_AFULL); ok = false; break;
                 }
                 for (int t = t0; t < t1 && ok; ++t, ++tile_no) {
                     const int b = tile_no & 1;
                     const long long c0 = clock64();
-                    if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, TC_WAIT_NS)) {
+                    if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                         tc_report_timeout(p.status, 5, B_TEMPTY + b); ok = false; break;
                     }
                     prof_tempty += clock64() - c0;
@@ -238,7 +255,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         const int s = use % p.nstage;
                         const uint32_t ph = (use / p.nstage) & 1;
                         const long long c1 = clock64();
-                        if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, TC_WAIT_NS)) {
+                        if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 5, B_FULL + s); ok = false; break;
                         }
                         prof_full += clock64() - c1;
@@ -289,6 +306,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const float tau_in = __ldcg(p.tau + qrow);
             float tau = tau_in;
             int cnt = 0;
+            float cls[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) cls[c] = neg_inf();
             const int nt = t1 - t0;
             const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
             for (int i = 0; i < nt; ++i, ++tile_no) {
@@ -296,7 +316,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = wg;
                 const long long c0 = clock64();
-                if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS))) {
+                if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
                     ok = false;
                     break;
@@ -312,6 +332,45 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 // tcgen05.wait::ld waits for every load in flight, so while one batch of 64
                 // columns is reduced the next one is already on its way.
                 uint32_t va[32], vb[32], vc[32], vd[32];
+                if (SEED) {
+                    auto fold = [&](uint32_t (&v)[32]) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c)
+                            cls[c] = fmax3(cls[c], __uint_as_float(v[c]), __uint_as_float(v[c + 16]));
+                    };
+                    tmem_ld_32x32b_x32(tile_taddr, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 32, vb);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 64, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 96, vd);
+                    fold(va);
+                    fold(vb);
+                    tmem_ld_wait();
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tmem_ld_32x32b_x32(tile_taddr + 128, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 160, vb);
+                    fold(vc);
+                    fold(vd);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 192, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 224, vd);
+                    fold(va);
+                    fold(vb);
+                    tmem_ld_wait();
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    fold(vc);
+                    fold(vd);
+                    continue;
+                }
                 unsigned hits = 0;
                 auto scan = [&](uint32_t (&v)[32], int slice) {
 #pragma unroll
@@ -364,77 +423,117 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
                 if (DBG && (p.dbg_flags & 1)) hits = 0;
 
-                // Pass 2, rare: the warp revisits every group some lane flagged, one group per trip
-                // through a small loop; the copy of the next group is in flight while the current
-                // one is handled, and the accumulator is handed back to the MMA warp as soon as the
-                // last copy has arrived.  A lone warp runs at a few cycles per instruction, so the
-                // common case -- a single passing score per flagged lane -- is kept short: the
-                // passing score is the group's maximum and its column comes from the bit mask.
+                // Pass 2, rare.  A lane seldom has more than one flagged group in a tile, so the
+                // work is split in two: (a) a small loop copies every flagged group from tensor
+                // memory and each flagged lane keeps the 8 scores of its first flagged group in
+                // registers -- after that the accumulator goes back to the MMA warp; (b) all lanes
+                // handle their kept group together in one straight-line step (a lone warp pays a
+                // few cycles per instruction, so once per tile beats once per group).  Further
+                // flagged groups of the same lane ("late") are handled one by one before (b).
                 unsigned wm = __reduce_or_sync(FULL_MASK, hits);
-                bool released = false;
                 if (wm) {
                     const long long cr0 = clock64();
-                    uint32_t rn[8];
-                    int g = __ffs(wm) - 1;
-                    wm &= wm - 1;
-                    tmem_ld_32x32b_x8(tile_taddr + g * 8, rn);
-#pragma unroll 1
-                    while (true) {
-                        tmem_ld_wait();
-                        reg_fence8(rn);
-                        float r[8];
+                    float sv[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) r[j] = __uint_as_float(rn[j]);
-                        const int gcur = g;
-                        const bool more = wm != 0;
-                        if (more) {
-                            g = __ffs(wm) - 1;
-                            wm &= wm - 1;
-                            tmem_ld_32x32b_x8(tile_taddr + g * 8, rn);
-                        } else {
-                            tc_fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
-                            released = true;
+                    for (int j = 0; j < 8; ++j) sv[j] = neg_inf();
+                    uint32_t scb = 0;
+                    bool have = false;
+                    unsigned late = 0;
+                    do {
+                        // four flagged groups per round trip: a copy from tensor memory takes a few
+                        // hundred cycles and tcgen05.wait::ld waits for all copies in flight
+                        int gs[4];
+                        bool live[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int f = __ffs(wm) - 1;          // -1 when no group is left
+                            live[k] = f >= 0;
+                            gs[k] = f >= 0 ? f : 0;
+                            wm &= wm - 1;                         // 0 stays 0
                         }
-                        ++prof_groups;
-                        // make room first, so the appends below never have to stop half way
+                        uint32_t rn[4][8];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) tmem_ld_32x32b_x8(tile_taddr + gs[k] * 8, rn[k]);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) reg_fence8(rn[k]);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const bool mine = live[k] && ((hits >> gs[k]) & 1u);
+                            const bool take = mine && !have;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) sv[j] = take ? __uint_as_float(rn[k][j]) : sv[j];
+                            scb = take ? row_base + gs[k] * 8 : scb;
+                            late |= (mine && have) ? (1u << gs[k]) : 0u;
+                            have = have || mine;
+                            prof_groups += live[k] ? 1 : 0;
+                        }
+                    } while (wm);
+                    unsigned wl = __reduce_or_sync(FULL_MASK, late);
+#pragma unroll 1
+                    while (wl) {
+                        const int g = __ffs(wl) - 1;
+                        wl &= wl - 1;
                         const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
                         if (need) {
                             prof_compact += __popc(need);
-                            const long long cc0 = clock64();
                             const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
-                            prof_cc += clock64() - cc0;
                             cnt = __float_as_int(cr.x);
                             tau = cr.y;
                         }
+                        uint32_t r[8];
+                        tmem_ld_32x32b_x8(tile_taddr + g * 8, r);
+                        tmem_ld_wait();
+                        reg_fence8(r);
                         unsigned pm = 0;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) pm |= (r[j] > tau) ? (1u << j) : 0u;
-                        pm = ((hits >> gcur) & 1u) ? pm : 0u;
-                        const uint32_t cb = row_base + gcur * 8;
-                        const int np = __popc(pm);
-                        if (!__any_sync(FULL_MASK, np > 1)) {
-                            // at most one passing score per lane: it is the maximum of the group
-                            const float mx = fmaxf(fmax3(r[0], r[1], r[2]), fmax3(fmax3(r[3], r[4], r[5]), r[6], r[7]));
-                            const int pos = np ? cnt : TC_CAP;          // slot TC_CAP is the row's scratch slot
-                            my_sc[pos] = mx;
-                            my_id[pos] = cb + (__ffs(pm) - 1);
-                        } else {
+                        for (int j = 0; j < 8; ++j) pm |= (__uint_as_float(r[j]) > tau) ? (1u << j) : 0u;
+                        pm = ((late >> g) & 1u) ? pm : 0u;
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
-                                my_sc[pos] = r[j];
-                                my_id[pos] = cb + j;
-                            }
+                        for (int j = 0; j < 8; ++j) {
+                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            my_sc[pos] = __uint_as_float(r[j]);     // slot TC_CAP is the row's scratch slot
+                            my_id[pos] = row_base + g * 8 + j;
                         }
-                        cnt += np;
-                        prof_append += np;
-                        if (!more) break;
+                        cnt += __popc(pm);
+                        prof_append += __popc(pm);
                     }
+                    // every flagged score is in registers or in a pool: hand the accumulator back
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    // (b) all lanes at once
+                    const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
+                    if (need) {
+                        prof_compact += __popc(need);
+                        const long long cc0 = clock64();
+                        const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                        prof_cc += clock64() - cc0;
+                        cnt = __float_as_int(cr.x);
+                        tau = cr.y;
+                    }
+                    unsigned pm = 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) pm |= (sv[j] > tau) ? (1u << j) : 0u;   // sv is -inf without a kept group
+                    const int np = __popc(pm);
+                    if (!__any_sync(FULL_MASK, np > 1)) {
+                        // at most one passing score per lane: it is the maximum of the group
+                        const float mx = fmaxf(fmax3(sv[0], sv[1], sv[2]), fmax3(fmax3(sv[3], sv[4], sv[5]), sv[6], sv[7]));
+                        const int pos = np ? cnt : TC_CAP;
+                        my_sc[pos] = mx;
+                        my_id[pos] = scb + (__ffs(pm) - 1);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            my_sc[pos] = sv[j];
+                            my_id[pos] = scb + j;
+                        }
+                    }
+                    cnt += np;
+                    prof_append += np;
                     prof_rare += clock64() - cr0;
-                }
-                if (!released) {
+                } else {
                     // nothing flagged: hand the accumulator back right away
                     tc_fence_before_sync();
                     __syncwarp();
@@ -442,6 +541,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
             }
             if (!ok) break;
+            if (SEED) {
+                float m = cls[0];
+#pragma unroll
+                for (int c = 1; c < 16; ++c) m = fminf(m, cls[c]);
+                if (m > neg_inf()) atomic_max_f32(p.tau + qrow, m);
+                continue;
+            }
             // end of the item: publish every row's pool as it stands (up to TC_CAP entries, the rest
             // padded) and the row's threshold.  The pool is not sorted here: the finalize kernel
             // merges the published entries anyway.
@@ -581,15 +687,33 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     {
         const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
         kp.dbg_flags = e ? atoi(e) : 0;
+        const char* h = getenv("FLASHLIB_B200_TC_HINT");
+        kp.wait_hint_ns = h ? (uint32_t)atoi(h) : 1000u;
     }
     const int items = kp.n_qtiles * kp.nsplit;
     const int grid = items < sm_count() ? items : sm_count();
+    kp.tile_stride = 1;
+    // Threshold seeding on a strided sample of 64 tiles when the database is large enough for
+    // the cold start of the pools to matter.
+    const char* noseed = getenv("FLASHLIB_B200_TC_NOSEED");
+    if (kp.n_tiles >= 1024 && !(noseed && atoi(noseed))) {
+        TcKernelParams sk = kp;
+        sk.nsplit = 1;
+        sk.tiles_per_split = 64;
+        sk.tile_stride = kp.n_tiles / 64;
+        sk.n_tiles = 64;
+        sk.dbg_scores = nullptr;
+        const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, true><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
+        FL_CHECK_LAUNCH();
+    }
     if (dbg != nullptr || kp.dbg_flags != 0) {
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<true><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<true, false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     } else {
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     }
     FL_CHECK_LAUNCH();
     return FL_OK;

@@ -37,7 +37,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // One attempt: the thread is suspended by the hardware until the phase completes or about
 // `hint_ns` have passed, so a waiting warp does not compete for issue slots with the warps
 // that share its scheduler.
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 1000u) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -54,12 +54,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // timeout (after raising the flag), so the caller can leave its loop and reach the
 // kernel's common exit, where TMEM is released.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns) {
-    if (mbar_try_wait(bar, parity)) return true;
+                                          uint64_t limit_ns, uint32_t hint_ns = 1000u) {
+    if (mbar_try_wait(bar, parity, hint_ns)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait(bar, parity, hint_ns)) return true;
         if ((++spins & 7u) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > limit_ns) {
