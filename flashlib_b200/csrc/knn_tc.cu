@@ -12,9 +12,10 @@
 // tile ever reaches global memory; a pool of K1 = 32 (score, row) pairs per query and
 // range is all that is written (published unsorted, up to 64 entries per query and range).
 //
-// Warp roles (320 threads): warps 0-7 epilogue in two warpgroups (group g takes accumulator
-// g, i.e. every other tile; warp w reads TMEM lanes 32(w%4)..32(w%4)+31, one query row per
-// thread, and keeps a pool per row), warp 8 TMA producer, warp 9 MMA issuer and TMEM owner.
+// Warp roles (320 threads): warps 0-7 epilogue in two warpgroups (group g takes columns
+// 128g..128g+127 of every accumulator; warp w reads TMEM lanes 32(w%4)..32(w%4)+31, one query
+// row per thread, and keeps a pool per row), warp 8 TMA producer, warp 9 MMA issuer and TMEM
+// owner.
 // Every wait is bounded; a wait that gives up raises a CTA-wide abort flag, records where
 // it happened in the status words and every role falls through to the common exit.
 #include "knn_internal.h"
@@ -29,7 +30,7 @@ using namespace tc;
 constexpr int TC_BM = 128;            // queries per tile (MMA M)
 constexpr int TC_BN = 256;            // database rows per tile (MMA N)
 constexpr int TC_BK = 64;             // bf16 features per shared-memory chunk (128 bytes)
-constexpr int TC_NWG = 2;             // epilogue warpgroups; group g owns accumulator g (every other tile)
+constexpr int TC_NWG = 2;             // epilogue warpgroups; group g owns columns 128g.. of every tile
 constexpr int TC_K1 = 12;             // entries a (query, warpgroup) pool keeps at compaction
 constexpr int TC_CAP = 32;            // pool capacity before compaction
 constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread); the extra slot is scratch
@@ -157,7 +158,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         for (int i = 0; i < TC_MAX_STAGES; ++i) { mbar_init(BAR(B_FULL + i), 1); mbar_init(BAR(B_EMPTY + i), 1); }
         mbar_init(BAR(B_AFULL), 1);
         mbar_init(BAR(B_AEMPTY), 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(BAR(B_TFULL + i), 1); mbar_init(BAR(B_TEMPTY + i), 4); }
+        for (int i = 0; i < 2; ++i) { mbar_init(BAR(B_TFULL + i), 1); mbar_init(BAR(B_TEMPTY + i), 4 * TC_NWG); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -285,8 +286,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
     } else {
         // ------------------------------ epilogue warps --------------------------------------
-        // warp = 4 * warpgroup + TMEM lane quarter; warpgroup g reads accumulator g, i.e. the
-        // tiles with tile_no % 2 == g, and keeps its own pool per query row.
+        // warp = 4 * warpgroup + TMEM lane quarter; warpgroup g reads columns 128g .. 128g+127 of
+        // every accumulator and keeps its own pool per query row.
         const int wg = warp >> 2, quarter = warp & 3;
         float* warp_sc = pool_sc + warp * 32 * TC_PSTR;
         uint32_t* warp_id = pool_id + warp * 32 * TC_PSTR;
@@ -312,9 +313,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const int nt = t1 - t0;
             const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
             for (int i = 0; i < nt; ++i, ++tile_no) {
-                if ((int)(tile_no & 1) != wg) continue;
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
-                const int b = wg;
+                const int b = tile_no & 1;
                 const long long c0 = clock64();
                 if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
@@ -323,8 +323,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
                 prof_tfull += clock64() - c0;
                 tc_fence_after_sync();
-                const uint32_t tile_taddr = lane_taddr + b * TC_BN;
-                const uint32_t row_base = (uint32_t)t * TC_BN;
+                // this warpgroup's half of the accumulator columns / of the tile's database rows
+                const uint32_t tile_taddr = lane_taddr + b * TC_BN + wg * (TC_BN / TC_NWG);
+                const uint32_t row_base = (uint32_t)t * TC_BN + wg * (TC_BN / TC_NWG);
 
                 // Pass 1, branch free: stream the 256 scores of this thread's query row through
                 // registers, 64 columns per wait, and note which groups of 8 columns hold a score
@@ -345,20 +346,6 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     reg_fence32(vb);
                     tmem_ld_32x32b_x32(tile_taddr + 64, vc);
                     tmem_ld_32x32b_x32(tile_taddr + 96, vd);
-                    fold(va);
-                    fold(vb);
-                    tmem_ld_wait();
-                    reg_fence32(vc);
-                    reg_fence32(vd);
-                    tmem_ld_32x32b_x32(tile_taddr + 128, va);
-                    tmem_ld_32x32b_x32(tile_taddr + 160, vb);
-                    fold(vc);
-                    fold(vd);
-                    tmem_ld_wait();
-                    reg_fence32(va);
-                    reg_fence32(vb);
-                    tmem_ld_32x32b_x32(tile_taddr + 192, vc);
-                    tmem_ld_32x32b_x32(tile_taddr + 224, vd);
                     fold(va);
                     fold(vb);
                     tmem_ld_wait();
@@ -404,22 +391,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     tmem_ld_wait();
                     reg_fence32(vc);
                     reg_fence32(vd);
-                    tmem_ld_32x32b_x32(tile_taddr + 128, va);
-                    tmem_ld_32x32b_x32(tile_taddr + 160, vb);
                     scan(vc, 2);
                     scan(vd, 3);
-                    tmem_ld_wait();
-                    reg_fence32(va);
-                    reg_fence32(vb);
-                    tmem_ld_32x32b_x32(tile_taddr + 192, vc);
-                    tmem_ld_32x32b_x32(tile_taddr + 224, vd);
-                    scan(va, 4);
-                    scan(vb, 5);
-                    tmem_ld_wait();
-                    reg_fence32(vc);
-                    reg_fence32(vd);
-                    scan(vc, 6);
-                    scan(vd, 7);
                 }
                 if (DBG && (p.dbg_flags & 1)) hits = 0;
 
