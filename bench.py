@@ -36,6 +36,9 @@ DIM = 128
 QUERIES_PER_GPU = 10_000
 N_COMP = 4096
 SEED = 2
+# dram__bytes_read.sum + dram__bytes_write.sum of one knn_tc_kernel launch on this workload (ncu capture
+# summarised in profiles/knn_tc_kernel_knn_1m.md); None until measured
+TC_KERNEL_DRAM_BYTES_PER_LAUNCH = 768_034_048
 METRIC = "exact_knn_queries_per_sec"
 UNIT = "queries/s"
 
@@ -56,54 +59,60 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons of one GPU through NVML (read-only)
+    every few milliseconds while the timed region runs."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
+    def __init__(self, cuda_index: int):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = False
+        self._thread = None
+        self.error = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            pr = torch.cuda.get_device_properties(cuda_index)
+            bus = f"{getattr(pr, 'pci_domain_id', 0):08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            self.h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # noqa: BLE001
+            self.error = f"NVML unavailable: {e}"
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception as e:  # noqa: BLE001
+                self.error = str(e)
+                break
+            time.sleep(0.004)
 
     def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
-                                         stdout=self.out, stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+        if self.error:
+            return
+        import threading
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.out.close()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        with open(self.path) as f:
-            for line in f:
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
-                    continue
-                try:
-                    sm.append(float(parts[1]))
-                    smax.append(float(parts[2]))
-                except ValueError:
-                    continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-        os.unlink(self.path)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self._thread is not None:
+            self._stop = True
+            self._thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0,
+                    "reasons": [self.error or "no samples"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples),
+                "sm_max_mhz": self.max_mhz, "samples": len(self.samples), "reasons": sorted(self.reasons)}
 
 
 def make_workload(rank: int, world: int):
@@ -157,14 +166,69 @@ def run_reference(args, rank: int, world: int):
     print(json.dumps(line), flush=True)
 
 
+def _time_steps(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_secondary(args):
+    """Single-GPU timings of the other configurations (k-means 1M x 128 / K=1024 / 20 Lloyd
+    iterations; IVF-Flat search nlist=1024, nprobe=16; exact kNN with k=100)."""
+    import flashlib_b200 as fl
+    from flashlib_b200 import synthetic
+    torch.cuda.set_device(0)
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    if args.workload == "knn_1m_k100":
+        X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
+        Xd, Qd = X.cuda(), Q.cuda()
+        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, 100), steps, warm)
+        line = {"workload": "knn_1m_k100", "metric": "exact_knn_queries_per_sec", "value": QUERIES_PER_GPU / (ms * 1e-3),
+                "unit": "queries/s", "ms_per_step": ms, "config": {"k": 100, "path": "exact fp32 CUDA-core scoring"}}
+    elif args.workload == "kmeans_1m":
+        cfg = synthetic.CONFIGS["kmeans_1m"]
+        X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
+        Xd = X.cuda()
+        init = Xd[:cfg["K"]].clone()
+        ms = _time_steps(lambda: fl.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init), steps, warm)
+        flop = 2.0 * cfg["n"] * cfg["K"] * cfg["d"] * cfg["iters"]
+        line = {"workload": "kmeans_1m", "metric": "kmeans_20_iterations_ms", "value": ms, "unit": "ms", "ms_per_step": ms,
+                "higher_is_better": False, "algorithmic_tflops": flop / (ms * 1e-3) / 1e12,
+                "config": {"n": cfg["n"], "d": cfg["d"], "K": cfg["K"], "iters": cfg["iters"], "init": "first K rows"}}
+    else:
+        cfg = synthetic.CONFIGS["ivf_1m"]
+        X, Q = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"], nq=cfg["nq"], clamp=True)
+        Xd, Qd = X.cuda(), Q.cuda()
+        ivf = fl.IVFFlat(nlist=cfg["nlist"], nprobe=cfg["nprobe"], niter=10, seed=cfg["seed"]).fit(Xd)
+        ms = _time_steps(lambda: ivf.kneighbors(Qd, cfg["k"]), steps, warm)
+        _, bi = fl.flash_knn(Qd[:1000], Xd, cfg["k"])
+        _, ii = ivf.kneighbors(Qd[:1000], cfg["k"])
+        recall = float(np.mean([len(set(a.tolist()) & set(b.tolist())) / cfg["k"] for a, b in zip(ii.cpu().numpy(), bi.cpu().numpy())]))
+        line = {"workload": "ivf_1m", "metric": "ivf_flat_queries_per_sec", "value": cfg["nq"] / (ms * 1e-3), "unit": "queries/s",
+                "ms_per_step": ms, "recall_at_10_vs_exact": recall,
+                "config": {"nlist": cfg["nlist"], "nprobe": cfg["nprobe"], "k": cfg["k"], "max_list_len": ivf.index_.max_list_len}}
+    line.update({"n_gpus": 1, "steps": steps, "warmup": warm, "data": "synthetic"})
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_1m_k100", "kmeans_1m", "ivf_1m"],
+                    help="knn_1m is the headline benchmark; the others time the remaining configurations on one GPU "
+                         "and print a shorter JSON line")
     ap.add_argument("--db-rows", type=int, default=None, help="with --profile-case: database rows")
     ap.add_argument("--queries", type=int, default=None, help="with --profile-case: queries per GPU")
     ap.add_argument("--profile-case", action="store_true",
@@ -182,6 +246,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "knn_1m":
+        run_secondary(args)
         return
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
@@ -286,7 +353,7 @@ def main():
         peak = peaks["bf16_tflops"]
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": (achieved / peak) if achieved else None, "traffic": None,
+            "frac": (achieved / peak) if achieved else None, "traffic": TC_KERNEL_DRAM_BYTES_PER_LAUNCH if resolved == _lib.FL_KNN_BF16_RERANK and not args.profile_case and world == 1 else None,
             "kernel": "knn_tc_kernel" if resolved == _lib.FL_KNN_BF16_RERANK else "knn_simt_kernel",
             "kernel_ms": k_ms, "launches_timed": len(kernel_ms),
             "algorithmic_flop_per_launch": flop_per_launch,

@@ -121,6 +121,57 @@ __device__ __forceinline__ void warp_sort_desc(float (&key)[NPL], uint32_t (&id)
     }
 }
 
+// Merges two DESCENDING sequences of NPL*32 (key, id) pairs (same position layout as
+// warp_sort_desc) and leaves the NPL*32 largest of their union in (ka, ia), descending.
+// Position p of the result is first max(a[p], b[N-1-p]) -- that picks the N largest and
+// forms a bitonic sequence -- which the final stages of the bitonic network then sort.
+template <int NPL, bool TIEBREAK>
+__device__ __forceinline__ void warp_merge_desc(float (&ka)[NPL], uint32_t (&ia)[NPL], const float (&kb)[NPL],
+                                                const uint32_t (&ib)[NPL]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const float ok = __shfl_sync(FULL_MASK, kb[NPL - 1 - r], 31 - lane);
+        const uint32_t oi = __shfl_sync(FULL_MASK, ib[NPL - 1 - r], 31 - lane);
+        bool take = ok > ka[r];
+        if (TIEBREAK) take = take || (ok == ka[r] && oi < ia[r]);
+        if (take) { ka[r] = ok; ia[r] = oi; }
+    }
+    constexpr int k = NPL * 32;
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+        if (j >= 32) {
+            const int jr = j >> 5;
+#pragma unroll
+            for (int r = 0; r < NPL; ++r) {
+                const int pr = r ^ jr;
+                if (pr > r) {
+                    const float a = ka[r], b = ka[pr];
+                    const uint32_t xa = ia[r], xb = ia[pr];
+                    bool a_lt_b = a < b;
+                    if (TIEBREAK) a_lt_b = a_lt_b || (a == b && xa > xb);
+                    if (a_lt_b) { ka[r] = b; ka[pr] = a; ia[r] = xb; ia[pr] = xa; }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < NPL; ++r) {
+                const float ok = __shfl_xor_sync(FULL_MASK, ka[r], j);
+                const uint32_t oi = __shfl_xor_sync(FULL_MASK, ia[r], j);
+                const bool lower = (lane & j) == 0;       // the lower position keeps the larger key
+                bool o_gt = ok > ka[r];
+                bool o_lt = ok < ka[r];
+                if (TIEBREAK) {
+                    o_gt = o_gt || (ok == ka[r] && oi < ia[r]);
+                    o_lt = o_lt || (ok == ka[r] && oi > ia[r]);
+                }
+                const bool take = lower ? o_gt : o_lt;
+                if (take) { ka[r] = ok; ia[r] = oi; }
+            }
+        }
+    }
+}
+
 // Compacts one row's candidate pool: reads `cnt` (score, id) entries from sc/idv (any
 // address space), keeps the K1 best (largest score) at positions [0, K1) in descending
 // order and returns the new threshold: the K1-th best score, or -inf while fewer than

@@ -218,12 +218,12 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
     if (slot >= count) return;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
-    constexpr int N2 = 2 * NPL1;
     const int K1 = p.K1;
 
-    // 1. merge the split pools: keep the K1 best scores.
-    float key[N2];
-    uint32_t id[N2];
+    // 1. merge the split pools: keep the K1 best scores.  Every pool is sorted on its own and
+    //    merged into the running list with one bitonic merge step.
+    float key[NPL1], kin[NPL1];
+    uint32_t id[NPL1], iin[NPL1];
 #pragma unroll
     for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
     const float* psc = p.part_sc + slot * p.nsplit * (int64_t)K1;
@@ -234,10 +234,11 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
             const int e = (r << 5) | lane;
             const uint32_t cid = pid[(int64_t)s * K1 + e];
             const bool real = cid < (uint32_t)p.m;   // padding rows of the operand plane never count
-            key[NPL1 + r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
-            id[NPL1 + r] = real ? cid : INVALID_ID;
+            kin[r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
+            iin[r] = real ? cid : INVALID_ID;
         }
-        warp_sort_desc<N2, false>(key, id);
+        warp_sort_desc<NPL1, false>(kin, iin);
+        warp_merge_desc<NPL1, false>(key, id, kin, iin);
     }
     // Upper bound on the score of every row that is not among the K1 entries kept here: the
     // K1-th kept score covers what this merge dropped, the published thresholds cover what
