@@ -49,12 +49,12 @@ struct TcSmemPlan {
     int off_a, off_b, off_pool_sc, off_pool_id, off_hbuf, off_bar, bytes;
 };
 
-static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit) {
+static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, bool pools = true) {
     TcSmemPlan s{};
     s.nkc = d_pad / TC_BK;
     int cur = 0;
     s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
-    const int pool = TC_NWG * TC_BM * TC_PSTR * 4;
+    const int pool = pools ? TC_NWG * TC_BM * TC_PSTR * 4 : 0;   // the assignment mode keeps no pools
     const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
     int ns = (smem_limit - fixed) / TC_B_STAGE;
     if (ns > TC_MAX_STAGES) ns = TC_MAX_STAGES;
@@ -83,6 +83,7 @@ struct TcKernelParams {
     float* part_sc; uint32_t* part_id;
     float* tau;
     float* part_tau;
+    float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
     int tile_stride;         // database tile actually read for loop index t is t * tile_stride (1 outside seeding)
@@ -125,11 +126,17 @@ __device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
     }
 }
 
-// SEED = true turns the kernel into the threshold-seeding pass: it scans a strided sample of
+// MODE 1 (TC_MODE_SEED) turns the kernel into the threshold-seeding pass: it scans a strided sample of
 // the database tiles and, instead of pools, keeps 16 running maxima per query row over
 // disjoint column classes; their minimum is a score that 16 distinct rows reach, i.e. a valid
 // starting threshold that spares the main pass most of its cold-start appends.
-template <bool DBG, bool SEED>
+//
+// MODE 2 (TC_MODE_ASSIGN) is the k-means assignment: the "database" is the (small) centroid
+// set, every row only needs its best centroid, so each thread keeps the best and second-best
+// score of its row in registers (the column index rides in the low 7 mantissa bits of the
+// score) and no pool is touched.
+constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2;
+template <bool DBG, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
               const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_db_aug,
@@ -310,6 +317,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             float cls[16];
 #pragma unroll
             for (int c = 0; c < 16; ++c) cls[c] = neg_inf();
+            float b1 = neg_inf(), b2 = neg_inf();   // assignment mode: best / second-best packed score
+            int tbest = 0;                           // tile that produced b1
             const int nt = t1 - t0;
             const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
             for (int i = 0; i < nt; ++i, ++tile_no) {
@@ -333,6 +342,39 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 // tcgen05.wait::ld waits for every load in flight, so while one batch of 64
                 // columns is reduced the next one is already on its way.
                 uint32_t va[32], vb[32], vc[32], vd[32];
+                constexpr bool SEED = (MODE == TC_MODE_SEED);
+                if (MODE == TC_MODE_ASSIGN) {
+                    const float b1_before = b1;
+                    auto top2 = [&](uint32_t (&v)[32], int slice) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            const float x = __uint_as_float((v[j] & 0xFFFFFF80u) | (uint32_t)(slice * 32 + j));
+                            const float y = __uint_as_float((v[j + 1] & 0xFFFFFF80u) | (uint32_t)(slice * 32 + j + 1));
+                            const float hi = fmaxf(x, y), lo = fminf(x, y);
+                            b2 = fmax3(b2, lo, fminf(b1, hi));
+                            b1 = fmaxf(b1, hi);
+                        }
+                    };
+                    tmem_ld_32x32b_x32(tile_taddr, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 32, vb);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 64, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 96, vd);
+                    top2(va, 0);
+                    top2(vb, 1);
+                    tmem_ld_wait();
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    top2(vc, 2);
+                    top2(vd, 3);
+                    if (b1 != b1_before) tbest = t;
+                    continue;
+                }
                 if (SEED) {
                     auto fold = [&](uint32_t (&v)[32]) {
 #pragma unroll
@@ -514,7 +556,14 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
             }
             if (!ok) break;
-            if (SEED) {
+            if (MODE == TC_MODE_ASSIGN) {
+                const int64_t o = qrow * TC_NWG + wg;
+                p.asg_sc[2 * o] = b1;
+                p.asg_sc[2 * o + 1] = b2;
+                p.asg_id[o] = (uint32_t)tbest * TC_BN + wg * (TC_BN / TC_NWG) + (__float_as_uint(b1) & 0x7Fu);
+                continue;
+            }
+            if (MODE == TC_MODE_SEED) {
                 float m = cls[0];
 #pragma unroll
                 for (int c = 1; c < 16; ++c) m = fminf(m, cls[c]);
@@ -677,16 +726,16 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         sk.n_tiles = 64;
         sk.dbg_scores = nullptr;
         const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, true><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_SEED><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
         FL_CHECK_LAUNCH();
     }
     if (dbg != nullptr || kp.dbg_flags != 0) {
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<true, false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<true, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     } else {
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, false><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     }
     FL_CHECK_LAUNCH();
     return FL_OK;
@@ -695,6 +744,36 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
 int tc_prof_read(unsigned long long* host_out, int words) {
     const size_t n = sizeof(unsigned long long) * (size_t)(words < 160 * TC_PROF_WORDS ? words : 160 * TC_PROF_WORDS);
     FL_CHECK_CUDA(cudaMemcpyFromSymbol(host_out, g_tc_prof, n));
+    return FL_OK;
+}
+
+// Assignment launch: queries = sample rows, database = centroids; writes per (row, warpgroup)
+// the best and second-best score and the best centroid.
+int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cudaStream_t st) {
+    FL_CHECK_ARG(p.qplane && p.dbrows && asg_sc && asg_id && p.tau, "tensor-core assignment launch with a null buffer");
+    CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
+    const int pitch = p.d_pad + PLANE_AUG_COLS;
+    int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
+    if (rc == FL_OK) rc = make_map_bf16(&map_q_aug, p.qplane, p.nq_pad, pitch, PLANE_AUG_COLS, TC_BM);
+    if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
+    if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
+    if (rc != FL_OK) return rc;
+    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), false);
+    if (sp.nstage < 2) { set_error("tensor-core assignment: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
+    TcKernelParams kp{};
+    kp.n_qtiles = (int)(p.nq_pad / TC_BM);
+    kp.n_tiles = (int)(p.m_pad / TC_BN);
+    kp.nsplit = 1;
+    kp.tiles_per_split = kp.n_tiles;
+    kp.nkc = sp.nkc; kp.nstage = sp.nstage;
+    kp.off_b = sp.off_b; kp.off_pool_sc = sp.off_pool_sc; kp.off_pool_id = sp.off_pool_id; kp.off_bar = sp.off_bar;
+    kp.nq_pad = p.nq_pad; kp.tau = p.tau; kp.status = p.status;
+    kp.asg_sc = asg_sc; kp.asg_id = asg_id;
+    kp.tile_stride = 1; kp.wait_hint_ns = 1000u;
+    const int grid = kp.n_qtiles < sm_count() ? kp.n_qtiles : sm_count();
+    FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_ASSIGN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+    knn_tc_kernel<false, TC_MODE_ASSIGN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    FL_CHECK_LAUNCH();
     return FL_OK;
 }
 
