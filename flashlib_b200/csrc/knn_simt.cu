@@ -210,6 +210,20 @@ int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) 
 
 // ------------------------------------------------------------------------------------
 // Finalisation: one warp per query slot.
+//
+// Input: `nsplit` published pools of K1 (score, row) entries per slot, and (tensor-core path)
+// the thresholds of the scoring pass: every row it did not publish scored at most u = the
+// largest threshold.  Output: the k rows of least exact fp32 distance among the candidates,
+// ordered by (distance, row).  With verification on, the result is accepted only when the k-th
+// exact distance lies below qsq - 2 (bound + eps), where `bound` is an upper bound on the
+// score of every row that was not re-scored exactly; otherwise the slot is queued for the
+// exact path.
+//
+// Candidates are taken in two attempts.  The first keeps only scores above u (entries at or
+// below u can never satisfy the proof) and at or above a floor f0 chosen so that a few dozen
+// entries survive, which are sorted once; dropped entries scored at most max(u, f0).  If that
+// set cannot be proven (or overflows), the second attempt sorts every pool and merges the K1
+// best, with bound = max(u, K1-th best).
 // ------------------------------------------------------------------------------------
 template <int NPL1>
 __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
@@ -219,41 +233,16 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     if (slot >= count) return;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
     const int K1 = p.K1;
-
-    // 1. merge the split pools: keep the K1 best scores.  Every pool is sorted on its own and
-    //    merged into the running list with one bitonic merge step.
-    float key[NPL1], kin[NPL1];
-    uint32_t id[NPL1], iin[NPL1];
-#pragma unroll
-    for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
     const float* psc = p.part_sc + slot * p.nsplit * (int64_t)K1;
     const uint32_t* pid = p.part_id + slot * p.nsplit * (int64_t)K1;
-    for (int s = 0; s < p.nsplit; ++s) {
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) {
-            const int e = (r << 5) | lane;
-            const uint32_t cid = pid[(int64_t)s * K1 + e];
-            const bool real = cid < (uint32_t)p.m;   // padding rows of the operand plane never count
-            kin[r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
-            iin[r] = real ? cid : INVALID_ID;
-        }
-        warp_sort_desc<NPL1, false>(kin, iin);
-        warp_merge_desc<NPL1, false>(key, id, kin, iin);
-    }
-    // Upper bound on the score of every row that is not among the K1 entries kept here: the
-    // K1-th kept score covers what this merge dropped, the published thresholds cover what
-    // the scoring pass never published.
-    float bound = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID
-                      ? __shfl_sync(FULL_MASK, key[NPL1 - 1], 31) : neg_inf();
+
+    float u = neg_inf();
     if (p.part_tau != nullptr) {
-        float u = neg_inf();
         for (int i = lane; i < p.ntau; i += 32) u = fmaxf(u, p.part_tau[slot * p.ntau + i]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
-        bound = fmaxf(bound, u);
     }
 
-    // 2. exact fp32 distances of the first `rerank` pool entries.
     const float* qp = p.q + qi * p.ldq;
     float qsq = 0.f;
     if (p.vec) {
@@ -266,94 +255,199 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
-
-    float dist[NPL1];
-#pragma unroll
-    for (int r = 0; r < NPL1; ++r) {
-        dist[r] = pos_inf();
-        for (int l0 = 0; l0 < 32; l0 += 4) {
-            if ((r << 5) + l0 >= p.rerank) break;
-            uint32_t cid[4];
-            float a[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                cid[u] = __shfl_sync(FULL_MASK, id[r], l0 + u);
-                if ((r << 5) + l0 + u >= p.rerank) cid[u] = INVALID_ID;
-                a[u] = 0.f;
-            }
-            if (p.vec) {
-                for (int c = lane * 4; c < p.d; c += 128) {
-                    const float4 qv = __ldg(reinterpret_cast<const float4*>(qp + c));
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (cid[u] != INVALID_ID) {
-                            const float4 xv = __ldg(
-                                reinterpret_cast<const float4*>(p.db + (int64_t)cid[u] * p.ldb + c));
-                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z,
-                                        d3 = qv.w - xv.w;
-                            a[u] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
-                        }
-                    }
-                }
-            } else {
-                for (int c = lane; c < p.d; c += 32) {
-                    const float qv = __ldg(qp + c);
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (cid[u] != INVALID_ID) {
-                            const float df = qv - __ldg(p.db + (int64_t)cid[u] * p.ldb + c);
-                            a[u] += df * df;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) a[u] += __shfl_xor_sync(FULL_MASK, a[u], o);
-                if (lane == l0 + u && cid[u] != INVALID_ID) dist[r] = a[u];
-            }
-        }
-    }
-
-    // 3. order by (exact distance, row) ascending and write the first k.
-    float k2[NPL1];
-    uint32_t id2[NPL1];
-#pragma unroll
-    for (int r = 0; r < NPL1; ++r) {
-        const bool ok = dist[r] < pos_inf();
-        k2[r] = ok ? -dist[r] : neg_inf();
-        id2[r] = ok ? id[r] : INVALID_ID;
-    }
-    warp_sort_desc<NPL1, true>(k2, id2);
-    float dk = pos_inf();
-#pragma unroll
-    for (int r = 0; r < NPL1; ++r) {
-        const int e = (r << 5) | lane;
-        if (e < p.k) {
-            const bool ok = id2[r] != INVALID_ID;
-            p.out_dist[qi * p.k + e] = ok ? -k2[r] : pos_inf();
-            p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)id2[r] + p.row_offset) : -1;
-        }
-        if (((p.k - 1) >> 5) == r) {
-            const float v = __shfl_sync(FULL_MASK, k2[r], (p.k - 1) & 31);
-            dk = (v > neg_inf()) ? -v : pos_inf();
-        }
-    }
-
-    // 4. verification: every row outside the pool scored <= bound, so its exact distance is
-    //    at least qsq - 2 (bound + eps).  The result is proven when the k-th exact distance
-    //    is below that bound; otherwise the row is queued for the exact path.
-    if (p.verify && bound > neg_inf()) {
+    float eps = 0.f, slack = 0.f;
+    if (p.verify) {
         const float mn = __ldg(p.maxnorm);
-        const float eps = p.eps_rel * sqrtf(qsq) * mn;
-        const float lb = qsq - 2.f * (bound + eps);
-        const float slack = 1e-5f * (qsq + mn * mn);
-        const bool ok = dk < lb - slack;
-        if (!ok && lane == 0) {
+        eps = p.eps_rel * sqrtf(qsq) * mn;
+        slack = 1e-5f * (qsq + mn * mn);
+    }
+
+    constexpr bool HAS_FILTER = NPL1 <= 2;
+    __shared__ float s_sc[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
+    __shared__ uint32_t s_id[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
+    const bool try_filter = HAS_FILTER && p.verify && p.part_tau != nullptr && u > neg_inf();
+
+    for (int attempt = try_filter ? 0 : 1; attempt < 2; ++attempt) {
+        float key[NPL1];
+        uint32_t id[NPL1];
+        float bound;
+        if (attempt == 0) {
+            // Each lane notes the best score it meets; the (k+14)-th largest of the 32 lane maxima
+            // is a floor with at least k+14 entries at or above it and, scores being spread evenly
+            // over the lanes, rarely more than fit the list.  Pool slots are ordered (best kept
+            // entries first), so the slot a lane reads rotates from pool to pool.
+            float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
+            uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
+            float lmax = neg_inf();
+            for (int s = 0; s < p.nsplit; ++s) {
+#pragma unroll
+                for (int r = 0; r < NPL1; ++r) {
+                    const int e = (r << 5) | ((lane + 5 * s + 16 * r) & 31);
+                    const float sc = psc[(int64_t)s * K1 + e];
+                    if (pid[(int64_t)s * K1 + e] < (uint32_t)p.m) lmax = fmaxf(lmax, sc);
+                }
+            }
+            int rank = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float o = __shfl_sync(FULL_MASK, lmax, j);
+                rank += (o > lmax || (o == lmax && j < lane)) ? 1 : 0;
+            }
+            const int want = p.k + 14 < 32 ? p.k + 14 : 32;
+            const unsigned sel = __ballot_sync(FULL_MASK, rank == want - 1);
+            const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
+            const unsigned lt = (1u << lane) - 1u;
+            int total = 0;
+            for (int s = 0; s < p.nsplit; ++s) {
+#pragma unroll
+                for (int r = 0; r < NPL1; ++r) {
+                    const int e = (r << 5) | lane;
+                    const float sc = psc[(int64_t)s * K1 + e];
+                    const bool pass = sc > u && sc >= f0;
+                    const uint32_t cid = pass ? pid[(int64_t)s * K1 + e] : INVALID_ID;
+                    const bool keep = pass && cid < (uint32_t)p.m;
+                    const unsigned mask = __ballot_sync(FULL_MASK, keep);
+                    const int pos = total + __popc(mask & lt);
+                    if (keep && pos < 32 * NPL1) { wsc[pos] = sc; wid[pos] = cid; }
+                    total += __popc(mask);
+                }
+            }
+            __syncwarp();
+            if (total > 32 * NPL1) continue;
+#pragma unroll
+            for (int r = 0; r < NPL1; ++r) {
+                const int e = (r << 5) | lane;
+                key[r] = e < total ? wsc[e] : neg_inf();
+                id[r] = e < total ? wid[e] : INVALID_ID;
+            }
+            __syncwarp();
+            warp_sort_desc<NPL1, false>(key, id);
+            bound = fmaxf(u, f0);
+        } else {
+            // Every pool is sorted on its own and merged into the running list with one bitonic
+            // merge step.  The K1-th kept score covers what this merge dropped.
+            float kin[NPL1];
+            uint32_t iin[NPL1];
+#pragma unroll
+            for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
+            for (int s = 0; s < p.nsplit; ++s) {
+#pragma unroll
+                for (int r = 0; r < NPL1; ++r) {
+                    const int e = (r << 5) | lane;
+                    const uint32_t cid = pid[(int64_t)s * K1 + e];
+                    const bool real = cid < (uint32_t)p.m;   // padding rows of the operand plane never count
+                    kin[r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
+                    iin[r] = real ? cid : INVALID_ID;
+                }
+                warp_sort_desc<NPL1, false>(kin, iin);
+                warp_merge_desc<NPL1, false>(key, id, kin, iin);
+            }
+            bound = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID
+                        ? __shfl_sync(FULL_MASK, key[NPL1 - 1], 31) : neg_inf();
+            bound = fmaxf(bound, u);
+        }
+
+        // Exact fp32 distances of the first `rerank` entries, best score first.  With
+        // verification on, the walk stops as soon as k of the exact distances seen so far lie
+        // below the lower bound that the next entry's score (and `bound`) puts on every row not
+        // yet re-scored.
+        bool stop = false;
+        float dist[NPL1];
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) dist[r] = pos_inf();
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            for (int l0 = 0; l0 < 32; l0 += 4) {
+                if (stop || (r << 5) + l0 >= p.rerank) break;
+                if (p.verify && (l0 & 7) == 0 && (r << 5) + l0 >= ((p.k + 7) & ~7)) {
+                    const float nxt = __shfl_sync(FULL_MASK, key[r], l0);
+                    const float T = qsq - 2.f * (fmaxf(nxt, bound) + eps) - slack;
+                    int cnt = 0;
+#pragma unroll
+                    for (int rr = 0; rr < NPL1; ++rr) cnt += __popc(__ballot_sync(FULL_MASK, dist[rr] < T));
+                    if (cnt >= p.k) { stop = true; bound = fmaxf(bound, nxt); break; }
+                }
+                uint32_t cid[4];
+                float a[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    cid[t] = __shfl_sync(FULL_MASK, id[r], l0 + t);
+                    if ((r << 5) + l0 + t >= p.rerank) cid[t] = INVALID_ID;
+                    a[t] = 0.f;
+                }
+                if (p.vec) {
+                    for (int c = lane * 4; c < p.d; c += 128) {
+                        const float4 qv = __ldg(reinterpret_cast<const float4*>(qp + c));
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            if (cid[t] != INVALID_ID) {
+                                const float4 xv = __ldg(
+                                    reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
+                                const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z,
+                                            d3 = qv.w - xv.w;
+                                a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                            }
+                        }
+                    }
+                } else {
+                    for (int c = lane; c < p.d; c += 32) {
+                        const float qv = __ldg(qp + c);
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            if (cid[t] != INVALID_ID) {
+                                const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
+                                a[t] += df * df;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
+                    if (lane == l0 + t && cid[t] != INVALID_ID) dist[r] = a[t];
+                }
+            }
+        }
+
+        // Order by (exact distance, row) ascending.
+        float k2[NPL1];
+        uint32_t id2[NPL1];
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            const bool ok = dist[r] < pos_inf();
+            k2[r] = ok ? -dist[r] : neg_inf();
+            id2[r] = ok ? id[r] : INVALID_ID;
+        }
+        warp_sort_desc<NPL1, true>(k2, id2);
+        float dk = pos_inf();
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            if (((p.k - 1) >> 5) == r) {
+                const float v = __shfl_sync(FULL_MASK, k2[r], (p.k - 1) & 31);
+                dk = (v > neg_inf()) ? -v : pos_inf();
+            }
+        }
+
+        // Verification: every row that was not re-scored has a score <= bound, so its exact
+        // distance is at least qsq - 2 (bound + eps).
+        bool proven = true;
+        if (p.verify && bound > neg_inf()) proven = dk < qsq - 2.f * (bound + eps) - slack;
+        if (!proven && attempt == 0) continue;
+#pragma unroll
+        for (int r = 0; r < NPL1; ++r) {
+            const int e = (r << 5) | lane;
+            if (e < p.k) {
+                const bool ok = id2[r] != INVALID_ID;
+                p.out_dist[qi * p.k + e] = ok ? -k2[r] : pos_inf();
+                p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)id2[r] + p.row_offset) : -1;
+            }
+        }
+        if (!proven && lane == 0) {
             const int i = atomicAdd(p.fb_count, 1);
             if (i < p.fb_cap) p.fb_list[i] = (int)qi;
         }
+        break;
     }
 }
 

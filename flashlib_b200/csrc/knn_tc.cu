@@ -668,7 +668,10 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_pe
     int64_t max_s = n_tiles / 8;
     if (max_s > 64) max_s = 64;
     if (max_s < 1) max_s = 1;
-    double best_eff = -1.0;
+    // Estimated run time in tile units: every SM works through `waves` items of `tps` tiles plus
+    // a fixed cost per item (query tile load, pipeline fill and drain, pool publication).
+    constexpr int64_t ITEM_OVERHEAD_TILES = 8;
+    int64_t best_cost = -1;
     int64_t best_s = 1;
     for (int64_t s = 1; s <= max_s; ++s) {
         const int64_t tps = ceil_div(n_tiles, s);
@@ -676,9 +679,8 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_pe
         const int64_t items = n_qtiles * s_eff;
         const int64_t grid = items < sms ? items : sms;
         const int64_t waves = ceil_div(items, grid);
-        // SMs busy over the run, counting idle SMs when there are fewer items than SMs
-        const double eff = (double)items / (double)(waves * sms);
-        if (eff > best_eff * 1.02) { best_eff = eff; best_s = s_eff; }
+        const int64_t cost = waves * (tps + ITEM_OVERHEAD_TILES);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s_eff; }
     }
     *tiles_per_split = ceil_div(n_tiles, best_s);
     *nsplit = (int)ceil_div(n_tiles, *tiles_per_split);
@@ -715,15 +717,18 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     const int items = kp.n_qtiles * kp.nsplit;
     const int grid = items < sm_count() ? items : sm_count();
     kp.tile_stride = 1;
-    // Threshold seeding on a strided sample of 64 tiles when the database is large enough for
-    // the cold start of the pools to matter.
+    // Threshold seeding on a strided sample of one tile in 16 (at most 64 tiles) when the
+    // database is large enough for the cold start of the pools to matter.
     const char* noseed = getenv("FLASHLIB_B200_TC_NOSEED");
-    if (kp.n_tiles >= 1024 && !(noseed && atoi(noseed))) {
+    int seed_tiles = kp.n_tiles >= 1024 ? 64 : kp.n_tiles / 16;
+    if (const char* e = getenv("FLASHLIB_B200_TC_SEED_TILES")) seed_tiles = atoi(e);
+    if (seed_tiles > kp.n_tiles / 2) seed_tiles = kp.n_tiles / 2;
+    if (seed_tiles >= 16 && !(noseed && atoi(noseed))) {
         TcKernelParams sk = kp;
         sk.nsplit = 1;
-        sk.tiles_per_split = 64;
-        sk.tile_stride = kp.n_tiles / 64;
-        sk.n_tiles = 64;
+        sk.tiles_per_split = seed_tiles;
+        sk.tile_stride = kp.n_tiles / seed_tiles;
+        sk.n_tiles = seed_tiles;
         sk.dbg_scores = nullptr;
         const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));

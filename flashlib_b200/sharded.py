@@ -29,16 +29,20 @@ def shard_bounds(m: int, world: int, rank: int) -> Tuple[int, int]:
 
 def gather_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
     """All-gathers ``(nq, k)`` candidates from every rank into ``(nq, world * k)`` tensors
-    (rank-major along the candidate axis)."""
+    (rank-major along the candidate axis).  Distances (fp32 bits) and row ids (int32) travel in
+    one int32 message per rank."""
     world = dist.get_world_size(group)
     nq, k = local_d.shape
-    gd = torch.empty((world, nq, k), dtype=local_d.dtype, device=local_d.device)
-    gi = torch.empty((world, nq, k), dtype=local_i.dtype, device=local_i.device)
-    # list form: supported by both the nccl and the gloo backend
-    dist.all_gather(list(gd.unbind(0)), local_d.contiguous(), group=group)
-    dist.all_gather(list(gi.unbind(0)), local_i.contiguous(), group=group)
-    cand_d = gd.permute(1, 0, 2).reshape(nq, world * k)
-    cand_i = gi.permute(1, 0, 2).reshape(nq, world * k)
+    packed = torch.cat([local_d.contiguous().view(torch.int32), local_i.to(torch.int32)], dim=1).contiguous()
+    g = torch.empty((world, nq, 2 * k), dtype=torch.int32, device=local_d.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(g, packed, group=group)
+    else:
+        # list form: the gloo backend has no tensor form
+        dist.all_gather(list(g.unbind(0)), packed, group=group)
+    g = g.permute(1, 0, 2)
+    cand_d = g[:, :, :k].reshape(nq, world * k).view(torch.float32)
+    cand_i = g[:, :, k:].reshape(nq, world * k)
     return cand_d, cand_i
 
 
