@@ -80,7 +80,7 @@ struct KnnWs {
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
     int64_t nq_pad; int d_pad; int fb_cap;
-    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_tau, off_cnt, off_fblist,
+    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_tau, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
 };
 
@@ -115,6 +115,7 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
         w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
         w.off_part_tau = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
+        w.off_part_cnt = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_tau = take(cur, w.nq_pad * 4);
         w.off_cnt = take(cur, 1024);
         w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
@@ -320,6 +321,8 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
     tp.tau = tau; tp.status = status;
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
+    tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
+    tp.k = k;
     profile_begin(st);
     rc = launch_knn_tc(tp, st);
     profile_end(st);
@@ -337,7 +340,8 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     fp.verify = 1; fp.eps_rel = 0.004f;  // 2^-8 operand rounding of both bf16 factors, rounded up
     fp.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
     fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = w.fb_cap;
-    rc = launch_knn_finalize(fp, nq, st);
+    fp.part_cnt = tp.part_cnt;
+    rc = tc_knn_big(k) ? launch_knn_finalize_big(fp, nq, st) : launch_knn_finalize(fp, nq, st);
     if (rc != FL_OK) return rc;
     fallback_fixup_kernel<<<1, 1, 0, st>>>(fb_count, w.fb_cap, status, w.K1);
     FL_CHECK_LAUNCH();

@@ -46,8 +46,11 @@ struct FinalizeParams {
     // thresholds the scoring pass published per (slot, range): every row it left out of its
     // published pool scored at most this much (nullptr: none were left out below the pool)
     const float* part_tau; int ntau;
+    const int* part_cnt;     // large-k finalisation: entries per published pool ([slot][ntau])
     int* fb_count; int* fb_list; int fb_cap;
 };
+// Finalisation of the large-k tensor-core pools (one block per query).
+int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);
 int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);
 
 // Tensor-core (tcgen05) candidate pass over the bf16 plane.
@@ -62,8 +65,12 @@ struct TcKnnParams {
     float* part_sc; uint32_t* part_id;     // [nq_pad][nsplit][tc_partial_len]
     float* tau;              // f32 [nq_pad], running per-query thresholds, -inf initialised
     float* part_tau;         // f32 [nq_pad][nsplit][tc_taus_per_range]: thresholds each (query, range) ended with
+    int* part_cnt;           // large-k pools only: i32 [nq_pad][nsplit][tc_taus_per_range] entries per pool
+    int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)
     int32_t* status;
 };
+// 1 when k takes the large pools (256 entries per (query, range, warpgroup), kept in global memory).
+int tc_knn_big(int k);
 // Returns FL_EUNSUPPORTED when the shape is outside the tensor-core kernel's range.
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k);
 int tc_pool_size(int k);

@@ -468,4 +468,174 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
     return FL_OK;
 }
 
+// ------------------------------------------------------------------------------------
+// Finalisation of the large-k tensor-core pools: one block per query.
+//
+// The scoring pass published, per (query, range, warpgroup), a pool of up to 256 (score, row)
+// entries with its entry count and final threshold; every row it did not publish scored at most
+// u = the largest threshold.  The block gathers the entries scoring above u (the others can
+// never satisfy the proof), sorts them by score, re-scores the best BIG_RERANK with exact fp32
+// sum (q - x)^2, sorts those by (distance, row) and accepts the first k when the k-th distance
+// lies below qsq - 2 (bound + eps), bound = max(u, best score that was not re-scored).
+// Otherwise (or when more than BIG_CAND entries survive) the query is queued for the exact path.
+// ------------------------------------------------------------------------------------
+constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 256;
+
+// Bitonic sort of n (power of two) entries in shared memory: larger key first, smaller id first
+// among equal keys.
+__device__ __forceinline__ void block_sort_desc(float* key, uint32_t* id, int n) {
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < (n >> 1); i += BIG_THREADS) {
+                const int a = 2 * i - (i & (stride - 1));
+                const int b = a + stride;
+                const float ka = key[a], kb = key[b];
+                const uint32_t ia = id[a], ib = id[b];
+                const bool a_first = ka > kb || (ka == kb && ia <= ib);
+                const bool desc = (a & size) == 0;
+                if (a_first != desc) { key[a] = kb; key[b] = ka; id[a] = ib; id[b] = ia; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeParams p) {
+    __shared__ float s_key[BIG_CAND];
+    __shared__ uint32_t s_id[BIG_CAND];
+    __shared__ float s_q[256];
+    __shared__ float s_red[BIG_THREADS / 32];
+    __shared__ int s_n;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t slot = blockIdx.x;
+    if (slot >= p.count) return;
+    const int64_t qi = slot;
+    const float* qp = p.q + qi * p.ldq;
+
+    // u and ||q||^2
+    float u = neg_inf(), qs = 0.f;
+    for (int i = tid; i < p.ntau; i += BIG_THREADS) u = fmaxf(u, p.part_tau[slot * p.ntau + i]);
+    for (int c = tid; c < p.d; c += BIG_THREADS) { const float v = __ldg(qp + c); s_q[c] = v; qs += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
+        qs += __shfl_xor_sync(FULL_MASK, qs, o);
+    }
+    if (lane == 0) s_red[warp] = u;
+    if (tid == 0) s_n = 0;
+    __syncthreads();
+    u = s_red[0];
+#pragma unroll
+    for (int w = 1; w < BIG_THREADS / 32; ++w) u = fmaxf(u, s_red[w]);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = qs;
+    __syncthreads();
+    float qsq = 0.f;
+#pragma unroll
+    for (int w = 0; w < BIG_THREADS / 32; ++w) qsq += s_red[w];
+
+    // gather the survivors: one pool per warp at a time
+    for (int pi = warp; pi < p.ntau; pi += BIG_THREADS / 32) {
+        int cnt = p.part_cnt[slot * p.ntau + pi];
+        cnt = cnt < BIG_POOL ? cnt : BIG_POOL;
+        const float* psc = p.part_sc + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
+        const uint32_t* pid = p.part_id + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
+        for (int e0 = 0; e0 < cnt; e0 += 32) {
+            const int e = e0 + lane;
+            float sc = neg_inf();
+            uint32_t cid = INVALID_ID;
+            if (e < cnt) { sc = psc[e]; cid = pid[e]; }
+            const bool keep = sc > u && cid < (uint32_t)p.m;
+            const unsigned mask = __ballot_sync(FULL_MASK, keep);
+            if (mask) {
+                int base = 0;
+                if (lane == 0) base = atomicAdd(&s_n, __popc(mask));
+                base = __shfl_sync(FULL_MASK, base, 0);
+                const int pos = base + __popc(mask & ((1u << lane) - 1u));
+                if (keep && pos < BIG_CAND) { s_key[pos] = sc; s_id[pos] = cid; }
+            }
+        }
+    }
+    __syncthreads();
+    const int total = s_n;
+    const bool overflow = total > BIG_CAND;
+    const int n = overflow ? BIG_CAND : total;
+    int P = BIG_RERANK;
+    while (P < n) P <<= 1;
+    for (int i = n + tid; i < P; i += BIG_THREADS) { s_key[i] = neg_inf(); s_id[i] = INVALID_ID; }
+    block_sort_desc(s_key, s_id, P);
+
+    // exact distances of the best BIG_RERANK; everything else scored at most `bound`
+    float bound = u;
+    if (n > BIG_RERANK) bound = fmaxf(bound, s_key[BIG_RERANK]);
+    __syncthreads();
+    for (int c0 = warp * 4; c0 < BIG_RERANK; c0 += (BIG_THREADS / 32) * 4) {
+        uint32_t cid[4];
+        float a[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) { cid[t] = s_id[c0 + t]; a[t] = 0.f; }
+        if (p.vec) {
+            for (int c = lane * 4; c < p.d; c += 128) {
+                const float4 qv = *reinterpret_cast<const float4*>(s_q + c);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    if (cid[t] != INVALID_ID) {
+                        const float4 xv = __ldg(reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
+                        const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
+                        a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                    }
+                }
+            }
+        } else {
+            for (int c = lane; c < p.d; c += 32) {
+                const float qv = s_q[c];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    if (cid[t] != INVALID_ID) {
+                        const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
+                        a[t] += df * df;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
+            if (lane == 0) s_key[c0 + t] = cid[t] != INVALID_ID ? -a[t] : neg_inf();
+        }
+    }
+    block_sort_desc(s_key, s_id, BIG_RERANK);
+
+    for (int e = tid; e < p.k; e += BIG_THREADS) {
+        const bool ok = s_id[e] != INVALID_ID;
+        p.out_dist[qi * p.k + e] = ok ? -s_key[e] : pos_inf();
+        p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)s_id[e] + p.row_offset) : -1;
+    }
+    if (tid == 0) {
+        bool proven = !overflow;
+        if (proven && bound > neg_inf()) {
+            const float mn = __ldg(p.maxnorm);
+            const float eps = p.eps_rel * sqrtf(qsq) * mn;
+            const float slack = 1e-5f * (qsq + mn * mn);
+            const float dk = s_id[p.k - 1] != INVALID_ID ? -s_key[p.k - 1] : pos_inf();
+            proven = dk < qsq - 2.f * (bound + eps) - slack;
+        }
+        if (!proven) {
+            const int i = atomicAdd(p.fb_count, 1);
+            if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+        }
+    }
+}
+
+int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
+    if (max_slots <= 0) return FL_OK;
+    FL_CHECK_ARG(p.part_cnt && p.part_tau && p.K1 == 2 * BIG_POOL && p.d <= 256 && p.k <= BIG_RERANK && p.count == max_slots,
+                 "large-k finalisation: bad parameters");
+    knn_finalize_big_kernel<<<(unsigned)max_slots, BIG_THREADS, 0, st>>>(p);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 }  // namespace fl

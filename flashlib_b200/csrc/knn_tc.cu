@@ -34,6 +34,8 @@ constexpr int TC_NWG = 2;             // epilogue warpgroups; group g owns colum
 constexpr int TC_K1 = 12;             // entries a (query, warpgroup) pool keeps at compaction
 constexpr int TC_CAP = 32;            // pool capacity before compaction
 constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread); the extra slot is scratch
+constexpr int TC_BIG_K1 = 128;        // large-k mode (16 < k <= 128): pools live in global memory,
+constexpr int TC_BIG_CAP = 256;       // directly in the published-pool buffers
 constexpr int TC_THREADS = (4 * TC_NWG + 2) * 32;
 constexpr int TC_A_CHUNK = TC_BM * 128;   // bytes of one K-chunk of the query tile
 constexpr int TC_A_AUG = TC_BM * 32;      // bytes of the query tile's 16 norm columns
@@ -83,6 +85,8 @@ struct TcKernelParams {
     float* part_sc; uint32_t* part_id;
     float* tau;
     float* part_tau;
+    int* part_cnt;           // large-k mode: entries of every published pool
+    int seed_classes;        // seeding: 16, 8 or 4 column classes per thread
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
@@ -101,16 +105,18 @@ __device__ __forceinline__ void tc_report_timeout(int32_t* status, int role, int
 
 // Compacts the pools of the rows named in `need` (one bit per lane = row of this warp).
 // Kept out of line: compaction is rare and the sorting network is large.
-static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp_sc, uint32_t* warp_id, int cnt,
-                                                      float tau) {
+// `stride` = elements between the pools of consecutive rows.
+template <int CAP, int K1>
+static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp_sc, uint32_t* warp_id, int64_t stride,
+                                                      int cnt, float tau) {
     const int lane = threadIdx.x & 31;
     __syncwarp();
     while (need) {
         const int src = __ffs(need) - 1;
         need &= need - 1;
         const int n = __shfl_sync(FULL_MASK, cnt, src);
-        const float thr = warp_pool_compact<TC_CAP / 32>(warp_sc + src * TC_PSTR, warp_id + src * TC_PSTR, n, TC_K1);
-        if (lane == src) { cnt = min(n, TC_K1); tau = fmaxf(tau, thr); }
+        const float thr = warp_pool_compact<CAP / 32>(warp_sc + src * stride, warp_id + src * stride, n, K1);
+        if (lane == src) { cnt = min(n, K1); tau = fmaxf(tau, thr); }
     }
     return make_float2(__int_as_float(cnt), tau);
 }
@@ -135,7 +141,12 @@ __device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
 // set, every row only needs its best centroid, so each thread keeps the best and second-best
 // score of its row in registers (the column index rides in the low 7 mantissa bits of the
 // score) and no pool is touched.
-constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2;
+//
+// MODE 3 (TC_MODE_KNN_BIG) is MODE 0 for 16 < k <= 128: pools of 256 entries (128 kept) that do not
+// fit shared memory; they live in global memory, in place in the published-pool buffers (appends
+// are predicated stores, compaction reads them back through the L2), and each pool's entry
+// count is published with it.
+constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3;
 template <bool DBG, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
@@ -296,8 +307,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // warp = 4 * warpgroup + TMEM lane quarter; warpgroup g reads columns 128g .. 128g+127 of
         // every accumulator and keeps its own pool per query row.
         const int wg = warp >> 2, quarter = warp & 3;
+        constexpr bool BIG = (MODE == TC_MODE_KNN_BIG);
+        constexpr int CAP = BIG ? TC_BIG_CAP : TC_CAP;
+        constexpr int K1 = BIG ? TC_BIG_K1 : TC_K1;
+        // pool of lane 0's row and distance (elements) between the pools of consecutive rows
         float* warp_sc = pool_sc + warp * 32 * TC_PSTR;
         uint32_t* warp_id = pool_id + warp * 32 * TC_PSTR;
+        int64_t pstride = TC_PSTR;
         float* my_sc = warp_sc + lane * TC_PSTR;
         uint32_t* my_id = warp_id + lane * TC_PSTR;
         const uint32_t lane_taddr = tmem_base + (uint32_t(quarter * 32) << 16);
@@ -312,6 +328,14 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
             const float tau_in = __ldcg(p.tau + qrow);
+            if (BIG) {
+                pstride = (int64_t)p.nsplit * TC_NWG * CAP;
+                const int64_t o = (((int64_t)(qt * TC_BM + quarter * 32) * p.nsplit + split) * TC_NWG + wg) * CAP;
+                warp_sc = p.part_sc + o;
+                warp_id = p.part_id + o;
+                my_sc = warp_sc + lane * pstride;
+                my_id = warp_id + lane * pstride;
+            }
             float tau = tau_in;
             int cnt = 0;
             float cls[16];
@@ -489,10 +513,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     while (wl) {
                         const int g = __ffs(wl) - 1;
                         wl &= wl - 1;
-                        const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
+                        const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
                         if (need) {
                             prof_compact += __popc(need);
-                            const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                            const float2 cr = tc_compact_rows<CAP, K1>(need, warp_sc, warp_id, pstride, cnt, tau);
                             cnt = __float_as_int(cr.x);
                             tau = cr.y;
                         }
@@ -506,9 +530,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         pm = ((late >> g) & 1u) ? pm : 0u;
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
-                            my_sc[pos] = __uint_as_float(r[j]);     // slot TC_CAP is the row's scratch slot
-                            my_id[pos] = row_base + g * 8 + j;
+                            const bool pass = (pm >> j) & 1u;
+                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            if (!BIG || pass) {       // shared pools: slot TC_CAP is the row's scratch slot
+                                my_sc[pos] = __uint_as_float(r[j]);
+                                my_id[pos] = row_base + g * 8 + j;
+                            }
                         }
                         cnt += __popc(pm);
                         prof_append += __popc(pm);
@@ -518,11 +545,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     __syncwarp();
                     if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
                     // (b) all lanes at once
-                    const unsigned need = __ballot_sync(FULL_MASK, cnt > TC_CAP - 8);
+                    const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
                     if (need) {
                         prof_compact += __popc(need);
                         const long long cc0 = clock64();
-                        const float2 cr = tc_compact_rows(need, warp_sc, warp_id, cnt, tau);
+                        const float2 cr = tc_compact_rows<CAP, K1>(need, warp_sc, warp_id, pstride, cnt, tau);
                         prof_cc += clock64() - cc0;
                         cnt = __float_as_int(cr.x);
                         tau = cr.y;
@@ -535,14 +562,19 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         // at most one passing score per lane: it is the maximum of the group
                         const float mx = fmaxf(fmax3(sv[0], sv[1], sv[2]), fmax3(fmax3(sv[3], sv[4], sv[5]), sv[6], sv[7]));
                         const int pos = np ? cnt : TC_CAP;
-                        my_sc[pos] = mx;
-                        my_id[pos] = scb + (__ffs(pm) - 1);
+                        if (!BIG || np) {
+                            my_sc[pos] = mx;
+                            my_id[pos] = scb + (__ffs(pm) - 1);
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const int pos = ((pm >> j) & 1u) ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
-                            my_sc[pos] = sv[j];
-                            my_id[pos] = scb + j;
+                            const bool pass = (pm >> j) & 1u;
+                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            if (!BIG || pass) {
+                                my_sc[pos] = sv[j];
+                                my_id[pos] = scb + j;
+                            }
                         }
                     }
                     cnt += np;
@@ -564,15 +596,32 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 continue;
             }
             if (MODE == TC_MODE_SEED) {
+                // fewer, larger classes give a tighter (higher) threshold that fewer rows reach
+                if (p.seed_classes <= 8) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) cls[c] = fmaxf(cls[c], cls[c + 8]);
+                }
+                if (p.seed_classes <= 4) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) cls[c] = fmaxf(cls[c], cls[c + 4]);
+                }
+                const int nc = p.seed_classes <= 4 ? 4 : p.seed_classes <= 8 ? 8 : 16;
                 float m = cls[0];
 #pragma unroll
-                for (int c = 1; c < 16; ++c) m = fminf(m, cls[c]);
+                for (int c = 1; c < 16; ++c) m = c < nc ? fminf(m, cls[c]) : m;
                 if (m > neg_inf()) atomic_max_f32(p.tau + qrow, m);
                 continue;
             }
             // end of the item: publish every row's pool as it stands (up to TC_CAP entries, the rest
             // padded) and the row's threshold.  The pool is not sorted here: the finalize kernel
             // merges the published entries anyway.
+            if (BIG) {
+                // the pools already are the published buffers
+                p.part_cnt[(qrow * p.nsplit + split) * TC_NWG + wg] = cnt;
+                p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
+                if (tau > tau_in) __stcg(p.tau + qrow, tau);
+                continue;
+            }
             __syncwarp();
 #pragma unroll 1
             for (int src = 0; src < 32; ++src) {
@@ -643,13 +692,14 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int c
     return FL_OK;
 }
 
-int tc_pool_size(int k) { (void)k; return TC_K1; }
-int tc_partial_len(int k) { (void)k; return TC_NWG * TC_CAP; }
+int tc_knn_big(int k) { return k > 16 ? 1 : 0; }
+int tc_pool_size(int k) { return tc_knn_big(k) ? TC_BIG_K1 : TC_K1; }
+int tc_partial_len(int k) { return TC_NWG * (tc_knn_big(k) ? TC_BIG_CAP : TC_CAP); }
 int tc_taus_per_range() { return TC_NWG; }
 
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k) {
     if (nq < 1 || m < 1) return FL_EUNSUPPORTED;
-    if (k > 16) return FL_EUNSUPPORTED;             // pool of 32 leaves the verification margin
+    if (k > 112) return FL_EUNSUPPORTED;            // pools keep 12 (k <= 16) or 128 entries: leave the proof a margin
     if (d > 256) return FL_EUNSUPPORTED;            // resident query tile: up to 4 chunks of 64 features
     if (round_up(m, 256) / 256 > (1 << 23)) return FL_EUNSUPPORTED;
     return FL_OK;
@@ -689,6 +739,8 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_pe
 static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
     FL_CHECK_ARG(p.qplane && p.dbrows && p.part_sc && p.part_id && p.tau && p.part_tau,
                  "tensor-core kNN launch with a null buffer");
+    const bool big = tc_knn_big(p.k) != 0;
+    FL_CHECK_ARG(!big || (p.part_cnt && !dbg), "tensor-core kNN launch (large k) without a count buffer");
     CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
     const int pitch = p.d_pad + PLANE_AUG_COLS;
     int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
@@ -696,7 +748,7 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
     if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
-    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes());
+    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), !big);
     if (sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     TcKernelParams kp{};
     kp.n_qtiles = (int)(p.nq_pad / TC_BM);
@@ -708,6 +760,8 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.off_bar = sp.off_bar;
     kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
     kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
+    kp.part_cnt = p.part_cnt;
+    kp.seed_classes = 16;
     {
         const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
         kp.dbg_flags = e ? atoi(e) : 0;
@@ -721,6 +775,13 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     // database is large enough for the cold start of the pools to matter.
     const char* noseed = getenv("FLASHLIB_B200_TC_NOSEED");
     int seed_tiles = kp.n_tiles >= 1024 ? 64 : kp.n_tiles / 16;
+    if (big) {
+        // large k: the pools seldom fill, so the seeded threshold is what filters; sample more
+        // tiles and fold the classes to 8 for a threshold that a few hundred rows reach
+        seed_tiles = kp.n_tiles >= 2048 ? 256 : kp.n_tiles / 8;
+        kp.seed_classes = 8;
+        if (const char* e = getenv("FLASHLIB_B200_TC_SEED_CLASSES")) kp.seed_classes = atoi(e);
+    }
     if (const char* e = getenv("FLASHLIB_B200_TC_SEED_TILES")) seed_tiles = atoi(e);
     if (seed_tiles > kp.n_tiles / 2) seed_tiles = kp.n_tiles / 2;
     if (seed_tiles >= 16 && !(noseed && atoi(noseed))) {
@@ -735,7 +796,10 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         knn_tc_kernel<false, TC_MODE_SEED><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
         FL_CHECK_LAUNCH();
     }
-    if (dbg != nullptr || kp.dbg_flags != 0) {
+    if (big) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_BIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_KNN_BIG><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    } else if (dbg != nullptr || kp.dbg_flags != 0) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<true, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     } else {

@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .knn import _as_f32_rows, _stream_ptr
+from .knn import _as_f32_rows, _evict_when_freed, _stream_ptr
 
 
 _XPLANE_CACHE = {}
@@ -37,6 +37,7 @@ def _x_plane(x: torch.Tensor) -> torch.Tensor:
     if len(_XPLANE_CACHE) >= 2:
         _XPLANE_CACHE.pop(next(iter(_XPLANE_CACHE)))
     _XPLANE_CACHE[key] = buf
+    _evict_when_freed(_XPLANE_CACHE, key, x)
     return buf
 
 

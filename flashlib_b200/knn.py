@@ -9,6 +9,7 @@ rejected because this library has no CPU path.
 from __future__ import annotations
 
 import os
+import weakref
 from collections import OrderedDict
 from typing import Optional
 
@@ -68,6 +69,13 @@ def _plane_key(db: torch.Tensor):
     return (db.data_ptr(), tuple(db.shape), db.stride(0), db._version, db.device.index)
 
 
+def _evict_when_freed(cache, key, t: torch.Tensor) -> None:
+    """Drops ``cache[key]`` when the tensor that owns ``t``'s memory dies: a later tensor can
+    be given the same address, shape and version, and must not meet the old entry."""
+    owner = t._base if t._base is not None else t
+    weakref.finalize(owner, cache.pop, key, None)
+
+
 _PLANE_CACHE: "OrderedDict[tuple, DbPlane]" = OrderedDict()
 _PLANE_CACHE_SIZE = 4
 
@@ -80,6 +88,7 @@ def get_plane(db: torch.Tensor) -> DbPlane:
         return hit
     plane = DbPlane(db)
     _PLANE_CACHE[key] = plane
+    _evict_when_freed(_PLANE_CACHE, key, db)
     while len(_PLANE_CACHE) > _PLANE_CACHE_SIZE:
         _PLANE_CACHE.popitem(last=False)
     return plane

@@ -80,11 +80,57 @@ def test_bf16_mode_equals_exact_mode_and_reports_fallbacks():
     assert same > 0.99, same
 
 
+BIG_K_SHAPES = [(64, 3000, 64, 17), (129, 20_000, 128, 32), (300, 60_000, 128, 100), (500, 150_000, 64, 64),
+                (100, 400, 96, 112), (257, 300_001, 96, 100), (33, 50_000, 200, 50)]
+
+
+@pytest.mark.parametrize("nq,m,d,k", BIG_K_SHAPES)
+def test_bf16_mode_large_k_vs_oracle(nq, m, d, k):
+    """16 < k <= 112: pools of 256 entries in global memory, block-per-query finalisation."""
+    g = torch.Generator().manual_seed(nq + m + k)
+    db = torch.randn(m, d, generator=g)
+    q = torch.randn(nq, d, generator=g)
+    _, ref_i = oracle.knn_naive(q.numpy(), db.numpy(), k)
+    d_tc, i_tc, info = knn_f32(q.cuda(), db.cuda(), k, mode=_lib.FL_KNN_BF16_RERANK)
+    res = parity.knn_parity(q.numpy(), db.numpy(), d_tc.cpu().numpy(), i_tc.cpu().numpy(), ref_i)
+    assert res["ok"], (res, info)
+    dn = d_tc.cpu().numpy()
+    assert (np.diff(dn, axis=1) >= 0).all()
+
+
+def test_large_k_mixture_matches_exact_mode():
+    """Clustered non-negative data (the benchmark's distribution), k = 100: tensor-core mode and
+    exact mode agree, and most rows are proven without the exact path."""
+    from flashlib_b200 import synthetic
+    X, Q = synthetic.mixture(200_000, 128, 512, 5, nq=600, clamp=True)
+    X, Q = X.cuda(), Q.cuda()
+    d_tc, i_tc, info = knn_f32(Q, X, 100, mode=_lib.FL_KNN_BF16_RERANK)
+    d_ex, i_ex, _ = knn_f32(Q, X, 100, mode=_lib.FL_KNN_EXACT_SIMT)
+    assert info["fallback_rows"] < 60, info
+    torch.testing.assert_close(d_tc, d_ex, rtol=1e-4, atol=1e-4)
+    same = (i_tc == i_ex).float().mean().item()
+    assert same > 0.999, same
+
+
+def test_plane_cache_does_not_outlive_its_tensor():
+    """A new database that the allocator places at the address of a freed one (same shape) must
+    get its own operand plane."""
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(64, 64, generator=g).cuda()
+    for _ in range(3):
+        db = torch.randn(20_000, 64, generator=g).cuda()
+        d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)
+        d_ex, i_ex, _ = knn_f32(q, db, 10, mode=_lib.FL_KNN_EXACT_SIMT)
+        assert info["fallback_rows"] < 8, info
+        assert (i_tc == i_ex).float().mean().item() > 0.999
+        del db
+
+
 def test_unsupported_k_raises_and_auto_falls_back():
     g = torch.Generator().manual_seed(1)
     db = torch.randn(5000, 32, generator=g).cuda()
     q = torch.randn(10, 32, generator=g).cuda()
     with pytest.raises(NotImplementedError):
-        fl.flash_knn(q, db, 100, mode="bf16")
-    vals, idxs = fl.flash_knn(q, db, 100)        # auto: exact path
-    assert vals.shape == (10, 100)
+        fl.flash_knn(q, db, 200, mode="bf16")
+    vals, idxs = fl.flash_knn(q, db, 200)        # auto: exact path
+    assert vals.shape == (10, 200)
