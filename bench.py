@@ -189,9 +189,15 @@ def run_secondary(args):
     if args.workload == "knn_1m_k100":
         X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
         Xd, Qd = X.cuda(), Q.cuda()
-        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, 100), steps, warm)
+        from flashlib_b200.knn import _mode_from, knn_f32
+        mode = _mode_from(args.mode)
+        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, 100, mode=args.mode), steps, warm)
+        _, _, info = knn_f32(Qd, Xd, 100, mode=mode)
+        path = {0: "exact fp32 CUDA-core scoring", 1: "tcgen05 bf16 candidates (pools of 256) + exact fp32 re-rank + verified fallback"}
         line = {"workload": "knn_1m_k100", "metric": "exact_knn_queries_per_sec", "value": QUERIES_PER_GPU / (ms * 1e-3),
-                "unit": "queries/s", "ms_per_step": ms, "config": {"k": 100, "path": "exact fp32 CUDA-core scoring"}}
+                "unit": "queries/s", "ms_per_step": ms,
+                "config": {"k": 100, "path": path.get(int(info["mode"]), str(info["mode"])),
+                           "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
     elif args.workload == "kmeans_1m":
         cfg = synthetic.CONFIGS["kmeans_1m"]
         X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])

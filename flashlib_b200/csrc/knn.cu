@@ -80,7 +80,7 @@ struct KnnWs {
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
     int64_t nq_pad; int d_pad; int fb_cap;
-    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_tau, off_cnt, off_fblist,
+    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_seed_cls, off_tau, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
 };
 
@@ -116,6 +116,7 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
         w.off_part_tau = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_part_cnt = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
+        w.off_seed_cls = take(cur, w.nq_pad * 32 * 4);
         w.off_tau = take(cur, w.nq_pad * 4);
         w.off_cnt = take(cur, 1024);
         w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
@@ -322,6 +323,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.tau = tau; tp.status = status;
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
+    tp.seed_cls = reinterpret_cast<float*>(base + w.off_seed_cls);
     tp.k = k;
     profile_begin(st);
     rc = launch_knn_tc(tp, st);

@@ -66,6 +66,7 @@ struct TcKnnParams {
     float* tau;              // f32 [nq_pad], running per-query thresholds, -inf initialised
     float* part_tau;         // f32 [nq_pad][nsplit][tc_taus_per_range]: thresholds each (query, range) ended with
     int* part_cnt;           // large-k pools only: i32 [nq_pad][nsplit][tc_taus_per_range] entries per pool
+    float* seed_cls;         // f32 [nq_pad][32] scratch of the threshold-seeding pass (nullptr: no seeding)
     int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)
     int32_t* status;
 };

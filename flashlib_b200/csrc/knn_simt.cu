@@ -535,30 +535,43 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
 #pragma unroll
     for (int w = 0; w < BIG_THREADS / 32; ++w) qsq += s_red[w];
 
-    // gather the survivors: one pool per warp at a time
-    for (int pi = warp; pi < p.ntau; pi += BIG_THREADS / 32) {
-        int cnt = p.part_cnt[slot * p.ntau + pi];
-        cnt = cnt < BIG_POOL ? cnt : BIG_POOL;
-        const float* psc = p.part_sc + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
-        const uint32_t* pid = p.part_id + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
-        for (int e0 = 0; e0 < cnt; e0 += 32) {
-            const int e = e0 + lane;
-            float sc = neg_inf();
-            uint32_t cid = INVALID_ID;
-            if (e < cnt) { sc = psc[e]; cid = pid[e]; }
-            const bool keep = sc > u && cid < (uint32_t)p.m;
-            const unsigned mask = __ballot_sync(FULL_MASK, keep);
-            if (mask) {
-                int base = 0;
-                if (lane == 0) base = atomicAdd(&s_n, __popc(mask));
-                base = __shfl_sync(FULL_MASK, base, 0);
-                const int pos = base + __popc(mask & ((1u << lane) - 1u));
-                if (keep && pos < BIG_CAND) { s_key[pos] = sc; s_id[pos] = cid; }
+    // Gather the survivors (score above `cut`), one pool per warp at a time.  If more than
+    // BIG_CAND survive (a loose starting threshold), the BIG_CAND that were stored -- an
+    // arbitrary subset -- are sorted, the cut moves up to the score at their first quarter and
+    // the gather is repeated; everything below the cut is covered by `bound`.
+    float cut = u;
+    int total = 0;
+    for (int round = 0; round < 4; ++round) {
+        __syncthreads();
+        if (tid == 0) s_n = 0;
+        __syncthreads();
+        for (int pi = warp; pi < p.ntau; pi += BIG_THREADS / 32) {
+            int cnt = p.part_cnt[slot * p.ntau + pi];
+            cnt = cnt < BIG_POOL ? cnt : BIG_POOL;
+            const float* psc = p.part_sc + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
+            const uint32_t* pid = p.part_id + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
+            for (int e0 = 0; e0 < cnt; e0 += 32) {
+                const int e = e0 + lane;
+                float sc = neg_inf();
+                uint32_t cid = INVALID_ID;
+                if (e < cnt) { sc = psc[e]; cid = pid[e]; }
+                const bool keep = sc > cut && cid < (uint32_t)p.m;
+                const unsigned mask = __ballot_sync(FULL_MASK, keep);
+                if (mask) {
+                    int base = 0;
+                    if (lane == 0) base = atomicAdd(&s_n, __popc(mask));
+                    base = __shfl_sync(FULL_MASK, base, 0);
+                    const int pos = base + __popc(mask & ((1u << lane) - 1u));
+                    if (keep && pos < BIG_CAND) { s_key[pos] = sc; s_id[pos] = cid; }
+                }
             }
         }
+        __syncthreads();
+        total = s_n;
+        if (total <= BIG_CAND) break;
+        block_sort_desc(s_key, s_id, BIG_CAND);
+        cut = fmaxf(cut, s_key[BIG_CAND / 4 - 1]);
     }
-    __syncthreads();
-    const int total = s_n;
     const bool overflow = total > BIG_CAND;
     const int n = overflow ? BIG_CAND : total;
     int P = BIG_RERANK;
@@ -567,7 +580,7 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
     block_sort_desc(s_key, s_id, P);
 
     // exact distances of the best BIG_RERANK; everything else scored at most `bound`
-    float bound = u;
+    float bound = cut;
     if (n > BIG_RERANK) bound = fmaxf(bound, s_key[BIG_RERANK]);
     __syncthreads();
     for (int c0 = warp * 4; c0 < BIG_RERANK; c0 += (BIG_THREADS / 32) * 4) {

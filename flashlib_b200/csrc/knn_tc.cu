@@ -86,7 +86,7 @@ struct TcKernelParams {
     float* tau;
     float* part_tau;
     int* part_cnt;           // large-k mode: entries of every published pool
-    int seed_classes;        // seeding: 16, 8 or 4 column classes per thread
+    float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
@@ -596,20 +596,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 continue;
             }
             if (MODE == TC_MODE_SEED) {
-                // fewer, larger classes give a tighter (higher) threshold that fewer rows reach
-                if (p.seed_classes <= 8) {
+                float4* o = reinterpret_cast<float4*>(p.seed_cls + (qrow * TC_NWG + wg) * 16);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) cls[c] = fmaxf(cls[c], cls[c + 8]);
-                }
-                if (p.seed_classes <= 4) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) cls[c] = fmaxf(cls[c], cls[c + 4]);
-                }
-                const int nc = p.seed_classes <= 4 ? 4 : p.seed_classes <= 8 ? 8 : 16;
-                float m = cls[0];
-#pragma unroll
-                for (int c = 1; c < 16; ++c) m = c < nc ? fminf(m, cls[c]) : m;
-                if (m > neg_inf()) atomic_max_f32(p.tau + qrow, m);
+                for (int c = 0; c < 4; ++c) o[c] = make_float4(cls[4 * c], cls[4 * c + 1], cls[4 * c + 2], cls[4 * c + 3]);
                 continue;
             }
             // end of the item: publish every row's pool as it stands (up to TC_CAP entries, the rest
@@ -654,6 +643,32 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
+}
+
+// Starting threshold of every query row from the seeding pass: the `rank`-th largest of the
+// row's 32 class maxima (16 column classes x 2 warpgroups, disjoint sets of database rows).  At
+// least `rank` distinct rows reach it, and being an order statistic of many classes it scatters
+// far less than the smallest of a few maxima.
+__global__ void tc_seed_select_kernel(const float* __restrict__ seed_cls, float* __restrict__ tau, int64_t nq_pad, int rank) {
+    const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= nq_pad) return;
+    float v[TC_NWG * 16];
+    const float4* src = reinterpret_cast<const float4*>(seed_cls + row * (TC_NWG * 16));
+#pragma unroll
+    for (int i = 0; i < TC_NWG * 4; ++i) {
+        const float4 t = __ldg(src + i);
+        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+    }
+    // rank of each value among the 32 (ties broken by position): a permutation
+    float pick = neg_inf();
+#pragma unroll
+    for (int i = 0; i < TC_NWG * 16; ++i) {
+        int r = 0;
+#pragma unroll
+        for (int j = 0; j < TC_NWG * 16; ++j) r += (v[j] > v[i] || (v[j] == v[i] && j < i)) ? 1 : 0;
+        if (r == rank - 1) pick = v[i];
+    }
+    if (pick > neg_inf()) tau[row] = pick;
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -761,7 +776,7 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
     kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
     kp.part_cnt = p.part_cnt;
-    kp.seed_classes = 16;
+    kp.seed_cls = p.seed_cls;
     {
         const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
         kp.dbg_flags = e ? atoi(e) : 0;
@@ -774,17 +789,27 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     // Threshold seeding on a strided sample of one tile in 16 (at most 64 tiles) when the
     // database is large enough for the cold start of the pools to matter.
     const char* noseed = getenv("FLASHLIB_B200_TC_NOSEED");
+    // Seeding sample.  The threshold is the seed_rank-th largest of 32 class maxima, which sits
+    // near rank 32 ln(32 / (32 - seed_rank)) of the sample, hence near that figure times
+    // n_tiles / seed_tiles of the whole database.
+    //  k <= 16: the pools tighten the threshold quickly; 64 tiles, k + 6 rows guaranteed.
+    //  large k: the pools seldom fill, so the seeded threshold is what filters.  Aim at about
+    //           rank 6 k of the database: loose enough that the k-th neighbour's error band
+    //           stays inside, tight enough that a few hundred rows per query are published.
     int seed_tiles = kp.n_tiles >= 1024 ? 64 : kp.n_tiles / 16;
+    int seed_rank = p.k + 6 < 32 ? p.k + 6 : 32;
     if (big) {
-        // large k: the pools seldom fill, so the seeded threshold is what filters; sample more
-        // tiles and fold the classes to 8 for a threshold that a few hundred rows reach
-        seed_tiles = kp.n_tiles >= 2048 ? 256 : kp.n_tiles / 8;
-        kp.seed_classes = 8;
-        if (const char* e = getenv("FLASHLIB_B200_TC_SEED_CLASSES")) kp.seed_classes = atoi(e);
+        seed_rank = p.k >= 64 ? 16 : 8;
+        const double sample_rank = p.k >= 64 ? 22.2 : 9.2;
+        seed_tiles = (int)((double)kp.n_tiles * sample_rank / (6.0 * p.k));
+        if (seed_tiles > kp.n_tiles / 8) seed_tiles = kp.n_tiles / 8;
     }
     if (const char* e = getenv("FLASHLIB_B200_TC_SEED_TILES")) seed_tiles = atoi(e);
+    if (const char* e = getenv("FLASHLIB_B200_TC_SEED_RANK")) seed_rank = atoi(e);
+    if (seed_rank < 1) seed_rank = 1;
+    if (seed_rank > 32) seed_rank = 32;
     if (seed_tiles > kp.n_tiles / 2) seed_tiles = kp.n_tiles / 2;
-    if (seed_tiles >= 16 && !(noseed && atoi(noseed))) {
+    if (seed_tiles >= 16 && p.seed_cls != nullptr && !(noseed && atoi(noseed))) {
         TcKernelParams sk = kp;
         sk.nsplit = 1;
         sk.tiles_per_split = seed_tiles;
@@ -794,6 +819,8 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<false, TC_MODE_SEED><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
+        FL_CHECK_LAUNCH();
+        tc_seed_select_kernel<<<(unsigned)ceil_div(p.nq_pad, 128), 128, 0, st>>>(p.seed_cls, p.tau, p.nq_pad, seed_rank);
         FL_CHECK_LAUNCH();
     }
     if (big) {
