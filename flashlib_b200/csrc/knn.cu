@@ -79,7 +79,7 @@ struct KnnWs {
     int mode, K1, K1f;
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
-    int64_t nq_pad; int d_pad; int fb_cap;
+    int64_t nq_pad; int d_pad; int fb_cap; int fb_bq, fb_blocks;
     int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_seed_cls, off_tau, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
 };
@@ -120,8 +120,14 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.off_tau = take(cur, w.nq_pad * 4);
         w.off_cnt = take(cur, 1024);
         w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
-        w.off_fbpart_sc = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * w.K1f * 4);
-        w.off_fbpart_id = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * w.K1f * 4);
+        // the fallback scan spreads its blocks over the live slots (simt_dyn_split): at most
+        // one pool per block
+        w.fb_bq = simt_block_queries(w.K1f);
+        w.fb_blocks = (int)(ceil_div(w.fb_cap, w.fb_bq > 0 ? w.fb_bq : 1) * w.nsplit_fb);
+        if (w.fb_blocks < 4 * sm_count()) w.fb_blocks = 4 * sm_count();
+        const int64_t fb_pools = (int64_t)w.fb_blocks * (w.fb_bq > 0 ? w.fb_bq : 1);
+        w.off_fbpart_sc = take(cur, fb_pools * w.K1f * 4);
+        w.off_fbpart_id = take(cur, fb_pools * w.K1f * 4);
     } else {
         w.K1 = simt_pool_size(k);
         w.K1f = w.K1;
@@ -355,6 +361,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     sp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
     sp.K1 = w.K1f; sp.cap = 2 * w.K1f; sp.npl = sp.cap / 32;
     sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
+    sp.dyn_blocks = w.fb_blocks; sp.dyn_bq = w.fb_bq;
     sp.part_sc = reinterpret_cast<float*>(base + w.off_fbpart_sc);
     sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_fbpart_id);
     sp.vecq = vecq; sp.vecd = vecd;
@@ -364,6 +371,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     ff.qlist = fb_list; ff.count_dev = fb_count; ff.count = 0;
     ff.part_sc = sp.part_sc; ff.part_id = sp.part_id; ff.nsplit = w.nsplit_fb; ff.K1 = w.K1f;
     ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0; ff.part_tau = nullptr; ff.ntau = 0;
+    ff.dyn_blocks = w.fb_blocks; ff.dyn_bq = w.fb_bq;
     rc = launch_knn_finalize(ff, w.fb_cap, st);
     return rc;
 }

@@ -18,6 +18,11 @@ struct SimtKnnParams {
     int nsplit; int64_t rows_per_split;
     float* part_sc; uint32_t* part_id;
     int vecq, vecd;
+    // dyn_blocks > 0 (fallback pass, slot count only known on the device): the launch is a
+    // 1-D grid of dyn_blocks blocks and the kernel spreads them over the live query blocks, so
+    // a handful of slots is scanned by many short ranges instead of a few long ones
+    // (simt_dyn_split); nsplit / rows_per_split are then ignored.
+    int dyn_blocks; int dyn_bq;
     // Inverted-file mode (ivf != 0): block b is work item b = (list c, group g of up to BQ
     // of the (query, probe) pairs that name list c).  item_off/pair_off are exclusive scans
     // over lists (nlist+1 entries), sorted_pair lists the pair ids grouped by list, and the
@@ -28,6 +33,20 @@ struct SimtKnnParams {
     const int64_t* list_offsets;
 };
 int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st);
+// Range split of the dynamic mode for `count` live slots: the same figures on the device
+// (scan and finalisation kernels) and on the host (buffer sizing).
+__host__ __device__ inline void simt_dyn_split(int64_t count, int bq, int blocks, int64_t m, int* nsplit,
+                                               int64_t* rows_per_split) {
+    const int64_t nqb = (count + bq - 1) / bq;
+    int64_t ns = nqb > 0 ? blocks / nqb : 1;
+    const int64_t tiles = (m + 127) / 128;
+    if (ns > tiles / 4) ns = tiles / 4;
+    if (ns > 296) ns = 296;     // two blocks per SM when a single query block is live
+    if (ns < 1) ns = 1;
+    const int64_t rps = ((m + ns - 1) / ns + 127) / 128 * 128;
+    *rows_per_split = rps;
+    *nsplit = (int)((m + rps - 1) / rps);
+}
 // Split count / rows per split the CUDA-core pass uses for a problem.
 void simt_split_plan(int64_t slots, int64_t m, int K1, int d, int* nsplit, int64_t* rows_per_split);
 // Queries per block the CUDA-core pass uses for a pool of K1 entries (0: does not fit).
@@ -46,6 +65,7 @@ struct FinalizeParams {
     // thresholds the scoring pass published per (slot, range): every row it left out of its
     // published pool scored at most this much (nullptr: none were left out below the pool)
     const float* part_tau; int ntau;
+    int dyn_blocks; int dyn_bq;   // pools written by a dynamic-mode scan: nsplit comes from simt_dyn_split
     const int* part_cnt;     // large-k finalisation: entries per published pool ([slot][ntau])
     int* fb_count; int* fb_list; int fb_cap;
 };

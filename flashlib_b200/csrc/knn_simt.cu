@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
     int* pslot = qmap + BQ;
     int64_t slot0, row_begin, row_end;
     int split;
+    int nsplit = p.nsplit;
     if (p.ivf) {
         const int b = blockIdx.x;
         if (b >= p.item_off[p.nlist]) return;
@@ -54,11 +55,21 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
         }
     } else {
         const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
-        slot0 = (int64_t)blockIdx.x * BQ;
-        if (slot0 >= count) return;
-        split = blockIdx.y;
-        row_begin = (int64_t)split * p.rows_per_split;
-        row_end = min(p.m, row_begin + p.rows_per_split);
+        int64_t rps = p.rows_per_split;
+        if (p.dyn_blocks > 0) {
+            if (count <= 0) return;
+            simt_dyn_split(count, BQ, p.dyn_blocks, p.m, &nsplit, &rps);
+            const int64_t nqb = (count + BQ - 1) / BQ;
+            slot0 = ((int64_t)blockIdx.x % nqb) * BQ;
+            split = (int)((int64_t)blockIdx.x / nqb);
+            if (split >= nsplit) return;
+        } else {
+            slot0 = (int64_t)blockIdx.x * BQ;
+            if (slot0 >= count) return;
+            split = blockIdx.y;
+        }
+        row_begin = (int64_t)split * rps;
+        row_end = min(p.m, row_begin + rps);
         for (int i = tid; i < BQ; i += 256) {
             const int64_t slot = slot0 + i;
             qmap[i] = slot < count ? (p.qlist ? p.qlist[slot] : (int)slot) : -1;
@@ -140,7 +151,7 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
         __syncwarp();
         pool_compact_dyn(sc, idp, cnt[row], p.K1, p.npl);
         const int64_t o = p.ivf ? (int64_t)pslot[row] * p.K1
-                                : ((slot0 + row) * p.nsplit + split) * (int64_t)p.K1;
+                                : ((slot0 + row) * nsplit + split) * (int64_t)p.K1;
         for (int e = lane; e < p.K1; e += 32) {
             p.part_sc[o + e] = sc[e];
             p.part_id[o + e] = idp[e];
@@ -187,6 +198,13 @@ static int launch_simt_t(const SimtKnnParams& p, int64_t max_slots, cudaStream_t
                                        (int)smem));
     dim3 grid(p.ivf ? (unsigned)max_slots : (unsigned)ceil_div(max_slots, SimtTile<TQ>::BQ),
               (unsigned)p.nsplit);
+    if (p.dyn_blocks > 0) {
+        if (p.ivf || p.dyn_bq != SimtTile<TQ>::BQ || p.count_dev == nullptr) {
+            set_error("dynamic split: plan made for %d queries per block, kernel uses %d", p.dyn_bq, SimtTile<TQ>::BQ);
+            return FL_EINVAL;
+        }
+        grid = dim3((unsigned)p.dyn_blocks, 1);
+    }
     knn_simt_kernel<TQ><<<grid, 256, smem, st>>>(p);
     FL_CHECK_LAUNCH();
     return FL_OK;
@@ -233,8 +251,13 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     if (slot >= count) return;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
     const int K1 = p.K1;
-    const float* psc = p.part_sc + slot * p.nsplit * (int64_t)K1;
-    const uint32_t* pid = p.part_id + slot * p.nsplit * (int64_t)K1;
+    int nsplit = p.nsplit;
+    if (p.dyn_blocks > 0) {
+        int64_t rps;
+        simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m, &nsplit, &rps);
+    }
+    const float* psc = p.part_sc + slot * nsplit * (int64_t)K1;
+    const uint32_t* pid = p.part_id + slot * nsplit * (int64_t)K1;
 
     float u = neg_inf();
     if (p.part_tau != nullptr) {
@@ -279,7 +302,7 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
             float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             float lmax = neg_inf();
-            for (int s = 0; s < p.nsplit; ++s) {
+            for (int s = 0; s < nsplit; ++s) {
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | ((lane + 5 * s + 16 * r) & 31);
@@ -298,7 +321,7 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
             const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
             const unsigned lt = (1u << lane) - 1u;
             int total = 0;
-            for (int s = 0; s < p.nsplit; ++s) {
+            for (int s = 0; s < nsplit; ++s) {
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | lane;
@@ -330,7 +353,7 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
             uint32_t iin[NPL1];
 #pragma unroll
             for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
-            for (int s = 0; s < p.nsplit; ++s) {
+            for (int s = 0; s < nsplit; ++s) {
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | lane;
