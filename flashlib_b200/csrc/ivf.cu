@@ -179,7 +179,7 @@ extern "C" int fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq, con
 
     SimtKnnParams sp{};
     sp.q = q; sp.ldq = ldq; sp.db = data; sp.m = m; sp.ldb = ldd; sp.d = d; sp.hnorm = hnorm;
-    sp.K1 = w.K1; sp.cap = 2 * w.K1; sp.npl = sp.cap / 32; sp.nsplit = 1; sp.rows_per_split = m;
+    sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k); sp.nsplit = 1; sp.rows_per_split = m;
     sp.part_sc = part_sc; sp.part_id = part_id;
     sp.vecq = (ldq % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
     sp.vecd = (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(data) & 15) == 0);

@@ -316,7 +316,7 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     sp.q = x; sp.ldq = ldx; sp.qlist = fb_list; sp.count_dev = fb_count; sp.count = 0;
     sp.db = c; sp.m = K; sp.ldb = ldc; sp.d = d;
     sp.hnorm = reinterpret_cast<const float*>(cpl + w.cl.off_hnorm);
-    sp.K1 = 32; sp.cap = 64; sp.npl = 2; sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
+    sp.K1 = 32; sp.cap = simt_pool_cap(32); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(32, 1); sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
     sp.part_sc = reinterpret_cast<float*>(base + w.off_fbpart_sc);
     sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_fbpart_id);
     sp.vecq = vecx; sp.vecd = vecc;

@@ -280,7 +280,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
         SimtKnnParams sp{};
         sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
         sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
-        sp.K1 = w.K1; sp.cap = 2 * w.K1; sp.npl = sp.cap / 32;
+        sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k);
         sp.nsplit = w.nsplit; sp.rows_per_split = w.rows_per_split;
         sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
         sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
@@ -359,7 +359,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     sp.q = q; sp.ldq = ldq; sp.qlist = fb_list; sp.count_dev = fb_count; sp.count = 0;
     sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d;
     sp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
-    sp.K1 = w.K1f; sp.cap = 2 * w.K1f; sp.npl = sp.cap / 32;
+    sp.K1 = w.K1f; sp.cap = simt_pool_cap(w.K1f); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1f, k);
     sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
     sp.dyn_blocks = w.fb_blocks; sp.dyn_bq = w.fb_bq;
     sp.part_sc = reinterpret_cast<float*>(base + w.off_fbpart_sc);

@@ -14,7 +14,8 @@ struct SimtKnnParams {
     int64_t count;          // slot count when count_dev is null
     const float* db; int64_t m; int64_t ldb; int d;
     const float* hnorm;     // ||x||^2 / 2 per database row
-    int K1, cap, npl;
+    int K1, cap, npl;       // published entries per pool, pool capacity, capacity / 32
+    int keep;               // entries kept at a compaction inside the scan (<= K1; 0: K1)
     int nsplit; int64_t rows_per_split;
     float* part_sc; uint32_t* part_id;
     int vecq, vecd;

@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
     }
 
     constexpr int RPW = BQ / 8;  // rows per warp in the pool phase
+    const int keep = p.keep > 0 ? p.keep : p.K1;
     for (int64_t tile_row = row_begin; tile_row < row_end; tile_row += 128) {
         const float* drow[4];
 #pragma unroll
@@ -132,8 +133,8 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
                     c += __popc(mask);
                     if (c > p.cap - 32) {
                         __syncwarp();
-                        t = pool_compact_dyn(sc, idp, c, p.K1, p.npl);
-                        c = min(c, p.K1);
+                        t = pool_compact_dyn(sc, idp, c, keep, p.npl);
+                        c = min(c, keep);
                     }
                 }
             }
@@ -173,11 +174,11 @@ static int simt_pick_tq(int cap) {
     return 0;
 }
 
-int simt_block_queries(int K1) { return 16 * simt_pick_tq(2 * K1); }
+int simt_block_queries(int K1) { return 16 * simt_pick_tq(simt_pool_cap(K1)); }
 
 void simt_split_plan(int64_t slots, int64_t m, int K1, int d, int* nsplit, int64_t* rows_per_split) {
     (void)d;
-    const int tq = simt_pick_tq(2 * K1);
+    const int tq = simt_pick_tq(simt_pool_cap(K1));
     const int bq = 16 * (tq > 0 ? tq : 1);
     const int64_t qblocks = ceil_div(slots > 0 ? slots : 1, bq);
     const int64_t tiles = ceil_div(m, 128);

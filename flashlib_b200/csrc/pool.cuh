@@ -26,4 +26,15 @@ static inline int simt_pool_size(int k) {
     return p < 32 ? 32 : p;
 }
 
+// Pool capacity for K1 published entries: room for at least 64 appends between compactions.
+static inline int simt_pool_cap(int K1) { return K1 <= 32 ? 128 : 2 * K1; }
+
+// Entries a pool keeps at a compaction inside the scan: the k wanted plus the margin the exact
+// re-rank takes (k + 8), in steps of 8.  Fewer than K1 keeps the threshold tight and leaves room
+// in the pool while it is still filling.
+static inline int simt_pool_keep(int K1, int k) {
+    const int want = (k + 8 + 7) / 8 * 8;
+    return want < K1 ? want : K1;
+}
+
 }  // namespace fl
