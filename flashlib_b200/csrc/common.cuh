@@ -200,6 +200,17 @@ __device__ __forceinline__ float warp_pool_compact(float* sc, uint32_t* idv, int
     return thr;
 }
 
+// Largest-value update of a float in global memory (compare-and-swap; a few writers at most).
+__device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
+    int* ai = reinterpret_cast<int*>(addr);
+    int old = *reinterpret_cast<volatile int*>(ai);
+    while (__int_as_float(old) < v) {
+        const int assumed = old;
+        old = atomicCAS(ai, assumed, __float_as_int(v));
+        if (old == assumed) break;
+    }
+}
+
 #endif  // __CUDACC__
 
 }  // namespace fl

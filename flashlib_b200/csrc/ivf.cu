@@ -90,7 +90,7 @@ struct IvfWs {
     int K1, bq;
     int64_t max_items;
     int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_part_sc, off_part_id,
-        off_hnorm, bytes;
+        off_hnorm, off_tau, bytes;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -114,6 +114,7 @@ static IvfWs ivf_ws_plan(int64_t nq, int nprobe, int nlist, int64_t m, int k) {
     w.off_part_sc = take(cur, npairs * w.K1 * 4);
     w.off_part_id = take(cur, npairs * w.K1 * 4);
     w.off_hnorm = take(cur, m * 4);
+    w.off_tau = take(cur, nq * 4);
     w.bytes = cur;
     return w;
 }
@@ -186,6 +187,11 @@ extern "C" int fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq, con
     sp.ivf = 1; sp.nlist = nlist; sp.nprobe = nprobe; sp.bq_items = w.bq;
     sp.item_off = item_off; sp.pair_off = pair_off; sp.sorted_pair = sorted_pair;
     sp.list_offsets = list_offsets;
+    sp.tau_q = reinterpret_cast<float*>(base + w.off_tau);
+    {
+        const int rc = launch_fill_f32(sp.tau_q, nq, -INFINITY, st);
+        if (rc != FL_OK) return rc;
+    }
     profile_begin(st);
     int rc = launch_knn_simt(sp, w.max_items, st);
     profile_end(st);

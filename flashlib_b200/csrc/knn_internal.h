@@ -32,6 +32,10 @@ struct SimtKnnParams {
     int ivf; int nlist; int nprobe; int bq_items;
     const int* item_off; const int* pair_off; const int* sorted_pair;
     const int64_t* list_offsets;
+    // Optional f32 [queries], -inf initialised: running threshold of every query, shared by the
+    // blocks that scan its probed lists.  A block starts from it and raises it to its own
+    // pool's threshold when it ends, so lists scanned later start warm.
+    float* tau_q;
 };
 int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st);
 // Range split of the dynamic mode for `count` live slots: the same figures on the device

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
             const int pr = (s0 + i < s1) ? p.sorted_pair[s0 + i] : -1;
             pslot[i] = pr;
             qmap[i] = pr >= 0 ? pr / p.nprobe : -1;
-            tau[i] = neg_inf();
+            tau[i] = (pr >= 0 && p.tau_q != nullptr) ? __ldcg(p.tau_q + pr / p.nprobe) : neg_inf();
             cnt[i] = 0;
         }
     } else {
@@ -151,6 +151,9 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
         uint32_t* idp = pool_id + row * p.cap;
         __syncwarp();
         pool_compact_dyn(sc, idp, cnt[row], p.K1, p.npl);
+        // tau[row] came from the shared threshold or from a compaction of this pool (keep-th
+        // best of rows this query probes): both hold for the query's other lists too
+        if (p.ivf && p.tau_q != nullptr && lane == 0 && tau[row] > neg_inf()) atomic_max_f32(p.tau_q + qmap[row], tau[row]);
         const int64_t o = p.ivf ? (int64_t)pslot[row] * p.K1
                                 : ((slot0 + row) * nsplit + split) * (int64_t)p.K1;
         for (int e = lane; e < p.K1; e += 32) {

@@ -121,17 +121,6 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
     return make_float2(__int_as_float(cnt), tau);
 }
 
-// Largest-value update of a float in global memory (compare-and-swap; a few writers at most).
-__device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
-    int* ai = reinterpret_cast<int*>(addr);
-    int old = *reinterpret_cast<volatile int*>(ai);
-    while (__int_as_float(old) < v) {
-        const int assumed = old;
-        old = atomicCAS(ai, assumed, __float_as_int(v));
-        if (old == assumed) break;
-    }
-}
-
 // MODE 1 (TC_MODE_SEED) turns the kernel into the threshold-seeding pass: it scans a strided sample of
 // the database tiles and, instead of pools, keeps 16 running maxima per query row over
 // disjoint column classes; their minimum is a score that 16 distinct rows reach, i.e. a valid
