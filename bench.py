@@ -11,6 +11,10 @@ A step is one batch of queries through the hot path.  Scaling is weak: every ran
 10,000 queries per step (global batch 10,000 x N) and holds 1/N of the database rows; the
 per-rank candidates are all-gathered (NCCL) and merged on every rank.  One JSON line is
 printed by rank 0.
+
+``--workload knn_100m`` runs the same flow on the sharded configuration (100,000,000 x 96 rows
+~ N(0,1) split over the ranks, 100,000 queries per step, k = 100; strong scaling: the total work
+is fixed).  The other ``--workload`` names time the remaining configurations on one GPU.
 """
 from __future__ import annotations
 
@@ -43,7 +47,15 @@ METRIC = "exact_knn_queries_per_sec"
 UNIT = "queries/s"
 
 
+SCALING = "weak"
+WORKLOAD = "knn_1m"
+
+
 def workload_name(n_gpus: int) -> str:
+    if WORKLOAD == "knn_100m":
+        return (f"knn_100m: exact kNN, database {DB_ROWS}x{DIM} fp32 ~ N(0,1) row-sharded over the ranks (drawn on "
+                f"each device, seed {SEED} + rank), {QUERIES_PER_GPU} queries ~ N(0,1) per step in total, "
+                f"k={K_NEIGHBOURS}, squared L2")
     return (f"knn_1m: exact kNN, database {DB_ROWS}x{DIM} fp32 (4096-component gaussian mixture, "
             f"clamped >= 0, seed {SEED}), {QUERIES_PER_GPU} queries per GPU per step, k={K_NEIGHBOURS}, squared L2")
 
@@ -118,6 +130,13 @@ class ClockSampler:
 def make_workload(rank: int, world: int):
     from flashlib_b200 import synthetic
     from flashlib_b200.sharded import shard_bounds
+    if WORKLOAD == "knn_100m":
+        # too large to draw on the host in bench time: every rank draws its own rows on its device
+        s, e = shard_bounds(DB_ROWS, world, rank)
+        g = torch.Generator(device="cuda").manual_seed(SEED + 1000 * (rank + 1))
+        X = torch.randn(e - s, DIM, generator=g, device="cuda")
+        Q = torch.randn(QUERIES_PER_GPU, DIM, generator=torch.Generator().manual_seed(SEED))
+        return X, Q, s, e
     X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU * world, clamp=True)
     s, e = shard_bounds(DB_ROWS, world, rank)
     return X, Q, s, e
@@ -198,6 +217,24 @@ def run_secondary(args):
                 "unit": "queries/s", "ms_per_step": ms,
                 "config": {"k": 100, "path": path.get(int(info["mode"]), str(info["mode"])),
                            "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+    elif args.workload == "knn_100m_shard":
+        # One GPU's share of the sharded configuration: 12.5M of the 100M rows x 96 features
+        # ~ N(0,1), all 100,000 queries, k = 100 (drawn on the device: 4.8 GB of rows).
+        cfg = synthetic.CONFIGS["knn_sharded_100m"]
+        rows = args.db_rows or cfg["m"] // 8
+        nq = args.queries or cfg["nq"]
+        g = torch.Generator(device="cuda").manual_seed(cfg["seed"])
+        Xd = torch.randn(rows, cfg["d"], generator=g, device="cuda")
+        Qd = torch.randn(nq, cfg["d"], generator=g, device="cuda")
+        from flashlib_b200.knn import _mode_from, knn_f32
+        mode = _mode_from(args.mode)
+        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, cfg["k"], mode=args.mode), steps, warm)
+        _, _, info = knn_f32(Qd, Xd, cfg["k"], mode=mode)
+        flop = 2.0 * nq * rows * cfg["d"]
+        line = {"workload": "knn_100m_shard", "metric": "exact_knn_queries_per_sec", "value": nq / (ms * 1e-3),
+                "unit": "queries/s", "ms_per_step": ms, "algorithmic_tflops": flop / (ms * 1e-3) / 1e12,
+                "config": {"rows_on_this_gpu": rows, "dim": cfg["d"], "queries": nq, "k": cfg["k"], "mode": int(info["mode"]),
+                           "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
     elif args.workload == "kmeans_1m":
         cfg = synthetic.CONFIGS["kmeans_1m"]
         X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
@@ -232,7 +269,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_1m_k100", "kmeans_1m", "ivf_1m"],
+    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
                     help="knn_1m is the headline benchmark; the others time the remaining configurations on one GPU "
                          "and print a shorter JSON line")
     ap.add_argument("--db-rows", type=int, default=None, help="with --profile-case: database rows")
@@ -242,7 +279,14 @@ def main():
                          "no end-to-end or CPU legs (its numbers are not benchmark values)")
     args = ap.parse_args()
 
-    global DB_ROWS, QUERIES_PER_GPU
+    global DB_ROWS, QUERIES_PER_GPU, DIM, K_NEIGHBOURS, SEED, SCALING, WORKLOAD
+    if args.workload == "knn_100m":
+        from flashlib_b200 import synthetic as _syn
+        c5 = _syn.CONFIGS["knn_sharded_100m"]
+        WORKLOAD, SCALING = "knn_100m", "strong"
+        DB_ROWS, DIM, K_NEIGHBOURS, SEED = args.db_rows or c5["m"], c5["d"], c5["k"], c5["seed"]
+        QUERIES_PER_GPU = args.queries or c5["nq"]      # per step in total: every rank scores all of them
+        args.no_cpu_baseline = True
     if args.profile_case:
         DB_ROWS, QUERIES_PER_GPU = args.db_rows or 524_288, args.queries or 2_048
         args.no_cpu_baseline = True
@@ -253,7 +297,7 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
-    if args.workload != "knn_1m":
+    if args.workload not in ("knn_1m", "knn_100m"):
         run_secondary(args)
         return
     if world != args.gpus:
@@ -274,14 +318,22 @@ def main():
 
     X, Q, s, e = make_workload(rank, world)
     nq = Q.shape[0]
-    db = X[s:e].contiguous().to(dev)
+    db = X if WORKLOAD == "knn_100m" else X[s:e].contiguous().to(dev)
     q_host = Q.contiguous().pin_memory()
     q_dev = q_host.to(dev)
     resolved = lib.fl_knn_resolve_mode(nq, db.shape[0], DIM, K_NEIGHBOURS) if mode == _lib.FL_KNN_AUTO else mode
     plane = get_plane(db) if resolved == _lib.FL_KNN_BF16_RERANK else None   # index-build-time work
     torch.cuda.synchronize()
 
+    # Timing hygiene: when this rank's operand plane is not well above the 126 MB L2 it would stay
+    # cache-resident from step to step, so a 256 MB buffer is overwritten before every step
+    # (inside the timed region).
+    plane_bytes = db.shape[0] * (((DIM + 63) // 64) * 64 + 16) * 2
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if plane_bytes < (256 << 20) else None
+
     def step_device():
+        if flush is not None:
+            flush.zero_()
         return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane)
 
     def barrier():
@@ -326,6 +378,8 @@ def main():
     out_i_host = torch.empty((nq, K_NEIGHBOURS), dtype=torch.int32).pin_memory()
 
     def step_e2e():
+        if flush is not None:
+            flush.zero_()
         qd = q_host.to(dev, non_blocking=True)
         if world == 1:
             d_, i_ = flash_knn(qd, db, K_NEIGHBOURS, mode=args.mode)
@@ -356,15 +410,18 @@ def main():
         flop_per_launch = 2.0 * nq * rows_local * DIM
         k_ms = statistics.mean(kernel_ms) if kernel_ms else None
         achieved = flop_per_launch / (k_ms * 1e-3) / 1e12 if k_ms else None
-        peak = peaks["bf16_tflops"]
+        # a kernel timed alone for a few ms runs at burst clocks; the seconds-long launches of the
+        # 100M-row workload run under the power cap: sustained figure
+        sustained = WORKLOAD == "knn_100m" and peaks.get("bf16_tflops_sustained")
+        peak = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": (achieved / peak) if achieved else None, "traffic": TC_KERNEL_DRAM_BYTES_PER_LAUNCH if resolved == _lib.FL_KNN_BF16_RERANK and not args.profile_case and world == 1 else None,
+            "frac": (achieved / peak) if achieved else None, "traffic": TC_KERNEL_DRAM_BYTES_PER_LAUNCH if resolved == _lib.FL_KNN_BF16_RERANK and not args.profile_case and world == 1 and WORKLOAD == "knn_1m" else None,
             "kernel": "knn_tc_kernel" if resolved == _lib.FL_KNN_BF16_RERANK else "knn_simt_kernel",
             "kernel_ms": k_ms, "launches_timed": len(kernel_ms),
             "algorithmic_flop_per_launch": flop_per_launch,
-            "peak_source": f"{peaks['source']} bf16 burst (MEASURED_PEAKS.json)" if peaks["source"] == "measured"
-            else "fallback 1.59 PFLOP/s",
+            "peak_source": (f"{peaks['source']} bf16 {'sustained' if sustained else 'burst'} (MEASURED_PEAKS.json)"
+                            if peaks["source"] == "measured" else "fallback 1.59 PFLOP/s burst / 1.4 sustained"),
         }
         cpu_base = None
         if not args.no_cpu_baseline and world == 1:
@@ -376,14 +433,17 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": n_warm, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
+            "scaling": SCALING, "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
             "data": "synthetic",
             "config": {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,
                        "queries_per_step": nq, "sharding": f"database rows over {world} rank(s); candidates "
                        "all-gathered and merged on every rank" if world > 1 else "single GPU",
                        "mode": {_lib.FL_KNN_EXACT_SIMT: "exact fp32 CUDA-core scoring + exact re-rank",
                                 _lib.FL_KNN_BF16_RERANK: "tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback"}[resolved],
-                       "l2": "no flush needed: each step streams the database operand (>= 256 MB), larger than the 126 MB L2"},
+                       "l2": ("a 256 MB buffer is overwritten before every step (inside the timed region): this rank's "
+                              f"operand plane is {plane_bytes >> 20} MB" if flush is not None else
+                              f"no flush needed: each step streams this rank's operand plane ({plane_bytes >> 20} MB), "
+                              "larger than the 126 MB L2")},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_d_host.numel() * 4 + out_i_host.numel() * 4),
                     "note": "queries from pinned host memory, results to pinned host memory; the database is the fitted index and stays resident"},
