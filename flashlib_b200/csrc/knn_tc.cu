@@ -696,11 +696,7 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int c
     return FL_OK;
 }
 
-int tc_knn_big(int k) {
-    static int force = -1;
-    if (force < 0) { const char* e = getenv("FLASHLIB_B200_TC_FORCE_BIG"); force = e ? atoi(e) : 0; }
-    return (k > 16 || force) ? 1 : 0;
-}
+int tc_knn_big(int k) { return k > 16 ? 1 : 0; }
 int tc_pool_size(int k) { return tc_knn_big(k) ? TC_BIG_K1 : TC_K1; }
 int tc_partial_len(int k) { return TC_NWG * (tc_knn_big(k) ? TC_BIG_CAP : TC_CAP); }
 int tc_taus_per_range() { return TC_NWG; }

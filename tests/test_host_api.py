@@ -49,3 +49,23 @@ def test_synthetic_is_seeded():
     a, qa = synthetic.mixture(100, 8, 4, seed=5, nq=10, clamp=True)
     b, qb = synthetic.mixture(100, 8, 4, seed=5, nq=10, clamp=True)
     assert torch.equal(a, b) and torch.equal(qa, qb) and a.min() >= 0
+
+
+def test_cache_entries_die_with_their_tensor():
+    """Operand-plane caches are keyed by address, shape and version; an entry must go when the
+    tensor that owns the memory is freed, because a new tensor can be given the same key."""
+    import gc
+    import torch
+    from flashlib_b200.knn import _evict_when_freed, _plane_key
+    cache = {}
+    base = torch.zeros(8, 4)
+    view = base[2:6]
+    cache[_plane_key(view)] = "plane of a view"
+    _evict_when_freed(cache, _plane_key(view), view)
+    key = _plane_key(view)
+    del view
+    gc.collect()
+    assert key in cache            # the owner of the memory is still alive
+    del base
+    gc.collect()
+    assert key not in cache
