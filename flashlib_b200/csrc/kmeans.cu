@@ -128,6 +128,64 @@ __global__ void kmeans_update_kernel(const float* __restrict__ x, int64_t n, int
     }
 }
 
+// Same, for rows and sums that allow 16-byte accesses (d, ldx multiples of 4, aligned bases): each
+// lane owns 4 contiguous features per 128, the next row is fetched while the current one is
+// accumulated, and a run is flushed with one 16-byte atomic add per lane.
+template <int V>
+__global__ void kmeans_update_vec_kernel(const float* __restrict__ x, int64_t n, int64_t ldx, int d,
+                                         const int32_t* __restrict__ labels, int K, float* __restrict__ sums,
+                                         int32_t* __restrict__ cnts, int rows_per_warp) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t r0 = w * rows_per_warp;
+    if (r0 >= n) return;
+    const int64_t r1 = min(n, r0 + (int64_t)rows_per_warp);
+    float4 acc[V], nxt[V];
+    auto load_row = [&](int64_t r, float4 (&v)[V]) {
+        const float* p = x + r * ldx;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int cidx = (i * 32 + lane) * 4;
+            v[i] = cidx < d ? __ldg(reinterpret_cast<const float4*>(p + cidx)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    };
+    auto flush = [&](int cur, int run) {
+        if (cur < 0 || cur >= K) return;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int cidx = (i * 32 + lane) * 4;
+            if (cidx < d) atomicAdd(reinterpret_cast<float4*>(sums + (int64_t)cur * d + cidx), acc[i]);
+        }
+        if (lane == 0) atomicAdd(cnts + cur, run);
+    };
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int cur = -1, run = 0;
+    int lab_n = __ldg(labels + r0);
+    load_row(r0, nxt);
+    for (int64_t r = r0; r < r1; ++r) {
+        const int lab = lab_n;
+        float4 v[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[i] = nxt[i];
+        if (r + 1 < r1) {
+            lab_n = __ldg(labels + r + 1);
+            load_row(r + 1, nxt);
+        }
+        if (lab != cur) {
+            flush(cur, run);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            cur = lab;
+            run = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) { acc[i].x += v[i].x; acc[i].y += v[i].y; acc[i].z += v[i].z; acc[i].w += v[i].w; }
+        ++run;
+    }
+    flush(cur, run);
+}
+
 // One block per centroid.
 __global__ void __launch_bounds__(128) kmeans_finalize_kernel(const float* __restrict__ sums,
                                                               const int32_t* __restrict__ cnts,
@@ -265,6 +323,15 @@ extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int 
     const int rows_per_warp = 16;
     const int64_t warps = ceil_div(n, rows_per_warp);
     const unsigned grid = (unsigned)ceil_div(warps, 8);
+    const bool vec = d % 4 == 0 && ldx % 4 == 0 && d <= 512 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(sums) & 15) == 0);
+    if (vec) {
+        if (d <= 128) kmeans_update_vec_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
+        else if (d <= 256) kmeans_update_vec_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
+        else kmeans_update_vec_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
+        FL_CHECK_LAUNCH();
+        return FL_OK;
+    }
     for (int dbase = 0; dbase < d; dbase += 256) {
         const int rem = d - dbase;
         if (rem <= 32)

@@ -114,7 +114,8 @@ int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 // k-means assignment on the same pipeline: asg_sc [nq_pad][2][2] (best, second-best score per
 // warpgroup half), asg_id [nq_pad][2] (best centroid per half).  Only qplane/nq_pad, dbrows/
 // m_pad/d_pad, tau (scratch) and status of `p` are used.
-int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cudaStream_t st);
+// nq_dev (optional): device-resident count of live rows; query tiles beyond it are skipped.
+int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, const int* nq_dev, cudaStream_t st);
 
 // bf16 query plane [nq_pad][d_pad] (zero padded) from fp32 queries.
 int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,

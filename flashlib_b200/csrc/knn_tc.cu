@@ -86,6 +86,7 @@ struct TcKernelParams {
     float* tau;
     float* part_tau;
     int* part_cnt;           // large-k mode: entries of every published pool
+    const int* nq_dev;       // optional: live query rows, counted on the device by an earlier kernel
     float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
@@ -183,7 +184,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int n_items = p.n_qtiles * p.nsplit;
+    // query tiles: fixed by the launch, or (nq_dev) cut down to the live rows counted on the device
+    int n_qtiles = p.n_qtiles;
+    if (p.nq_dev != nullptr) {
+        const int live = (__ldcg(p.nq_dev) + TC_BM - 1) / TC_BM;
+        n_qtiles = live < n_qtiles ? live : n_qtiles;
+    }
+    const int n_items = n_qtiles * p.nsplit;
     const int d_pad = p.nkc * TC_BK;
 
     if (warp == W_PRODUCER) {
@@ -194,7 +201,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             bool ok = true;
             long long prof_a = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
-                const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
+                const int split = it / n_qtiles, qt = it - split * n_qtiles;
                 const int t0 = split * p.tiles_per_split;
                 const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
@@ -205,7 +212,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     tma_load_2d(a_addr + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, BAR(B_AFULL));
                 tma_load_2d(a_aug_addr, &map_q_aug, d_pad, qt * TC_BM, BAR(B_AFULL));
                 const int nt = t1 - t0;
-                const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
+                const int rot = (int)(((int64_t)qt * nt) / n_qtiles);
                 for (int i = 0; i < nt && ok; ++i) {
                     // Query tiles walk their range from different starting tiles, so the CTAs of a
                     // wave do not all ask the L2 for the same lines at the same moment.
@@ -244,7 +251,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             bool ok = true;
             long long prof_full = 0, prof_tempty = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
-                const int split = it / p.n_qtiles;
+                const int split = it / n_qtiles;
                 const int t0 = split * p.tiles_per_split;
                 const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
@@ -312,7 +319,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         unsigned prof_groups = 0, prof_compact = 0, prof_append = 0;
         const long long prof_t0 = clock64();
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-            const int split = it / p.n_qtiles, qt = it - split * p.n_qtiles;
+            const int split = it / n_qtiles, qt = it - split * n_qtiles;
             const int t0 = split * p.tiles_per_split;
             const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
@@ -333,7 +340,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             float b1 = neg_inf(), b2 = neg_inf();   // assignment mode: best / second-best packed score
             int tbest = 0;                           // tile that produced b1
             const int nt = t1 - t0;
-            const int rot = (int)(((int64_t)qt * nt) / p.n_qtiles);
+            const int rot = (int)(((int64_t)qt * nt) / n_qtiles);
             for (int i = 0; i < nt; ++i, ++tile_no) {
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = tile_no & 1;
@@ -834,7 +841,7 @@ int tc_prof_read(unsigned long long* host_out, int words) {
 
 // Assignment launch: queries = sample rows, database = centroids; writes per (row, warpgroup)
 // the best and second-best score and the best centroid.
-int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cudaStream_t st) {
+int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, const int* nq_dev, cudaStream_t st) {
     FL_CHECK_ARG(p.qplane && p.dbrows && asg_sc && asg_id && p.tau, "tensor-core assignment launch with a null buffer");
     CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
     const int pitch = p.d_pad + PLANE_AUG_COLS;
@@ -854,6 +861,7 @@ int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cuda
     kp.off_b = sp.off_b; kp.off_pool_sc = sp.off_pool_sc; kp.off_pool_id = sp.off_pool_id; kp.off_bar = sp.off_bar;
     kp.nq_pad = p.nq_pad; kp.tau = p.tau; kp.status = p.status;
     kp.asg_sc = asg_sc; kp.asg_id = asg_id;
+    kp.nq_dev = nq_dev;
     kp.tile_stride = 1; kp.wait_hint_ns = 1000u;
     const int grid = kp.n_qtiles < sm_count() ? kp.n_qtiles : sm_count();
     FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_ASSIGN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
