@@ -178,7 +178,7 @@ struct AssignTcWs {
     int64_t n_pad; int d_pad, pitch; int fb_cap;
     int split;          // 1: a second stage with split (hi/lo) operand planes of 3 d_pad columns
     int l1_cap; int64_t l1_pad; int pitch3;
-    int nsplit_fb; int64_t rows_per_split_fb;
+    int nsplit_fb; int64_t rows_per_split_fb; int fb_bq, fb_blocks;
     PlaneLayout cl, cl3;
     int64_t off_cplane, off_cplane3, off_xplane, off_xsplit, off_asg_sc, off_asg_id, off_tau, off_cnt, off_l1list,
         off_fblist, off_fbpart_sc, off_fbpart_id, off_fbdist, bytes;
@@ -208,6 +208,12 @@ static AssignTcWs assign_tc_plan(int64_t n, int K, int d, int have_xplane) {
     w.l1_cap = w.split ? (int)((n + 1) / 2) : 0;
     w.l1_pad = round_up(w.l1_cap > 0 ? w.l1_cap : 1, 128);
     simt_split_plan(w.fb_cap, K, 32, d, &w.nsplit_fb, &w.rows_per_split_fb);
+    // the exact pass spreads a fixed grid over the live points (simt_dyn_split): one pool per
+    // (block, query slot) at most
+    w.fb_bq = simt_block_queries(32);
+    w.fb_blocks = (int)(ceil_div(w.fb_cap, w.fb_bq > 0 ? w.fb_bq : 1) * w.nsplit_fb);
+    if (w.fb_blocks < 4 * sm_count()) w.fb_blocks = 4 * sm_count();
+    const int64_t fb_pools = (int64_t)w.fb_blocks * (w.fb_bq > 0 ? w.fb_bq : 1);
     int64_t cur = 0;
     w.off_cplane = take(cur, w.cl.bytes);
     w.off_cplane3 = w.split ? take(cur, w.cl3.bytes) : -1;
@@ -219,8 +225,8 @@ static AssignTcWs assign_tc_plan(int64_t n, int K, int d, int have_xplane) {
     w.off_cnt = take(cur, 1024);
     w.off_l1list = take(cur, (int64_t)(w.l1_cap > 0 ? w.l1_cap : 1) * 4);
     w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
-    w.off_fbpart_sc = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * 32 * 4);
-    w.off_fbpart_id = take(cur, (int64_t)w.fb_cap * w.nsplit_fb * 32 * 4);
+    w.off_fbpart_sc = take(cur, fb_pools * 32 * 4);
+    w.off_fbpart_id = take(cur, fb_pools * 32 * 4);
     w.off_fbdist = take(cur, n * 4);
     w.bytes = cur;
     return w;
@@ -355,6 +361,7 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     sp.hnorm = reinterpret_cast<const float*>(cpl + w.cl.off_hnorm);
     sp.K1 = 32; sp.cap = simt_pool_cap(32); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(32, 1);
     sp.nsplit = w.nsplit_fb; sp.rows_per_split = w.rows_per_split_fb;
+    sp.dyn_blocks = w.fb_blocks; sp.dyn_bq = w.fb_bq;
     sp.part_sc = reinterpret_cast<float*>(base + w.off_fbpart_sc);
     sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_fbpart_id);
     sp.vecq = vecx; sp.vecd = vecc;
@@ -364,6 +371,7 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     fp.q = x; fp.ldq = ldx; fp.qlist = fb_list; fp.count_dev = fb_count; fp.count = 0;
     fp.db = c; fp.m = K; fp.ldb = ldc; fp.d = d; fp.vec = vec;
     fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit_fb; fp.K1 = 32;
+    fp.dyn_blocks = w.fb_blocks; fp.dyn_bq = w.fb_bq;
     fp.k = 1; fp.rerank = 9; fp.row_offset = 0;
     fp.out_dist = reinterpret_cast<float*>(base + w.off_fbdist); fp.out_idx = labels; fp.verify = 0;
     return launch_knn_finalize(fp, w.fb_cap, st);

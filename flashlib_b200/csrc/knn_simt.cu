@@ -248,11 +248,8 @@ int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) 
 // best, with bound = max(u, K1-th best).
 // ------------------------------------------------------------------------------------
 template <int NPL1>
-__global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
+__device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int64_t slot, const int64_t count) {
     const int lane = threadIdx.x & 31;
-    const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
-    if (slot >= count) return;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
     const int K1 = p.K1;
     int nsplit = p.nsplit;
@@ -478,9 +475,23 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     }
 }
 
+// One warp per slot, grid-stride: the slot count may only be known on the device, and a grid
+// sized for the largest possible count would mostly launch blocks that have nothing to do.
+template <int NPL1>
+__global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
+    const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
+    for (int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); slot < count; slot += (int64_t)gridDim.x * 4) {
+        finalize_slot<NPL1>(p, slot, count);
+        __syncwarp();
+    }
+}
+
 int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
     if (max_slots <= 0) return FL_OK;
-    const unsigned grid = (unsigned)ceil_div(max_slots, 4);
+    int64_t blocks = ceil_div(max_slots, 4);
+    const int64_t cap = (int64_t)sm_count() * (p.count_dev ? 32 : 1024);
+    if (blocks > cap) blocks = cap;
+    const unsigned grid = (unsigned)blocks;
     switch (p.K1 / 32) {
         case 1: knn_finalize_kernel<1><<<grid, 128, 0, st>>>(p); break;
         case 2: knn_finalize_kernel<2><<<grid, 128, 0, st>>>(p); break;
