@@ -200,6 +200,27 @@ __device__ __forceinline__ float warp_pool_compact(float* sc, uint32_t* idv, int
     return thr;
 }
 
+// Bitonic sort of n (power of two) entries in shared memory: larger key first, smaller id first
+// among equal keys.  All THREADS threads of the block must call it.
+template <int THREADS>
+__device__ __forceinline__ void block_sort_desc(float* key, uint32_t* id, int n) {
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < (n >> 1); i += THREADS) {
+                const int a = 2 * i - (i & (stride - 1));
+                const int b = a + stride;
+                const float ka = key[a], kb = key[b];
+                const uint32_t ia = id[a], ib = id[b];
+                const bool a_first = ka > kb || (ka == kb && ia <= ib);
+                const bool desc = (a & size) == 0;
+                if (a_first != desc) { key[a] = kb; key[b] = ka; id[a] = ib; id[b] = ia; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
 // Largest-value update of a float in global memory (compare-and-swap; a few writers at most).
 __device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
     int* ai = reinterpret_cast<int*>(addr);

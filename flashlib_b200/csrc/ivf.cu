@@ -119,6 +119,20 @@ static IvfWs ivf_ws_plan(int64_t nq, int nprobe, int nlist, int64_t m, int k) {
     return w;
 }
 
+// Groups the (query, probe) pairs by list: per-list pair counts, exclusive scans of the pairs and
+// of the work items (groups of bq pairs; lists without rows get none), pair ids sorted by list.
+int launch_ivf_group(const int32_t* probed, int64_t npairs, int nlist, int bq, const int64_t* list_offsets, int* cnt,
+                     int* pair_off, int* item_off, int* cursor, int* sorted_pair, cudaStream_t st) {
+    FL_CHECK_CUDA(cudaMemsetAsync(cnt, 0, sizeof(int) * (size_t)(nlist + 1), st));
+    ivf_count_kernel<<<(unsigned)ceil_div(npairs, 256), 256, 0, st>>>(probed, npairs, nlist, cnt);
+    FL_CHECK_LAUNCH();
+    ivf_scan_kernel<<<1, 1024, 0, st>>>(cnt, nlist, bq, list_offsets, pair_off, item_off, cursor);
+    FL_CHECK_LAUNCH();
+    ivf_scatter_kernel<<<(unsigned)ceil_div(npairs, 256), 256, 0, st>>>(probed, npairs, nlist, pair_off, cursor, sorted_pair);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 }  // namespace fl
 
 using namespace fl;

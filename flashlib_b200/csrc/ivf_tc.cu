@@ -1,0 +1,430 @@
+// IVF-Flat fine scan on the tensor-core candidate kernel (knn_tc.cu).
+//
+// Index side (once per index): a bf16 operand plane of the list-sorted rows in which every
+// non-empty list is padded to whole tiles of 256 rows, so a database tile never straddles two
+// lists and padding rows can never be candidates (they score -3e38), plus the map from plane
+// rows back to data rows.
+//
+// Search side (per call): the (query, probe) pairs are grouped by list on the device; every
+// group of up to 128 pairs of one list becomes one query tile of a gathered bf16 query plane
+// and one work item of the scoring kernel: that query tile against the tiles of its list.  The
+// kernel publishes a candidate pool and a threshold per gathered row; the finalisation kernel
+// (one warp per query) follows the pair -> gathered-row map to the query's nprobe pools, re-scores
+// the candidates exactly and proves the result against the scoring error bound.  Queries it
+// cannot prove are recomputed by an exact per-query scan of their probed lists.
+#include "knn_internal.h"
+#include "plane.h"
+#include "pool.cuh"
+#include <cuda_bf16.h>
+
+namespace fl {
+
+constexpr int IVF_TC_BQ = 128;       // pairs per query tile
+constexpr int IVF_TC_TILE = 256;     // database rows per tile
+
+struct IvfPlaneLayout {
+    int64_t rows_max;      // plane rows: every list padded to whole tiles
+    PlaneLayout pl;        // rows / half norms / max norm, as for a kNN database of rows_max rows
+    int64_t off_tile_off;  // i32 [nlist + 1]: first tile of every list (exclusive scan)
+    int64_t off_row_map;   // i32 [rows_max]: data row of every plane row, -1 for padding
+    int64_t bytes;
+};
+
+static IvfPlaneLayout ivf_plane_layout(int64_t m, int nlist, int d) {
+    IvfPlaneLayout L{};
+    L.rows_max = round_up(m + (int64_t)(IVF_TC_TILE - 1) * nlist, IVF_TC_TILE);
+    L.pl = plane_layout(L.rows_max, d);
+    L.off_tile_off = L.pl.bytes;
+    L.off_row_map = L.off_tile_off + round_up((int64_t)(nlist + 1) * 4, 1024);
+    L.bytes = L.off_row_map + round_up(L.rows_max * 4, 1024);
+    return L;
+}
+
+// Single block: exclusive scan of the tiles per list.
+__global__ void __launch_bounds__(1024) ivf_tile_scan_kernel(const int64_t* __restrict__ list_offsets, int nlist,
+                                                             int* __restrict__ tile_off) {
+    __shared__ int s_t[1024];
+    __shared__ int carry;
+    const int t = threadIdx.x;
+    if (t == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < nlist; base += 1024) {
+        const int c = base + t;
+        int nt = 0;
+        if (c < nlist) nt = (int)((list_offsets[c + 1] - list_offsets[c] + IVF_TC_TILE - 1) / IVF_TC_TILE);
+        s_t[t] = nt;
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {
+            const int a = t >= o ? s_t[t - o] : 0;
+            __syncthreads();
+            s_t[t] += a;
+            __syncthreads();
+        }
+        if (c < nlist) tile_off[c] = carry + s_t[t] - nt;
+        __syncthreads();
+        if (t == 1023) carry += s_t[t];
+        __syncthreads();
+    }
+    if (t == 0) tile_off[nlist] = carry;
+}
+
+// One block per list: data row of every plane row of the list (row_map is pre-filled with -1).
+__global__ void ivf_row_map_kernel(const int64_t* __restrict__ list_offsets, const int* __restrict__ tile_off,
+                                   int* __restrict__ row_map) {
+    const int c = blockIdx.x;
+    const int64_t r0 = list_offsets[c];
+    const int len = (int)(list_offsets[c + 1] - r0);
+    const int64_t p0 = (int64_t)tile_off[c] * IVF_TC_TILE;
+    for (int r = threadIdx.x; r < len; r += blockDim.x) row_map[p0 + r] = (int)(r0 + r);
+}
+
+// One warp per plane row: bf16 features, the split -||x||^2/2 columns, half norm, max norm.
+__global__ void ivf_plane_rows_kernel(const float* __restrict__ data, int64_t ld, int d, const int* __restrict__ row_map,
+                                      int64_t rows_max, __nv_bfloat16* __restrict__ rows, float* __restrict__ hnorm,
+                                      unsigned int* __restrict__ maxnorm_bits, int d_pad) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows_max) return;
+    const int pitch = d_pad + PLANE_AUG_COLS;
+    __nv_bfloat16* o = rows + row * pitch;
+    const int src = __ldg(row_map + row);
+    if (src < 0) {
+        for (int c = lane; c < pitch; c += 32) o[c] = __float2bfloat16_rn(c == d_pad ? -3.0e38f : 0.f);
+        if (lane == 0) hnorm[row] = pos_inf();
+        return;
+    }
+    const float* p = data + (int64_t)src * ld;
+    float s = 0.f;
+    for (int c = lane; c < d_pad; c += 32) {
+        const float v = (c < d) ? __ldg(p + c) : 0.f;
+        s += v * v;
+        o[c] = __float2bfloat16_rn(v);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(FULL_MASK, s, off);
+    if (lane == 0) {
+        hnorm[row] = 0.5f * s;
+        atomicMax(maxnorm_bits, __float_as_uint(sqrtf(s)));
+    }
+    if (lane < PLANE_AUG_COLS) {
+        const float nh = -0.5f * s;
+        const __nv_bfloat16 h1 = __float2bfloat16_rn(nh);
+        const float r1 = nh - __bfloat162float(h1);
+        const __nv_bfloat16 h2 = __float2bfloat16_rn(r1);
+        const float r2 = r1 - __bfloat162float(h2);
+        const __nv_bfloat16 h3 = __float2bfloat16_rn(r2);
+        o[d_pad + lane] = lane == 0 ? h1 : lane == 1 ? h2 : lane == 2 ? h3 : __float2bfloat16_rn(0.f);
+    }
+}
+
+// One block per list: the work items of the list (groups of IVF_TC_BQ of its pairs), the pair
+// of every gathered query row and the gathered row of every pair (pair_row is pre-filled with -1).
+__global__ void ivf_tc_items_kernel(const int* __restrict__ cnt, const int* __restrict__ pair_off,
+                                    const int* __restrict__ item_off, const int* __restrict__ sorted_pair,
+                                    const int* __restrict__ tile_off, int nlist, int* __restrict__ item_t0,
+                                    int* __restrict__ item_t1, int* __restrict__ grow, int* __restrict__ pair_row,
+                                    int* __restrict__ live_rows) {
+    const int c = blockIdx.x;
+    if (c == 0 && threadIdx.x == 0) *live_rows = item_off[nlist] * IVF_TC_BQ;
+    const int n = cnt[c];
+    const int t0 = tile_off[c], t1 = tile_off[c + 1];
+    if (n == 0 || t1 == t0) return;     // nobody probes the list, or it has no rows (no item: ivf_scan_kernel)
+    const int items = (n + IVF_TC_BQ - 1) / IVF_TC_BQ;
+    for (int g = 0; g < items; ++g) {
+        const int item = item_off[c] + g;
+        if (threadIdx.x == 0) { item_t0[item] = t0; item_t1[item] = t1; }
+        for (int j = threadIdx.x; j < IVF_TC_BQ; j += blockDim.x) {
+            const int idx = g * IVF_TC_BQ + j;
+            const int pair = idx < n ? sorted_pair[pair_off[c] + idx] : -1;
+            grow[item * IVF_TC_BQ + j] = pair;
+            if (pair >= 0) pair_row[pair] = item * IVF_TC_BQ + j;
+        }
+    }
+}
+
+// One warp per gathered query row (grid-stride over the live rows): the bf16 row of the pair's
+// query with ones in the norm columns and a -inf starting threshold; rows without a pair are
+// zero and get a +inf threshold, so nothing is ever a candidate for them.
+__global__ void ivf_tc_gather_kernel(const float* __restrict__ q, int64_t ldq, int d, int nprobe,
+                                     const int* __restrict__ grow, const int* __restrict__ live_rows,
+                                     __nv_bfloat16* __restrict__ qplane, float* __restrict__ tau, int d_pad) {
+    const int lane = threadIdx.x & 31;
+    const int pitch = d_pad + PLANE_AUG_COLS;
+    const int live = *live_rows;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < live; r += nwarps) {
+        const int pair = grow[r];
+        __nv_bfloat16* o = qplane + (int64_t)r * pitch;
+        if (pair < 0) {
+            for (int c = lane; c < pitch; c += 32) o[c] = __float2bfloat16_rn(0.f);
+            if (lane == 0) tau[r] = pos_inf();
+            continue;
+        }
+        const float* src = q + (int64_t)(pair / nprobe) * ldq;
+        for (int c = lane; c < d_pad; c += 32) o[c] = __float2bfloat16_rn(c < d ? __ldg(src + c) : 0.f);
+        if (lane < PLANE_AUG_COLS) o[d_pad + lane] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
+        if (lane == 0) tau[r] = neg_inf();
+    }
+}
+
+// Exact scan for the queries the proof rejected: one block per listed query walks the rows of the
+// query's probed lists (one warp per row, fp32 sum (q - x)^2 with the summation order of the
+// finalisation kernel), collects rows closer than the running k-th distance and compacts the
+// collection with a block sort whenever it is half full.
+constexpr int IVFX_THREADS = 256, IVFX_CAP = 4096, IVFX_CHUNK = 2048;
+__global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
+    const float* __restrict__ q, int64_t ldq, const float* __restrict__ data, int64_t ldd, int d, int vec,
+    const int64_t* __restrict__ list_offsets, int nlist, const int32_t* __restrict__ probed, int nprobe, int k,
+    const int* __restrict__ fb_list, const int* __restrict__ fb_count, float* __restrict__ out_dist,
+    int32_t* __restrict__ out_pos) {
+    __shared__ float s_key[IVFX_CAP];       // -distance: the block sort puts larger keys first
+    __shared__ uint32_t s_id[IVFX_CAP];
+    __shared__ __align__(16) float s_q[512];
+    __shared__ int s_n;
+    __shared__ float s_T;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int count = *fb_count;
+    for (int slot = blockIdx.x; slot < count; slot += gridDim.x) {
+        const int qi = fb_list[slot];
+        __syncthreads();
+        for (int c = tid; c < d; c += IVFX_THREADS) s_q[c] = __ldg(q + (int64_t)qi * ldq + c);
+        if (tid == 0) { s_n = 0; s_T = pos_inf(); }
+        __syncthreads();
+        auto compact = [&]() {
+            // all threads; keeps the k best, tightens the threshold
+            const int n = s_n;
+            int P = 32;
+            while (P < n) P <<= 1;
+            for (int i = n + tid; i < P; i += IVFX_THREADS) { s_key[i] = neg_inf(); s_id[i] = INVALID_ID; }
+            block_sort_desc<IVFX_THREADS>(s_key, s_id, P);
+            if (tid == 0) {
+                s_n = n < k ? n : k;
+                if (n >= k) s_T = -s_key[k - 1];
+            }
+            __syncthreads();
+        };
+        for (int j = 0; j < nprobe; ++j) {
+            const int c = probed[(int64_t)qi * nprobe + j];
+            if (c < 0 || c >= nlist) continue;
+            const int64_t r0 = list_offsets[c], r1 = list_offsets[c + 1];
+            for (int64_t base = r0; base < r1; base += IVFX_CHUNK) {
+                const int64_t end = base + IVFX_CHUNK < r1 ? base + IVFX_CHUNK : r1;
+                const float T = s_T;
+                for (int64_t r = base + warp; r < end; r += IVFX_THREADS / 32) {
+                    const float* xp = data + r * ldd;
+                    float a = 0.f;
+                    if (vec) {
+                        for (int t = lane * 4; t < d; t += 128) {
+                            const float4 qv = *reinterpret_cast<const float4*>(s_q + t);
+                            const float4 xv = __ldg(reinterpret_cast<const float4*>(xp + t));
+                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
+                            a += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                        }
+                    } else {
+                        for (int t = lane; t < d; t += 32) { const float df = s_q[t] - __ldg(xp + t); a += df * df; }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(FULL_MASK, a, o);
+                    if (lane == 0 && a <= T) {
+                        const int pos = atomicAdd(&s_n, 1);
+                        s_key[pos] = -a;                 // <= IVFX_CHUNK appends per chunk, <= IVFX_CHUNK kept before it
+                        s_id[pos] = (uint32_t)r;
+                    }
+                }
+                __syncthreads();
+                const int n_now = s_n;      // read by every thread before anyone appends again
+                __syncthreads();
+                if (n_now > IVFX_CAP - IVFX_CHUNK) compact();
+            }
+        }
+        __syncthreads();
+        compact();
+        const int n = s_n;
+        for (int e = tid; e < k; e += IVFX_THREADS) {
+            out_dist[(int64_t)qi * k + e] = e < n ? -s_key[e] : pos_inf();
+            out_pos[(int64_t)qi * k + e] = e < n ? (int32_t)s_id[e] : -1;
+        }
+    }
+}
+
+struct IvfTcWs {
+    int64_t npairs, max_items, cap_rows; int d_pad, pitch;
+    int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_pair_row, off_item_t0, off_item_t1,
+        off_grow, off_counters, off_qplane, off_tau, off_part_sc, off_part_id, off_part_tau, off_fblist, bytes;
+};
+
+static int64_t take(int64_t& cur, int64_t bytes) {
+    const int64_t o = cur;
+    cur += round_up(bytes > 0 ? bytes : 1, 1024);
+    return o;
+}
+
+static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
+    IvfTcWs w{};
+    w.npairs = nq * nprobe;
+    w.max_items = ceil_div(w.npairs, IVF_TC_BQ) + nlist;
+    w.cap_rows = w.max_items * IVF_TC_BQ;
+    w.d_pad = (int)round_up(d, 64);
+    w.pitch = w.d_pad + PLANE_AUG_COLS;
+    (void)k;
+    const int plen = tc_deep_partial_len();
+    int64_t cur = 0;
+    w.off_cnt = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_pair_off = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_item_off = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_cursor = take(cur, (int64_t)(nlist + 1) * 4);
+    w.off_sorted = take(cur, w.npairs * 4);
+    w.off_pair_row = take(cur, w.npairs * 4);
+    w.off_item_t0 = take(cur, w.max_items * 4);
+    w.off_item_t1 = take(cur, w.max_items * 4);
+    w.off_grow = take(cur, w.cap_rows * 4);
+    w.off_counters = take(cur, 1024);
+    w.off_qplane = take(cur, w.cap_rows * w.pitch * 2);
+    w.off_tau = take(cur, w.cap_rows * 4);
+    w.off_part_sc = take(cur, w.cap_rows * plen * 4);
+    w.off_part_id = take(cur, w.cap_rows * plen * 4);
+    w.off_part_tau = take(cur, w.cap_rows * tc_taus_per_range() * 4);
+    w.off_fblist = take(cur, nq * 4);
+    w.bytes = cur;
+    return w;
+}
+
+static int ivf_tc_supported(int64_t nq, int nprobe, int nlist, int64_t m, int d, int k) {
+    if (nq < 1 || nprobe < 1 || nlist < 1 || m < 1) return 0;
+    if (k > 16 || d > 128) return 0;      // deep pools + resident query tile + two ring slots: 128 features
+    if (nq * (int64_t)nprobe >= (1ll << 31) / IVF_TC_BQ || m + (int64_t)IVF_TC_TILE * nlist >= (1ll << 31)) return 0;
+    return 1;
+}
+
+}  // namespace fl
+
+using namespace fl;
+
+extern "C" int64_t fl_ivf_plane_bytes(int64_t m, int nlist, int d) {
+    if (m < 1 || nlist < 1 || d < 1 || d > 128) return 0;
+    return ivf_plane_layout(m, nlist, d).bytes;
+}
+
+extern "C" int fl_ivf_prepare_f32(const float* data, int64_t m, int64_t ldd, int d, const int64_t* list_offsets,
+                                  int nlist, void* plane, int64_t plane_bytes, void* stream) {
+    FL_CHECK_ARG(m >= 1 && d >= 1 && nlist >= 1 && ldd >= d, "fl_ivf_prepare_f32: bad shape");
+    FL_CHECK_ARG(data && list_offsets && plane, "fl_ivf_prepare_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0, "fl_ivf_prepare_f32: plane must be 256-byte aligned");
+    if (d > 128) { set_error("fl_ivf_prepare_f32: d=%d > 128 is not supported", d); return FL_EUNSUPPORTED; }
+    const IvfPlaneLayout L = ivf_plane_layout(m, nlist, d);
+    if (plane_bytes < L.bytes) { set_error("fl_ivf_prepare_f32: plane buffer %lld < %lld bytes", (long long)plane_bytes, (long long)L.bytes); return FL_EWORKSPACE; }
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(plane);
+    int* tile_off = reinterpret_cast<int*>(base + L.off_tile_off);
+    int* row_map = reinterpret_cast<int*>(base + L.off_row_map);
+    FL_CHECK_CUDA(cudaMemsetAsync(row_map, 0xFF, (size_t)L.rows_max * 4, st));
+    FL_CHECK_CUDA(cudaMemsetAsync(base + L.pl.off_meta, 0, 1024, st));
+    ivf_tile_scan_kernel<<<1, 1024, 0, st>>>(list_offsets, nlist, tile_off);
+    FL_CHECK_LAUNCH();
+    ivf_row_map_kernel<<<(unsigned)nlist, 256, 0, st>>>(list_offsets, tile_off, row_map);
+    FL_CHECK_LAUNCH();
+    const int wpb = 8;
+    ivf_plane_rows_kernel<<<(unsigned)ceil_div(L.rows_max, wpb), wpb * 32, 0, st>>>(
+        data, ldd, d, row_map, L.rows_max, reinterpret_cast<__nv_bfloat16*>(base + L.pl.off_rows),
+        reinterpret_cast<float*>(base + L.pl.off_hnorm), reinterpret_cast<unsigned int*>(base + L.pl.off_meta),
+        L.pl.d_pad);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+extern "C" int64_t fl_ivf_fine_scan_tc_workspace_bytes(int64_t nq, int nprobe, int nlist, int64_t m, int d, int k) {
+    if (!ivf_tc_supported(nq, nprobe, nlist, m, d, k)) return 0;
+    return ivf_tc_plan(nq, nprobe, nlist, d, k).bytes;
+}
+
+extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, const float* data, int64_t m,
+                                       int64_t ldd, int d, const int64_t* list_offsets, int nlist,
+                                       const int32_t* probed, int nprobe, int k, const void* ivf_plane,
+                                       float* out_dist, int32_t* out_pos, void* ws, int64_t ws_bytes,
+                                       int32_t* status, void* stream) {
+    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1 && nlist >= 1 && nprobe >= 1 && k >= 1, "fl_ivf_fine_scan_tc_f32: bad shape");
+    FL_CHECK_ARG(ldq >= d && ldd >= d, "fl_ivf_fine_scan_tc_f32: leading dimensions smaller than d");
+    if (nq == 0) return FL_OK;
+    if (!ivf_tc_supported(nq, nprobe, nlist, m, d, k)) {
+        set_error("fl_ivf_fine_scan_tc_f32: k=%d / d=%d / sizes outside the tensor-core scan (k <= 16, d <= 128)", k, d);
+        return FL_EUNSUPPORTED;
+    }
+    FL_CHECK_ARG(q && data && list_offsets && probed && ivf_plane && out_dist && out_pos && ws, "fl_ivf_fine_scan_tc_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0 && (reinterpret_cast<uintptr_t>(ivf_plane) & 255) == 0,
+                 "fl_ivf_fine_scan_tc_f32: workspace and plane must be 256-byte aligned");
+    const IvfTcWs w = ivf_tc_plan(nq, nprobe, nlist, d, k);
+    if (ws_bytes < w.bytes) { set_error("fl_ivf_fine_scan_tc_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes); return FL_EWORKSPACE; }
+    const IvfPlaneLayout L = ivf_plane_layout(m, nlist, d);
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(ws);
+    const char* pl = static_cast<const char*>(ivf_plane);
+    const int* tile_off = reinterpret_cast<const int*>(pl + L.off_tile_off);
+    const int* row_map = reinterpret_cast<const int*>(pl + L.off_row_map);
+    int* cnt = reinterpret_cast<int*>(base + w.off_cnt);
+    int* pair_off = reinterpret_cast<int*>(base + w.off_pair_off);
+    int* item_off = reinterpret_cast<int*>(base + w.off_item_off);
+    int* cursor = reinterpret_cast<int*>(base + w.off_cursor);
+    int* sorted_pair = reinterpret_cast<int*>(base + w.off_sorted);
+    int* pair_row = reinterpret_cast<int*>(base + w.off_pair_row);
+    int* item_t0 = reinterpret_cast<int*>(base + w.off_item_t0);
+    int* item_t1 = reinterpret_cast<int*>(base + w.off_item_t1);
+    int* grow = reinterpret_cast<int*>(base + w.off_grow);
+    int* counters = reinterpret_cast<int*>(base + w.off_counters);
+    int* live_rows = counters;
+    int* fb_count = counters + 64;
+    int* fb_list = reinterpret_cast<int*>(base + w.off_fblist);
+    float* tau = reinterpret_cast<float*>(base + w.off_tau);
+    if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
+    FL_CHECK_CUDA(cudaMemsetAsync(counters, 0, 1024, st));
+    FL_CHECK_CUDA(cudaMemsetAsync(pair_row, 0xFF, (size_t)w.npairs * 4, st));
+
+    // group the pairs by list, cut every list's pairs into query tiles
+    int rc = launch_ivf_group(probed, w.npairs, nlist, IVF_TC_BQ, list_offsets, cnt, pair_off, item_off, cursor,
+                              sorted_pair, st);
+    if (rc != FL_OK) return rc;
+    ivf_tc_items_kernel<<<(unsigned)nlist, 128, 0, st>>>(cnt, pair_off, item_off, sorted_pair, tile_off, nlist, item_t0,
+                                                        item_t1, grow, pair_row, live_rows);
+    FL_CHECK_LAUNCH();
+    ivf_tc_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(
+        q, ldq, d, nprobe, grow, live_rows, reinterpret_cast<__nv_bfloat16*>(base + w.off_qplane), tau, w.d_pad);
+    FL_CHECK_LAUNCH();
+
+    TcKnnParams tp{};
+    tp.qplane = base + w.off_qplane; tp.nq = w.cap_rows; tp.nq_pad = w.cap_rows;
+    tp.dbrows = pl + L.pl.off_rows; tp.hnorm = reinterpret_cast<const float*>(pl + L.pl.off_hnorm);
+    tp.m = L.rows_max; tp.m_pad = L.pl.m_pad; tp.d_pad = L.pl.d_pad; tp.K1 = tc_deep_pool_size();
+    tp.deep_pools = 1;     // a query has two pools per probed list only
+    tp.nsplit = 1; tp.tiles_per_split = L.pl.m_pad / IVF_TC_TILE;
+    tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    tp.tau = tau; tp.status = status;
+    tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
+    tp.k = k;
+    tp.nq_dev = live_rows; tp.item_t0 = item_t0; tp.item_t1 = item_t1;
+    profile_begin(st);
+    rc = launch_knn_tc(tp, st);
+    profile_end(st);
+    if (rc != FL_OK) return rc;
+
+    const int vecq = (ldq % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
+    const int vecd = (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(data) & 15) == 0);
+    FinalizeParams fp{};
+    fp.q = q; fp.ldq = ldq; fp.count = nq; fp.db = data; fp.m = m; fp.ldb = ldd; fp.d = d;
+    fp.vec = vecq && vecd && (d % 4 == 0);
+    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = nprobe; fp.K1 = tc_deep_partial_len();
+    fp.k = k; fp.rerank = fp.K1; fp.row_offset = 0;
+    fp.part_tau = tp.part_tau; fp.ntau = nprobe * tc_taus_per_range();
+    fp.out_dist = out_dist; fp.out_idx = out_pos;
+    fp.verify = 1; fp.eps_rel = 0.004f;
+    fp.maxnorm = reinterpret_cast<const float*>(pl + L.pl.off_meta);
+    fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = (int)nq;
+    fp.pool_row = pair_row; fp.id_map = row_map; fp.id_bound = L.rows_max;
+    rc = launch_knn_finalize(fp, nq, st);
+    if (rc != FL_OK) return rc;
+    rc = launch_fallback_fixup(fb_count, (int)nq, status, tc_deep_pool_size(), st);
+    if (rc != FL_OK) return rc;
+    ivf_exact_query_kernel<<<(unsigned)(2 * sm_count()), IVFX_THREADS, 0, st>>>(
+        q, ldq, data, ldd, d, fp.vec, list_offsets, nlist, probed, nprobe, k, fb_list, fb_count, out_dist, out_pos);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}

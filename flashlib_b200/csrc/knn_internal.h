@@ -71,6 +71,10 @@ struct FinalizeParams {
     // published pool scored at most this much (nullptr: none were left out below the pool)
     const float* part_tau; int ntau;
     int dyn_blocks; int dyn_bq;   // pools written by a dynamic-mode scan: nsplit comes from simt_dyn_split
+    // Optional indirections (inverted-file scan on the tensor-core kernel): pool s of slot q is
+    // pool number pool_row[q * nsplit + s] (< 0: empty) instead of q * nsplit + s, and candidate
+    // ids are rows of a padded operand plane that id_map turns into database rows (< 0: padding).
+    const int* pool_row; const int* id_map; int64_t id_bound;
     const int* part_cnt;     // large-k finalisation: entries per published pool ([slot][ntau])
     int* fb_count; int* fb_list; int fb_cap;
 };
@@ -92,6 +96,11 @@ struct TcKnnParams {
     float* part_tau;         // f32 [nq_pad][nsplit][tc_taus_per_range]: thresholds each (query, range) ended with
     int* part_cnt;           // large-k pools only: i32 [nq_pad][nsplit][tc_taus_per_range] entries per pool
     float* seed_cls;         // f32 [nq_pad][32] scratch of the threshold-seeding pass (nullptr: no seeding)
+    int deep_pools;          // 1: pools keep tc_deep_pool_size() entries and publish tc_deep_partial_len() per
+                             //    (query, range) (k <= 16): for queries with only a few pools each
+    const int* nq_dev;       // optional: live query rows (device); query tiles beyond them are skipped
+    const int* item_t0;      // optional, with nsplit == 1: database tile range [item_t0[t], item_t1[t]) of
+    const int* item_t1;      //   query tile t instead of one uniform range (inverted-file scan)
     int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)
     int32_t* status;
 };
@@ -102,6 +111,8 @@ int tc_knn_supported(int64_t nq, int64_t m, int d, int k);
 int tc_pool_size(int k);
 // Entries the tensor-core pass publishes per (query, range): a multiple of the pool size.
 int tc_partial_len(int k);
+int tc_deep_pool_size();
+int tc_deep_partial_len();
 // Thresholds the tensor-core pass publishes per (query, range).
 int tc_taus_per_range();
 // 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
@@ -124,6 +135,8 @@ int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qpl
 // Small helpers shared by the entry points.
 int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st);
 int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t st);
+int launch_ivf_group(const int32_t* probed, int64_t npairs, int nlist, int bq, const int64_t* list_offsets, int* cnt,
+                     int* pair_off, int* item_off, int* cursor, int* sorted_pair, cudaStream_t st);
 int launch_fallback_fixup(int* fb_count, int fb_cap, int32_t* status, int K1, cudaStream_t st);
 
 }  // namespace fl

@@ -257,12 +257,33 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
         int64_t rps;
         simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m, &nsplit, &rps);
     }
-    const float* psc = p.part_sc + slot * nsplit * (int64_t)K1;
-    const uint32_t* pid = p.part_id + slot * nsplit * (int64_t)K1;
+    // pool s of this slot: offset of its first entry (negative: the pool does not exist)
+    auto pool_base = [&](int s) -> int64_t {
+        if (p.pool_row == nullptr) return (slot * nsplit + s) * (int64_t)K1;
+        const int row = __ldg(p.pool_row + slot * nsplit + s);
+        return row >= 0 ? (int64_t)row * K1 : -1;
+    };
+    // published id -> database row, INVALID_ID for padding rows of the operand plane
+    auto real_id = [&](uint32_t raw) -> uint32_t {
+        if (p.id_map == nullptr) return raw < (uint32_t)p.m ? raw : INVALID_ID;
+        if (raw >= (uint32_t)p.id_bound) return INVALID_ID;
+        const int mapped = __ldg(p.id_map + raw);
+        return mapped >= 0 ? (uint32_t)mapped : INVALID_ID;
+    };
+    const float* psc = p.part_sc;
+    const uint32_t* pid = p.part_id;
 
     float u = neg_inf();
     if (p.part_tau != nullptr) {
-        for (int i = lane; i < p.ntau; i += 32) u = fmaxf(u, p.part_tau[slot * p.ntau + i]);
+        const int per_pool = p.ntau / nsplit;
+        for (int i = lane; i < p.ntau; i += 32) {
+            int64_t t = slot * p.ntau + i;
+            if (p.pool_row != nullptr) {
+                const int row = __ldg(p.pool_row + slot * nsplit + i / per_pool);
+                t = row >= 0 ? (int64_t)row * per_pool + i % per_pool : -1;
+            }
+            if (t >= 0) u = fmaxf(u, p.part_tau[t]);
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
     }
@@ -286,7 +307,7 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
         slack = 1e-5f * (qsq + mn * mn);
     }
 
-    constexpr bool HAS_FILTER = NPL1 <= 2;
+    constexpr bool HAS_FILTER = NPL1 <= 4;
     __shared__ float s_sc[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
     __shared__ uint32_t s_id[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
     const bool try_filter = HAS_FILTER && p.verify && p.part_tau != nullptr && u > neg_inf();
@@ -304,11 +325,14 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             float lmax = neg_inf();
             for (int s = 0; s < nsplit; ++s) {
+                const int64_t pb = pool_base(s);
+                if (pb < 0) continue;
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | ((lane + 5 * s + 16 * r) & 31);
-                    const float sc = psc[(int64_t)s * K1 + e];
-                    if (pid[(int64_t)s * K1 + e] < (uint32_t)p.m) lmax = fmaxf(lmax, sc);
+                    const float sc = psc[pb + e];
+                    // (padding rows of an operand plane score -3e38: no need to look their ids up)
+                    if (pid[pb + e] != INVALID_ID) lmax = fmaxf(lmax, sc);
                 }
             }
             int rank = 0;
@@ -323,13 +347,15 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             const unsigned lt = (1u << lane) - 1u;
             int total = 0;
             for (int s = 0; s < nsplit; ++s) {
+                const int64_t pb = pool_base(s);
+                if (pb < 0) continue;
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | lane;
-                    const float sc = psc[(int64_t)s * K1 + e];
+                    const float sc = psc[pb + e];
                     const bool pass = sc > u && sc >= f0;
-                    const uint32_t cid = pass ? pid[(int64_t)s * K1 + e] : INVALID_ID;
-                    const bool keep = pass && cid < (uint32_t)p.m;
+                    const uint32_t cid = pass ? real_id(pid[pb + e]) : INVALID_ID;
+                    const bool keep = pass && cid != INVALID_ID;
                     const unsigned mask = __ballot_sync(FULL_MASK, keep);
                     const int pos = total + __popc(mask & lt);
                     if (keep && pos < 32 * NPL1) { wsc[pos] = sc; wid[pos] = cid; }
@@ -355,12 +381,14 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
 #pragma unroll
             for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
             for (int s = 0; s < nsplit; ++s) {
+                const int64_t pb = pool_base(s);
+                if (pb < 0) continue;
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | lane;
-                    const uint32_t cid = pid[(int64_t)s * K1 + e];
-                    const bool real = cid < (uint32_t)p.m;   // padding rows of the operand plane never count
-                    kin[r] = real ? psc[(int64_t)s * K1 + e] : neg_inf();
+                    const uint32_t cid = real_id(pid[pb + e]);
+                    const bool real = cid != INVALID_ID;   // padding rows of the operand plane never count
+                    kin[r] = real ? psc[pb + e] : neg_inf();
                     iin[r] = real ? cid : INVALID_ID;
                 }
                 warp_sort_desc<NPL1, false>(kin, iin);
@@ -519,26 +547,6 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
 // ------------------------------------------------------------------------------------
 constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 256;
 
-// Bitonic sort of n (power of two) entries in shared memory: larger key first, smaller id first
-// among equal keys.
-__device__ __forceinline__ void block_sort_desc(float* key, uint32_t* id, int n) {
-    for (int size = 2; size <= n; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < (n >> 1); i += BIG_THREADS) {
-                const int a = 2 * i - (i & (stride - 1));
-                const int b = a + stride;
-                const float ka = key[a], kb = key[b];
-                const uint32_t ia = id[a], ib = id[b];
-                const bool a_first = ka > kb || (ka == kb && ia <= ib);
-                const bool desc = (a & size) == 0;
-                if (a_first != desc) { key[a] = kb; key[b] = ka; id[a] = ib; id[b] = ia; }
-            }
-        }
-    }
-    __syncthreads();
-}
-
 __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeParams p) {
     __shared__ float s_key[BIG_CAND];
     __shared__ uint32_t s_id[BIG_CAND];
@@ -607,7 +615,7 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
         __syncthreads();
         total = s_n;
         if (total <= BIG_CAND) break;
-        block_sort_desc(s_key, s_id, BIG_CAND);
+        block_sort_desc<BIG_THREADS>(s_key, s_id, BIG_CAND);
         cut = fmaxf(cut, s_key[BIG_CAND / 4 - 1]);
     }
     const bool overflow = total > BIG_CAND;
@@ -615,7 +623,7 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
     int P = BIG_RERANK;
     while (P < n) P <<= 1;
     for (int i = n + tid; i < P; i += BIG_THREADS) { s_key[i] = neg_inf(); s_id[i] = INVALID_ID; }
-    block_sort_desc(s_key, s_id, P);
+    block_sort_desc<BIG_THREADS>(s_key, s_id, P);
 
     // exact distances of the best BIG_RERANK; everything else scored at most `bound`
     float bound = cut;
@@ -657,7 +665,7 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
             if (lane == 0) s_key[c0 + t] = cid[t] != INVALID_ID ? -a[t] : neg_inf();
         }
     }
-    block_sort_desc(s_key, s_id, BIG_RERANK);
+    block_sort_desc<BIG_THREADS>(s_key, s_id, BIG_RERANK);
 
     for (int e = tid; e < p.k; e += BIG_THREADS) {
         const bool ok = s_id[e] != INVALID_ID;

@@ -36,6 +36,9 @@ constexpr int TC_CAP = 32;            // pool capacity before compaction
 constexpr int TC_PSTR = TC_CAP + 1;   // padded pool row stride (bank spread); the extra slot is scratch
 constexpr int TC_BIG_K1 = 128;        // large-k mode (16 < k <= 128): pools live in global memory,
 constexpr int TC_BIG_CAP = 256;       // directly in the published-pool buffers
+constexpr int TC_MID_K1 = 24;         // deep-pool mode: a query has few pools (inverted-file scan: two per
+constexpr int TC_MID_CAP = 48;        // probed list), so each must reach further below the k-th neighbour
+constexpr int TC_MID_PUB = 64;        // published entries per pool in that mode (padded)
 constexpr int TC_THREADS = (4 * TC_NWG + 2) * 32;
 constexpr int TC_A_CHUNK = TC_BM * 128;   // bytes of one K-chunk of the query tile
 constexpr int TC_A_AUG = TC_BM * 32;      // bytes of the query tile's 16 norm columns
@@ -51,12 +54,12 @@ struct TcSmemPlan {
     int off_a, off_b, off_pool_sc, off_pool_id, off_hbuf, off_bar, bytes;
 };
 
-static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, bool pools = true) {
+static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_PSTR) {
     TcSmemPlan s{};
     s.nkc = d_pad / TC_BK;
     int cur = 0;
     s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
-    const int pool = pools ? TC_NWG * TC_BM * TC_PSTR * 4 : 0;   // the assignment mode keeps no pools
+    const int pool = TC_NWG * TC_BM * pool_stride * 4;   // 0: no pools in shared memory
     const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
     int ns = (smem_limit - fixed) / TC_B_STAGE;
     if (ns > TC_MAX_STAGES) ns = TC_MAX_STAGES;
@@ -87,6 +90,8 @@ struct TcKernelParams {
     float* part_tau;
     int* part_cnt;           // large-k mode: entries of every published pool
     const int* nq_dev;       // optional: live query rows, counted on the device by an earlier kernel
+    const int* item_t0;      // optional (one range per query tile): first / one-past-last database
+    const int* item_t1;      //   tile of query tile `it`, instead of the uniform ranges
     float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
@@ -116,7 +121,7 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
         const int src = __ffs(need) - 1;
         need &= need - 1;
         const int n = __shfl_sync(FULL_MASK, cnt, src);
-        const float thr = warp_pool_compact<CAP / 32>(warp_sc + src * stride, warp_id + src * stride, n, K1);
+        const float thr = warp_pool_compact<(CAP + 31) / 32>(warp_sc + src * stride, warp_id + src * stride, n, K1);
         if (lane == src) { cnt = min(n, K1); tau = fmaxf(tau, thr); }
     }
     return make_float2(__int_as_float(cnt), tau);
@@ -136,7 +141,10 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
 // fit shared memory; they live in global memory, in place in the published-pool buffers (appends
 // are predicated stores, compaction reads them back through the L2), and each pool's entry
 // count is published with it.
-constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3;
+//
+// MODE 4 (TC_MODE_KNN_MID) is MODE 0 with deeper pools in shared memory (24 of 48 kept, 64
+// published): for callers whose queries have only a few pools each.
+constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3, TC_MODE_KNN_MID = 4;
 template <bool DBG, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
@@ -202,8 +210,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             long long prof_a = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
                 const int split = it / n_qtiles, qt = it - split * n_qtiles;
-                const int t0 = split * p.tiles_per_split;
-                const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
+                const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
+                const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
@@ -252,8 +260,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             long long prof_full = 0, prof_tempty = 0;
             for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
                 const int split = it / n_qtiles;
-                const int t0 = split * p.tiles_per_split;
-                const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
+                const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
+                const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 5, B_AFULL); ok = false; break;
                 }
@@ -304,14 +312,17 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // every accumulator and keeps its own pool per query row.
         const int wg = warp >> 2, quarter = warp & 3;
         constexpr bool BIG = (MODE == TC_MODE_KNN_BIG);
-        constexpr int CAP = BIG ? TC_BIG_CAP : TC_CAP;
-        constexpr int K1 = BIG ? TC_BIG_K1 : TC_K1;
+        constexpr bool MID = (MODE == TC_MODE_KNN_MID);
+        constexpr int CAP = BIG ? TC_BIG_CAP : MID ? TC_MID_CAP : TC_CAP;
+        constexpr int K1 = BIG ? TC_BIG_K1 : MID ? TC_MID_K1 : TC_K1;
+        constexpr int PSTR = CAP + 1;                    // shared pools: padded stride, slot CAP is scratch
+        constexpr int PUB = BIG ? TC_BIG_CAP : MID ? TC_MID_PUB : TC_CAP;   // published entries per pool
         // pool of lane 0's row and distance (elements) between the pools of consecutive rows
-        float* warp_sc = pool_sc + warp * 32 * TC_PSTR;
-        uint32_t* warp_id = pool_id + warp * 32 * TC_PSTR;
-        int64_t pstride = TC_PSTR;
-        float* my_sc = warp_sc + lane * TC_PSTR;
-        uint32_t* my_id = warp_id + lane * TC_PSTR;
+        float* warp_sc = pool_sc + warp * 32 * PSTR;
+        uint32_t* warp_id = pool_id + warp * 32 * PSTR;
+        int64_t pstride = PSTR;
+        float* my_sc = warp_sc + lane * PSTR;
+        uint32_t* my_id = warp_id + lane * PSTR;
         const uint32_t lane_taddr = tmem_base + (uint32_t(quarter * 32) << 16);
         uint32_t tile_no = 0;
         bool ok = true;
@@ -320,8 +331,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const long long prof_t0 = clock64();
         for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
             const int split = it / n_qtiles, qt = it - split * n_qtiles;
-            const int t0 = split * p.tiles_per_split;
-            const int t1 = min(p.n_tiles, t0 + p.tiles_per_split);
+            const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
+            const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
             const float tau_in = __ldcg(p.tau + qrow);
             if (BIG) {
@@ -527,8 +538,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const bool pass = (pm >> j) & 1u;
-                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
-                            if (!BIG || pass) {       // shared pools: slot TC_CAP is the row's scratch slot
+                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : CAP;
+                            if (!BIG || pass) {       // shared pools: slot CAP is the row's scratch slot
                                 my_sc[pos] = __uint_as_float(r[j]);
                                 my_id[pos] = row_base + g * 8 + j;
                             }
@@ -557,7 +568,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     if (!__any_sync(FULL_MASK, np > 1)) {
                         // at most one passing score per lane: it is the maximum of the group
                         const float mx = fmaxf(fmax3(sv[0], sv[1], sv[2]), fmax3(fmax3(sv[3], sv[4], sv[5]), sv[6], sv[7]));
-                        const int pos = np ? cnt : TC_CAP;
+                        const int pos = np ? cnt : CAP;
                         if (!BIG || np) {
                             my_sc[pos] = mx;
                             my_id[pos] = scb + (__ffs(pm) - 1);
@@ -566,7 +577,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const bool pass = (pm >> j) & 1u;
-                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : TC_CAP;
+                            const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : CAP;
                             if (!BIG || pass) {
                                 my_sc[pos] = sv[j];
                                 my_id[pos] = scb + j;
@@ -611,12 +622,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 #pragma unroll 1
             for (int src = 0; src < 32; ++src) {
                 const int n = __shfl_sync(FULL_MASK, cnt, src);
-                const float* rsc = warp_sc + src * TC_PSTR;
-                const uint32_t* rid = warp_id + src * TC_PSTR;
+                const float* rsc = warp_sc + src * PSTR;
+                const uint32_t* rid = warp_id + src * PSTR;
                 const int64_t q = (int64_t)qt * TC_BM + quarter * 32 + src;
-                const int64_t o = ((q * p.nsplit + split) * TC_NWG + wg) * TC_CAP;
+                const int64_t o = ((q * p.nsplit + split) * TC_NWG + wg) * PUB;
 #pragma unroll
-                for (int e = lane; e < TC_CAP; e += 32) {
+                for (int e = lane; e < PUB; e += 32) {
                     p.part_sc[o + e] = e < n ? rsc[e] : neg_inf();
                     p.part_id[o + e] = e < n ? rid[e] : INVALID_ID;
                 }
@@ -706,6 +717,8 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int c
 int tc_knn_big(int k) { return k > 16 ? 1 : 0; }
 int tc_pool_size(int k) { return tc_knn_big(k) ? TC_BIG_K1 : TC_K1; }
 int tc_partial_len(int k) { return TC_NWG * (tc_knn_big(k) ? TC_BIG_CAP : TC_CAP); }
+int tc_deep_pool_size() { return TC_MID_K1; }
+int tc_deep_partial_len() { return TC_NWG * TC_MID_PUB; }
 int tc_taus_per_range() { return TC_NWG; }
 
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k) {
@@ -759,7 +772,9 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
     if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
-    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), !big);
+    const bool mid = p.deep_pools != 0;
+    FL_CHECK_ARG(!(mid && (big || dbg)), "tensor-core kNN launch: deep pools go with k <= 16");
+    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), big ? 0 : mid ? TC_MID_CAP + 1 : TC_PSTR);
     if (sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     TcKernelParams kp{};
     kp.n_qtiles = (int)(p.nq_pad / TC_BM);
@@ -773,6 +788,9 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
     kp.part_cnt = p.part_cnt;
     kp.seed_cls = p.seed_cls;
+    kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1;
+    FL_CHECK_ARG((p.item_t0 == nullptr) == (p.item_t1 == nullptr) && (p.item_t0 == nullptr || (p.nsplit == 1 && !big)),
+                 "tensor-core kNN launch: per-tile ranges need one range per query tile and k <= 16");
     {
         const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
         kp.dbg_flags = e ? atoi(e) : 0;
@@ -819,7 +837,10 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         tc_seed_select_kernel<<<(unsigned)ceil_div(p.nq_pad, 128), 128, 0, st>>>(p.seed_cls, p.tau, p.nq_pad, seed_rank);
         FL_CHECK_LAUNCH();
     }
-    if (big) {
+    if (mid) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_MID>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_KNN_MID><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+    } else if (big) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_BIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<false, TC_MODE_KNN_BIG><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     } else if (dbg != nullptr || kp.dbg_flags != 0) {
@@ -850,7 +871,7 @@ int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cons
     if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
     if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
-    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), false);
+    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), 0);
     if (sp.nstage < 2) { set_error("tensor-core assignment: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     TcKernelParams kp{};
     kp.n_qtiles = (int)(p.nq_pad / TC_BM);

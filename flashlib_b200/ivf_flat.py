@@ -38,6 +38,8 @@ class IvfFlatIndex:
     nprobe: int
     max_list_len: int = 0
     _hnorm: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
+    _tc_plane: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
+    _last_status: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
 
     @property
     def M(self) -> int:
@@ -118,9 +120,26 @@ def index_from_centroids(Xp: torch.Tensor, centroids: torch.Tensor, *, D: int, n
                         nlist=int(nlist), nprobe=int(nprobe), max_list_len=max_list_len)
 
 
-def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k: int):
+def _tc_plane(index: IvfFlatIndex, data: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
+    """bf16 operand plane of the stored rows for the tensor-core fine scan, built on first use."""
+    if index._tc_plane is None or index._tc_plane.device != data.device:
+        lib = _lib.load()
+        m, d = data.shape
+        nbytes = lib.fl_ivf_plane_bytes(m, index.nlist, d)
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=data.device)
+        with torch.cuda.device(data.device):
+            _lib.check(lib.fl_ivf_prepare_f32(data.data_ptr(), m, data.stride(0), d, offs.data_ptr(), index.nlist,
+                                              buf.data_ptr(), nbytes, _stream_ptr(data.device)))
+        index._tc_plane = buf
+    return index._tc_plane
+
+
+def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k: int, mode: Optional[str] = None):
     """Fine scan of the probed lists: ``(vals fp32 (nq,k), pos int32 (nq,k))``, ``+inf`` / ``-1``
-    padded when a query's lists hold fewer than ``k`` rows."""
+    padded when a query's lists hold fewer than ``k`` rows.  ``mode`` ``"exact"`` forces the
+    CUDA-core scan, ``"bf16"`` the tensor-core scan (k <= 16, d <= 128); ``None`` takes the
+    tensor cores for k <= 10 when the batch has at least 2,048 (query, probe) pairs.  Both
+    return the same neighbours."""
     lib = _lib.load()
     _lib.require_device()
     q = _as_f32_rows(Qp)
@@ -132,6 +151,25 @@ def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k
     offs = index.list_offsets.to(torch.int64).contiguous()
     vals = torch.empty((nq, k), dtype=torch.float32, device=q.device)
     pos = torch.empty((nq, k), dtype=torch.int32, device=q.device)
+    if mode not in (None, "auto", "exact", "simt", "bf16", "tc"):
+        raise ValueError(f"unknown fine-scan mode {mode!r} (exact|bf16|None)")
+    same_data = data.data_ptr() == index.data.data_ptr()
+    tc_bytes = lib.fl_ivf_fine_scan_tc_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k) if same_data else 0
+    if mode in ("bf16", "tc") and tc_bytes == 0:
+        raise NotImplementedError("tensor-core fine scan needs k <= 16, d <= 128 and fp32 rows stored in the index")
+    # auto: the candidate pools keep 12 entries per (pair, half list), enough to prove k <= 10
+    if nq > 0 and tc_bytes > 0 and (mode in ("bf16", "tc") or
+                                    (mode in (None, "auto") and k <= 10 and nq * nprobe >= 2048)):
+        plane = _tc_plane(index, data, offs)
+        ws = torch.empty(tc_bytes, dtype=torch.uint8, device=q.device)
+        status = torch.zeros(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=q.device)
+        with torch.cuda.device(q.device):
+            _lib.check(lib.fl_ivf_fine_scan_tc_f32(q.data_ptr(), nq, q.stride(0), data.data_ptr(), m, data.stride(0), d,
+                                                   offs.data_ptr(), index.nlist, probed.data_ptr(), nprobe, k,
+                                                   plane.data_ptr(), vals.data_ptr(), pos.data_ptr(),
+                                                   ws.data_ptr(), tc_bytes, status.data_ptr(), _stream_ptr(q.device)))
+        index._last_status = status     # status[FL_STATUS_FALLBACK]: queries recomputed by the exact scan
+        return vals, pos
     ws_bytes = lib.fl_ivf_fine_scan_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
     hn = index.half_norms() if data.data_ptr() == index.data.data_ptr() else None
@@ -149,7 +187,9 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
                           backend: Optional[str] = None, variant: str = "auto"):
     """``(vals fp32, ids int64)`` of the ``k`` nearest probed rows per query, ``-1`` / ``+inf``
     padded (``ivf_flat/triton/search.py:52-108``).  ``variant`` is validated like the
-    reference's and otherwise ignored: one fine-scan kernel serves every batch size."""
+    reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 16 and
+    d <= 128, the CUDA-core scan otherwise), ``"elementwise"`` for the CUDA-core scan,
+    ``"auto"`` picks by batch size.  All variants return the same neighbours."""
     if variant not in ("auto", "gemm", "elementwise"):
         raise ValueError(f"unknown variant {variant!r} (auto|gemm|elementwise)")
     if not Q.is_cuda or Q.ndim != 2:
@@ -162,7 +202,10 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     # coarse probe in the exact-rank mode: near-tied centroids must rank as in fp32
     probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
                        return_distances=False, mode="exact")[0]
-    vals, pos = ivf_fine_scan(Qp, index, probed, k)
+    mode = {"auto": None, "elementwise": "exact", "gemm": "bf16"}[variant]
+    if mode == "bf16" and (k > 10 or index.Dp > 128):
+        mode = "exact"
+    vals, pos = ivf_fine_scan(Qp, index, probed, k, mode=mode)
     valid = pos >= 0
     pos_safe = pos.clamp_min(0).to(torch.int64)
     ids = torch.where(valid, index.ids[pos_safe], torch.full_like(pos_safe, -1))

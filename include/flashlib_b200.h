@@ -196,6 +196,28 @@ int     fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq,
                              float* out_dist, int32_t* out_pos,
                              void* ws, int64_t ws_bytes, void* stream);
 
+/* The same fine scan on the tensor cores (k <= 16, d <= 128), the counterpart of the     */
+/* reference's GEMM variant (ivf_flat/triton/fine_scan_gemm.py:41-272).                   */
+/* fl_ivf_prepare_f32 builds, once per index, the bf16 operand plane of the stored rows    */
+/* (every list padded to whole 256-row tiles) and the map back to stored rows, in a         */
+/* caller buffer of fl_ivf_plane_bytes bytes.  fl_ivf_fine_scan_tc_f32 has the contract of  */
+/* fl_ivf_fine_scan_f32 (same outputs, bit-for-bit the same distances for proven rows):     */
+/* candidates come from bf16 scoring and are re-scored exactly; a query whose result       */
+/* cannot be proven against the scoring error bound is recomputed by an exact scan of its   */
+/* probed lists (status[FL_STATUS_FALLBACK] counts them).  Workspace size 0 = unsupported.  */
+int64_t fl_ivf_plane_bytes(int64_t m, int nlist, int d);
+int     fl_ivf_prepare_f32(const float* data, int64_t m, int64_t ldd, int d,
+                           const int64_t* list_offsets, int nlist,
+                           void* plane, int64_t plane_bytes, void* stream);
+int64_t fl_ivf_fine_scan_tc_workspace_bytes(int64_t nq, int nprobe, int nlist, int64_t m, int d, int k);
+int     fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq,
+                                const float* data, int64_t m, int64_t ldd, int d,
+                                const int64_t* list_offsets, int nlist,
+                                const int32_t* probed, int nprobe, int k,
+                                const void* ivf_plane,
+                                float* out_dist, int32_t* out_pos,
+                                void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

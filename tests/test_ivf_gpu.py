@@ -82,3 +82,51 @@ def test_small_dim_padding_and_short_lists():
     assert torch.all(ids[:, 0] == torch.arange(20, device="cuda"))
     with pytest.raises(ValueError):
         ivf.kneighbors(X[:2], 201)
+
+
+@pytest.mark.parametrize("k,nprobe", [(10, 4), (5, 32), (1, 1), (8, 8)])
+def test_tensor_core_fine_scan_matches_reference_fixture(k, nprobe):
+    """variant="gemm": the fine scan on the tensor-core kernel, against the reference's outputs on
+    the same index (and against the CUDA-core variant)."""
+    d, index = golden_index()
+    q = torch.from_numpy(d["q"]).cuda()
+    vals, ids = fl.flash_ivf_flat_search(index, q, k, nprobe=nprobe, variant="gemm")
+    ev, ei = fl.flash_ivf_flat_search(index, q, k, nprobe=nprobe, variant="elementwise")
+    assert index._tc_plane is not None and index._last_status is not None
+    assert index._last_status[0].item() == 0
+    torch.testing.assert_close(vals, ev, rtol=1e-5, atol=1e-5)
+    assert (ids == ei).float().mean().item() >= 0.999
+    key = f"vals_k{k}_p{nprobe}"
+    if key in d.files:
+        ref_v, ref_i = d[key], d[f"ids_k{k}_p{nprobe}"]
+        v, i = vals.cpu().numpy(), ids.cpu().numpy()
+        finite = np.isfinite(ref_v)
+        assert np.array_equal(np.isfinite(v), finite)
+        assert parity.rel_close(v[finite], ref_v[finite], rel=1e-4, atol=1e-4)
+        same = np.mean([set(a[f].tolist()) == set(b[f].tolist()) for a, b, f in zip(i, ref_i, finite)])
+        assert same >= 0.99, same
+
+
+@pytest.mark.parametrize("n,dim,nlist,nprobe,nq,k", [(60_000, 64, 128, 8, 700, 10), (30_000, 96, 37, 5, 1500, 16),
+                                                   (5_000, 128, 300, 20, 64, 3), (100_000, 128, 256, 16, 4000, 10)])
+def test_tensor_core_fine_scan_equals_cuda_core_scan(n, dim, nlist, nprobe, nq, k):
+    """Same index, same probed lists: both fine scans return the same rows and distances.  Shapes
+    cover lists shorter than k, empty lists (more lists than a cluster structure fills), query
+    tiles with a few pairs and lists probed by more than 128 queries."""
+    from flashlib_b200.ivf_flat import ivf_fine_scan
+    g = torch.Generator().manual_seed(n + nq)
+    means = 2 * torch.randn(40, dim, generator=g)
+    X = (means[torch.randint(0, 40, (n,), generator=g)] + torch.randn(n, dim, generator=g)).cuda()
+    Q = (means[torch.randint(0, 40, (nq,), generator=g)] + torch.randn(nq, dim, generator=g)).cuda()
+    index = fl.flash_ivf_flat_build(X, nlist, nprobe=nprobe, niter=4, seed=3)
+    probed = fl.flash_knn(Q, index.centroids, nprobe, return_distances=False, mode="exact")
+    ev, ep = ivf_fine_scan(Q, index, probed, k, mode="exact")
+    tv, tp = ivf_fine_scan(Q, index, probed, k, mode="bf16")
+    st = index._last_status.tolist()
+    assert st[0] == 0, st
+    assert torch.equal(torch.isfinite(tv), torch.isfinite(ev))
+    fin = torch.isfinite(ev)
+    torch.testing.assert_close(tv[fin], ev[fin], rtol=1e-5, atol=1e-5)
+    assert (tp == ep).float().mean().item() >= 0.9995
+    if k <= 10:                            # (pools keep 12 entries: beyond k = 10 many queries
+        assert st[2] <= nq // 10, st       #  take the exact scan, which is why "auto" stops there)
