@@ -147,7 +147,8 @@ __global__ void ivf_tc_items_kernel(const int* __restrict__ cnt, const int* __re
 // zero and get a +inf threshold, so nothing is ever a candidate for them.
 __global__ void ivf_tc_gather_kernel(const float* __restrict__ q, int64_t ldq, int d, int nprobe,
                                      const int* __restrict__ grow, const int* __restrict__ live_rows,
-                                     __nv_bfloat16* __restrict__ qplane, float* __restrict__ tau, int d_pad) {
+                                     __nv_bfloat16* __restrict__ qplane, float* __restrict__ tau,
+                                     int* __restrict__ row_query, int d_pad) {
     const int lane = threadIdx.x & 31;
     const int pitch = d_pad + PLANE_AUG_COLS;
     const int live = *live_rows;
@@ -157,13 +158,13 @@ __global__ void ivf_tc_gather_kernel(const float* __restrict__ q, int64_t ldq, i
         __nv_bfloat16* o = qplane + (int64_t)r * pitch;
         if (pair < 0) {
             for (int c = lane; c < pitch; c += 32) o[c] = __float2bfloat16_rn(0.f);
-            if (lane == 0) tau[r] = pos_inf();
+            if (lane == 0) { tau[r] = pos_inf(); row_query[r] = -1; }
             continue;
         }
         const float* src = q + (int64_t)(pair / nprobe) * ldq;
         for (int c = lane; c < d_pad; c += 32) o[c] = __float2bfloat16_rn(c < d ? __ldg(src + c) : 0.f);
         if (lane < PLANE_AUG_COLS) o[d_pad + lane] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
-        if (lane == 0) tau[r] = neg_inf();
+        if (lane == 0) { tau[r] = neg_inf(); row_query[r] = pair / nprobe; }
     }
 }
 
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
 struct IvfTcWs {
     int64_t npairs, max_items, cap_rows; int d_pad, pitch;
     int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_pair_row, off_item_t0, off_item_t1,
-        off_grow, off_counters, off_qplane, off_tau, off_part_sc, off_part_id, off_part_tau, off_fblist, bytes;
+        off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_part_sc, off_part_id, off_part_tau, off_fblist, bytes;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -278,6 +279,8 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
     w.off_item_t0 = take(cur, w.max_items * 4);
     w.off_item_t1 = take(cur, w.max_items * 4);
     w.off_grow = take(cur, w.cap_rows * 4);
+    w.off_row_query = take(cur, w.cap_rows * 4);
+    w.off_tau_q = take(cur, nq * 4);
     w.off_counters = take(cur, 1024);
     w.off_qplane = take(cur, w.cap_rows * w.pitch * 2);
     w.off_tau = take(cur, w.cap_rows * 4);
@@ -386,8 +389,12 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
                                                         item_t1, grow, pair_row, live_rows);
     FL_CHECK_LAUNCH();
     ivf_tc_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(
-        q, ldq, d, nprobe, grow, live_rows, reinterpret_cast<__nv_bfloat16*>(base + w.off_qplane), tau, w.d_pad);
+        q, ldq, d, nprobe, grow, live_rows, reinterpret_cast<__nv_bfloat16*>(base + w.off_qplane), tau,
+        reinterpret_cast<int*>(base + w.off_row_query), w.d_pad);
     FL_CHECK_LAUNCH();
+    float* tau_q = reinterpret_cast<float*>(base + w.off_tau_q);
+    rc = launch_fill_f32(tau_q, nq, -INFINITY, st);
+    if (rc != FL_OK) return rc;
 
     TcKnnParams tp{};
     tp.qplane = base + w.off_qplane; tp.nq = w.cap_rows; tp.nq_pad = w.cap_rows;
@@ -401,6 +408,7 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     tp.k = k;
     tp.nq_dev = live_rows; tp.item_t0 = item_t0; tp.item_t1 = item_t1;
+    tp.row_query = reinterpret_cast<const int*>(base + w.off_row_query); tp.tau_q = tau_q;
     profile_begin(st);
     rc = launch_knn_tc(tp, st);
     profile_end(st);

@@ -99,6 +99,8 @@ struct TcKnnParams {
     int deep_pools;          // 1: pools keep tc_deep_pool_size() entries and publish tc_deep_partial_len() per
                              //    (query, range) (k <= 16): for queries with only a few pools each
     const int* nq_dev;       // optional: live query rows (device); query tiles beyond them are skipped
+    const int* row_query;    // optional: query index of every query row (-1: none) and a running threshold
+    float* tau_q;            //   per query (f32, -inf initialised) shared by the rows of that query
     const int* item_t0;      // optional, with nsplit == 1: database tile range [item_t0[t], item_t1[t]) of
     const int* item_t1;      //   query tile t instead of one uniform range (inverted-file scan)
     int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)

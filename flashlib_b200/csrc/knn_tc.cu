@@ -90,6 +90,8 @@ struct TcKernelParams {
     float* part_tau;
     int* part_cnt;           // large-k mode: entries of every published pool
     const int* nq_dev;       // optional: live query rows, counted on the device by an earlier kernel
+    const int* row_query;    // optional: query of every (gathered) query row, -1 for rows without one, and
+    float* tau_q;            //   a running threshold per query shared by all rows of that query
     const int* item_t0;      // optional (one range per query tile): first / one-past-last database
     const int* item_t1;      //   tile of query tile `it`, instead of the uniform ranges
     float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
@@ -334,7 +336,14 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
             const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
-            const float tau_in = __ldcg(p.tau + qrow);
+            float tau_in = __ldcg(p.tau + qrow);
+            int qidx = -1;
+            if (p.row_query != nullptr) {
+                // rows that belong to the same query (one per probed list) pass their thresholds on:
+                // a score below what 24 rows of another probed list reach cannot be among the k best
+                qidx = __ldg(p.row_query + qrow);
+                if (qidx >= 0) tau_in = fmaxf(tau_in, __ldcg(p.tau_q + qidx));
+            }
             if (BIG) {
                 pstride = (int64_t)p.nsplit * TC_NWG * CAP;
                 const int64_t o = (((int64_t)(qt * TC_BM + quarter * 32) * p.nsplit + split) * TC_NWG + wg) * CAP;
@@ -634,6 +643,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             }
             p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
             if (tau > tau_in) __stcg(p.tau + qrow, tau);
+            if (qidx >= 0 && tau > tau_in) atomic_max_f32(p.tau_q + qidx, tau);
         }
         if (warp == 0 && lane == 0 && blockIdx.x < 160) {
             unsigned long long* pr = g_tc_prof + blockIdx.x * TC_PROF_WORDS;
@@ -789,6 +799,8 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     kp.part_cnt = p.part_cnt;
     kp.seed_cls = p.seed_cls;
     kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1;
+    kp.row_query = p.row_query; kp.tau_q = p.tau_q;
+    FL_CHECK_ARG((p.row_query == nullptr) == (p.tau_q == nullptr), "tensor-core kNN launch: row_query and tau_q go together");
     FL_CHECK_ARG((p.item_t0 == nullptr) == (p.item_t1 == nullptr) && (p.item_t0 == nullptr || (p.nsplit == 1 && !big)),
                  "tensor-core kNN launch: per-tile ranges need one range per query tile and k <= 16");
     {
