@@ -324,6 +324,7 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             float lmax = neg_inf();
+#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
@@ -346,6 +347,7 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
             const unsigned lt = (1u << lane) - 1u;
             int total = 0;
+#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
