@@ -84,12 +84,12 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
 
 // Tensor-core (tcgen05) candidate pass over the bf16 plane.
 struct TcKnnParams {
-    const void* qplane;      // bf16 [nq_pad][d_pad], zero padded
+    const void* qplane;      // bf16 [nq_pad][d_pad + 16]: features zero padded, ones in the norm columns
     int64_t nq, nq_pad;
     const void* dbrows;      // bf16 [m_pad][d_pad]
     const float* hnorm;      // f32 [m_pad]
     int64_t m, m_pad; int d_pad;
-    int K1;                  // pool size (32)
+    int K1;                  // entries a pool keeps (informational: fixed by the kernel mode)
     int nsplit; int64_t tiles_per_split;   // database tiles of 256 rows per split
     float* part_sc; uint32_t* part_id;     // [nq_pad][nsplit][tc_partial_len]
     float* tau;              // f32 [nq_pad], running per-query thresholds, -inf initialised
@@ -130,7 +130,7 @@ int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 // nq_dev (optional): device-resident count of live rows; query tiles beyond it are skipped.
 int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, const int* nq_dev, cudaStream_t st);
 
-// bf16 query plane [nq_pad][d_pad] (zero padded) from fp32 queries.
+// bf16 query plane [nq_pad][d_pad + 16] (features zero padded, ones in the norm columns) from fp32 queries.
 int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
                        int d_pad, cudaStream_t st);
 

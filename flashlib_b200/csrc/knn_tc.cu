@@ -8,9 +8,10 @@
 // step makes every accumulator element the score
 //     s = <q, x> - ||x||^2 / 2          (larger = closer)
 // and the epilogue only compares: scores above a row's threshold feed that query's
-// candidate pool in shared memory.  Nothing of the 128 x 256 score
-// tile ever reaches global memory; a pool of K1 = 32 (score, row) pairs per query and
-// range is all that is written (published unsorted, up to 64 entries per query and range).
+// candidate pool in shared memory.  Nothing of the 128 x 256 score tile ever reaches global
+// memory; per query and range only the two warpgroups' pools (32 entries each, 12 kept at a
+// compaction; deeper or global-memory pools in the modes described below) and their final
+// thresholds are written, unsorted.
 //
 // Warp roles (320 threads): warps 0-7 epilogue in two warpgroups (group g takes columns
 // 128g..128g+127 of every accumulator; warp w reads TMEM lanes 32(w%4)..32(w%4)+31, one query
