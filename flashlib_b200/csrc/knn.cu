@@ -97,10 +97,10 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
     if (mode == FL_KNN_BF16_RERANK) {
         w.K1 = tc_pool_size(k);
         w.K1f = simt_pool_size(k);
-        w.nq_pad = round_up(nq, 128);
+        w.nq_pad = tc_query_rows_padded(nq);
         w.d_pad = (int)round_up(d, 64);
         const int64_t m_pad = round_up(m, 256);
-        tc_split_plan(w.nq_pad, m_pad, &w.nsplit, &w.rows_per_split);
+        tc_split_plan(w.nq_pad, m_pad, k, &w.nsplit, &w.rows_per_split);
         w.fb_cap = (int)(nq < 4096 ? nq : (nq / 4 > 4096 ? nq / 4 : 4096));
         // fallback splits: bounded partial storage (<= 128 MB), at least 4 tiles per split
         int64_t s = (int64_t)(128ll << 20) / ((int64_t)w.fb_cap * w.K1f * 8);

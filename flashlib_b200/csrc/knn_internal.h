@@ -122,7 +122,11 @@ int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
 // Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].
 int tc_prof_read(unsigned long long* host_out, int words);
 int launch_knn_tc_debug(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st);
-void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_per_split);
+void tc_split_plan(int64_t nq_pad, int64_t m_pad, int k, int* nsplit, int64_t* tiles_per_split);
+int tc_pair_enabled(int64_t nq_pad, int k);
+// Query rows of the bf16 query plane for nq queries: whole tiles of 128 (whole pairs of tiles when
+// CTA pairs are requested).
+int64_t tc_query_rows_padded(int64_t nq);
 int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 // k-means assignment on the same pipeline: asg_sc [nq_pad][2][2] (best, second-best score per
 // warpgroup half), asg_id [nq_pad][2] (best centroid per half).  Only qplane/nq_pad, dbrows/

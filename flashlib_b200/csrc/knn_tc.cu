@@ -55,17 +55,17 @@ struct TcSmemPlan {
     int off_a, off_b, off_pool_sc, off_pool_id, off_hbuf, off_bar, bytes;
 };
 
-static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_PSTR) {
+static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_PSTR, int slot_bytes = TC_B_STAGE) {
     TcSmemPlan s{};
     s.nkc = d_pad / TC_BK;
     int cur = 0;
     s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
     const int pool = TC_NWG * TC_BM * pool_stride * 4;   // 0: no pools in shared memory
     const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
-    int ns = (smem_limit - fixed) / TC_B_STAGE;
+    int ns = (smem_limit - fixed) / slot_bytes;
     if (ns > TC_MAX_STAGES) ns = TC_MAX_STAGES;
     s.nstage = ns;
-    s.off_b = cur; cur += (ns > 0 ? ns : 0) * TC_B_STAGE;
+    s.off_b = cur; cur += (ns > 0 ? ns : 0) * slot_bytes;
     s.off_pool_sc = cur; cur += pool;
     s.off_pool_id = cur; cur += pool;
     s.off_hbuf = cur;
@@ -101,7 +101,8 @@ struct TcKernelParams {
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
     int tile_stride;         // database tile actually read for loop index t is t * tile_stride (1 outside seeding)
     int dbg_flags;           // timing experiments (results invalid): 1 skip pass 2, 2 skip the
-                             // reductions of pass 1, 4 skip the tensor-memory loads too
+                             // reductions of pass 1, 4 skip the tensor-memory loads too, 8 skip the
+                             // norm-column MMA step
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
     int64_t dbg_ld;
 };
@@ -148,7 +149,15 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
 // MODE 4 (TC_MODE_KNN_MID) is MODE 0 with deeper pools in shared memory (24 of 48 kept, 64
 // published): for callers whose queries have only a few pools each.
 constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3, TC_MODE_KNN_MID = 4;
-template <bool DBG, int MODE>
+//
+// PAIR: two CTAs of a cluster work as one (tcgen05 cta_group::2).  CTA r of the pair owns query
+// tile 2 i + r of pair-item i, loads its own query tile and rows 128 r .. 128 r + 127 of every
+// 256-row database tile (half the L2 and shared-memory traffic per CTA), the leader (r = 0)
+// issues one M = 256 MMA per step that reads both halves and writes each CTA's 128 x 256
+// accumulator into that CTA's tensor memory; both CTAs run the epilogue on their own rows.
+// Operand and accumulator barriers live in the leader; "slot free", "query tile free" and
+// "accumulator full" are committed to both CTAs.
+template <bool DBG, int MODE, bool PAIR = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_q_aug,
               const __grid_constant__ CUtensorMap map_db, const __grid_constant__ CUtensorMap map_db_aug,
@@ -172,12 +181,18 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+    const bool leader = cta_rank == 0;
+    // geometry of one ring slot and of the work split
+    constexpr int B_ROWS = PAIR ? TC_BN / 2 : TC_BN;          // database rows this CTA loads per tile
+    constexpr int SLOT_CHUNK = B_ROWS * 128, SLOT_BYTES = B_ROWS * 128 + B_ROWS * 32;
+    constexpr uint32_t OPERAND_CTAS = PAIR ? 2u : 1u;         // CTAs whose loads one operand barrier counts
 
     if (tid == 0) {
         for (int i = 0; i < TC_MAX_STAGES; ++i) { mbar_init(BAR(B_FULL + i), 1); mbar_init(BAR(B_EMPTY + i), 1); }
         mbar_init(BAR(B_AFULL), 1);
         mbar_init(BAR(B_AEMPTY), 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(BAR(B_TFULL + i), 1); mbar_init(BAR(B_TEMPTY + i), 4 * TC_NWG); }
+        for (int i = 0; i < 2; ++i) { mbar_init(BAR(B_TFULL + i), 1); mbar_init(BAR(B_TEMPTY + i), 4 * TC_NWG * OPERAND_CTAS); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -187,11 +202,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         prefetch_tensormap(&map_db); prefetch_tensormap(&map_db_aug);
     }
     if (warp == W_MMA) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
-        tmem_relinquish();
+        if (PAIR) { tmem_alloc_pair(smem_u32(tmem_slot), 512); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -201,7 +217,12 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const int live = (__ldcg(p.nq_dev) + TC_BM - 1) / TC_BM;
         n_qtiles = live < n_qtiles ? live : n_qtiles;
     }
-    const int n_items = n_qtiles * p.nsplit;
+    // item = (range, query tile) or, for CTA pairs, (range, pair of query tiles); a pair walks the
+    // items together
+    const int n_units = PAIR ? n_qtiles / 2 : n_qtiles;
+    const int n_items = n_units * p.nsplit;
+    const int it_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int it_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int d_pad = p.nkc * TC_BK;
 
     if (warp == W_PRODUCER) {
@@ -211,19 +232,24 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t item_no = 0;
             bool ok = true;
             long long prof_a = 0;
-            for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
-                const int split = it / n_qtiles, qt = it - split * n_qtiles;
+            // loads of a pair are credited to the leader's barrier, which expects both CTAs' bytes
+            auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+                if (PAIR) tma_load_2d_pair(dst, map, c0, c1, bar); else tma_load_2d(dst, map, c0, c1, bar);
+            };
+            for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
+                const int split = it / n_units, unit = it - split * n_units;
+                const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
                 const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
                 const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
-                mbar_expect_tx(BAR(B_AFULL), p.nkc * TC_A_CHUNK + TC_A_AUG);
+                if (leader) mbar_expect_tx(BAR(B_AFULL), (p.nkc * TC_A_CHUNK + TC_A_AUG) * OPERAND_CTAS);
                 for (int kc = 0; kc < p.nkc; ++kc)
-                    tma_load_2d(a_addr + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, BAR(B_AFULL));
-                tma_load_2d(a_aug_addr, &map_q_aug, d_pad, qt * TC_BM, BAR(B_AFULL));
+                    load(a_addr + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, BAR(B_AFULL));
+                load(a_aug_addr, &map_q_aug, d_pad, qt * TC_BM, BAR(B_AFULL));
                 const int nt = t1 - t0;
-                const int rot = (int)(((int64_t)qt * nt) / n_qtiles);
+                const int rot = (int)(((int64_t)unit * nt) / n_units);
                 for (int i = 0; i < nt && ok; ++i) {
                     // Query tiles walk their range from different starting tiles, so the CTAs of a
                     // wave do not all ask the L2 for the same lines at the same moment.
@@ -237,11 +263,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         }
                         prof_a += clock64() - c0;
                         const bool last = (kc == p.nkc - 1);
-                        mbar_expect_tx(BAR(B_FULL + s), last ? TC_B_STAGE : TC_B_CHUNK);
-                        tma_load_2d(b_addr + s * TC_B_STAGE, &map_db, kc * TC_BK, t * p.tile_stride * TC_BN, BAR(B_FULL + s));
-                        if (last)
-                            tma_load_2d(b_addr + s * TC_B_STAGE + TC_B_CHUNK, &map_db_aug, d_pad,
-                                        t * p.tile_stride * TC_BN, BAR(B_FULL + s));
+                        const int row0 = t * p.tile_stride * TC_BN + (int)cta_rank * B_ROWS;
+                        if (leader) mbar_expect_tx(BAR(B_FULL + s), (last ? SLOT_BYTES : SLOT_CHUNK) * OPERAND_CTAS);
+                        load(b_addr + s * SLOT_BYTES, &map_db, kc * TC_BK, row0, BAR(B_FULL + s));
+                        if (last) load(b_addr + s * SLOT_BYTES + SLOT_CHUNK, &map_db_aug, d_pad, row0, BAR(B_FULL + s));
                     }
                 }
             }
@@ -254,15 +279,19 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
     } else if (warp == W_MMA) {
         // ------------------------------ MMA issuer -----------------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(TC_BM, TC_BN);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * TC_BM : TC_BM, TC_BN);
+            auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
+                if (PAIR) umma_bf16_pair(d, a, b, idesc, acc); else umma_bf16(d, a, b, idesc, acc);
+            };
+            auto commit = [&](uint32_t bar) { if (PAIR) umma_commit_pair(bar); else umma_commit(bar); };
             uint32_t use = 0;      // database chunks consumed so far
             uint32_t tile_no = 0;  // tiles issued so far (accumulator ring position)
             uint32_t item_no = 0;
             bool ok = true;
             long long prof_full = 0, prof_tempty = 0;
-            for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++item_no) {
-                const int split = it / n_qtiles;
+            for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
+                const int split = it / n_units;
                 const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
                 const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
                 if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
@@ -287,22 +316,21 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         prof_full += clock64() - c1;
                         tc_fence_after_sync();
                         const uint64_t da = umma_desc(a_addr + kc * TC_A_CHUNK);
-                        const uint64_t db = umma_desc(b_addr + s * TC_B_STAGE);
+                        const uint64_t db = umma_desc(b_addr + s * SLOT_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
                             // +32 bytes per 16-feature step inside the 128-byte swizzled row
-                            umma_bf16(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kc | k4) != 0 ? 1u : 0u);
+                            mma(d_tmem, da + 2 * k4, db + 2 * k4, (kc | k4) != 0 ? 1u : 0u);
                         }
-                        if (kc == p.nkc - 1) {
+                        if (kc == p.nkc - 1 && !(DBG && (p.dbg_flags & 8))) {
                             // norm columns: ones x split(-||x||^2/2), 32-byte rows, 32-byte swizzle
-                            umma_bf16(d_tmem, umma_desc_sw32(a_aug_addr),
-                                      umma_desc_sw32(b_addr + s * TC_B_STAGE + TC_B_CHUNK), idesc, 1u);
+                            mma(d_tmem, umma_desc_sw32(a_aug_addr), umma_desc_sw32(b_addr + s * SLOT_BYTES + SLOT_CHUNK), 1u);
                         }
-                        umma_commit(BAR(B_EMPTY + s));   // slot reusable once these MMAs retire
+                        commit(BAR(B_EMPTY + s));   // slot reusable once these MMAs retire
                     }
-                    if (ok) umma_commit(BAR(B_TFULL + b));
+                    if (ok) commit(BAR(B_TFULL + b));
                 }
-                if (ok) umma_commit(BAR(B_AEMPTY));       // query tile reusable
+                if (ok) commit(BAR(B_AEMPTY));       // query tile reusable
             }
             if (blockIdx.x < 160) {
                 g_tc_prof[blockIdx.x * TC_PROF_WORDS + 1] = prof_full;
@@ -332,8 +360,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         long long prof_tfull = 0, prof_rare = 0, prof_cc = 0;
         unsigned prof_groups = 0, prof_compact = 0, prof_append = 0;
         const long long prof_t0 = clock64();
-        for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-            const int split = it / n_qtiles, qt = it - split * n_qtiles;
+        // hands accumulator b back to the MMA lane (of the leader, for a pair)
+        auto release_acc = [&](int b) {
+            if (PAIR) mbar_arrive_cluster(BAR(B_TEMPTY + b), 0u); else mbar_arrive(BAR(B_TEMPTY + b));
+        };
+        for (int it = it_first; it < n_items && ok; it += it_step) {
+            const int split = it / n_units, unit = it - split * n_units;
+            const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
             const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
             const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
@@ -361,7 +394,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             float b1 = neg_inf(), b2 = neg_inf();   // assignment mode: best / second-best packed score
             int tbest = 0;                           // tile that produced b1
             const int nt = t1 - t0;
-            const int rot = (int)(((int64_t)qt * nt) / n_qtiles);
+            const int rot = (int)(((int64_t)unit * nt) / n_units);
             for (int i = 0; i < nt; ++i, ++tile_no) {
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = tile_no & 1;
@@ -410,7 +443,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     reg_fence32(vd);
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    if (lane == 0) release_acc(b);
                     top2(vc, 2);
                     top2(vd, 3);
                     if (b1 != b1_before) tbest = t;
@@ -436,7 +469,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     reg_fence32(vd);
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    if (lane == 0) release_acc(b);
                     fold(vc);
                     fold(vd);
                     continue;
@@ -560,7 +593,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     // every flagged score is in registers or in a pool: hand the accumulator back
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    if (lane == 0) release_acc(b);
                     // (b) all lanes at once
                     const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
                     if (need) {
@@ -601,7 +634,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     // nothing flagged: hand the accumulator back right away
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(BAR(B_TEMPTY + b));
+                    if (lane == 0) release_acc(b);
                 }
             }
             if (!ok) break;
@@ -657,9 +690,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     // ------------------------------ common exit ----------------------------------------------
     tc_fence_before_sync();
     __syncthreads();
+    if (PAIR) cluster_sync_all();      // neither CTA leaves while the other may still touch its memory
     if (warp == W_MMA) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -746,10 +780,26 @@ int tc_knn_auto(int64_t nq, int64_t m, int d, int k) {
     return (m >= 2048 && nq * m >= (int64_t(1) << 24)) ? 1 : 0;
 }
 
-void tc_split_plan(int64_t nq_pad, int64_t m_pad, int* nsplit, int64_t* tiles_per_split) {
-    const int64_t n_qtiles = nq_pad / TC_BM;
+// CTA pairs (cta_group::2) for plain k <= 16 scoring.  Measured on the 1M x 128 benchmark they are
+// 7 % slower than single CTAs (the leader's MMA reads half of every database tile from the peer's
+// shared memory and waits for both CTAs' epilogues), so they are off unless FLASHLIB_B200_TC_PAIR=1.
+int tc_pair_requested() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("FLASHLIB_B200_TC_PAIR"); on = (e && atoi(e) != 0) ? 1 : 0; }
+    return on;
+}
+// Pairs need an even number of query tiles (tc_query_rows_padded provides it).
+int tc_pair_enabled(int64_t nq_pad, int k) {
+    return tc_pair_requested() && !tc_knn_big(k) && (nq_pad / TC_BM) % 2 == 0 && nq_pad / TC_BM >= 2;
+}
+int64_t tc_query_rows_padded(int64_t nq) { return round_up(nq, tc_pair_requested() ? 2 * TC_BM : TC_BM); }
+
+void tc_split_plan(int64_t nq_pad, int64_t m_pad, int k, int* nsplit, int64_t* tiles_per_split) {
+    const bool pair = tc_pair_enabled(nq_pad, k) != 0;
+    // work units that walk a range together, and how many of them the GPU runs at once
+    const int64_t n_qtiles = pair ? nq_pad / TC_BM / 2 : nq_pad / TC_BM;
     const int64_t n_tiles = m_pad / TC_BN;
-    const int sms = sm_count();
+    const int sms = pair ? sm_count() / 2 : sm_count();
     int64_t max_s = n_tiles / 8;
     if (max_s > 64) max_s = 64;
     if (max_s < 1) max_s = 1;
@@ -850,7 +900,36 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         tc_seed_select_kernel<<<(unsigned)ceil_div(p.nq_pad, 128), 128, 0, st>>>(p.seed_cls, p.tau, p.nq_pad, seed_rank);
         FL_CHECK_LAUNCH();
     }
-    if (mid) {
+    // CTA pairs (cta_group::2): plain k <= 16 scoring over uniform ranges, an even number of query
+    // tiles, at least one pair-item per cluster of a full grid.  FLASHLIB_B200_TC_PAIR=0/1 overrides.
+    const bool pair = !mid && dbg == nullptr && p.item_t0 == nullptr && p.nq_dev == nullptr &&
+                      tc_pair_enabled(p.nq_pad, p.k);
+    if (pair) {
+        CUtensorMap map_db_h, map_db_aug_h;
+        rc = make_map_bf16(&map_db_h, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN / 2);
+        if (rc == FL_OK) rc = make_map_bf16(&map_db_aug_h, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN / 2);
+        if (rc != FL_OK) return rc;
+        const TcSmemPlan spp = tc_smem_plan(p.d_pad, smem_optin_bytes(), TC_PSTR, TC_B_STAGE / 2);
+        TcKernelParams kq = kp;
+        kq.nstage = spp.nstage; kq.off_b = spp.off_b; kq.off_pool_sc = spp.off_pool_sc; kq.off_pool_id = spp.off_pool_id;
+        kq.off_bar = spp.off_bar;
+        const int pair_items = (kp.n_qtiles / 2) * kp.nsplit;
+        int clusters = sm_count() / 2;
+        if (clusters > pair_items) clusters = pair_items;
+        auto kern = kp.dbg_flags != 0 ? knn_tc_kernel<true, TC_MODE_KNN, true> : knn_tc_kernel<false, TC_MODE_KNN, true>;
+        FL_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, spp.bytes));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(2 * clusters));
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = (size_t)spp.bytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        FL_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, map_q, map_q_aug, map_db_h, map_db_aug_h, kq));
+    } else if (mid) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_MID>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<false, TC_MODE_KNN_MID><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
     } else if (big) {

@@ -134,3 +134,29 @@ def test_unsupported_k_raises_and_auto_falls_back():
         fl.flash_knn(q, db, 200, mode="bf16")
     vals, idxs = fl.flash_knn(q, db, 200)        # auto: exact path
     assert vals.shape == (10, 200)
+
+
+def test_cta_pair_variant_in_a_subprocess():
+    """The cta_group::2 variant of the scoring kernel (two CTAs share every database tile) is
+    switched on by an environment variable that the library reads once, so it runs in its own
+    process: same neighbours as the exact mode, no rows on the exact path beyond a handful."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from flashlib_b200 import _lib\n"
+        "from flashlib_b200.knn import knn_f32\n"
+        "g = torch.Generator().manual_seed(11)\n"
+        "db = torch.randn(150_000, 128, generator=g).cuda(); q = torch.randn(1000, 128, generator=g).cuda()\n"
+        "d1, i1, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)\n"
+        "d0, i0, _ = knn_f32(q, db, 10, mode=_lib.FL_KNN_EXACT_SIMT)\n"
+        "assert info['status'][0].item() == 0, info\n"
+        "assert info['fallback_rows'] < 20, info\n"
+        "assert (i1 == i0).float().mean().item() > 0.999\n"
+        "torch.testing.assert_close(d1, d0, rtol=1e-4, atol=1e-4)\n"
+        "print('pair ok')\n")
+    env = dict(os.environ, FLASHLIB_B200_TC_PAIR="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "pair ok" in out.stdout, out.stdout + out.stderr
