@@ -40,8 +40,8 @@ struct SimtKnnParams {
 int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st);
 // Range split of the dynamic mode for `count` live slots: the same figures on the device
 // (scan and finalisation kernels) and on the host (buffer sizing).
-__host__ __device__ inline void simt_dyn_split(int64_t count, int bq, int blocks, int64_t m, int* nsplit,
-                                               int64_t* rows_per_split) {
+struct SimtDynSplit { int nsplit; int64_t rows_per_split; };
+__host__ __device__ inline SimtDynSplit simt_dyn_split(int64_t count, int bq, int blocks, int64_t m) {
     const int64_t nqb = (count + bq - 1) / bq;
     int64_t ns = nqb > 0 ? blocks / nqb : 1;
     const int64_t tiles = (m + 127) / 128;
@@ -49,8 +49,10 @@ __host__ __device__ inline void simt_dyn_split(int64_t count, int bq, int blocks
     if (ns > 296) ns = 296;     // two blocks per SM when a single query block is live
     if (ns < 1) ns = 1;
     const int64_t rps = ((m + ns - 1) / ns + 127) / 128 * 128;
-    *rows_per_split = rps;
-    *nsplit = (int)((m + rps - 1) / rps);
+    SimtDynSplit r;
+    r.rows_per_split = rps;
+    r.nsplit = (int)((m + rps - 1) / rps);
+    return r;
 }
 // Split count / rows per split the CUDA-core pass uses for a problem.
 void simt_split_plan(int64_t slots, int64_t m, int K1, int d, int* nsplit, int64_t* rows_per_split);

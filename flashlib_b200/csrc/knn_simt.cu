@@ -58,7 +58,9 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
         int64_t rps = p.rows_per_split;
         if (p.dyn_blocks > 0) {
             if (count <= 0) return;
-            simt_dyn_split(count, BQ, p.dyn_blocks, p.m, &nsplit, &rps);
+            const SimtDynSplit ds = simt_dyn_split(count, BQ, p.dyn_blocks, p.m);
+            nsplit = ds.nsplit;
+            rps = ds.rows_per_split;
             const int64_t nqb = (count + BQ - 1) / BQ;
             slot0 = ((int64_t)blockIdx.x % nqb) * BQ;
             split = (int)((int64_t)blockIdx.x / nqb);
@@ -247,25 +249,21 @@ int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) 
 // set cannot be proven (or overflows), the second attempt sorts every pool and merges the K1
 // best, with bound = max(u, K1-th best).
 // ------------------------------------------------------------------------------------
-template <int NPL1>
+template <int NPL1, bool INDIRECT>
 __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int64_t slot, const int64_t count) {
     const int lane = threadIdx.x & 31;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
     const int K1 = p.K1;
-    int nsplit = p.nsplit;
-    if (p.dyn_blocks > 0) {
-        int64_t rps;
-        simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m, &nsplit, &rps);
-    }
+    const int nsplit = p.dyn_blocks > 0 ? simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m).nsplit : p.nsplit;
     // pool s of this slot: offset of its first entry (negative: the pool does not exist)
     auto pool_base = [&](int s) -> int64_t {
-        if (p.pool_row == nullptr) return (slot * nsplit + s) * (int64_t)K1;
+        if (!INDIRECT) return (slot * nsplit + s) * (int64_t)K1;
         const int row = __ldg(p.pool_row + slot * nsplit + s);
         return row >= 0 ? (int64_t)row * K1 : -1;
     };
     // published id -> database row, INVALID_ID for padding rows of the operand plane
     auto real_id = [&](uint32_t raw) -> uint32_t {
-        if (p.id_map == nullptr) return raw < (uint32_t)p.m ? raw : INVALID_ID;
+        if (!INDIRECT) return raw < (uint32_t)p.m ? raw : INVALID_ID;
         if (raw >= (uint32_t)p.id_bound) return INVALID_ID;
         const int mapped = __ldg(p.id_map + raw);
         return mapped >= 0 ? (uint32_t)mapped : INVALID_ID;
@@ -278,7 +276,7 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
         const int per_pool = p.ntau / nsplit;
         for (int i = lane; i < p.ntau; i += 32) {
             int64_t t = slot * p.ntau + i;
-            if (p.pool_row != nullptr) {
+            if (INDIRECT) {
                 const int row = __ldg(p.pool_row + slot * nsplit + i / per_pool);
                 t = row >= 0 ? (int64_t)row * per_pool + i % per_pool : -1;
             }
@@ -324,7 +322,6 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             float lmax = neg_inf();
-#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
@@ -347,7 +344,6 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
             const unsigned lt = (1u << lane) - 1u;
             int total = 0;
-#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
@@ -507,11 +503,17 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
 
 // One warp per slot, grid-stride: the slot count may only be known on the device, and a grid
 // sized for the largest possible count would mostly launch blocks that have nothing to do.
-template <int NPL1>
+template <int NPL1, bool INDIRECT>
 __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
-    const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
+    if (p.count_dev == nullptr) {
+        // slot count known at launch: one slot per warp
+        const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+        if (slot < p.count) finalize_slot<NPL1, INDIRECT>(p, slot, p.count);
+        return;
+    }
+    const int64_t count = (int64_t)(*p.count_dev);
     for (int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); slot < count; slot += (int64_t)gridDim.x * 4) {
-        finalize_slot<NPL1>(p, slot, count);
+        finalize_slot<NPL1, INDIRECT>(p, slot, count);
         __syncwarp();
     }
 }
@@ -519,15 +521,23 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
 int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
     if (max_slots <= 0) return FL_OK;
     int64_t blocks = ceil_div(max_slots, 4);
-    const int64_t cap = (int64_t)sm_count() * (p.count_dev ? 32 : 1024);
-    if (blocks > cap) blocks = cap;
+    if (p.count_dev != nullptr && blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
     const unsigned grid = (unsigned)blocks;
+    const bool indirect = p.pool_row != nullptr;
+    if (indirect && (p.id_map == nullptr || p.K1 != 128)) {
+        set_error("finalisation: pool indirection goes with an id map and 128 published entries per pool");
+        return FL_EINVAL;
+    }
+    if (!indirect && p.id_map != nullptr) { set_error("finalisation: id map without pool indirection"); return FL_EINVAL; }
     switch (p.K1 / 32) {
-        case 1: knn_finalize_kernel<1><<<grid, 128, 0, st>>>(p); break;
-        case 2: knn_finalize_kernel<2><<<grid, 128, 0, st>>>(p); break;
-        case 4: knn_finalize_kernel<4><<<grid, 128, 0, st>>>(p); break;
-        case 8: knn_finalize_kernel<8><<<grid, 128, 0, st>>>(p); break;
-        case 16: knn_finalize_kernel<16><<<grid, 128, 0, st>>>(p); break;
+        case 1: knn_finalize_kernel<1, false><<<grid, 128, 0, st>>>(p); break;
+        case 2: knn_finalize_kernel<2, false><<<grid, 128, 0, st>>>(p); break;
+        case 4:
+            if (indirect) knn_finalize_kernel<4, true><<<grid, 128, 0, st>>>(p);
+            else knn_finalize_kernel<4, false><<<grid, 128, 0, st>>>(p);
+            break;
+        case 8: knn_finalize_kernel<8, false><<<grid, 128, 0, st>>>(p); break;
+        case 16: knn_finalize_kernel<16, false><<<grid, 128, 0, st>>>(p); break;
         default:
             set_error("unsupported pool size %d", p.K1);
             return FL_EUNSUPPORTED;
