@@ -249,12 +249,12 @@ int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) 
 // set cannot be proven (or overflows), the second attempt sorts every pool and merges the K1
 // best, with bound = max(u, K1-th best).
 // ------------------------------------------------------------------------------------
-template <int NPL1, bool INDIRECT>
+template <int NPL1, bool INDIRECT, bool DYN>
 __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int64_t slot, const int64_t count) {
     const int lane = threadIdx.x & 31;
     const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
     const int K1 = p.K1;
-    const int nsplit = p.dyn_blocks > 0 ? simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m).nsplit : p.nsplit;
+    const int nsplit = DYN ? simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m).nsplit : p.nsplit;
     // pool s of this slot: offset of its first entry (negative: the pool does not exist)
     auto pool_base = [&](int s) -> int64_t {
         if (!INDIRECT) return (slot * nsplit + s) * (int64_t)K1;
@@ -503,17 +503,17 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
 
 // One warp per slot, grid-stride: the slot count may only be known on the device, and a grid
 // sized for the largest possible count would mostly launch blocks that have nothing to do.
-template <int NPL1, bool INDIRECT>
+template <int NPL1, bool INDIRECT, bool DYN>
 __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     if (p.count_dev == nullptr) {
         // slot count known at launch: one slot per warp
         const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-        if (slot < p.count) finalize_slot<NPL1, INDIRECT>(p, slot, p.count);
+        if (slot < p.count) finalize_slot<NPL1, INDIRECT, DYN>(p, slot, p.count);
         return;
     }
     const int64_t count = (int64_t)(*p.count_dev);
     for (int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); slot < count; slot += (int64_t)gridDim.x * 4) {
-        finalize_slot<NPL1, INDIRECT>(p, slot, count);
+        finalize_slot<NPL1, INDIRECT, DYN>(p, slot, count);
         __syncwarp();
     }
 }
@@ -529,19 +529,28 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
         return FL_EINVAL;
     }
     if (!indirect && p.id_map != nullptr) { set_error("finalisation: id map without pool indirection"); return FL_EINVAL; }
+    const bool dyn = p.dyn_blocks > 0;
+    if (dyn && (indirect || p.count_dev == nullptr)) { set_error("finalisation: dynamic split goes with a device-side count"); return FL_EINVAL; }
+#define FL_FINALIZE_CASE(N)                                                                   \
+    case N:                                                                                   \
+        if (dyn) knn_finalize_kernel<N, false, true><<<grid, 128, 0, st>>>(p);                \
+        else knn_finalize_kernel<N, false, false><<<grid, 128, 0, st>>>(p);                   \
+        break;
     switch (p.K1 / 32) {
-        case 1: knn_finalize_kernel<1, false><<<grid, 128, 0, st>>>(p); break;
-        case 2: knn_finalize_kernel<2, false><<<grid, 128, 0, st>>>(p); break;
+        FL_FINALIZE_CASE(1)
+        FL_FINALIZE_CASE(2)
         case 4:
-            if (indirect) knn_finalize_kernel<4, true><<<grid, 128, 0, st>>>(p);
-            else knn_finalize_kernel<4, false><<<grid, 128, 0, st>>>(p);
+            if (indirect) knn_finalize_kernel<4, true, false><<<grid, 128, 0, st>>>(p);
+            else if (dyn) knn_finalize_kernel<4, false, true><<<grid, 128, 0, st>>>(p);
+            else knn_finalize_kernel<4, false, false><<<grid, 128, 0, st>>>(p);
             break;
-        case 8: knn_finalize_kernel<8, false><<<grid, 128, 0, st>>>(p); break;
-        case 16: knn_finalize_kernel<16, false><<<grid, 128, 0, st>>>(p); break;
+        FL_FINALIZE_CASE(8)
+        FL_FINALIZE_CASE(16)
         default:
             set_error("unsupported pool size %d", p.K1);
             return FL_EUNSUPPORTED;
     }
+#undef FL_FINALIZE_CASE
     FL_CHECK_LAUNCH();
     return FL_OK;
 }
