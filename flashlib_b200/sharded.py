@@ -9,7 +9,10 @@ sample set), runs the single-GPU kernels on it and exchanges only what the algor
 * kNN: the ``(nq, k)`` local candidates with global row ids are all-gathered and every rank
   picks the k best of ``world * k`` per query with ``fl_topk_merge_f32``;
 * k-means: the per-cluster sums and counts are all-reduced, every rank finalises the same
-  centroids (no broadcast), labels stay sharded.
+  centroids (no broadcast), labels stay sharded;
+* IVF-Flat: every rank indexes its own rows under the SAME coarse centroids, so a query probes
+  the same lists on every rank and the union of the ranks' list members is the unsharded list;
+  the per-rank ``(nq, k)`` results (global row ids) are all-gathered and merged like kNN.
 """
 from __future__ import annotations
 
@@ -119,3 +122,41 @@ def sharded_kmeans(x_shard: torch.Tensor, n_clusters: int, *, max_iters: int = 1
         if tol > 0.0 and float(shift.max()) < tol:
             break
     return labels, cur, it + 1
+
+
+def sharded_ivf_build(x_shard: torch.Tensor, centroids: torch.Tensor, *, row_offset: int, nprobe: int = 8,
+                      build_fn: Optional[Callable] = None):
+    """This rank's part of a row-sharded IVF-Flat index: its rows assigned to the shared coarse
+    ``centroids`` (identical on every rank, e.g. trained on rank 0's sample and broadcast) and
+    laid out list-contiguously; ``ids`` are global row ids (``row_offset`` + local row).
+    ``build_fn(x_padded, centroids) -> index`` replaces the device path in the CPU tests."""
+    if build_fn is None:
+        from .ivf_flat import _pad_features, index_from_centroids
+        D = x_shard.shape[1]
+        Dp = max(int(D), 16)
+        xp = _pad_features(x_shard, Dp).contiguous()
+        cp = _pad_features(centroids, Dp).contiguous()
+        index = index_from_centroids(xp, cp, D=int(D), nprobe=nprobe)
+    else:
+        index = build_fn(x_shard, centroids)
+    index.ids = index.ids + int(row_offset)
+    return index
+
+
+def sharded_ivf_search(index, q: torch.Tensor, k: int, *, nprobe: Optional[int] = None, group=None,
+                       search_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
+    """IVF-Flat search over a row-sharded index (``sharded_ivf_build`` on every rank): the same
+    ``(vals fp32, ids int64)`` on every rank as a search of the unsharded index with the same
+    centroids.  A rank whose probed lists hold fewer than ``k`` rows contributes ``+inf`` / ``-1``
+    padding, which the merge drops."""
+    if search_fn is None:
+        from .ivf_flat import flash_ivf_flat_search as search_fn
+    if merge_fn is None:
+        from .knn import topk_merge as merge_fn
+    vals, ids = search_fn(index, q, k, nprobe=nprobe)
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return vals, ids
+    ids32 = ids.to(torch.int32)        # row ids fit 31 bits (the kernels index rows with int32)
+    cand_d, cand_i = gather_candidates(vals.float().contiguous(), ids32.contiguous(), group)
+    out_d, out_i = merge_fn(cand_d, cand_i, k)
+    return out_d, out_i.to(torch.int64)

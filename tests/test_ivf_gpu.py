@@ -130,3 +130,28 @@ def test_tensor_core_fine_scan_equals_cuda_core_scan(n, dim, nlist, nprobe, nq, 
     assert (tp == ep).float().mean().item() >= 0.9995
     if k <= 10:                            # (pools keep 12 entries: beyond k = 10 many queries
         assert st[2] <= nq // 10, st       #  take the exact scan, which is why "auto" stops there)
+
+
+def test_row_sharded_index_merges_to_the_unsharded_result():
+    """Two row shards indexed under the same centroids, searched separately and merged with
+    fl_topk_merge_f32 (what sharded_ivf_search does per rank) equal the unsharded index."""
+    from flashlib_b200 import sharded
+    from flashlib_b200.knn import topk_merge
+    g = torch.Generator().manual_seed(31)
+    means = 2 * torch.randn(30, 48, generator=g)
+    X = (means[torch.randint(0, 30, (40_000,), generator=g)] + torch.randn(40_000, 48, generator=g)).cuda()
+    Q = (means[torch.randint(0, 30, (500,), generator=g)] + torch.randn(500, 48, generator=g)).cuda()
+    whole = fl.flash_ivf_flat_build(X, 64, nprobe=6, niter=4, seed=5)
+    wv, wi = fl.flash_ivf_flat_search(whole, Q, 10)
+    cents = whole.centroids[:, :48].contiguous()
+    parts = []
+    for r in range(2):
+        s, e = sharded.shard_bounds(X.shape[0], 2, r)
+        local = sharded.sharded_ivf_build(X[s:e], cents, row_offset=s, nprobe=6)
+        assert int(local.list_offsets[-1].item()) == e - s
+        parts.append(sharded.sharded_ivf_search(local, Q, 10))          # world of one: the local result
+    cd = torch.cat([p[0] for p in parts], 1)
+    ci = torch.cat([p[1] for p in parts], 1).to(torch.int32)
+    mv, mi = topk_merge(cd, ci, 10)
+    torch.testing.assert_close(mv, wv, rtol=1e-5, atol=1e-5)
+    assert (mi.long() == wi).float().mean().item() > 0.999
