@@ -217,6 +217,20 @@ def run_secondary(args):
                 "unit": "queries/s", "ms_per_step": ms,
                 "config": {"k": 100, "path": path.get(int(info["mode"]), str(info["mode"])),
                            "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+    elif args.workload == "knn_self_1m":
+        # the "graph build" regime of flash_knn's internal callers: every row of the 1M x 128
+        # database is a query against the same database
+        X, _ = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, clamp=True)
+        Xd = X.cuda()
+        from flashlib_b200.knn import _mode_from, knn_f32
+        mode = _mode_from(args.mode)
+        ms = _time_steps(lambda: fl.flash_knn(Xd, Xd, K_NEIGHBOURS, mode=args.mode), min(steps, 2), 1)
+        _, _, info = knn_f32(Xd, Xd, K_NEIGHBOURS, mode=mode)
+        line = {"workload": "knn_self_1m", "metric": "exact_knn_queries_per_sec", "value": DB_ROWS / (ms * 1e-3),
+                "unit": "queries/s", "ms_per_step": ms,
+                "algorithmic_tflops": 2.0 * DB_ROWS * DB_ROWS * DIM / (ms * 1e-3) / 1e12,
+                "config": {"rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS, "mode": int(info["mode"]),
+                           "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
     elif args.workload == "knn_100m_shard":
         # One GPU's share of the sharded configuration: 12.5M of the 100M rows x 96 features
         # ~ N(0,1), all 100,000 queries, k = 100 (drawn on the device: 4.8 GB of rows).
@@ -269,7 +283,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
+    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_self_1m", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
                     help="knn_1m is the headline benchmark; the others time the remaining configurations on one GPU "
                          "and print a shorter JSON line")
     ap.add_argument("--db-rows", type=int, default=None, help="with --profile-case: database rows")

@@ -77,6 +77,7 @@ int launch_fallback_fixup(int* fb_count, int fb_cap, int32_t* status, int K1, cu
 // ---- workspace layout -----------------------------------------------------------------
 struct KnnWs {
     int mode, K1, K1f;
+    int deep, plen;                            // tensor-core path: deep pools, published entries per (query, range)
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
     int64_t nq_pad; int d_pad; int fb_cap; int fb_bq, fb_blocks;
@@ -112,8 +113,11 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.nsplit_fb = (int)ceil_div(m, w.rows_per_split_fb);
         w.off_hnorm = -1;
         w.off_qplane = take(cur, w.nq_pad * (w.d_pad + PLANE_AUG_COLS) * 2);
-        w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
-        w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)tc_partial_len(k) * 4);
+        w.deep = tc_use_deep_pools(k, w.d_pad, w.nsplit, w.nq_pad);
+        w.plen = w.deep ? tc_deep_partial_len() : tc_partial_len(k);
+        if (w.deep) w.K1 = tc_deep_pool_size();
+        w.off_part_sc = take(cur, w.nq_pad * w.nsplit * (int64_t)w.plen * 4);
+        w.off_part_id = take(cur, w.nq_pad * w.nsplit * (int64_t)w.plen * 4);
         w.off_part_tau = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_part_cnt = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_seed_cls = take(cur, w.nq_pad * 32 * 4);
@@ -329,6 +333,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.tau = tau; tp.status = status;
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
+    tp.deep_pools = w.deep;
     tp.seed_cls = reinterpret_cast<float*>(base + w.off_seed_cls);
     tp.k = k;
     profile_begin(st);
@@ -341,7 +346,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
     // Re-rank the tc_partial_len best scores of the union of the published pools; what the
     // scoring pass left out is bounded by the thresholds it published.
-    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = w.nsplit; fp.K1 = tc_partial_len(k);
+    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.plen;
     fp.k = k; fp.rerank = fp.K1; fp.row_offset = row_offset;
     fp.part_tau = tp.part_tau; fp.ntau = w.nsplit * tc_taus_per_range();
     fp.out_dist = out_dist; fp.out_idx = out_idx;

@@ -116,6 +116,7 @@ int tc_pool_size(int k);
 // Entries the tensor-core pass publishes per (query, range): a multiple of the pool size.
 int tc_partial_len(int k);
 int tc_deep_pool_size();
+int tc_use_deep_pools(int k, int d_pad, int nsplit, int64_t nq_pad);
 int tc_deep_partial_len();
 // Thresholds the tensor-core pass publishes per (query, range).
 int tc_taus_per_range();
