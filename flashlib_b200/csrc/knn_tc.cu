@@ -762,11 +762,13 @@ static int make_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int c
 int tc_knn_big(int k) { return k > 16 ? 1 : 0; }
 int tc_pool_size(int k) { return tc_knn_big(k) ? TC_BIG_K1 : TC_K1; }
 int tc_partial_len(int k) { return TC_NWG * (tc_knn_big(k) ? TC_BIG_CAP : TC_CAP); }
-// Deep pools for plain k <= 16 scoring when a query ends up with only a few pools (one to three
-// database ranges): with two shallow pools the largest threshold sits too close to the k-th
-// neighbour for the proof.  Needs the 128-feature shared-memory budget.
+// Deep pools for plain k <= 16 scoring when the whole database is one range, i.e. a query ends up
+// with just two pools: the larger of two 12th-best scores sits too close to the k-th neighbour
+// for the proof (a quarter of the rows of a 1M x 1M self-kNN failed it).  With three ranges the
+// shallow pools prove every row of the benchmark mixture and are faster.  Needs the 128-feature
+// shared-memory budget.
 int tc_use_deep_pools(int k, int d_pad, int nsplit, int64_t nq_pad) {
-    return !tc_knn_big(k) && d_pad <= 128 && nsplit <= 3 && !tc_pair_enabled(nq_pad, k);
+    return !tc_knn_big(k) && d_pad <= 128 && nsplit == 1 && !tc_pair_enabled(nq_pad, k);
 }
 int tc_deep_pool_size() { return TC_MID_K1; }
 int tc_deep_partial_len() { return TC_NWG * TC_MID_PUB; }
