@@ -69,3 +69,12 @@ def test_cache_entries_die_with_their_tensor():
     del base
     gc.collect()
     assert key not in cache
+
+
+def test_large_kmeans_block_partition():
+    """Blocks of the host-resident sample set are dealt to the ranks contiguously, the first
+    ranks taking the remainder (flashlib/primitives/kmeans/large.py:74-78)."""
+    from flashlib_b200.kmeans_large import block_range
+    assert [block_range(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert [block_range(2, 4, r) for r in range(4)] == [(0, 1), (1, 2), (2, 2), (2, 2)]
+    assert block_range(7, 1, 0) == (0, 7)

@@ -121,3 +121,22 @@ def test_tensor_core_assign_near_duplicate_centroids():
     got = d64[torch.arange(3000, device="cuda"), tc.long()]
     assert torch.all((got - best).abs() <= 1e-5 * best + 1e-6)
     assert not torch.any(tc >= 128)          # rows 128.. duplicate rows 0..15 exactly: lower index wins
+
+
+def test_large_n_streaming_matches_resident_kmeans():
+    """kmeans_largeN (samples in pinned host memory, streamed in blocks over two streams) follows
+    the same Lloyd iterations as flash_kmeans on GPU-resident data."""
+    import flashlib_b200 as fl
+    g = torch.Generator().manual_seed(17)
+    means = 3 * torch.randn(40, 32, generator=g)
+    X = (means[torch.randint(0, 40, (150_000,), generator=g)] + torch.randn(150_000, 32, generator=g))
+    init = X[:40].clone()
+    ids_l, cent_l = fl.kmeans_largeN(X.pin_memory(), 40, max_iters=6, BLOCK_N=40_000, init_centroids=init)
+    ids_r, cent_r, _ = fl.flash_kmeans(X.cuda(), 40, max_iters=6, init_centroids=init.cuda())
+    assert ids_l.dtype == torch.int32 and not ids_l.is_cuda and ids_l.shape == (150_000,)
+    torch.testing.assert_close(cent_l.cpu(), cent_r.cpu(), rtol=1e-4, atol=1e-4)
+    # flash_kmeans returns the labels of the last assignment (before the last update), like kmeans_largeN
+    assert (ids_l == ids_r.cpu()).float().mean().item() > 0.999
+    again = fl.kmeans_largeN_assign(X, cent_l, BLOCK_N=64_000)
+    direct = fl.euclid_assign_triton(X.cuda()[None], cent_l.float()[None])[0].cpu()
+    assert torch.equal(again, direct)
