@@ -646,45 +646,71 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
     for (int i = n + tid; i < P; i += BIG_THREADS) { s_key[i] = neg_inf(); s_id[i] = INVALID_ID; }
     block_sort_desc<BIG_THREADS>(s_key, s_id, P);
 
-    // exact distances of the best BIG_RERANK; everything else scored at most `bound`
+    // Exact distances in rounds of 64 candidates, best scores first.  After a round the walk stops
+    // when k of the exact distances seen so far lie below the lower bound that the next
+    // candidate's score (and the cut) puts on every row not yet re-scored; at most BIG_RERANK.
+    __shared__ float s_dist[BIG_RERANK];
+    const float mn = __ldg(p.maxnorm);
+    const float eps = p.eps_rel * sqrtf(qsq) * mn;
+    const float slack = 1e-5f * (qsq + mn * mn);
+    const int n_rr = n < BIG_RERANK ? n : BIG_RERANK;
     float bound = cut;
-    if (n > BIG_RERANK) bound = fmaxf(bound, s_key[BIG_RERANK]);
+    int done = 0;
     __syncthreads();
-    for (int c0 = warp * 4; c0 < BIG_RERANK; c0 += (BIG_THREADS / 32) * 4) {
-        uint32_t cid[4];
-        float a[4];
+    for (int r0 = 0; r0 < n_rr; r0 += 64) {
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            const int c0 = r0 + warp * 8 + h * 4;
+            uint32_t cid[4];
+            float a[4];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) { cid[t] = s_id[c0 + t]; a[t] = 0.f; }
-        if (p.vec) {
-            for (int c = lane * 4; c < p.d; c += 128) {
-                const float4 qv = *reinterpret_cast<const float4*>(s_q + c);
+            for (int t = 0; t < 4; ++t) { cid[t] = s_id[c0 + t]; a[t] = 0.f; }
+            if (p.vec) {
+                for (int c = lane * 4; c < p.d; c += 128) {
+                    const float4 qv = *reinterpret_cast<const float4*>(s_q + c);
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    if (cid[t] != INVALID_ID) {
-                        const float4 xv = __ldg(reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
-                        const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
-                        a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                    for (int t = 0; t < 4; ++t) {
+                        if (cid[t] != INVALID_ID) {
+                            const float4 xv = __ldg(reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
+                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
+                            a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                        }
+                    }
+                }
+            } else {
+                for (int c = lane; c < p.d; c += 32) {
+                    const float qv = s_q[c];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (cid[t] != INVALID_ID) {
+                            const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
+                            a[t] += df * df;
+                        }
                     }
                 }
             }
-        } else {
-            for (int c = lane; c < p.d; c += 32) {
-                const float qv = s_q[c];
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    if (cid[t] != INVALID_ID) {
-                        const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
-                        a[t] += df * df;
-                    }
-                }
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
+                if (lane == 0) s_dist[c0 + t] = cid[t] != INVALID_ID ? a[t] : pos_inf();
             }
         }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
-            if (lane == 0) s_key[c0 + t] = cid[t] != INVALID_ID ? -a[t] : neg_inf();
-        }
+        done = r0 + 64;
+        // everything from position `done` on scored at most s_key[done] (sorted) or the cut
+        const float nxt = done < n ? s_key[done] : neg_inf();
+        bound = fmaxf(cut, nxt);
+        const float T = qsq - 2.f * (bound + eps) - slack;
+        __syncthreads();                                   // this round's distances are written
+        const int below = __syncthreads_count(tid < done && s_dist[tid] < T);
+        if (done >= p.k && below >= p.k) break;
+    }
+    // order the re-scored candidates by (distance, row)
+    __syncthreads();
+    for (int i = tid; i < BIG_RERANK; i += BIG_THREADS) {
+        const bool have = i < done && i < n_rr && s_id[i] != INVALID_ID;
+        s_key[i] = have ? -s_dist[i] : neg_inf();
+        if (!have) s_id[i] = INVALID_ID;
     }
     block_sort_desc<BIG_THREADS>(s_key, s_id, BIG_RERANK);
 
@@ -696,9 +722,6 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
     if (tid == 0) {
         bool proven = !overflow;
         if (proven && bound > neg_inf()) {
-            const float mn = __ldg(p.maxnorm);
-            const float eps = p.eps_rel * sqrtf(qsq) * mn;
-            const float slack = 1e-5f * (qsq + mn * mn);
             const float dk = s_id[p.k - 1] != INVALID_ID ? -s_key[p.k - 1] : pos_inf();
             proven = dk < qsq - 2.f * (bound + eps) - slack;
         }
