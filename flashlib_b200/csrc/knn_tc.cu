@@ -102,7 +102,7 @@ struct TcKernelParams {
     int tile_stride;         // database tile actually read for loop index t is t * tile_stride (1 outside seeding)
     int dbg_flags;           // timing experiments (results invalid): 1 skip pass 2, 2 skip the
                              // reductions of pass 1, 4 skip the tensor-memory loads too, 8 skip the
-                             // norm-column MMA step
+                             // norm-column MMA step, 16 issue no MMA at all (operand streaming only)
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
     int64_t dbg_ld;
 };
@@ -282,6 +282,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = umma_idesc_bf16(PAIR ? 2 * TC_BM : TC_BM, TC_BN);
             auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t acc) {
+                if (DBG && (p.dbg_flags & 16)) return;     // timing experiment: operand streaming only
                 if (PAIR) umma_bf16_pair(d, a, b, idesc, acc); else umma_bf16(d, a, b, idesc, acc);
             };
             auto commit = [&](uint32_t bar) { if (PAIR) umma_commit_pair(bar); else umma_commit(bar); };
