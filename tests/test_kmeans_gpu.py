@@ -125,18 +125,29 @@ def test_tensor_core_assign_near_duplicate_centroids():
 
 def test_large_n_streaming_matches_resident_kmeans():
     """kmeans_largeN (samples in pinned host memory, streamed in blocks over two streams) follows
-    the same Lloyd iterations as flash_kmeans on GPU-resident data."""
+    the same Lloyd iterations as flash_kmeans on GPU-resident data.  One iteration is compared
+    value for value; over several iterations the fp32 atomics of the centroid sums let a boundary
+    point flip between runs (of either path), so the clusterings are compared by their inertia."""
     import flashlib_b200 as fl
     g = torch.Generator().manual_seed(17)
     means = 3 * torch.randn(40, 32, generator=g)
     X = (means[torch.randint(0, 40, (150_000,), generator=g)] + torch.randn(150_000, 32, generator=g))
     init = X[:40].clone()
-    ids_l, cent_l = fl.kmeans_largeN(X.pin_memory(), 40, max_iters=6, BLOCK_N=40_000, init_centroids=init)
-    ids_r, cent_r, _ = fl.flash_kmeans(X.cuda(), 40, max_iters=6, init_centroids=init.cuda())
+    Xp, Xd = X.pin_memory(), X.cuda()
+    ids_l, cent_l = fl.kmeans_largeN(Xp, 40, max_iters=1, BLOCK_N=40_000, init_centroids=init)
+    ids_r, cent_r, _ = fl.flash_kmeans(Xd, 40, max_iters=1, init_centroids=init.cuda())
     assert ids_l.dtype == torch.int32 and not ids_l.is_cuda and ids_l.shape == (150_000,)
+    assert torch.equal(ids_l, ids_r.cpu())
     torch.testing.assert_close(cent_l.cpu(), cent_r.cpu(), rtol=1e-4, atol=1e-4)
-    # flash_kmeans returns the labels of the last assignment (before the last update), like kmeans_largeN
+
+    def inertia(cent):
+        lab = fl.euclid_assign_triton(Xd[None], cent.cuda().float()[None])[0].long()
+        return float(((Xd - cent.cuda().float()[lab]) ** 2).sum(1).mean())
+
+    ids_l, cent_l = fl.kmeans_largeN(Xp, 40, max_iters=6, BLOCK_N=40_000, init_centroids=init)
+    ids_r, cent_r, _ = fl.flash_kmeans(Xd, 40, max_iters=6, init_centroids=init.cuda())
+    assert abs(inertia(cent_l) - inertia(cent_r)) <= 1e-3 * inertia(cent_r)
     assert (ids_l == ids_r.cpu()).float().mean().item() > 0.999
     again = fl.kmeans_largeN_assign(X, cent_l, BLOCK_N=64_000)
-    direct = fl.euclid_assign_triton(X.cuda()[None], cent_l.float()[None])[0].cpu()
+    direct = fl.euclid_assign_triton(Xd[None], cent_l.float()[None])[0].cpu()
     assert torch.equal(again, direct)
