@@ -127,8 +127,10 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         // the fallback scan spreads its blocks over the live slots (simt_dyn_split): at most
         // one pool per block
         w.fb_bq = simt_block_queries(w.K1f);
-        w.fb_blocks = (int)(ceil_div(w.fb_cap, w.fb_bq > 0 ? w.fb_bq : 1) * w.nsplit_fb);
-        if (w.fb_blocks < 4 * sm_count()) w.fb_blocks = 4 * sm_count();
+        // four blocks per SM either way: enough ranges for a handful of rows, no long tail of
+        // blocks that only find out they have nothing to do
+        w.fb_blocks = 4 * sm_count();
+        if (w.fb_blocks < ceil_div(w.fb_cap, w.fb_bq > 0 ? w.fb_bq : 1)) w.fb_blocks = (int)ceil_div(w.fb_cap, w.fb_bq > 0 ? w.fb_bq : 1);
         const int64_t fb_pools = (int64_t)w.fb_blocks * (w.fb_bq > 0 ? w.fb_bq : 1);
         w.off_fbpart_sc = take(cur, fb_pools * w.K1f * 4);
         w.off_fbpart_id = take(cur, fb_pools * w.K1f * 4);
