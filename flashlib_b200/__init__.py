@@ -15,7 +15,7 @@ __version__ = "0.1.0"
 
 _LAZY = {
     "flash_knn": "knn", "flash_knn_dispatch": "knn", "flash_knn_triton": "knn",
-    "triton_knn_gather_sqdist": "knn", "row_sqnorm": "knn", "topk_merge": "knn", "DbPlane": "knn",
+    "triton_knn_gather_sqdist": "knn", "row_sqnorm": "knn", "topk_merge": "knn", "DbPlane": "knn", "check_pending": "knn",
     "kmeans_largeN": "kmeans_large", "kmeans_largeN_assign": "kmeans_large",
     "flash_kmeans": "kmeans", "batch_kmeans_Euclid": "kmeans", "euclid_assign_triton": "kmeans",
     "triton_lloyd_centroid_step_euclid": "kmeans", "triton_centroid_finalize": "kmeans",

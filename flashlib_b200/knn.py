@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import os
 import weakref
-from collections import OrderedDict
+from collections import OrderedDict, deque
 from typing import Optional
 
 import torch
@@ -98,9 +98,52 @@ def clear_plane_cache() -> None:
     _PLANE_CACHE.clear()
 
 
+# Status words of calls whose check was deferred: (pinned host copy, event of the copy).  The
+# tensor-core kernel reports a timed-out wait there; reading it right after the call would
+# serialise host and device once per call, so the public entry points look at the words of
+# EARLIER calls instead (and ``check_pending()`` looks at all of them).
+_PENDING_STATUS: deque = deque()
+
+
+def _raise_on_status(st) -> None:
+    if st[_lib.FL_STATUS_ERROR] != 0:
+        raise _lib.FlashlibError(
+            f"tensor-core kNN kernel reported status {st[_lib.FL_STATUS_ERROR]} "
+            f"(where={st[_lib.FL_STATUS_WHERE]:#x})")
+
+
+def check_pending(block: bool = True) -> None:
+    """Raises if an earlier call whose status check was deferred reported an error.  With
+    ``block=False`` only calls that have already finished on the device are looked at."""
+    while _PENDING_STATUS:
+        host, ev = _PENDING_STATUS[0]
+        if not block and not ev.query():
+            return
+        ev.synchronize()
+        _PENDING_STATUS.popleft()
+        _raise_on_status(host.tolist())
+
+
+def _defer_status_check(status: torch.Tensor) -> None:
+    check_pending(block=False)
+    host = torch.empty(_lib.FL_STATUS_WORDS, dtype=torch.int32).pin_memory()
+    host.copy_(status, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(status.device))
+    _PENDING_STATUS.append((host, ev))
+    while len(_PENDING_STATUS) > 64:              # bounded: the oldest calls have long finished
+        check_pending_one = _PENDING_STATUS[0]
+        check_pending_one[1].synchronize()
+        _PENDING_STATUS.popleft()
+        _raise_on_status(check_pending_one[0].tolist())
+
+
 def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KNN_AUTO,
-            row_offset: int = 0, plane: Optional[DbPlane] = None, check_status: bool = True):
-    """One 2-D problem through ``fl_knn_f32``: returns ``(dist fp32 (nq,k), idx int32 (nq,k), info)``."""
+            row_offset: int = 0, plane: Optional[DbPlane] = None, check_status=True):
+    """One 2-D problem through ``fl_knn_f32``: returns ``(dist fp32 (nq,k), idx int32 (nq,k), info)``.
+    ``check_status=True`` reads the kernel's status words before returning (one host/device
+    round trip; ``info["fallback_rows"]`` is filled), ``"deferred"`` leaves that to a later call
+    or to ``check_pending()``, ``False`` skips it."""
     lib = _lib.load()
     _lib.require_device()
     nq, d = q.shape
@@ -120,7 +163,9 @@ def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KN
                         status.data_ptr(), _stream_ptr(dev))
     _lib.check(rc)
     info = {"mode": resolved, "status": status}
-    if check_status and resolved == _lib.FL_KNN_BF16_RERANK:
+    if check_status == "deferred" and resolved == _lib.FL_KNN_BF16_RERANK:
+        _defer_status_check(status)
+    elif check_status and resolved == _lib.FL_KNN_BF16_RERANK:
         st = status.tolist()
         info["fallback_rows"] = st[_lib.FL_STATUS_FALLBACK]
         if st[_lib.FL_STATUS_ERROR] != 0:
@@ -170,7 +215,7 @@ def flash_knn_dispatch(x: torch.Tensor, c: torch.Tensor, k: int, *, tol: Optiona
         for b in range(B):
             qb = _as_f32_rows(x[b])
             cb = _as_f32_rows(c[b])
-            d_b, i_b, _ = knn_f32(qb, cb, k, mode=m)
+            d_b, i_b, _ = knn_f32(qb, cb, k, mode=m, check_status="deferred")
             vals[b] = d_b
             idxs[b] = i_b
     if not return_distances:

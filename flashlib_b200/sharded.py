@@ -63,7 +63,8 @@ def sharded_knn(q: torch.Tensor, db_shard: torch.Tensor, k: int, *, row_offset: 
         from .knn import _mode_from, knn_f32
 
         def local_fn(q_, db_, k_, off_):
-            d_, i_, _ = knn_f32(q_, db_, k_, mode=_mode_from(mode), row_offset=off_, plane=plane)
+            d_, i_, _ = knn_f32(q_, db_, k_, mode=_mode_from(mode), row_offset=off_, plane=plane,
+                                check_status="deferred")
             return d_, i_
     if merge_fn is None:
         from .knn import topk_merge as merge_fn
