@@ -283,6 +283,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--result", default="owner", choices=["owner", "replicated"],
+                    help="N > 1: 'owner' = all-to-all, every rank merges and returns its own slice of the step's queries; "
+                         "'replicated' = all-gather, every rank merges and returns all of them")
     ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_self_1m", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
                     help="knn_1m is the headline benchmark; the others time the remaining configurations on one GPU "
                          "and print a shorter JSON line")
@@ -348,7 +351,7 @@ def main():
     def step_device():
         if flush is not None:
             flush.zero_()
-        return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane)
+        return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane, result=args.result)
 
     def barrier():
         if world > 1:
@@ -394,8 +397,10 @@ def main():
     # overlaps the scoring of its neighbour (as a serving loop would); the host reads a step's
     # results (waits for its copy-out event) before it reuses that slot two steps later, and
     # everything is drained before the clock stops.
-    out_d_host = [torch.empty((nq, K_NEIGHBOURS), dtype=torch.float32).pin_memory() for _ in range(2)]
-    out_i_host = [torch.empty((nq, K_NEIGHBOURS), dtype=torch.int32).pin_memory() for _ in range(2)]
+    from flashlib_b200.sharded import shard_bounds
+    qs_, qe_ = shard_bounds(nq, world, rank) if (world > 1 and args.result == "owner") else (0, nq)
+    out_d_host = [torch.empty((qe_ - qs_, K_NEIGHBOURS), dtype=torch.float32).pin_memory() for _ in range(2)]
+    out_i_host = [torch.empty((qe_ - qs_, K_NEIGHBOURS), dtype=torch.int32).pin_memory() for _ in range(2)]
     q_slots = [torch.empty_like(q_dev) for _ in range(2)]
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     main = torch.cuda.current_stream(dev)
@@ -420,7 +425,8 @@ def main():
         if world == 1:
             d_, i_ = flash_knn(q_slots[j], db, K_NEIGHBOURS, mode=args.mode)
         else:
-            d_, i_ = sharded_knn(q_slots[j], db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane)
+            d_, i_ = sharded_knn(q_slots[j], db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane,
+                                 result=args.result)
         ev_used[j].record(main)
         ev_done[j].record(main)
         keep[j] = (d_, i_)
@@ -488,8 +494,11 @@ def main():
             "scaling": SCALING, "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
             "data": "synthetic",
             "config": {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,
-                       "queries_per_step": nq, "sharding": f"database rows over {world} rank(s); candidates "
-                       "all-gathered and merged on every rank" if world > 1 else "single GPU",
+                       "queries_per_step": nq, "sharding": (f"database rows over {world} ranks; every rank scores all of the step's queries; "
+                                    + ("candidates exchanged all-to-all, every rank merges and returns its own "
+                                       f"{qe_ - qs_} queries" if args.result == "owner" else
+                                       "candidates all-gathered, every rank merges and returns all queries"))
+                       if world > 1 else "single GPU",
                        "mode": {_lib.FL_KNN_EXACT_SIMT: "exact fp32 CUDA-core scoring + exact re-rank",
                                 _lib.FL_KNN_BF16_RERANK: "tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback"}[resolved],
                        "l2": ("a 256 MB buffer is overwritten before every step (inside the timed region): this rank's "

@@ -49,16 +49,39 @@ def gather_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
     return cand_d, cand_i
 
 
+def exchange_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None):
+    """All-to-all form of :func:`gather_candidates`: rank ``r`` receives, from every rank, only the
+    candidates of the queries ``shard_bounds(nq, world, r)`` it owns.  Returns ``(cand_d, cand_i)`` of
+    shape ``(owned, world * k)``; inbound volume and merge work are ``1/world`` of the all-gather's."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    nq, k = local_d.shape
+    packed = torch.cat([local_d.contiguous().view(torch.int32), local_i.to(torch.int32)], dim=1).contiguous()
+    counts = [shard_bounds(nq, world, r)[1] - shard_bounds(nq, world, r)[0] for r in range(world)]
+    mine = counts[rank]
+    g = torch.empty((world * mine, 2 * k), dtype=torch.int32, device=local_d.device)
+    dist.all_to_all_single(g, packed, output_split_sizes=[mine] * world, input_split_sizes=counts, group=group)
+    g = g.view(world, mine, 2 * k).permute(1, 0, 2)
+    cand_d = g[:, :, :k].reshape(mine, world * k).view(torch.float32)
+    cand_i = g[:, :, k:].reshape(mine, world * k)
+    return cand_d, cand_i
+
+
 def sharded_knn(q: torch.Tensor, db_shard: torch.Tensor, k: int, *, row_offset: int, group=None,
-                mode: Optional[str] = None, plane=None,
+                mode: Optional[str] = None, plane=None, result: str = "replicated",
                 local_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
     """Exact kNN of the replicated queries ``q`` against a row-sharded database.
 
     ``db_shard`` is this rank's rows, ``row_offset`` its first global row id.  A shard with
-    fewer than ``k`` rows contributes ``+inf`` / ``-1`` padding.  Returns the same
-    ``(dist fp32 (nq,k), idx int32 (nq,k))`` on every rank.  ``local_fn`` / ``merge_fn``
-    replace the device kernels (used by the CPU tests of the exchange logic).
+    fewer than ``k`` rows contributes ``+inf`` / ``-1`` padding.  ``result="replicated"`` returns
+    the same ``(dist fp32 (nq,k), idx int32 (nq,k))`` on every rank (all-gather of the candidates,
+    every rank merges all queries); ``result="owner"`` returns on rank ``r`` the rows
+    ``shard_bounds(nq, world, r)`` of that result only (all-to-all, every rank merges its own
+    queries).  ``local_fn`` / ``merge_fn`` replace the device kernels (used by the CPU tests of the
+    exchange logic).
     """
+    if result not in ("replicated", "owner"):
+        raise ValueError(f"result must be 'replicated' or 'owner', got {result!r}")
     if local_fn is None:
         from .knn import _mode_from, knn_f32
 
@@ -83,7 +106,10 @@ def sharded_knn(q: torch.Tensor, db_shard: torch.Tensor, k: int, *, row_offset: 
         i_loc = torch.cat([i_loc, pad_i], 1)
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return d_loc, i_loc
-    cand_d, cand_i = gather_candidates(d_loc, i_loc, group)
+    if result == "owner":
+        cand_d, cand_i = exchange_candidates(d_loc, i_loc, group)
+    else:
+        cand_d, cand_i = gather_candidates(d_loc, i_loc, group)
     return merge_fn(cand_d, cand_i, k)
 
 

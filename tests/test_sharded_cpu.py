@@ -39,11 +39,16 @@ def _knn_worker(rank, world, port, m, k, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     g = torch.Generator().manual_seed(5)
     db = torch.randn(m, 16, generator=g)
-    q = torch.randn(40, 16, generator=g)
+    q = torch.randn(41, 16, generator=g)
     s, e = sharded.shard_bounds(m, world, rank)
     d, i = sharded.sharded_knn(q, db[s:e], k, row_offset=s, local_fn=_local_knn, merge_fn=_merge)
     ref_v, ref_i = oracle.knn_naive(q.numpy(), db.numpy(), k)
     ok = np.array_equal(i.numpy(), ref_i.astype(np.int32)) and np.allclose(d.numpy(), ref_v, rtol=1e-5, atol=1e-5)
+    # owner form: every rank holds the rows of its own query slice only (all-to-all exchange)
+    qs, qe = sharded.shard_bounds(q.shape[0], world, rank)
+    d2, i2 = sharded.sharded_knn(q, db[s:e], k, row_offset=s, result="owner", local_fn=_local_knn, merge_fn=_merge)
+    ok = ok and d2.shape == (qe - qs, k) and np.array_equal(i2.numpy(), ref_i[qs:qe].astype(np.int32)) \
+        and np.allclose(d2.numpy(), ref_v[qs:qe], rtol=1e-5, atol=1e-5)
     out[rank] = bool(ok)
     dist.destroy_process_group()
 
