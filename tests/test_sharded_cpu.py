@@ -34,12 +34,12 @@ def _merge(cd, ci, k):
     return torch.from_numpy(np.take_along_axis(cd, order, 1)), torch.from_numpy(np.take_along_axis(ci, order, 1))
 
 
-def _knn_worker(rank, world, port, m, k, out):
+def _knn_worker(rank, world, port, m, k, nq, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     g = torch.Generator().manual_seed(5)
     db = torch.randn(m, 16, generator=g)
-    q = torch.randn(41, 16, generator=g)
+    q = torch.randn(nq, 16, generator=g)
     s, e = sharded.shard_bounds(m, world, rank)
     d, i = sharded.sharded_knn(q, db[s:e], k, row_offset=s, local_fn=_local_knn, merge_fn=_merge)
     ref_v, ref_i = oracle.knn_naive(q.numpy(), db.numpy(), k)
@@ -53,12 +53,13 @@ def _knn_worker(rank, world, port, m, k, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("m,k", [(1000, 10), (7, 5)])       # second case: a shard shorter than k
-def test_sharded_knn_two_ranks(m, k):
+# second case: a shard shorter than k; third: fewer queries than ranks (rank 1 owns none)
+@pytest.mark.parametrize("m,k,nq", [(1000, 10, 41), (7, 5, 41), (300, 4, 1)])
+def test_sharded_knn_two_ranks(m, k, nq):
     world = 2
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_knn_worker, args=(world, _free_port(), m, k, out), nprocs=world, join=True)
+        mp.spawn(_knn_worker, args=(world, _free_port(), m, k, nq, out), nprocs=world, join=True)
         assert dict(out) == {0: True, 1: True}
 
 
