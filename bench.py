@@ -8,9 +8,12 @@ configuration, database row-sharded over the GPUs of one box.
     python bench.py --impl reference ...      # CPU restatement of the reference's torch path
 
 A step is one batch of queries through the hot path.  Scaling is weak: every rank brings
-10,000 queries per step (global batch 10,000 x N) and holds 1/N of the database rows; the
-per-rank candidates are all-gathered (NCCL) and merged on every rank.  One JSON line is
-printed by rank 0.
+10,000 queries per step (global batch 10,000 x N) and holds 1/N of the database rows; the ranks
+share their threshold seeds (one all-reduce), score, exchange their candidates (all-to-all, or
+all-gather with --result replicated) and merge.  One JSON line is printed by rank 0; it carries
+a "parity" object (a sample of the last step's results against the CPU oracle, at every N),
+and at N = 1 a "secondary" object (the k-means, IVF-Flat and k=100 configurations, timed and
+checked the same way) and a "sustained" object (the same loop run for seconds).
 
 ``--workload knn_100m`` runs the same flow on the sharded configuration (100,000,000 x 96 rows
 ~ N(0,1) split over the ranks, 100,000 queries per step, k = 100; strong scaling: the total work
@@ -142,10 +145,63 @@ def make_workload(rank: int, world: int):
     return X, Q, s, e
 
 
+def config_dict(world: int, result: str, resolved_tc: bool, nq: int) -> dict:
+    """The `config` object of the JSON line: the same for both arms (the reference arm reports the
+    configuration it stands in for; what it ran itself is in its `cpu_baseline.sample`)."""
+    from flashlib_b200.sharded import shard_bounds
+    rows_local = shard_bounds(DB_ROWS, world, 0)
+    plane_bytes = (rows_local[1] - rows_local[0]) * (((DIM + 63) // 64) * 64 + 16) * 2
+    owned = shard_bounds(nq, world, 0)
+    flushes = plane_bytes < (256 << 20)
+    return {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,
+            "queries_per_step": nq,
+            "sharding": (f"database rows over {world} ranks; every rank scores all of the step's queries; "
+                         + ("threshold seeds shared by one all-reduce; " if K_NEIGHBOURS <= 16 else "")
+                         + ("candidates exchanged all-to-all, every rank merges and returns its own "
+                            f"{owned[1] - owned[0]} queries" if result == "owner" else
+                            "candidates all-gathered, every rank merges and returns all queries"))
+            if world > 1 else "single GPU",
+            "mode": ("tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback" if resolved_tc else
+                     "exact fp32 CUDA-core scoring + exact re-rank"),
+            "l2": ("a 256 MB buffer is overwritten before every step (inside the timed region): a rank's "
+                   f"operand plane is {plane_bytes >> 20} MB" if flushes else
+                   f"no flush needed: each step streams the rank's operand plane ({plane_bytes >> 20} MB), "
+                   "larger than the 126 MB L2")}
+
+
+def knn_rows_agree(q, got_d, got_i, ref_d, ref_i, rel_tie=1e-5, rel_dist=1e-4):
+    """Number of rows of (got_d, got_i) that disagree with the oracle's (ref_d, ref_i) when the
+    database rows are not at hand to recompute distances in fp64: index sets must be equal except
+    between candidates whose distances differ by <= rel_tie relative, distances within rel_dist
+    relative.  The oracle's distances come from the fp32 expansion ||q||^2 + ||x||^2 - 2 q.x, whose
+    round-off (about 1e-6 of the norms) is added to both bands."""
+    q = np.asarray(q, np.float64)
+    got_d, ref_d = np.asarray(got_d, np.float64), np.asarray(ref_d, np.float64)
+    got_i, ref_i = np.asarray(got_i, np.int64), np.asarray(ref_i, np.int64)
+    bad = 0
+    for r in range(got_i.shape[0]):
+        hi_all = float(max(ref_d[r].max(), got_d[r].max()))
+        noise = 1e-6 * (2.0 * float((q[r] * q[r]).sum()) + hi_all)
+        if np.any(np.abs(np.sort(got_d[r]) - np.sort(ref_d[r])) > rel_dist * hi_all + noise):
+            bad += 1
+            continue
+        sg, sr = set(got_i[r].tolist()), set(ref_i[r].tolist())
+        if sg == sr:
+            continue
+        dg = [got_d[r][j] for j in range(got_i.shape[1]) if got_i[r][j] not in sr]
+        dr = [ref_d[r][j] for j in range(ref_i.shape[1]) if ref_i[r][j] not in sg]
+        lo, hi = min(dg + dr), max(dg + dr)
+        if len(sg) != got_i.shape[1] or hi - lo > rel_tie * hi + noise:
+            bad += 1
+    return bad
+
+
 def cpu_baseline_run(X: torch.Tensor, Q: torch.Tensor, n_queries: int, repeats: int = 1):
-    """Times the numpy restatement of the reference's chunked torch path on `n_queries` queries
-    against the whole database; returns (queries/s, threads)."""
+    """Times the torch-CPU restatement of the reference's chunked path (`oracle/oracle_torch.py`,
+    the same ATen operators the reference calls) on `n_queries` queries against the whole
+    database; returns (queries/s, threads)."""
     from oracle import oracle_torch
+    torch.set_num_threads(os.cpu_count() or 1)
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
@@ -158,7 +214,9 @@ def cpu_baseline_run(X: torch.Tensor, Q: torch.Tensor, n_queries: int, repeats: 
 def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
-    from flashlib_b200 import synthetic
+    # torch.distributed.run exports OMP_NUM_THREADS=1: the CPU arm takes every host core it can get
+    torch.set_num_threads(os.cpu_count() or 1)
+    from flashlib_b200 import _lib, synthetic
     X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
     from oracle import oracle_torch
     sample = 1024
@@ -171,14 +229,17 @@ def run_reference(args, rank: int, world: int):
     dt = time.perf_counter() - t0
     qps = args.steps * sample / dt
     cores = torch.get_num_threads()
+    nq = QUERIES_PER_GPU * args.gpus
+    rows0 = DB_ROWS // max(args.gpus, 1)
+    tc = _lib.load().fl_knn_resolve_mode(nq, rows0, DIM, K_NEIGHBOURS) == _lib.FL_KNN_BF16_RERANK
     line = {
         "impl": "reference", "metric": METRIC, "value": qps, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.gpus), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS},
+        "config": config_dict(args.gpus, args.result, tc, nq),
         "cpu_baseline": {"value": qps, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} queries per step against all {DB_ROWS} rows; torch-CPU "
-                                   "restatement of knn_torch_chunked, chunk 8192"},
+                         "sample": f"{sample} queries per step against all {DB_ROWS} rows on {cores} host threads "
+                                   "(os.cpu_count()); torch-CPU restatement of knn_torch_chunked, chunk 8192"},
         "e2e": {"value": qps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -198,25 +259,113 @@ def _time_steps(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
+def _roof(bound: str, work: float, ms: float, peaks: dict) -> dict:
+    """Roofline entry of a secondary workload: algorithmic FLOP (tensor) or bytes (hbm) per step
+    over the step time, against the measured burst peak."""
+    if bound == "tensor":
+        achieved, peak, unit = work / (ms * 1e-3) / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+    else:
+        achieved, peak, unit = work / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "algorithmic_work_per_step": work, "peak_source": peaks["source"]}
+
+
+def secondary_knn_k100(Xd, Qd, X, Q, steps, warm, mode_name, peaks):
+    import flashlib_b200 as fl
+    from flashlib_b200.knn import _mode_from, knn_f32
+    from oracle import oracle_torch
+    from tests import parity
+    ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, 100, mode=mode_name), steps, warm)
+    d_, i_, info = knn_f32(Qd, Xd, 100, mode=_mode_from(mode_name))
+    n_chk = 64
+    _, ref_i = oracle_torch.knn_chunked(Q[:n_chk], X, 100, chunk_size=8192)
+    res = parity.knn_parity(Q[:n_chk].numpy(), X.numpy(), d_[:n_chk].cpu().numpy(), i_[:n_chk].cpu().numpy(), ref_i.numpy())
+    path = {0: "exact fp32 CUDA-core scoring", 1: "tcgen05 bf16 candidates (pools of 256) + exact fp32 re-rank + verified fallback"}
+    nq, m, d = Qd.shape[0], Xd.shape[0], Xd.shape[1]
+    return {"workload": "knn_1m_k100", "metric": "exact_knn_queries_per_sec", "value": nq / (ms * 1e-3),
+            "unit": "queries/s", "ms_per_step": ms, "roofline": _roof("tensor", 2.0 * nq * m * d, ms, peaks),
+            "parity_ok": bool(res["ok"]), "parity": {"rows": n_chk, "bad_rows": len(res["bad_rows"]),
+                                                     "worst_rel_dist_err": res["worst_rel_dist_err"]},
+            "config": {"k": 100, "path": path.get(int(info["mode"]), str(info["mode"])),
+                       "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+
+
+def secondary_kmeans(steps, warm, peaks):
+    """k-means 1,000,000 x 128, K = 1024, 20 Lloyd iterations from the first K rows.  Parity: the
+    assignment under the final centroids against the oracle on 8,192 points (tie band), and the
+    centroid update from those labels against the oracle's over all points."""
+    import flashlib_b200 as fl
+    from flashlib_b200 import synthetic
+    from oracle import oracle
+    from tests import parity
+    cfg = synthetic.CONFIGS["kmeans_1m"]
+    X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
+    Xd = X.cuda()
+    init = Xd[:cfg["K"]].clone()
+    ms = _time_steps(lambda: fl.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init), steps, warm)
+    _, cents, _ = fl.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init)
+    lab = fl.euclid_assign_triton(Xd[None], cents[None])[0]
+    new, _, _ = fl.triton_lloyd_centroid_step_euclid(Xd[None], lab[None], cents[None])
+    sub = torch.randperm(cfg["n"], generator=torch.Generator().manual_seed(0))[:8192]
+    cn = cents.cpu().numpy()
+    ref_lab = oracle.kmeans_assign(X[sub].numpy(), cn)
+    lp = parity.label_parity(X[sub].numpy(), cn, lab.cpu()[sub].numpy(), ref_lab)
+    new_ref, _, _ = oracle.kmeans_update(X.numpy(), lab.cpu().numpy().astype(np.int64), cn)
+    upd_ok = parity.rel_close(new[0].cpu().numpy(), new_ref, rel=1e-4, atol=1e-5)
+    flop = 2.0 * cfg["n"] * cfg["K"] * cfg["d"] * cfg["iters"]
+    return {"workload": "kmeans_1m", "metric": "kmeans_20_iterations_ms", "value": ms, "unit": "ms", "ms_per_step": ms,
+            "higher_is_better": False, "roofline": _roof("tensor", flop, ms, peaks),
+            "parity_ok": bool(lp["ok"] and upd_ok),
+            "parity": {"labels_checked": lp["n"], "labels_differ": lp["differ"], "labels_bad": lp["bad"],
+                       "centroid_update_within_1e-4": bool(upd_ok)},
+            "config": {"n": cfg["n"], "d": cfg["d"], "K": cfg["K"], "iters": cfg["iters"], "init": "first K rows"}}
+
+
+def secondary_ivf(steps, warm, peaks):
+    """IVF-Flat 1,000,000 x 128, nlist 1024 (10 Lloyd iterations), nprobe 16, 10,000 queries, k = 10.
+    Parity: the oracle's search of the SAME index for 128 queries."""
+    import flashlib_b200 as fl
+    from flashlib_b200 import synthetic
+    from oracle import oracle
+    from tests import parity
+    cfg = synthetic.CONFIGS["ivf_1m"]
+    X, Q = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"], nq=cfg["nq"], clamp=True)
+    Xd, Qd = X.cuda(), Q.cuda()
+    ivf = fl.IVFFlat(nlist=cfg["nlist"], nprobe=cfg["nprobe"], niter=10, seed=cfg["seed"]).fit(Xd)
+    ms = _time_steps(lambda: ivf.kneighbors(Qd, cfg["k"]), steps, warm)
+    _, bi = fl.flash_knn(Qd[:1000], Xd, cfg["k"])
+    vals, ii = ivf.kneighbors(Qd, cfg["k"])
+    recall = float(np.mean([len(set(a.tolist()) & set(b.tolist())) / cfg["k"]
+                            for a, b in zip(ii[:1000].cpu().numpy(), bi.cpu().numpy())]))
+    idx = ivf.index_
+    n_chk = 128
+    ov, oi, _ = oracle.ivf_search(idx.centroids.cpu().numpy(), idx.data.cpu().numpy(), idx.ids.cpu().numpy(),
+                                  idx.list_offsets.cpu().numpy(), Q[:n_chk].numpy(), cfg["k"], cfg["nprobe"])
+    v, i = vals[:n_chk].cpu().numpy(), ii[:n_chk].cpu().numpy()
+    fin = np.isfinite(ov)
+    same_rows = float(np.mean([set(a[f].tolist()) == set(b[f].tolist()) for a, b, f in zip(i, oi, fin)]))
+    ok = bool(np.array_equal(np.isfinite(v), fin) and parity.rel_close(v[fin], ov[fin], rel=1e-4, atol=1e-4)
+              and same_rows >= 0.99)
+    # every probed list streamed once (fp32 rows) + the gathered queries + the results
+    lens = idx.list_lengths().cpu().numpy()
+    work = float(cfg["n"] * cfg["d"] * 4 + cfg["nq"] * cfg["nprobe"] * cfg["d"] * 4 + cfg["nq"] * cfg["k"] * 12)
+    return {"workload": "ivf_1m", "metric": "ivf_flat_queries_per_sec", "value": cfg["nq"] / (ms * 1e-3), "unit": "queries/s",
+            "ms_per_step": ms, "recall_at_10_vs_exact": recall, "roofline": _roof("hbm", work, ms, peaks),
+            "parity_ok": ok, "parity": {"rows": n_chk, "rows_with_identical_sets": same_rows},
+            "config": {"nlist": cfg["nlist"], "nprobe": cfg["nprobe"], "k": cfg["k"], "max_list_len": int(lens.max())}}
+
+
 def run_secondary(args):
     """Single-GPU timings of the other configurations (k-means 1M x 128 / K=1024 / 20 Lloyd
     iterations; IVF-Flat search nlist=1024, nprobe=16; exact kNN with k=100)."""
     import flashlib_b200 as fl
     from flashlib_b200 import synthetic
     torch.cuda.set_device(0)
+    peaks = load_peaks()
     steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
     if args.workload == "knn_1m_k100":
         X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
-        Xd, Qd = X.cuda(), Q.cuda()
-        from flashlib_b200.knn import _mode_from, knn_f32
-        mode = _mode_from(args.mode)
-        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, 100, mode=args.mode), steps, warm)
-        _, _, info = knn_f32(Qd, Xd, 100, mode=mode)
-        path = {0: "exact fp32 CUDA-core scoring", 1: "tcgen05 bf16 candidates (pools of 256) + exact fp32 re-rank + verified fallback"}
-        line = {"workload": "knn_1m_k100", "metric": "exact_knn_queries_per_sec", "value": QUERIES_PER_GPU / (ms * 1e-3),
-                "unit": "queries/s", "ms_per_step": ms,
-                "config": {"k": 100, "path": path.get(int(info["mode"]), str(info["mode"])),
-                           "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+        line = secondary_knn_k100(X.cuda(), Q.cuda(), X, Q, steps, warm, args.mode, peaks)
     elif args.workload == "knn_self_1m":
         # the "graph build" regime of flash_knn's internal callers: every row of the 1M x 128
         # database is a query against the same database
@@ -250,27 +399,9 @@ def run_secondary(args):
                 "config": {"rows_on_this_gpu": rows, "dim": cfg["d"], "queries": nq, "k": cfg["k"], "mode": int(info["mode"]),
                            "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
     elif args.workload == "kmeans_1m":
-        cfg = synthetic.CONFIGS["kmeans_1m"]
-        X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
-        Xd = X.cuda()
-        init = Xd[:cfg["K"]].clone()
-        ms = _time_steps(lambda: fl.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init), steps, warm)
-        flop = 2.0 * cfg["n"] * cfg["K"] * cfg["d"] * cfg["iters"]
-        line = {"workload": "kmeans_1m", "metric": "kmeans_20_iterations_ms", "value": ms, "unit": "ms", "ms_per_step": ms,
-                "higher_is_better": False, "algorithmic_tflops": flop / (ms * 1e-3) / 1e12,
-                "config": {"n": cfg["n"], "d": cfg["d"], "K": cfg["K"], "iters": cfg["iters"], "init": "first K rows"}}
+        line = secondary_kmeans(steps, warm, peaks)
     else:
-        cfg = synthetic.CONFIGS["ivf_1m"]
-        X, Q = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"], nq=cfg["nq"], clamp=True)
-        Xd, Qd = X.cuda(), Q.cuda()
-        ivf = fl.IVFFlat(nlist=cfg["nlist"], nprobe=cfg["nprobe"], niter=10, seed=cfg["seed"]).fit(Xd)
-        ms = _time_steps(lambda: ivf.kneighbors(Qd, cfg["k"]), steps, warm)
-        _, bi = fl.flash_knn(Qd[:1000], Xd, cfg["k"])
-        _, ii = ivf.kneighbors(Qd[:1000], cfg["k"])
-        recall = float(np.mean([len(set(a.tolist()) & set(b.tolist())) / cfg["k"] for a, b in zip(ii.cpu().numpy(), bi.cpu().numpy())]))
-        line = {"workload": "ivf_1m", "metric": "ivf_flat_queries_per_sec", "value": cfg["nq"] / (ms * 1e-3), "unit": "queries/s",
-                "ms_per_step": ms, "recall_at_10_vs_exact": recall,
-                "config": {"nlist": cfg["nlist"], "nprobe": cfg["nprobe"], "k": cfg["k"], "max_list_len": ivf.index_.max_list_len}}
+        line = secondary_ivf(steps, warm, peaks)
     line.update({"n_gpus": 1, "steps": steps, "warmup": warm, "data": "synthetic"})
     print(json.dumps(line), flush=True)
 
@@ -283,6 +414,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the k-means / IVF-Flat / k=100 legs")
     ap.add_argument("--result", default="owner", choices=["owner", "replicated"],
                     help="N > 1: 'owner' = all-to-all, every rank merges and returns its own slice of the step's queries; "
                          "'replicated' = all-gather, every rank merges and returns all of them")
@@ -340,6 +472,9 @@ def main():
     q_dev = q_host.to(dev)
     resolved = lib.fl_knn_resolve_mode(nq, db.shape[0], DIM, K_NEIGHBOURS) if mode == _lib.FL_KNN_AUTO else mode
     plane = get_plane(db) if resolved == _lib.FL_KNN_BF16_RERANK else None   # index-build-time work
+    # the sharded index (a collective: global max norm, smallest shard) is index-build-time work too
+    from flashlib_b200.sharded import ShardedKnnIndex
+    index = ShardedKnnIndex(db, s, plane=plane) if world > 1 else None
     torch.cuda.synchronize()
 
     # Timing hygiene: when this rank's operand plane is not well above the 126 MB L2 it would stay
@@ -351,7 +486,8 @@ def main():
     def step_device():
         if flush is not None:
             flush.zero_()
-        return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane, result=args.result)
+        return sharded_knn(q_dev, db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane, result=args.result,
+                           index=index)
 
     def barrier():
         if world > 1:
@@ -426,7 +562,7 @@ def main():
             d_, i_ = flash_knn(q_slots[j], db, K_NEIGHBOURS, mode=args.mode)
         else:
             d_, i_ = sharded_knn(q_slots[j], db, K_NEIGHBOURS, row_offset=s, mode=args.mode, plane=plane,
-                                 result=args.result)
+                                 result=args.result, index=index)
         ev_used[j].record(main)
         ev_done[j].record(main)
         keep[j] = (d_, i_)
@@ -462,6 +598,100 @@ def main():
     e2e_s = float(t.item())
     e2e_value = nq * e2e_steps / e2e_s
 
+    # ---- parity of the last timed step's results, outside the timed region ---------------------
+    # Every rank checks a sample of the queries whose results it holds against the CPU oracle on the
+    # WHOLE database; the counts are summed over the ranks.  This is the check the real NCCL
+    # exchange gets at every N.
+    parity_line = None
+    if not args.profile_case:
+        from oracle import oracle_torch
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
+        out_d, out_i = out
+        n_chk = min(out_d.shape[0], max(16, 128 // world))
+        q_chk = Q[qs_:qs_ + n_chk]
+        got_d, got_i = out_d[:n_chk].cpu().numpy(), out_i[:n_chk].cpu().numpy()
+        if WORKLOAD == "knn_100m":
+            # the rows live on the devices only: every rank runs the oracle on its shard for the first
+            # queries of the batch, the per-shard lists are gathered and merged on the host
+            n_chk = 32
+            ld = torch.full((n_chk, K_NEIGHBOURS), float("inf"))
+            li = torch.full((n_chk, K_NEIGHBOURS), -1, dtype=torch.int64)
+            piece = 2_000_000                      # rows copied to the host at a time (0.8 GB)
+            for p0 in range(0, db.shape[0], piece):
+                pd, pi = oracle_torch.knn_chunked(Q[:n_chk], db[p0:p0 + piece].cpu(), K_NEIGHBOURS, chunk_size=65536)
+                cv, ci_ = torch.cat([ld, pd], 1), torch.cat([li, pi + (s + p0)], 1)
+                sel = cv.argsort(dim=1, stable=True)[:, :K_NEIGHBOURS]
+                ld, li = cv.gather(1, sel), ci_.gather(1, sel)
+            if world > 1:
+                gl = [None] * world
+                dist.all_gather_object(gl, (ld.numpy(), li.numpy()))
+            else:
+                gl = [(ld.numpy(), li.numpy())]
+            cd = np.concatenate([g_[0] for g_ in gl], 1)
+            ci = np.concatenate([g_[1] for g_ in gl], 1)
+            order = np.argsort(cd, axis=1, kind="stable")[:, :K_NEIGHBOURS]
+            ref_d, ref_i = np.take_along_axis(cd, order, 1), np.take_along_axis(ci, order, 1)
+            # ... and compared with the rows of the distributed result this rank holds
+            lo, hi = max(qs_, 0), min(qe_, n_chk)
+            rows_chk = max(0, hi - lo)
+            bad = knn_rows_agree(Q[lo:hi].numpy(), out_d[lo - qs_:hi - qs_].cpu().numpy(), out_i[lo - qs_:hi - qs_].cpu().numpy(),
+                                 ref_d[lo:hi], ref_i[lo:hi]) if rows_chk else 0
+            worst = 0.0
+        else:
+            from tests import parity as tparity
+            _, ref_i = oracle_torch.knn_chunked(q_chk, X, K_NEIGHBOURS, chunk_size=8192)
+            res = tparity.knn_parity(q_chk.numpy(), X.numpy(), got_d, got_i, ref_i.numpy())
+            rows_chk, bad, worst = n_chk, len(res["bad_rows"]) + res["unsorted_rows"], res["worst_rel_dist_err"]
+            if worst > tparity.REL_DIST:
+                bad = max(bad, 1)
+        t = torch.tensor([rows_chk, bad, worst], device=dev, dtype=torch.float64)
+        if world > 1:
+            tm = t.clone()
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+            t[2] = tm[2]
+        parity_line = {"rows": int(t[0].item()), "bad_rows": int(t[1].item()), "ok": int(t[1].item()) == 0 and int(t[0].item()) > 0,
+                       "worst_rel_dist_err": float(t[2].item()),
+                       "against": "oracle_torch.knn_chunked on the whole database, every rank a sample of the queries it holds"}
+
+    # ---- sustained: the same device-resident loop for seconds (what a serving loop gets) ---------
+    sustained_line = None
+    if world == 1 and not args.profile_case and WORKLOAD == "knn_1m":
+        per_chunk = 20
+        chunks = int(max(3.0 / max(ms_total * 1e-3 / args.steps * per_chunk, 1e-6), 5))
+        samp2 = ClockSampler(local_rank)
+        samp2.start()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(chunks + 1)]
+        evs[0].record()
+        for c in range(chunks):
+            for _ in range(per_chunk):
+                step_device()
+            evs[c + 1].record()
+        torch.cuda.synchronize()
+        check_pending()
+        clk2 = samp2.stop()
+        qps = [nq * per_chunk / (evs[c].elapsed_time(evs[c + 1]) * 1e-3) for c in range(chunks)]
+        tail = qps[len(qps) // 2:]                  # the second half: clocks have settled under the power cap
+        peaks_ = load_peaks()
+        med = statistics.median(tail)
+        tf = 2.0 * DB_ROWS * DIM * med / 1e12
+        sustained_line = {"value": med, "unit": UNIT, "seconds": sum(evs[c].elapsed_time(evs[c + 1]) for c in range(chunks)) * 1e-3,
+                          "steps": chunks * per_chunk, "first_chunk_value": qps[0],
+                          "tensor_tflops_algorithmic": tf, "peak": peaks_.get("bf16_tflops_sustained"),
+                          "frac": tf / peaks_["bf16_tflops_sustained"] if peaks_.get("bf16_tflops_sustained") else None,
+                          "clocks": clk2}
+
+    # ---- the other configurations, on the driver's clock (N = 1 only) ------------------------------
+    secondary = None
+    if world == 1 and not args.profile_case and WORKLOAD == "knn_1m" and not args.no_secondary:
+        peaks_ = load_peaks()
+        secondary = {}
+        secondary["knn_1m_k100"] = secondary_knn_k100(db, q_dev, X, Q, 5, 2, args.mode, peaks_)
+        del out
+        secondary["kmeans_1m"] = secondary_kmeans(3, 1, peaks_)
+        torch.cuda.empty_cache()
+        secondary["ivf_1m"] = secondary_ivf(5, 2, peaks_)
+
     if rank == 0:
         peaks = load_peaks()
         rows_local = e - s
@@ -493,18 +723,7 @@ def main():
             "warmup": n_warm, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": SCALING, "vs_baseline": None, "dtype": "bf16" if resolved == _lib.FL_KNN_BF16_RERANK else "f32",
             "data": "synthetic",
-            "config": {"workload": workload_name(world), "db_rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS,
-                       "queries_per_step": nq, "sharding": (f"database rows over {world} ranks; every rank scores all of the step's queries; "
-                                    + ("candidates exchanged all-to-all, every rank merges and returns its own "
-                                       f"{qe_ - qs_} queries" if args.result == "owner" else
-                                       "candidates all-gathered, every rank merges and returns all queries"))
-                       if world > 1 else "single GPU",
-                       "mode": {_lib.FL_KNN_EXACT_SIMT: "exact fp32 CUDA-core scoring + exact re-rank",
-                                _lib.FL_KNN_BF16_RERANK: "tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback"}[resolved],
-                       "l2": ("a 256 MB buffer is overwritten before every step (inside the timed region): this rank's "
-                              f"operand plane is {plane_bytes >> 20} MB" if flush is not None else
-                              f"no flush needed: each step streams this rank's operand plane ({plane_bytes >> 20} MB), "
-                              "larger than the 126 MB L2")},
+            "config": config_dict(world, args.result, resolved == _lib.FL_KNN_BF16_RERANK, nq),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(q_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_d_host[0].numel() * 4 + out_i_host[0].numel() * 4),
                     "note": "every step: queries from pinned host memory, results to pinned host memory, copies on "
@@ -512,6 +731,9 @@ def main():
             "gpu_launches": int(launches),
             "roofline": roofline,
             "cpu_baseline": cpu_base,
+            "parity": parity_line,
+            "sustained": sustained_line,
+            "secondary": secondary,
             "clocks": clocks,
             "tensor_tflops_algorithmic": 2.0 * nq * DB_ROWS * DIM * args.steps / (ms_total * 1e-3) / 1e12 / world,
         }

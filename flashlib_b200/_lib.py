@@ -44,11 +44,24 @@ SIGNATURES = {
     "fl_knn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int, c_int]),
     "fl_knn_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_knn_seed_floats": (c_int64, [c_int64]),
+    "fl_knn_seed_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_knn_plane_maxnorm_offset": (c_int64, [c_int64, c_int]),
+    "fl_knn_seeded_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
+                                  c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                  c_void_p, c_void_p]),
+    "fl_debug_tc_experiment": (c_int, [c_int, ctypes.c_uint]),
     "fl_debug_tc_prof_read": (c_int, [c_void_p, c_int]),
     "fl_knn_resolve_mode": (c_int, [c_int64, c_int64, c_int, c_int]),
     "fl_debug_knn_tc_scores": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p, c_int64,
                                        c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_topk_merge_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fl_knn_pack_ints": (c_int64, [c_int64, c_int, c_int, c_int]),
+    "fl_knn_pack_f32": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fl_knn_merge_packed_f32": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "fl_f32_to_bf16_down": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "fl_bf16_to_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "fl_gather_l2sq_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "fl_kmeans_assign_workspace_bytes": (c_int64, [c_int64, c_int, c_int]),
@@ -69,6 +82,9 @@ SIGNATURES = {
     "fl_ivf_fine_scan_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int,
                                      c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "fl_ivf_build_workspace_bytes": (c_int64, [c_int64, c_int]),
+    "fl_ivf_build_csr_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_int64, c_void_p]),
     "fl_ivf_plane_bytes": (c_int64, [c_int64, c_int, c_int]),
     "fl_ivf_prepare_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "fl_ivf_fine_scan_tc_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int64, c_int, c_int]),

@@ -133,9 +133,156 @@ int launch_ivf_group(const int32_t* probed, int64_t npairs, int nlist, int bq, c
     return FL_OK;
 }
 
+// ---- index build: cell-contiguous (CSR) layout from per-row list labels ------------------
+// The rows are cut into units of `unit_rows` consecutive rows.  cnt[u][l] counts the rows of unit
+// u with label l; a scan down the units turns it into the rank, within list l, of the unit's first
+// such row.  One warp then walks its unit in row order and gives every row its position
+// list_offsets[l] + rank -- rows of one list keep their original order (a stable partition, the
+// order of a stable argsort by label) -- and a last kernel moves the rows.
+__global__ void ivf_build_count_kernel(const int32_t* __restrict__ labels, int64_t m, int nlist, int64_t unit_rows,
+                                       int* __restrict__ cnt) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m) return;
+    const int l = labels[i];
+    if (l >= 0 && l < nlist) atomicAdd(cnt + (i / unit_rows) * nlist + l, 1);
+}
+
+// Thread per list: exclusive scan of cnt[.][l] down the units (in place), total[l] = list length.
+__global__ void ivf_build_colscan_kernel(int* __restrict__ cnt, int64_t units, int nlist, int* __restrict__ total) {
+    const int l = blockIdx.x * blockDim.x + threadIdx.x;
+    if (l >= nlist) return;
+    int run = 0;
+    for (int64_t u = 0; u < units; ++u) {
+        const int c = cnt[u * nlist + l];
+        cnt[u * nlist + l] = run;
+        run += c;
+    }
+    total[l] = run;
+}
+
+// Single block: list_offsets = exclusive scan of the list lengths (int64), and the longest list.
+__global__ void __launch_bounds__(1024) ivf_build_offsets_kernel(const int* __restrict__ total, int nlist,
+                                                                 int64_t* __restrict__ list_offsets,
+                                                                 int32_t* __restrict__ max_len) {
+    __shared__ long long s_v[1024];
+    __shared__ long long carry;
+    __shared__ int s_max;
+    const int t = threadIdx.x;
+    if (t == 0) { carry = 0; s_max = 0; }
+    __syncthreads();
+    for (int base = 0; base < nlist; base += 1024) {
+        const int c = base + t;
+        const int n = c < nlist ? total[c] : 0;
+        atomicMax(&s_max, n);
+        s_v[t] = n;
+        __syncthreads();
+        for (int o = 1; o < 1024; o <<= 1) {
+            const long long a = t >= o ? s_v[t - o] : 0;
+            __syncthreads();
+            s_v[t] += a;
+            __syncthreads();
+        }
+        if (c < nlist) list_offsets[c] = carry + s_v[t] - n;
+        __syncthreads();
+        if (t == 1023) carry += s_v[t];
+        __syncthreads();
+    }
+    if (t == 0) { list_offsets[nlist] = carry; if (max_len) *max_len = s_max; }
+}
+
+// One warp per unit, 32 rows per step in row order: position of every row in the list-sorted layout.
+// Lanes with the same label are ranked by lane (match_any), the unit's running count of each label
+// lives in its row of `cnt` (only this warp touches it).  Rows with a label outside [0, nlist) get -1.
+__global__ void ivf_build_rank_kernel(const int32_t* __restrict__ labels, int64_t m, int nlist, int64_t unit_rows,
+                                      int* __restrict__ cnt, const int64_t* __restrict__ list_offsets,
+                                      int64_t* __restrict__ pos) {
+    const int lane = threadIdx.x & 31;
+    const int64_t u = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t r0 = u * unit_rows;
+    if (r0 >= m) return;
+    const int64_t r1 = min(m, r0 + unit_rows);
+    int* mine = cnt + u * nlist;
+    for (int64_t base = r0; base < r1; base += 32) {
+        const int64_t r = base + lane;
+        int l = r < r1 ? labels[r] : -1;
+        if (l >= nlist) l = -1;
+        const unsigned same = __match_any_sync(FULL_MASK, l);
+        const int before = __popc(same & ((1u << lane) - 1u));
+        int start = 0;
+        if (l >= 0) start = mine[l];
+        __syncwarp();
+        if (l >= 0 && before == 0) mine[l] = start + __popc(same);     // the first lane of each label advances it
+        __syncwarp();
+        if (r < r1) pos[r] = l >= 0 ? list_offsets[l] + start + before : -1;
+    }
+}
+
+// One warp per row: the row goes to its position, ids[position] = the row's original index.
+__global__ void ivf_build_move_kernel(const float* __restrict__ x, int64_t m, int64_t ldx, int d,
+                                      const int64_t* __restrict__ pos, float* __restrict__ data, int64_t* __restrict__ ids) {
+    const int lane = threadIdx.x & 31;
+    const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= m) return;
+    const int64_t p = pos[r];
+    if (p < 0) return;
+    const float* src = x + r * ldx;
+    float* dst = data + p * d;
+    for (int c = lane; c < d; c += 32) dst[c] = __ldg(src + c);
+    if (lane == 0) ids[p] = r;
+}
+
+struct IvfBuildWs { int64_t unit_rows, units, off_cnt, off_total, off_pos, bytes; };
+static IvfBuildWs ivf_build_plan(int64_t m, int nlist) {
+    IvfBuildWs w{};
+    // units of at least 2048 rows, few enough that the count matrix stays below 2^24 entries
+    int64_t ur = 2048;
+    const int64_t need = ceil_div(m * (int64_t)nlist, (int64_t)1 << 24);
+    if (need > ur) ur = round_up(need, 32);
+    w.unit_rows = ur;
+    w.units = ceil_div(m, ur);
+    int64_t cur = 0;
+    w.off_cnt = take(cur, w.units * nlist * 4);
+    w.off_total = take(cur, (int64_t)nlist * 4);
+    w.off_pos = take(cur, m * 8);
+    w.bytes = cur;
+    return w;
+}
+
 }  // namespace fl
 
 using namespace fl;
+
+extern "C" int64_t fl_ivf_build_workspace_bytes(int64_t m, int nlist) {
+    if (m < 1 || nlist < 1) return 0;
+    return ivf_build_plan(m, nlist).bytes;
+}
+
+extern "C" int fl_ivf_build_csr_f32(const float* x, int64_t m, int64_t ldx, int d, const int32_t* labels, int nlist,
+                                    float* data, int64_t* ids, int64_t* list_offsets, int32_t* max_list_len,
+                                    void* ws, int64_t ws_bytes, void* stream) {
+    FL_CHECK_ARG(m >= 1 && d >= 1 && nlist >= 1 && ldx >= d, "fl_ivf_build_csr_f32: bad shape");
+    FL_CHECK_ARG(x && labels && data && ids && list_offsets && ws, "fl_ivf_build_csr_f32: null pointer");
+    FL_CHECK_ARG(m < (1ll << 31), "fl_ivf_build_csr_f32: more than 2^31 rows");
+    const IvfBuildWs w = ivf_build_plan(m, nlist);
+    if (ws_bytes < w.bytes) { set_error("fl_ivf_build_csr_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes); return FL_EWORKSPACE; }
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(ws);
+    int* cnt = reinterpret_cast<int*>(base + w.off_cnt);
+    int* total = reinterpret_cast<int*>(base + w.off_total);
+    int64_t* pos = reinterpret_cast<int64_t*>(base + w.off_pos);
+    FL_CHECK_CUDA(cudaMemsetAsync(cnt, 0, (size_t)(w.units * nlist) * 4, st));
+    ivf_build_count_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, st>>>(labels, m, nlist, w.unit_rows, cnt);
+    FL_CHECK_LAUNCH();
+    ivf_build_colscan_kernel<<<(unsigned)ceil_div(nlist, 128), 128, 0, st>>>(cnt, w.units, nlist, total);
+    FL_CHECK_LAUNCH();
+    ivf_build_offsets_kernel<<<1, 1024, 0, st>>>(total, nlist, list_offsets, max_list_len);
+    FL_CHECK_LAUNCH();
+    ivf_build_rank_kernel<<<(unsigned)ceil_div(w.units, 4), 128, 0, st>>>(labels, m, nlist, w.unit_rows, cnt, list_offsets, pos);
+    FL_CHECK_LAUNCH();
+    ivf_build_move_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(x, m, ldx, d, pos, data, ids);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
 
 extern "C" int64_t fl_ivf_fine_scan_workspace_bytes(int64_t nq, int nprobe, int nlist, int64_t m, int d,
                                                     int k) {

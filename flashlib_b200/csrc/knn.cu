@@ -81,7 +81,7 @@ struct KnnWs {
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
     int64_t nq_pad; int d_pad; int fb_cap; int fb_bq, fb_blocks;
-    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_seed_cls, off_tau, off_cnt, off_fblist,
+    int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_seed_cls, off_tau, off_cert, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
 };
 
@@ -102,8 +102,12 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.d_pad = (int)round_up(d, 64);
         const int64_t m_pad = round_up(m, 256);
         tc_split_plan(w.nq_pad, m_pad, k, &w.nsplit, &w.rows_per_split);
-        w.fb_cap = (int)(nq < 4096 ? nq : (nq / 4 > 4096 ? nq / 4 : 4096));
-        // fallback splits: bounded partial storage (<= 128 MB), at least 4 tiles per split
+        // Every query may fail its proof (near-duplicate or offset data): the list holds them all, so
+        // no row is ever returned unproven.  The exact pass sizes its partial storage by blocks, not
+        // by rows x ranges (simt_dyn_split), so the cost of the full list is nq pools of K1f entries.
+        w.fb_cap = (int)nq;
+        // range split of a non-dynamic fallback pass (kept for the plan's completeness; the
+        // dynamic split below is what runs): at least 4 tiles per split
         int64_t s = (int64_t)(128ll << 20) / ((int64_t)w.fb_cap * w.K1f * 8);
         const int64_t tiles = ceil_div(m, 128);
         if (s > tiles / 4) s = tiles / 4;
@@ -122,6 +126,7 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         w.off_part_cnt = take(cur, w.nq_pad * w.nsplit * tc_taus_per_range() * 4);
         w.off_seed_cls = take(cur, w.nq_pad * 32 * 4);
         w.off_tau = take(cur, w.nq_pad * 4);
+        w.off_cert = take(cur, w.nq_pad * 4);
         w.off_cnt = take(cur, 1024);
         w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
         // the fallback scan spreads its blocks over the live slots (simt_dyn_split): at most
@@ -229,101 +234,64 @@ extern "C" int64_t fl_knn_workspace_bytes(int64_t nq, int64_t m, int d, int k, i
     return knn_ws_plan(nq, m, d, k, mode).bytes;
 }
 
-extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
-                          int64_t ldb, int d, int k, int mode, const void* plane, int64_t row_offset,
-                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes,
-                          int32_t* status, void* stream) {
-    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1, "fl_knn_f32: bad shape nq=%lld m=%lld d=%d", (long long)nq,
-                 (long long)m, d);
-    FL_CHECK_ARG(k >= 1 && k <= m, "fl_knn_f32: k must be in [1, m=%lld] (got %d)", (long long)m, k);
-    FL_CHECK_ARG(ldq >= d && ldb >= d, "fl_knn_f32: leading dimensions smaller than d");
-    FL_CHECK_ARG(m < (1ll << 31) && nq < (1ll << 31), "fl_knn_f32: more than 2^31 rows");
-    FL_CHECK_ARG(row_offset >= 0 && row_offset + m <= (1ll << 31),
-                 "fl_knn_f32: row_offset + m exceeds int32 index range");
+// Argument checks shared by the kNN entry points; resolves FL_KNN_AUTO.
+static int knn_check_args(const char* who, const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
+                          int64_t ldb, int d, int k, int* mode, const void* plane, int64_t row_offset,
+                          const float* out_dist, const int32_t* out_idx, const void* ws) {
+    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1, "%s: bad shape nq=%lld m=%lld d=%d", who, (long long)nq, (long long)m, d);
+    FL_CHECK_ARG(k >= 1 && k <= m, "%s: k must be in [1, m=%lld] (got %d)", who, (long long)m, k);
+    FL_CHECK_ARG(ldq >= d && ldb >= d, "%s: leading dimensions smaller than d", who);
+    FL_CHECK_ARG(m < (1ll << 31) && nq < (1ll << 31), "%s: more than 2^31 rows", who);
+    FL_CHECK_ARG(row_offset >= 0 && row_offset + m <= (1ll << 31), "%s: row_offset + m exceeds int32 index range", who);
     if (k > 512) {
-        set_error("fl_knn_f32: k=%d > 512 is not supported", k);
+        set_error("%s: k=%d > 512 is not supported", who, k);
         return FL_EUNSUPPORTED;
     }
     if (nq == 0) return FL_OK;
-    FL_CHECK_ARG(q && db && out_dist && out_idx && ws, "fl_knn_f32: null pointer");
-    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0, "fl_knn_f32: workspace must be 256-byte aligned");
-    cudaStream_t st = (cudaStream_t)stream;
-
-    if (mode == FL_KNN_BF16_RERANK && tc_knn_supported(nq, m, d, k) != FL_OK) {
-        set_error("fl_knn_f32: shape (nq=%lld m=%lld d=%d k=%d) outside the tensor-core kernel's range",
+    FL_CHECK_ARG(q && db && out_dist && out_idx && ws, "%s: null pointer", who);
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0, "%s: workspace must be 256-byte aligned", who);
+    if (*mode == FL_KNN_BF16_RERANK && tc_knn_supported(nq, m, d, k) != FL_OK) {
+        set_error("%s: shape (nq=%lld m=%lld d=%d k=%d) outside the tensor-core kernel's range", who,
                   (long long)nq, (long long)m, d, k);
         return FL_EUNSUPPORTED;
     }
-    mode = resolve_mode(nq, m, d, k, mode);
-    if (mode == FL_KNN_BF16_RERANK && plane == nullptr) {
-        FL_CHECK_ARG(false, "fl_knn_f32: the tensor-core mode needs the plane built by fl_knn_prepare_db_f32");
+    *mode = resolve_mode(nq, m, d, k, *mode);
+    if (*mode == FL_KNN_BF16_RERANK) {
+        FL_CHECK_ARG(plane != nullptr, "%s: the tensor-core mode needs the plane built by fl_knn_prepare_db_f32", who);
+        FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0, "%s: plane must be 256-byte aligned", who);
     }
-    FL_CHECK_ARG(mode == FL_KNN_EXACT_SIMT || mode == FL_KNN_BF16_RERANK, "fl_knn_f32: unknown mode %d", mode);
+    FL_CHECK_ARG(*mode == FL_KNN_EXACT_SIMT || *mode == FL_KNN_BF16_RERANK, "%s: unknown mode %d", who, *mode);
+    return FL_OK;
+}
 
-    const KnnWs w = knn_ws_plan(nq, m, d, k, mode);
+// The tensor-core path in three phases, so that a row-sharded caller can exchange the seeding
+// results between the first and the second:
+//   TC_PREP    status / counters cleared, thresholds -inf, bf16 query plane built in the workspace
+//   TC_SEED    class maxima of the seeding sample into `seed_cls`
+//   TC_SCORE   thresholds from `seed_cls` (lowered by the cross-shard margin when `gmaxnorm` is
+//              given), scoring pass, finalisation, exact pass for what could not be proven
+enum { TC_PREP = 1, TC_SEED = 2, TC_SCORE = 4 };
+
+static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb,
+                         int d, int k, const void* plane, int64_t row_offset, float* seed_cls, const float* gmaxnorm,
+                         float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status,
+                         cudaStream_t st) {
+    const KnnWs w = knn_ws_plan(nq, m, d, k, FL_KNN_BF16_RERANK);
     if (ws_bytes < w.bytes) {
-        set_error("fl_knn_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
+        set_error("fl_knn: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
         return FL_EWORKSPACE;
     }
     char* base = static_cast<char*>(ws);
     const int vecq = (ldq % 4 == 0) && aligned16(q);
     const int vecd = (ldb % 4 == 0) && aligned16(db);
     const int vec = vecq && vecd && (d % 4 == 0);
-    if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
-
-    if (mode == FL_KNN_EXACT_SIMT) {
-        FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
-        const float* hnorm;
-        if (plane) {
-            const PlaneLayout L = plane_layout(m, d);
-            hnorm = reinterpret_cast<const float*>(static_cast<const char*>(plane) + L.off_hnorm);
-        } else {
-            float* h = reinterpret_cast<float*>(base + w.off_hnorm);
-            halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h);
-            FL_CHECK_LAUNCH();
-            hnorm = h;
-        }
-        SimtKnnParams sp{};
-        sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
-        sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
-        sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k);
-        sp.nsplit = w.nsplit; sp.rows_per_split = w.rows_per_split;
-        sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
-        sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
-        sp.vecq = vecq; sp.vecd = vecd;
-        profile_begin(st);
-        int rc = launch_knn_simt(sp, nq, st);
-        profile_end(st);
-        if (rc != FL_OK) return rc;
-
-        FinalizeParams fp{};
-        fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
-        fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
-        fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
-        fp.k = k; fp.rerank = (k + 8 < w.K1) ? k + 8 : w.K1; fp.row_offset = row_offset;
-        fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 0;
-        rc = launch_knn_finalize(fp, nq, st);
-        if (rc != FL_OK) return rc;
-        if (status) {
-            fallback_fixup_kernel<<<1, 1, 0, st>>>(reinterpret_cast<int*>(base + w.off_cnt), 1 << 30,
-                                                   status, w.K1);
-            FL_CHECK_LAUNCH();
-        }
-        return FL_OK;
-    }
-
-    // ---- tensor-core candidates + exact re-rank + verified fallback ---------------------
     const PlaneLayout L = plane_layout(m, d);
     const char* pl = static_cast<const char*>(plane);
-    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0, "fl_knn_f32: plane must be 256-byte aligned");
     int* fb_count = reinterpret_cast<int*>(base + w.off_cnt);
     int* fb_list = reinterpret_cast<int*>(base + w.off_fblist);
     float* tau = reinterpret_cast<float*>(base + w.off_tau);
-    FL_CHECK_CUDA(cudaMemsetAsync(fb_count, 0, 1024, st));
-    fill_f32_kernel<<<(unsigned)ceil_div(w.nq_pad, 256), 256, 0, st>>>(tau, w.nq_pad, -INFINITY);
-    FL_CHECK_LAUNCH();
-    int rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st);
-    if (rc != FL_OK) return rc;
+    float* cert = reinterpret_cast<float*>(base + w.off_cert);
+    if (seed_cls == nullptr) seed_cls = reinterpret_cast<float*>(base + w.off_seed_cls);
 
     TcKnnParams tp{};
     tp.qplane = base + w.off_qplane; tp.nq = nq; tp.nq_pad = w.nq_pad;
@@ -336,10 +304,37 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
     tp.deep_pools = w.deep;
-    tp.seed_cls = reinterpret_cast<float*>(base + w.off_seed_cls);
+    tp.seed_cls = seed_cls;
     tp.k = k;
-    profile_begin(st);
-    rc = launch_knn_tc(tp, st);
+    int rc;
+
+    if (phases & TC_SCORE) FL_CHECK_CUDA(cudaMemsetAsync(fb_count, 0, 1024, st));
+    if (phases & TC_PREP) {
+        if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
+        rc = launch_fill_f32(tau, w.nq_pad, -INFINITY, st);
+        if (rc != FL_OK) return rc;
+        rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st);
+        if (rc != FL_OK) return rc;
+    }
+    if (phases & TC_SEED) {
+        if (phases & TC_SCORE) profile_begin(st);
+        rc = launch_knn_tc_seed(tp, st);
+        if (rc != FL_OK) return rc;
+    }
+    if (!(phases & TC_SCORE)) return FL_OK;
+
+    if (!(phases & TC_PREP)) {
+        rc = launch_fill_f32(tau, w.nq_pad, -INFINITY, st);
+        if (rc != FL_OK) return rc;
+    }
+    if (!(phases & TC_SEED)) profile_begin(st);
+    TcSeedMargin mg{};
+    if (gmaxnorm != nullptr) {
+        mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.maxnorm = gmaxnorm; mg.eps_rel = 0.004f; mg.cert_out = cert;
+    }
+    rc = launch_knn_tc_seed_select(tp, mg, st);
+    if (rc != FL_OK) return rc;
+    rc = launch_knn_tc_scoring(tp, st);
     profile_end(st);
     if (rc != FL_OK) return rc;
 
@@ -353,7 +348,9 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     fp.part_tau = tp.part_tau; fp.ntau = w.nsplit * tc_taus_per_range();
     fp.out_dist = out_dist; fp.out_idx = out_idx;
     fp.verify = 1; fp.eps_rel = 0.004f;  // 2^-8 operand rounding of both bf16 factors, rounded up
-    fp.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
+    // a sharded caller's error bound must hold for rows of every shard: the largest norm of all
+    fp.maxnorm = gmaxnorm != nullptr ? gmaxnorm : reinterpret_cast<const float*>(pl + L.off_meta);
+    fp.cert_tau = gmaxnorm != nullptr ? cert : nullptr;
     fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = w.fb_cap;
     fp.part_cnt = tp.part_cnt;
     rc = tc_knn_big(k) ? launch_knn_finalize_big(fp, nq, st) : launch_knn_finalize(fp, nq, st);
@@ -378,9 +375,113 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     ff.qlist = fb_list; ff.count_dev = fb_count; ff.count = 0;
     ff.part_sc = sp.part_sc; ff.part_id = sp.part_id; ff.nsplit = w.nsplit_fb; ff.K1 = w.K1f;
     ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0; ff.part_tau = nullptr; ff.ntau = 0;
+    ff.cert_tau = nullptr;
     ff.dyn_blocks = w.fb_blocks; ff.dyn_bq = w.fb_bq;
-    rc = launch_knn_finalize(ff, w.fb_cap, st);
-    return rc;
+    return launch_knn_finalize(ff, w.fb_cap, st);
+}
+
+extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
+                          int64_t ldb, int d, int k, int mode, const void* plane, int64_t row_offset,
+                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes,
+                          int32_t* status, void* stream) {
+    int rc = knn_check_args("fl_knn_f32", q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
+    if (rc != FL_OK || nq == 0) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (mode == FL_KNN_BF16_RERANK)
+        return knn_tc_phases(TC_PREP | TC_SEED | TC_SCORE, q, nq, ldq, db, m, ldb, d, k, plane, row_offset, nullptr,
+                             nullptr, out_dist, out_idx, ws, ws_bytes, status, st);
+
+    const KnnWs w = knn_ws_plan(nq, m, d, k, mode);
+    if (ws_bytes < w.bytes) {
+        set_error("fl_knn_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
+        return FL_EWORKSPACE;
+    }
+    char* base = static_cast<char*>(ws);
+    const int vecq = (ldq % 4 == 0) && aligned16(q);
+    const int vecd = (ldb % 4 == 0) && aligned16(db);
+    const int vec = vecq && vecd && (d % 4 == 0);
+    if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
+    FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
+    const float* hnorm;
+    if (plane) {
+        const PlaneLayout L = plane_layout(m, d);
+        hnorm = reinterpret_cast<const float*>(static_cast<const char*>(plane) + L.off_hnorm);
+    } else {
+        float* h = reinterpret_cast<float*>(base + w.off_hnorm);
+        halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h);
+        FL_CHECK_LAUNCH();
+        hnorm = h;
+    }
+    SimtKnnParams sp{};
+    sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
+    sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
+    sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k);
+    sp.nsplit = w.nsplit; sp.rows_per_split = w.rows_per_split;
+    sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    sp.vecq = vecq; sp.vecd = vecd;
+    profile_begin(st);
+    rc = launch_knn_simt(sp, nq, st);
+    profile_end(st);
+    if (rc != FL_OK) return rc;
+
+    FinalizeParams fp{};
+    fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
+    fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
+    fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
+    fp.k = k; fp.rerank = (k + 8 < w.K1) ? k + 8 : w.K1; fp.row_offset = row_offset;
+    fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 0;
+    rc = launch_knn_finalize(fp, nq, st);
+    if (rc != FL_OK) return rc;
+    if (status) {
+        fallback_fixup_kernel<<<1, 1, 0, st>>>(reinterpret_cast<int*>(base + w.off_cnt), 1 << 30,
+                                               status, w.K1);
+        FL_CHECK_LAUNCH();
+    }
+    return FL_OK;
+}
+
+extern "C" int64_t fl_knn_seed_floats(int64_t nq) {
+    if (nq < 1) return 0;
+    return tc_query_rows_padded(nq) * 32;
+}
+
+extern "C" int fl_knn_seed_f32(const float* q, int64_t nq, int64_t ldq, int d, int k, const void* plane, int64_t m,
+                               float* seed_cls, void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
+    FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1 && k >= 1 && ldq >= d, "fl_knn_seed_f32: bad shape");
+    if (nq == 0) return FL_OK;
+    FL_CHECK_ARG(q && plane && seed_cls && ws, "fl_knn_seed_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(ws) & 255) == 0 && (reinterpret_cast<uintptr_t>(plane) & 255) == 0 &&
+                 (reinterpret_cast<uintptr_t>(seed_cls) & 15) == 0, "fl_knn_seed_f32: misaligned buffer");
+    // a shard with fewer than k rows still takes part (its maxima count for the other shards)
+    if (tc_knn_supported(nq, m, d, k < 112 ? k : 112) != FL_OK) {
+        set_error("fl_knn_seed_f32: shape (nq=%lld m=%lld d=%d) outside the tensor-core kernel's range", (long long)nq, (long long)m, d);
+        return FL_EUNSUPPORTED;
+    }
+    return knn_tc_phases(TC_PREP | TC_SEED, q, nq, ldq, nullptr, m, d, d, k, plane, 0, seed_cls, nullptr, nullptr, nullptr,
+                         ws, ws_bytes, status, (cudaStream_t)stream);
+}
+
+extern "C" int fl_knn_seeded_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb,
+                                 int d, int k, const void* plane, int64_t row_offset, const float* seed_cls,
+                                 const float* global_maxnorm, float* out_dist, int32_t* out_idx, void* ws,
+                                 int64_t ws_bytes, int32_t* status, void* stream) {
+    int mode = FL_KNN_BF16_RERANK;
+    int rc = knn_check_args("fl_knn_seeded_f32", q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
+    if (rc != FL_OK || nq == 0) return rc;
+    FL_CHECK_ARG(seed_cls != nullptr && global_maxnorm != nullptr, "fl_knn_seeded_f32: null pointer");
+    return knn_tc_phases(TC_SCORE, q, nq, ldq, db, m, ldb, d, k, plane, row_offset, const_cast<float*>(seed_cls),
+                         global_maxnorm, out_dist, out_idx, ws, ws_bytes, status, (cudaStream_t)stream);
+}
+
+extern "C" int64_t fl_knn_plane_maxnorm_offset(int64_t m, int d) {
+    if (m < 1 || d < 1) return -1;
+    return plane_layout(m, d).off_meta;
+}
+
+extern "C" int fl_debug_tc_experiment(int flags, unsigned wait_us) {
+    tc_debug_set(flags, wait_us);
+    return FL_OK;
 }
 
 extern "C" int fl_topk_merge_f32(const float* cand_dist, const int32_t* cand_idx, int64_t nq, int ncand,

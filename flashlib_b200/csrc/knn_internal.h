@@ -78,6 +78,10 @@ struct FinalizeParams {
     // ids are rows of a padded operand plane that id_map turns into database rows (< 0: padding).
     const int* pool_row; const int* id_map; int64_t id_bound;
     const int* part_cnt;     // large-k finalisation: entries per published pool ([slot][ntau])
+    // Optional f32 [queries] (row-sharded databases, k <= 16): a slot is also accepted when every row
+    // that was not re-scored scored at most cert_tau[query] -- such rows lie at least as far from the
+    // query as k rows known to exist somewhere in the database, so this shard's list may be short
+    const float* cert_tau;
     int* fb_count; int* fb_list; int fb_cap;
 };
 // Finalisation of the large-k tensor-core pools (one block per query).
@@ -122,6 +126,21 @@ int tc_deep_partial_len();
 int tc_taus_per_range();
 // 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
 int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
+// Margin applied by the threshold selection when the class maxima cover more than this shard's rows
+// (q == nullptr: none): the threshold is lowered by 2 eps_rel ||q|| *maxnorm + slack and copied to
+// cert_out (f32 [nq_pad], may be null).
+struct TcSeedMargin {
+    const float* q; int64_t ldq; int d; int64_t nq;
+    const float* maxnorm; float eps_rel;
+    float* cert_out;
+};
+// Seeding pass alone (class maxima into p.seed_cls, -inf when the database is too small to sample),
+// threshold selection alone (p.seed_cls -> p.tau), and the main scoring launch alone.
+int launch_knn_tc_seed(const TcKnnParams& p, cudaStream_t st);
+int launch_knn_tc_seed_select(const TcKnnParams& p, const TcSeedMargin& mg, cudaStream_t st);
+int launch_knn_tc_scoring(const TcKnnParams& p, cudaStream_t st);
+// Experiment flags of the scoring kernel and the limit of its barrier waits (0: default).
+void tc_debug_set(int flags, unsigned wait_us);
 // Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].
 int tc_prof_read(unsigned long long* host_out, int words);
 int launch_knn_tc_debug(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st);

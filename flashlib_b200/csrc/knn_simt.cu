@@ -483,6 +483,7 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
         // distance is at least qsq - 2 (bound + eps).
         bool proven = true;
         if (p.verify && bound > neg_inf()) proven = dk < qsq - 2.f * (bound + eps) - slack;
+        if (!proven && p.cert_tau != nullptr) proven = bound <= __ldg(p.cert_tau + qi);
         if (!proven && attempt == 0) continue;
 #pragma unroll
         for (int r = 0; r < NPL1; ++r) {

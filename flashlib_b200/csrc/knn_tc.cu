@@ -48,7 +48,7 @@ constexpr int TC_B_AUG = TC_BN * 32;      // bytes of a database tile's 16 norm 
 constexpr int TC_B_STAGE = TC_B_CHUNK + TC_B_AUG;   // ring slot: a K-chunk, plus the norm
                                                     // columns when it is the tile's last chunk
 constexpr int TC_MAX_STAGES = 6;
-constexpr uint64_t TC_WAIT_NS = 2000000000ull;   // 2 s per wait
+constexpr uint64_t TC_WAIT_DEFAULT_NS = 2000000000ull;   // 2 s per wait unless the launch says otherwise
 
 struct TcSmemPlan {
     int nkc, nstage;
@@ -99,10 +99,16 @@ struct TcKernelParams {
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
+    uint64_t wait_ns;        // limit of the MMA lane's barrier waits; a wait that runs out aborts the CTA
+                             // (FL_ETIMEOUT).  The producer and the epilogue warps, which can only starve
+                             // after the MMA lane has, wait twice as long, so the status names the wait
+                             // nearest to the cause.
     int tile_stride;         // database tile actually read for loop index t is t * tile_stride (1 outside seeding)
     int dbg_flags;           // timing experiments (results invalid): 1 skip pass 2, 2 skip the
                              // reductions of pass 1, 4 skip the tensor-memory loads too, 8 skip the
-                             // norm-column MMA step, 16 issue no MMA at all (operand streaming only)
+                             // norm-column MMA step, 16 issue no MMA at all (operand streaming only);
+                             // 32 the producer leaves out its fourth operand load, so the MMA lane's
+                             // wait for it runs out (host-visible test of the bounded-wait exit)
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
     int64_t dbg_ld;
 };
@@ -181,6 +187,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
+    // a timing experiment leaves work out: whoever reads the status words learns that the
+    // neighbours of this launch are not to be used
+    if (DBG && (p.dbg_flags & 31) && blockIdx.x == 0 && tid == 0 && p.status != nullptr) {
+        if (atomicCAS(p.status + FL_STATUS_ERROR, 0, FL_EUNSUPPORTED) == 0) p.status[FL_STATUS_WHERE] = 0xDB600 | p.dbg_flags;
+    }
     const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
     const bool leader = cta_rank == 0;
     // geometry of one ring slot and of the work split
@@ -241,7 +252,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
                 const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
                 const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
-                if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
+                if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
                 if (leader) mbar_expect_tx(BAR(B_AFULL), (p.nkc * TC_A_CHUNK + TC_A_AUG) * OPERAND_CTAS);
@@ -258,12 +269,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         const int s = fill % p.nstage;
                         const uint32_t ph = (fill / p.nstage) & 1;
                         const long long c0 = clock64();
-                        if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
+                        if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 4, B_EMPTY + s); ok = false; break;
                         }
                         prof_a += clock64() - c0;
                         const bool last = (kc == p.nkc - 1);
                         const int row0 = t * p.tile_stride * TC_BN + (int)cta_rank * B_ROWS;
+                        if (DBG && (p.dbg_flags & 32) && fill == 3) continue;   // this slot never fills
                         if (leader) mbar_expect_tx(BAR(B_FULL + s), (last ? SLOT_BYTES : SLOT_CHUNK) * OPERAND_CTAS);
                         load(b_addr + s * SLOT_BYTES, &map_db, kc * TC_BK, row0, BAR(B_FULL + s));
                         if (last) load(b_addr + s * SLOT_BYTES + SLOT_CHUNK, &map_db_aug, d_pad, row0, BAR(B_FULL + s));
@@ -295,13 +307,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int split = it / n_units;
                 const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
                 const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
-                if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
+                if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 5, B_AFULL); ok = false; break;
                 }
                 for (int t = t0; t < t1 && ok; ++t, ++tile_no) {
                     const int b = tile_no & 1;
                     const long long c0 = clock64();
-                    if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
+                    if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                         tc_report_timeout(p.status, 5, B_TEMPTY + b); ok = false; break;
                     }
                     prof_tempty += clock64() - c0;
@@ -311,7 +323,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         const int s = use % p.nstage;
                         const uint32_t ph = (use / p.nstage) & 1;
                         const long long c1 = clock64();
-                        if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, TC_WAIT_NS, p.wait_hint_ns)) {
+                        if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 5, B_FULL + s); ok = false; break;
                         }
                         prof_full += clock64() - c1;
@@ -400,7 +412,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = tile_no & 1;
                 const long long c0 = clock64();
-                if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, TC_WAIT_NS, p.wait_hint_ns))) {
+                if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
                     ok = false;
                     break;
@@ -701,27 +713,43 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 // Starting threshold of every query row from the seeding pass: the `rank`-th largest of the
 // row's 32 class maxima (16 column classes x 2 warpgroups, disjoint sets of database rows).  At
 // least `rank` distinct rows reach it, and being an order statistic of many classes it scatters
-// far less than the smallest of a few maxima.
-__global__ void tc_seed_select_kernel(const float* __restrict__ seed_cls, float* __restrict__ tau, int64_t nq_pad, int rank) {
-    const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+// far less than the smallest of a few maxima.  One warp per row, lane = class.
+//
+// With a margin (row-sharded databases: the class maxima are the element-wise maximum over all
+// shards, so the `rank` rows may live on other shards) the threshold is lowered by twice the
+// scoring error bound plus the fp32 slack: a row whose score stays at or below
+//     cert = pick - 2 eps_rel ||q|| maxnorm - slack
+// is at least as far from the query as each of those `rank` rows, whichever shard holds them,
+// so a shard that re-scores every row above `cert` cannot miss a global neighbour.  `cert` is
+// also written to mg.cert_out, where the finalisation reads it.
+__global__ void __launch_bounds__(256) tc_seed_select_kernel(const float* __restrict__ seed_cls, float* __restrict__ tau,
+                                                             int64_t nq_pad, int rank, const TcSeedMargin mg) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= nq_pad) return;
-    float v[TC_NWG * 16];
-    const float4* src = reinterpret_cast<const float4*>(seed_cls + row * (TC_NWG * 16));
-#pragma unroll
-    for (int i = 0; i < TC_NWG * 4; ++i) {
-        const float4 t = __ldg(src + i);
-        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-    }
+    const float v = __ldg(seed_cls + row * (TC_NWG * 16) + lane);
     // rank of each value among the 32 (ties broken by position): a permutation
-    float pick = neg_inf();
+    int r = 0;
 #pragma unroll
-    for (int i = 0; i < TC_NWG * 16; ++i) {
-        int r = 0;
-#pragma unroll
-        for (int j = 0; j < TC_NWG * 16; ++j) r += (v[j] > v[i] || (v[j] == v[i] && j < i)) ? 1 : 0;
-        if (r == rank - 1) pick = v[i];
+    for (int j = 0; j < 32; ++j) {
+        const float o = __shfl_sync(FULL_MASK, v, j);
+        r += (o > v || (o == v && j < lane)) ? 1 : 0;
     }
-    if (pick > neg_inf()) tau[row] = pick;
+    const unsigned sel = __ballot_sync(FULL_MASK, r == rank - 1);
+    float pick = __shfl_sync(FULL_MASK, v, __ffs(sel) - 1);
+    if (mg.q != nullptr) {
+        float qsq = 0.f;
+        if (row < mg.nq) {
+            const float* qp = mg.q + row * mg.ldq;
+            for (int c = lane; c < mg.d; c += 32) { const float x = __ldg(qp + c); qsq += x * x; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
+        const float mn = __ldg(mg.maxnorm);
+        if (pick > neg_inf()) pick -= 2.f * mg.eps_rel * sqrtf(qsq) * mn + 1e-5f * (qsq + mn * mn);
+        if (lane == 0 && mg.cert_out != nullptr) mg.cert_out[row] = pick;
+    }
+    if (lane == 0 && pick > neg_inf()) tau[row] = pick;
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -830,93 +858,198 @@ void tc_split_plan(int64_t nq_pad, int64_t m_pad, int k, int* nsplit, int64_t* t
     *nsplit = (int)ceil_div(n_tiles, *tiles_per_split);
 }
 
-static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
-    FL_CHECK_ARG(p.qplane && p.dbrows && p.part_sc && p.part_id && p.tau && p.part_tau,
-                 "tensor-core kNN launch with a null buffer");
-    const bool big = tc_knn_big(p.k) != 0;
-    FL_CHECK_ARG(!big || (p.part_cnt && !dbg), "tensor-core kNN launch (large k) without a count buffer");
-    CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
-    const int pitch = p.d_pad + PLANE_AUG_COLS;
-    int rc = make_map_bf16(&map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
-    if (rc == FL_OK) rc = make_map_bf16(&map_q_aug, p.qplane, p.nq_pad, pitch, PLANE_AUG_COLS, TC_BM);
-    if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
-    if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
+// ---- experiment controls ------------------------------------------------------------------
+// Timing experiments and seeding overrides.  The environment is read once, when the first
+// tensor-core launch is prepared; fl_debug_tc_experiment changes the flags and the wait limit
+// afterwards (tests of the bounded-wait exit).  Launches with experiment flags 1..16 set mark
+// the status words (FL_EUNSUPPORTED): their neighbours are not to be used.
+struct TcExperiment {
+    int flags = 0;
+    uint32_t hint_ns = 1000u;
+    uint64_t wait_ns = TC_WAIT_DEFAULT_NS;
+    int noseed = 0, seed_tiles = -1, seed_rank = -1;
+};
+static TcExperiment& tc_experiment() {
+    static TcExperiment e = [] {
+        TcExperiment x;
+        if (const char* v = getenv("FLASHLIB_B200_TC_DEBUG")) x.flags = atoi(v);
+        if (const char* v = getenv("FLASHLIB_B200_TC_HINT")) x.hint_ns = (uint32_t)atoi(v);
+        if (const char* v = getenv("FLASHLIB_B200_TC_NOSEED")) x.noseed = atoi(v) != 0;
+        if (const char* v = getenv("FLASHLIB_B200_TC_SEED_TILES")) x.seed_tiles = atoi(v);
+        if (const char* v = getenv("FLASHLIB_B200_TC_SEED_RANK")) x.seed_rank = atoi(v);
+        return x;
+    }();
+    return e;
+}
+void tc_debug_set(int flags, unsigned wait_us) {
+    TcExperiment& e = tc_experiment();
+    e.flags = flags;
+    e.wait_ns = wait_us ? (uint64_t)wait_us * 1000ull : TC_WAIT_DEFAULT_NS;
+}
+
+// Tensor maps are encoded once per (buffer, shape, box) and kept in a small per-thread cache:
+// a serving loop calls with the same plane and the same workspace over and over.
+struct MapKey { const void* base; int64_t rows; int cols, box_cols, box_rows; };
+static int cached_map_bf16(CUtensorMap* map, const void* base, int64_t rows, int cols, int box_cols, int box_rows) {
+    constexpr int SLOTS = 16;
+    thread_local MapKey keys[SLOTS];
+    thread_local CUtensorMap maps[SLOTS];
+    thread_local int used = 0, next = 0;
+    for (int i = 0; i < used; ++i) {
+        const MapKey& k = keys[i];
+        if (k.base == base && k.rows == rows && k.cols == cols && k.box_cols == box_cols && k.box_rows == box_rows) {
+            *map = maps[i];
+            return FL_OK;
+        }
+    }
+    const int rc = make_map_bf16(map, base, rows, cols, box_cols, box_rows);
     if (rc != FL_OK) return rc;
-    const bool mid = p.deep_pools != 0;
-    FL_CHECK_ARG(!(mid && (big || dbg)), "tensor-core kNN launch: deep pools go with k <= 16");
-    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), big ? 0 : mid ? TC_MID_CAP + 1 : TC_PSTR);
-    if (sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
-    TcKernelParams kp{};
+    const int slot = used < SLOTS ? used++ : (next++ % SLOTS);
+    keys[slot] = MapKey{base, rows, cols, box_cols, box_rows};
+    maps[slot] = *map;
+    return FL_OK;
+}
+
+int tc_seed_tiles(int64_t m_pad, int k);
+
+struct TcLaunch {
+    CUtensorMap map_q, map_q_aug, map_db, map_db_aug;
+    TcSmemPlan sp;
+    TcKernelParams kp;
+    int seed_tiles, seed_rank;
+    bool big, mid;
+};
+
+// Everything a launch needs: tensor maps, shared-memory plan, kernel parameters and the size of
+// the seeding sample.
+static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch* L) {
+    FL_CHECK_ARG(p.qplane && p.dbrows && p.tau, "tensor-core kNN launch with a null buffer");
+    L->big = tc_knn_big(p.k) != 0;
+    L->mid = p.deep_pools != 0;
+    const int pitch = p.d_pad + PLANE_AUG_COLS;
+    int rc = cached_map_bf16(&L->map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
+    if (rc == FL_OK) rc = cached_map_bf16(&L->map_q_aug, p.qplane, p.nq_pad, pitch, PLANE_AUG_COLS, TC_BM);
+    if (rc == FL_OK) rc = cached_map_bf16(&L->map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
+    if (rc == FL_OK) rc = cached_map_bf16(&L->map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
+    if (rc != FL_OK) return rc;
+    FL_CHECK_ARG(!(L->mid && (L->big || dbg)), "tensor-core kNN launch: deep pools go with k <= 16");
+    L->sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), L->big ? 0 : L->mid ? TC_MID_CAP + 1 : TC_PSTR);
+    if (L->sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
+    const TcExperiment& ex = tc_experiment();
+    TcKernelParams& kp = L->kp;
+    kp = TcKernelParams{};
     kp.n_qtiles = (int)(p.nq_pad / TC_BM);
     kp.n_tiles = (int)(p.m_pad / TC_BN);
     kp.nsplit = p.nsplit;
     kp.tiles_per_split = (int)p.tiles_per_split;
-    kp.nkc = sp.nkc; kp.nstage = sp.nstage;
-    kp.off_b = sp.off_b; kp.off_pool_sc = sp.off_pool_sc; kp.off_pool_id = sp.off_pool_id;
-    kp.off_bar = sp.off_bar;
+    kp.nkc = L->sp.nkc; kp.nstage = L->sp.nstage;
+    kp.off_b = L->sp.off_b; kp.off_pool_sc = L->sp.off_pool_sc; kp.off_pool_id = L->sp.off_pool_id;
+    kp.off_bar = L->sp.off_bar;
     kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
     kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
     kp.part_cnt = p.part_cnt;
     kp.seed_cls = p.seed_cls;
     kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1;
     kp.row_query = p.row_query; kp.tau_q = p.tau_q;
-    FL_CHECK_ARG((p.row_query == nullptr) == (p.tau_q == nullptr), "tensor-core kNN launch: row_query and tau_q go together");
-    FL_CHECK_ARG((p.item_t0 == nullptr) == (p.item_t1 == nullptr) && (p.item_t0 == nullptr || (p.nsplit == 1 && !big)),
-                 "tensor-core kNN launch: per-tile ranges need one range per query tile and k <= 16");
-    {
-        const char* e = getenv("FLASHLIB_B200_TC_DEBUG");
-        kp.dbg_flags = e ? atoi(e) : 0;
-        const char* h = getenv("FLASHLIB_B200_TC_HINT");
-        kp.wait_hint_ns = h ? (uint32_t)atoi(h) : 1000u;
-    }
-    const int items = kp.n_qtiles * kp.nsplit;
-    const int grid = items < sm_count() ? items : sm_count();
+    kp.dbg_flags = ex.flags;
+    kp.wait_hint_ns = ex.hint_ns;
+    kp.wait_ns = ex.wait_ns;
     kp.tile_stride = 1;
-    // Threshold seeding on a strided sample of one tile in 16 (at most 64 tiles) when the
-    // database is large enough for the cold start of the pools to matter.
-    const char* noseed = getenv("FLASHLIB_B200_TC_NOSEED");
     // Seeding sample.  The threshold is the seed_rank-th largest of 32 class maxima, which sits
     // near rank 32 ln(32 / (32 - seed_rank)) of the sample, hence near that figure times
     // n_tiles / seed_tiles of the whole database.
-    //  k <= 16: the pools tighten the threshold quickly; 64 tiles, k + 6 rows guaranteed.
+    //  k <= 16: the pools tighten the threshold quickly; one tile in 16 (at most 64 tiles), k + 6
+    //           rows guaranteed.
     //  large k: the pools seldom fill, so the seeded threshold is what filters.  Aim at about
     //           rank 6 k of the database: loose enough that the k-th neighbour's error band
     //           stays inside, tight enough that a few hundred rows per query are published.
-    int seed_tiles = kp.n_tiles >= 1024 ? 64 : kp.n_tiles / 16;
     int seed_rank = p.k + 6 < 32 ? p.k + 6 : 32;
-    if (big) {
-        seed_rank = p.k >= 64 ? 16 : 8;
-        const double sample_rank = p.k >= 64 ? 22.2 : 9.2;
-        seed_tiles = (int)((double)kp.n_tiles * sample_rank / (6.0 * p.k));
-        if (seed_tiles > kp.n_tiles / 8) seed_tiles = kp.n_tiles / 8;
-    }
-    if (const char* e = getenv("FLASHLIB_B200_TC_SEED_TILES")) seed_tiles = atoi(e);
-    if (const char* e = getenv("FLASHLIB_B200_TC_SEED_RANK")) seed_rank = atoi(e);
+    if (L->big) seed_rank = p.k >= 64 ? 16 : 8;
+    if (ex.seed_rank >= 0) seed_rank = ex.seed_rank;
     if (seed_rank < 1) seed_rank = 1;
     if (seed_rank > 32) seed_rank = 32;
-    if (seed_tiles > kp.n_tiles / 2) seed_tiles = kp.n_tiles / 2;
-    if (seed_tiles >= 16 && p.seed_cls != nullptr && !(noseed && atoi(noseed))) {
-        TcKernelParams sk = kp;
-        sk.nsplit = 1;
-        sk.tiles_per_split = seed_tiles;
-        sk.tile_stride = kp.n_tiles / seed_tiles;
-        sk.n_tiles = seed_tiles;
-        sk.dbg_scores = nullptr;
-        const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
-        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, TC_MODE_SEED><<<sgrid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, sk);
-        FL_CHECK_LAUNCH();
-        tc_seed_select_kernel<<<(unsigned)ceil_div(p.nq_pad, 128), 128, 0, st>>>(p.seed_cls, p.tau, p.nq_pad, seed_rank);
-        FL_CHECK_LAUNCH();
+    const int seed_tiles = tc_seed_tiles(p.m_pad, p.k);
+    L->seed_tiles = seed_tiles;
+    L->seed_rank = seed_rank;
+    return FL_OK;
+}
+
+// Database tiles the seeding pass samples (0: no seeding for this shape).
+int tc_seed_tiles(int64_t m_pad, int k) {
+    const int n_tiles = (int)(m_pad / TC_BN);
+    const TcExperiment& ex = tc_experiment();
+    int seed_tiles = n_tiles >= 1024 ? 64 : n_tiles / 16;
+    if (tc_knn_big(k)) {
+        const double sample_rank = k >= 64 ? 22.2 : 9.2;
+        seed_tiles = (int)((double)n_tiles * sample_rank / (6.0 * k));
+        if (seed_tiles > n_tiles / 8) seed_tiles = n_tiles / 8;
     }
+    if (ex.seed_tiles >= 0) seed_tiles = ex.seed_tiles;
+    if (seed_tiles > n_tiles / 2) seed_tiles = n_tiles / 2;
+    if (seed_tiles < 16 || ex.noseed) seed_tiles = 0;
+    return seed_tiles;
+}
+
+// Seeding pass: class maxima of a strided sample of the database tiles into p.seed_cls
+// ([nq_pad][32]).  Without a sample (database too small) the maxima are set to -inf.
+int launch_knn_tc_seed(const TcKnnParams& p, cudaStream_t st) {
+    FL_CHECK_ARG(p.seed_cls != nullptr, "tensor-core seeding pass without a class buffer");
+    TcLaunch L;
+    int rc = tc_prepare(p, nullptr, 0, &L);
+    if (rc != FL_OK) return rc;
+    if (L.seed_tiles == 0) return launch_fill_f32(p.seed_cls, p.nq_pad * (TC_NWG * 16), -INFINITY, st);
+    TcKernelParams sk = L.kp;
+    sk.nsplit = 1;
+    sk.tiles_per_split = L.seed_tiles;
+    sk.tile_stride = L.kp.n_tiles / L.seed_tiles;
+    sk.n_tiles = L.seed_tiles;
+    sk.dbg_scores = nullptr;
+    sk.item_t0 = sk.item_t1 = nullptr; sk.nq_dev = nullptr; sk.row_query = nullptr; sk.tau_q = nullptr;
+    // the seeding kernel keeps no pools: the ring gets the shared memory the pools would take
+    const TcSmemPlan sp = L.sp;
+    const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
+    FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_SEED>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+    knn_tc_kernel<false, TC_MODE_SEED><<<sgrid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, sk);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+// Starting thresholds from class maxima (this shard's, or the element-wise maximum over all
+// shards of a sharded database): see tc_seed_select_kernel.
+int launch_knn_tc_seed_select(const TcKnnParams& p, const TcSeedMargin& mg, cudaStream_t st) {
+    FL_CHECK_ARG(p.seed_cls != nullptr && p.tau != nullptr, "tensor-core threshold selection without buffers");
+    TcLaunch L;
+    int rc = tc_prepare(p, nullptr, 0, &L);
+    if (rc != FL_OK) return rc;
+    tc_seed_select_kernel<<<(unsigned)ceil_div(p.nq_pad, 8), 256, 0, st>>>(p.seed_cls, p.tau, p.nq_pad, L.seed_rank, mg);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+// Main scoring launch (thresholds in p.tau as they stand).
+static int launch_tc_main(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
+    FL_CHECK_ARG(p.part_sc && p.part_id && p.part_tau, "tensor-core kNN launch with a null buffer");
+    TcLaunch L;
+    int rc = tc_prepare(p, dbg, dbg_ld, &L);
+    if (rc != FL_OK) return rc;
+    const bool big = L.big, mid = L.mid;
+    FL_CHECK_ARG(!big || (p.part_cnt && !dbg), "tensor-core kNN launch (large k) without a count buffer");
+    FL_CHECK_ARG((p.row_query == nullptr) == (p.tau_q == nullptr), "tensor-core kNN launch: row_query and tau_q go together");
+    FL_CHECK_ARG((p.item_t0 == nullptr) == (p.item_t1 == nullptr) && (p.item_t0 == nullptr || (p.nsplit == 1 && !big)),
+                 "tensor-core kNN launch: per-tile ranges need one range per query tile and k <= 16");
+    const TcKernelParams& kp = L.kp;
+    const TcSmemPlan& sp = L.sp;
+    const int pitch = p.d_pad + PLANE_AUG_COLS;
+    const int items = kp.n_qtiles * kp.nsplit;
+    const int grid = items < sm_count() ? items : sm_count();
     // CTA pairs (cta_group::2): plain k <= 16 scoring over uniform ranges, an even number of query
     // tiles, at least one pair-item per cluster of a full grid.  FLASHLIB_B200_TC_PAIR=0/1 overrides.
     const bool pair = !mid && dbg == nullptr && p.item_t0 == nullptr && p.nq_dev == nullptr &&
                       tc_pair_enabled(p.nq_pad, p.k);
     if (pair) {
         CUtensorMap map_db_h, map_db_aug_h;
-        rc = make_map_bf16(&map_db_h, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN / 2);
-        if (rc == FL_OK) rc = make_map_bf16(&map_db_aug_h, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN / 2);
+        rc = cached_map_bf16(&map_db_h, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN / 2);
+        if (rc == FL_OK) rc = cached_map_bf16(&map_db_aug_h, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN / 2);
         if (rc != FL_OK) return rc;
         const TcSmemPlan spp = tc_smem_plan(p.d_pad, smem_optin_bytes(), TC_PSTR, TC_B_STAGE / 2);
         TcKernelParams kq = kp;
@@ -937,23 +1070,36 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        FL_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, map_q, map_q_aug, map_db_h, map_db_aug_h, kq));
+        FL_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, L.map_q, L.map_q_aug, map_db_h, map_db_aug_h, kq));
     } else if (mid) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_MID>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, TC_MODE_KNN_MID><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        knn_tc_kernel<false, TC_MODE_KNN_MID><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
     } else if (big) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_BIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, TC_MODE_KNN_BIG><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        knn_tc_kernel<false, TC_MODE_KNN_BIG><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
     } else if (dbg != nullptr || kp.dbg_flags != 0) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<true, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        knn_tc_kernel<true, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
     } else {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
-        knn_tc_kernel<false, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(map_q, map_q_aug, map_db, map_db_aug, kp);
+        knn_tc_kernel<false, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
     }
     FL_CHECK_LAUNCH();
     return FL_OK;
 }
+
+// Seeding (when p.seed_cls is given and the database is large enough for it to matter), threshold
+// selection and the main scoring launch.
+static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
+    if (p.seed_cls != nullptr && tc_seed_tiles(p.m_pad, p.k) > 0) {
+        int rc = launch_knn_tc_seed(p, st);
+        if (rc != FL_OK) return rc;
+        rc = launch_knn_tc_seed_select(p, TcSeedMargin{}, st);
+        if (rc != FL_OK) return rc;
+    }
+    return launch_tc_main(p, dbg, dbg_ld, st);
+}
+int launch_knn_tc_scoring(const TcKnnParams& p, cudaStream_t st) { return launch_tc_main(p, nullptr, 0, st); }
 
 int tc_prof_read(unsigned long long* host_out, int words) {
     const size_t n = sizeof(unsigned long long) * (size_t)(words < 160 * TC_PROF_WORDS ? words : 160 * TC_PROF_WORDS);

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .kmeans import euclid_assign_triton, flash_kmeans
-from .knn import _as_f32_rows, _stream_ptr, flash_knn, row_sqnorm
+from .knn import _as_f32_rows, _defer_status_check, _stream_ptr, flash_knn, row_sqnorm
 
 
 @dataclass
@@ -36,7 +36,7 @@ class IvfFlatIndex:
     Dp: int
     nlist: int
     nprobe: int
-    max_list_len: int = 0
+    max_list_len: int = 0      # may be given as a 1-element device tensor: read back (one sync) on first use
     _hnorm: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
     _tc_plane: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
     _last_status: Optional[torch.Tensor] = field(default=None, repr=False, compare=False)
@@ -61,6 +61,23 @@ class IvfFlatIndex:
         if self._hnorm is None or self._hnorm.device != self.data.device:
             self._hnorm = row_sqnorm(self.data).mul_(0.5)
         return self._hnorm
+
+
+def _get_max_list_len(self) -> int:
+    v = self.__dict__.get("_max_list_len", 0)
+    if isinstance(v, torch.Tensor):
+        v = int(v.item())
+        self.__dict__["_max_list_len"] = v
+    return v
+
+
+def _set_max_list_len(self, v) -> None:
+    self.__dict__["_max_list_len"] = v
+
+
+# The device-side build leaves the longest list's length on the device; nothing on the build or
+# search path needs it, so it is only fetched when somebody reads the attribute.
+IvfFlatIndex.max_list_len = property(_get_max_list_len, _set_max_list_len)
 
 
 def _pad_features(x: torch.Tensor, Dp: int) -> torch.Tensor:
@@ -106,18 +123,30 @@ def flash_ivf_flat_build(X: torch.Tensor, nlist: int, *, metric: str = "l2", npr
 
 def index_from_centroids(Xp: torch.Tensor, centroids: torch.Tensor, *, D: int, nprobe: int,
                          metric: str = "l2") -> IvfFlatIndex:
-    """Assign every (padded) row to its nearest centroid and build the CSR layout."""
+    """Assign every (padded) row to its nearest centroid and build the cell-contiguous layout on
+    the device: per-list histogram, exclusive scan, stable partition of the rows (the order of the
+    reference's stable ``argsort`` by list, ``ivf_flat/triton/build.py:59-95``) -- one C-ABI call,
+    no host synchronisation."""
+    lib = _lib.load()
     nlist = centroids.shape[0]
-    assign = euclid_assign_triton(Xp.unsqueeze(0), centroids.unsqueeze(0)).squeeze(0).to(torch.int64)
-    counts = torch.bincount(assign, minlength=nlist)
-    offsets = torch.zeros(nlist + 1, dtype=torch.int64, device=Xp.device)
-    offsets[1:] = counts.cumsum(0)
-    order = torch.argsort(assign, stable=True)
-    data_sorted = Xp.index_select(0, order).contiguous()
-    max_list_len = int(counts.max().item())
-    return IvfFlatIndex(centroids=centroids, data=data_sorted, ids=order.to(torch.int64),
-                        list_offsets=offsets, metric=metric, D=int(D), Dp=int(Xp.shape[1]),
-                        nlist=int(nlist), nprobe=int(nprobe), max_list_len=max_list_len)
+    M, Dp = Xp.shape
+    x32 = _as_f32_rows(Xp)
+    assign = euclid_assign_triton(x32.unsqueeze(0), centroids.float().unsqueeze(0)).squeeze(0)
+    dev = Xp.device
+    data = torch.empty((M, Dp), dtype=torch.float32, device=dev)
+    ids = torch.empty(M, dtype=torch.int64, device=dev)
+    offsets = torch.empty(nlist + 1, dtype=torch.int64, device=dev)
+    longest = torch.empty(1, dtype=torch.int32, device=dev)
+    ws_bytes = lib.fl_ivf_build_workspace_bytes(M, nlist)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.fl_ivf_build_csr_f32(x32.data_ptr(), M, x32.stride(0), Dp, assign.data_ptr(), nlist,
+                                            data.data_ptr(), ids.data_ptr(), offsets.data_ptr(), longest.data_ptr(),
+                                            ws.data_ptr(), ws_bytes, _stream_ptr(dev)))
+    if Xp.dtype != torch.float32:
+        data = data.to(Xp.dtype)
+    return IvfFlatIndex(centroids=centroids, data=data, ids=ids, list_offsets=offsets, metric=metric, D=int(D),
+                        Dp=int(Dp), nlist=int(nlist), nprobe=int(nprobe), max_list_len=longest)
 
 
 def _tc_plane(index: IvfFlatIndex, data: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
@@ -169,6 +198,7 @@ def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k
                                                    plane.data_ptr(), vals.data_ptr(), pos.data_ptr(),
                                                    ws.data_ptr(), tc_bytes, status.data_ptr(), _stream_ptr(q.device)))
         index._last_status = status     # status[FL_STATUS_FALLBACK]: queries recomputed by the exact scan
+        _defer_status_check(status)     # an error word raises at a later call or in check_pending()
         return vals, pos
     ws_bytes = lib.fl_ivf_fine_scan_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=q.device)
@@ -187,9 +217,10 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
                           backend: Optional[str] = None, variant: str = "auto"):
     """``(vals fp32, ids int64)`` of the ``k`` nearest probed rows per query, ``-1`` / ``+inf``
     padded (``ivf_flat/triton/search.py:52-108``).  ``variant`` is validated like the
-    reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 16 and
-    d <= 128, the CUDA-core scan otherwise), ``"elementwise"`` for the CUDA-core scan,
-    ``"auto"`` picks by batch size.  All variants return the same neighbours."""
+    reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 10 and
+    d <= 128, where its candidate pools prove nearly every query; the CUDA-core scan
+    otherwise), ``"elementwise"`` for the CUDA-core scan, ``"auto"`` picks by batch size.
+    All variants return the same neighbours."""
     if variant not in ("auto", "gemm", "elementwise"):
         raise ValueError(f"unknown variant {variant!r} (auto|gemm|elementwise)")
     if not Q.is_cuda or Q.ndim != 2:

@@ -14,7 +14,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from .knn import _as_f32_rows, _evict_when_freed, _stream_ptr
+from .knn import _as_f32_rows, _defer_status_check, _evict_when_freed, _stream_ptr
 
 
 _XPLANE_CACHE = {}
@@ -63,9 +63,13 @@ def _assign_2d(x: torch.Tensor, c: torch.Tensor, out: torch.Tensor, mode: Option
         xplane = _x_plane(x)
         ws_bytes = lib.fl_kmeans_assign_tc_workspace_bytes(n, K, d, 1)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+        status = torch.zeros(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=x.device)
         _lib.check(lib.fl_kmeans_assign_tc_f32(x.data_ptr(), n, x.stride(0), xplane.data_ptr(), c.data_ptr(), K,
-                                               c.stride(0), d, out.data_ptr(), ws.data_ptr(), ws_bytes, None,
-                                               _stream_ptr(x.device)))
+                                               c.stride(0), d, out.data_ptr(), ws.data_ptr(), ws_bytes,
+                                               status.data_ptr(), _stream_ptr(x.device)))
+        # a bounded wait that gave up leaves garbage labels: the status words are looked at by a
+        # later call or by check_pending(), without a host round trip per iteration
+        _defer_status_check(status)
         return
     ws_bytes = lib.fl_kmeans_assign_workspace_bytes(n, K, d)
     ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)

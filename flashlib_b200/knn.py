@@ -105,11 +105,17 @@ def clear_plane_cache() -> None:
 _PENDING_STATUS: deque = deque()
 
 
+_STATUS_TEXT = {_lib.FL_ETIMEOUT: "a bounded device-side wait ran out",
+                _lib.FL_EUNSUPPORTED: "the call ran with timing-experiment flags set",
+                _lib.FL_EWORKSPACE: "the fallback list overflowed"}
+
+
 def _raise_on_status(st) -> None:
-    if st[_lib.FL_STATUS_ERROR] != 0:
+    err = st[_lib.FL_STATUS_ERROR]
+    if err != 0:
         raise _lib.FlashlibError(
-            f"tensor-core kNN kernel reported status {st[_lib.FL_STATUS_ERROR]} "
-            f"(where={st[_lib.FL_STATUS_WHERE]:#x})")
+            f"tensor-core kernel reported status {err} ({_STATUS_TEXT.get(err, 'unknown')}; "
+            f"where={st[_lib.FL_STATUS_WHERE]:#x}): the results of that call are invalid")
 
 
 def check_pending(block: bool = True) -> None:
@@ -168,10 +174,7 @@ def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KN
     elif check_status and resolved == _lib.FL_KNN_BF16_RERANK:
         st = status.tolist()
         info["fallback_rows"] = st[_lib.FL_STATUS_FALLBACK]
-        if st[_lib.FL_STATUS_ERROR] != 0:
-            raise _lib.FlashlibError(
-                f"tensor-core kNN kernel reported status {st[_lib.FL_STATUS_ERROR]} "
-                f"(where={st[_lib.FL_STATUS_WHERE]:#x})")
+        _raise_on_status(st)
     return out_d, out_i, info
 
 

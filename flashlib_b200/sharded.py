@@ -67,50 +67,226 @@ def exchange_candidates(local_d: torch.Tensor, local_i: torch.Tensor, group=None
     return cand_d, cand_i
 
 
-def sharded_knn(q: torch.Tensor, db_shard: torch.Tensor, k: int, *, row_offset: int, group=None,
-                mode: Optional[str] = None, plane=None, result: str = "replicated",
-                local_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None):
+class DeviceKnnKernels:
+    """The device side of :func:`sharded_knn`: every method is one or two C-ABI calls on the
+    current stream.  The CPU tests of the exchange logic pass an object with the same methods
+    built on the oracle."""
+
+    def tensor_core(self, nq: int, m: int, d: int, k: int, mode) -> bool:
+        """True when a shard of ``m`` rows takes the tensor-core path for this call."""
+        from . import _lib
+        from .knn import _mode_from
+        md = _mode_from(mode)
+        if md == _lib.FL_KNN_EXACT_SIMT or m < 1:
+            return False
+        if md == _lib.FL_KNN_AUTO:
+            return _lib.load().fl_knn_resolve_mode(nq, m, d, k) == _lib.FL_KNN_BF16_RERANK
+        return d <= 256 and k <= 112          # forced: the shapes the tensor-core kernel takes
+
+    def plane_of(self, db: torch.Tensor):
+        from .knn import get_plane
+        return get_plane(db)
+
+    def max_norm(self, db: torch.Tensor, plane) -> torch.Tensor:
+        """Largest row norm of this shard as a 1-element fp32 device tensor."""
+        from . import _lib
+        off = _lib.load().fl_knn_plane_maxnorm_offset(db.shape[0], db.shape[1])
+        return plane.buf[off:off + 4].view(torch.float32).clone()
+
+    def local(self, q, db, k, row_offset, mode, plane):
+        from .knn import _mode_from, knn_f32
+        d_, i_, info = knn_f32(q, db, k, mode=_mode_from(mode), row_offset=row_offset, plane=plane, check_status=False)
+        return d_, i_, info["status"]
+
+    def seed(self, q, db, k, plane):
+        from . import _lib
+        from .knn import _stream_ptr
+        lib = _lib.load()
+        nq, d = q.shape
+        m = db.shape[0]
+        ws_bytes = lib.fl_knn_workspace_bytes(nq, m, d, k, _lib.FL_KNN_BF16_RERANK)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        cls = torch.empty(lib.fl_knn_seed_floats(nq), dtype=torch.float32, device=q.device)
+        status = torch.empty(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=q.device)
+        _lib.check(lib.fl_knn_seed_f32(q.data_ptr(), nq, q.stride(0), d, k, plane.ptr, m, cls.data_ptr(),
+                                       ws.data_ptr(), ws_bytes, status.data_ptr(), _stream_ptr(q.device)))
+        return cls, (ws, ws_bytes, status)
+
+    def compress(self, cls: torch.Tensor) -> torch.Tensor:
+        """bf16 copy of the class maxima, rounded toward -inf (half the bytes on the wire)."""
+        from . import _lib
+        from .knn import _stream_ptr
+        out = torch.empty(cls.numel(), dtype=torch.bfloat16, device=cls.device)
+        _lib.check(_lib.load().fl_f32_to_bf16_down(cls.data_ptr(), out.data_ptr(), cls.numel(), _stream_ptr(cls.device)))
+        return out
+
+    def expand(self, comp: torch.Tensor, cls: torch.Tensor) -> torch.Tensor:
+        from . import _lib
+        from .knn import _stream_ptr
+        _lib.check(_lib.load().fl_bf16_to_f32(comp.data_ptr(), cls.data_ptr(), cls.numel(), _stream_ptr(cls.device)))
+        return cls
+
+    def seeded(self, q, db, k, row_offset, plane, cls, gmax, ctx):
+        from . import _lib
+        from .knn import _stream_ptr
+        lib = _lib.load()
+        ws, ws_bytes, status = ctx
+        nq, d = q.shape
+        out_d = torch.empty((nq, k), dtype=torch.float32, device=q.device)
+        out_i = torch.empty((nq, k), dtype=torch.int32, device=q.device)
+        _lib.check(lib.fl_knn_seeded_f32(q.data_ptr(), nq, q.stride(0), db.data_ptr(), db.shape[0], db.stride(0), d, k,
+                                         plane.ptr, row_offset, cls.data_ptr(), gmax.data_ptr(), out_d.data_ptr(),
+                                         out_i.data_ptr(), ws.data_ptr(), ws_bytes, status.data_ptr(),
+                                         _stream_ptr(q.device)))
+        return out_d, out_i, status
+
+    def pack(self, d_, i_, status, world: int, owner: bool) -> torch.Tensor:
+        from . import _lib
+        from .knn import _stream_ptr
+        lib = _lib.load()
+        nq, k = d_.shape
+        out = torch.empty(lib.fl_knn_pack_ints(nq, k, world, int(owner)), dtype=torch.int32, device=d_.device)
+        d_, i_ = d_.contiguous(), i_.contiguous()
+        _lib.check(lib.fl_knn_pack_f32(d_.data_ptr(), i_.data_ptr(), nq, k, world, int(owner),
+                                       status.data_ptr() if status is not None else None, out.data_ptr(),
+                                       _stream_ptr(d_.device)))
+        return out
+
+    def merge(self, msgs: torch.Tensor, rows: int, k: int, world: int):
+        from . import _lib
+        from .knn import _stream_ptr
+        lib = _lib.load()
+        out_d = torch.empty((rows, k), dtype=torch.float32, device=msgs.device)
+        out_i = torch.empty((rows, k), dtype=torch.int32, device=msgs.device)
+        status = torch.empty(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=msgs.device)
+        _lib.check(lib.fl_knn_merge_packed_f32(msgs.data_ptr(), rows, k, world, out_d.data_ptr(), out_i.data_ptr(),
+                                               status.data_ptr(), _stream_ptr(msgs.device)))
+        return out_d, out_i, status
+
+    def defer(self, status: torch.Tensor) -> None:
+        from .knn import _defer_status_check
+        _defer_status_check(status)
+
+
+class ShardedKnnIndex:
+    """One rank's shard of a row-sharded database together with the facts that need a collective
+    to establish: the smallest shard's row count, whether every shard can take the tensor-core
+    path, and the largest row norm over all shards (the scoring error bound of
+    ``fl_knn_seeded_f32`` must hold for rows of every shard).
+
+    Constructing it is a COLLECTIVE call: every rank of ``group`` must do so at the same point of
+    its program.  It is the ``fit`` step of the sharded search; :func:`sharded_knn` uses it to share
+    the threshold seeds between the ranks."""
+
+    def __init__(self, db_shard: torch.Tensor, row_offset: int, *, group=None, plane=None, kernels=None):
+        kern = kernels if kernels is not None else DeviceKnnKernels()
+        self.db = db_shard
+        self.row_offset = int(row_offset)
+        self.group = group
+        m, d = db_shard.shape
+        can_tc = m > 0 and kern.tensor_core(1 << 20, m, d, min(10, m), "bf16")
+        self.plane = plane if plane is not None else (kern.plane_of(db_shard) if can_tc else None)
+        gmax = kern.max_norm(db_shard, self.plane) if self.plane is not None else torch.zeros(1, device=db_shard.device)
+        facts = torch.tensor([m, 1 if self.plane is not None else 0], dtype=torch.int64, device=db_shard.device)
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+            dist.all_reduce(facts, op=dist.ReduceOp.MIN, group=group)
+        self.global_max_norm = gmax
+        self.min_rows, all_tc = (int(v) for v in facts.tolist())
+        self.all_tensor_core = bool(all_tc)
+
+
+def sharded_knn(q: torch.Tensor, db_shard: Optional[torch.Tensor], k: int, *, row_offset: Optional[int] = None,
+                group=None, mode: Optional[str] = None, plane=None, result: str = "replicated",
+                index: Optional[ShardedKnnIndex] = None, share_seeds: Optional[bool] = None, kernels=None):
     """Exact kNN of the replicated queries ``q`` against a row-sharded database.
 
-    ``db_shard`` is this rank's rows, ``row_offset`` its first global row id.  A shard with
-    fewer than ``k`` rows contributes ``+inf`` / ``-1`` padding.  ``result="replicated"`` returns
-    the same ``(dist fp32 (nq,k), idx int32 (nq,k))`` on every rank (all-gather of the candidates,
-    every rank merges all queries); ``result="owner"`` returns on rank ``r`` the rows
+    ``db_shard`` is this rank's rows, ``row_offset`` its first global row id (or pass ``index``, a
+    :class:`ShardedKnnIndex` built once for the shard).  A shard with fewer than ``k`` rows
+    contributes ``+inf`` / ``-1`` padding.  ``result="replicated"`` returns the same
+    ``(dist fp32 (nq,k), idx int32 (nq,k))`` on every rank (all-gather of the candidates, every
+    rank merges all queries); ``result="owner"`` returns on rank ``r`` the rows
     ``shard_bounds(nq, world, r)`` of that result only (all-to-all, every rank merges its own
-    queries).  ``local_fn`` / ``merge_fn`` replace the device kernels (used by the CPU tests of the
-    exchange logic).
+    queries).
+
+    With an ``index`` (and ``share_seeds`` not False), k <= 16, at least k rows in every shard and
+    the tensor-core path on every rank, the ranks exchange the class maxima of their threshold-
+    seeding passes (one all-reduce with MAX, bf16) before they score: every rank then starts from
+    thresholds that k + 6 rows of the WHOLE database reach, instead of rows of its own shard, so
+    candidate insertion costs what it costs on one GPU, and a rank returns only rows that can
+    still be among the database's k nearest.
+
+    The status words of every rank's kernels travel with its candidates; the merged status is
+    looked at by a later call or ``flashlib_b200.knn.check_pending()`` on every rank alike, so a
+    kernel error on one rank raises everywhere instead of leaving the others in a collective.
+    ``kernels`` replaces the device calls (CPU tests of the exchange logic).
     """
     if result not in ("replicated", "owner"):
         raise ValueError(f"result must be 'replicated' or 'owner', got {result!r}")
-    if local_fn is None:
-        from .knn import _mode_from, knn_f32
-
-        def local_fn(q_, db_, k_, off_):
-            d_, i_, _ = knn_f32(q_, db_, k_, mode=_mode_from(mode), row_offset=off_, plane=plane,
-                                check_status="deferred")
-            return d_, i_
-    if merge_fn is None:
-        from .knn import topk_merge as merge_fn
+    kern = kernels if kernels is not None else DeviceKnnKernels()
+    if index is not None:
+        db_shard, row_offset, group = index.db, index.row_offset, index.group
+        plane = index.plane if plane is None else plane
+    if db_shard is None or row_offset is None:
+        raise ValueError("sharded_knn needs db_shard and row_offset, or an index")
     m_local = db_shard.shape[0]
-    k_local = min(k, m_local)
-    nq = q.shape[0]
-    if k_local > 0:
-        d_loc, i_loc = local_fn(q, db_shard, k_local, row_offset)
+    nq, d = q.shape
+    multi = dist.is_initialized() and dist.get_world_size(group) > 1
+    world = dist.get_world_size(group) if multi else 1
+    rank = dist.get_rank(group) if multi else 0
+
+    # every rank must take the same branch (the seeded flow has one more collective): the decision
+    # uses only facts that are identical everywhere
+    seeded = (multi and index is not None and share_seeds is not False and nq > 0 and k <= 16
+              and index.all_tensor_core and index.min_rows >= k
+              and (share_seeds is True or kern.tensor_core(nq, index.min_rows, d, k, mode)))
+    gmax = index.global_max_norm if index is not None else None
+
+    if seeded:
+        cls, ctx = kern.seed(q, db_shard, k, plane)
+        comp = kern.compress(cls)
+        dist.all_reduce(comp, op=dist.ReduceOp.MAX, group=group)
+        cls = kern.expand(comp, cls)
+        d_loc, i_loc, status = kern.seeded(q, db_shard, k, row_offset, plane, cls, gmax, ctx)
     else:
-        d_loc = torch.empty((nq, 0), dtype=torch.float32, device=q.device)
-        i_loc = torch.empty((nq, 0), dtype=torch.int32, device=q.device)
-    if k_local < k:
-        pad_d = torch.full((nq, k - k_local), float("inf"), dtype=torch.float32, device=q.device)
-        pad_i = torch.full((nq, k - k_local), -1, dtype=torch.int32, device=q.device)
-        d_loc = torch.cat([d_loc, pad_d], 1)
-        i_loc = torch.cat([i_loc, pad_i], 1)
-    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        k_local = min(k, m_local)
+        status = None
+        if k_local > 0 and nq > 0:
+            d_loc, i_loc, status = kern.local(q, db_shard, k_local, row_offset, mode, plane)
+        else:
+            d_loc = torch.empty((nq, 0), dtype=torch.float32, device=q.device)
+            i_loc = torch.empty((nq, 0), dtype=torch.int32, device=q.device)
+        if k_local < k:
+            pad_d = torch.full((nq, k - k_local), float("inf"), dtype=torch.float32, device=q.device)
+            pad_i = torch.full((nq, k - k_local), -1, dtype=torch.int32, device=q.device)
+            d_loc = torch.cat([d_loc, pad_d], 1)
+            i_loc = torch.cat([i_loc, pad_i], 1)
+    if not multi:
+        if status is not None:
+            kern.defer(status)
         return d_loc, i_loc
-    if result == "owner":
-        cand_d, cand_i = exchange_candidates(d_loc, i_loc, group)
+
+    owner = result == "owner"
+    msg = kern.pack(d_loc, i_loc, status, world, owner)
+    words = msg.numel() - nq * 2 * k
+    per_status = words // (world if owner else 1)
+    if owner:
+        counts = [shard_bounds(nq, world, r)[1] - shard_bounds(nq, world, r)[0] for r in range(world)]
+        mine = counts[rank]
+        recv = torch.empty(world * (mine * 2 * k + per_status), dtype=torch.int32, device=q.device)
+        dist.all_to_all_single(recv, msg, output_split_sizes=[mine * 2 * k + per_status] * world,
+                               input_split_sizes=[c * 2 * k + per_status for c in counts], group=group)
+        rows = mine
     else:
-        cand_d, cand_i = gather_candidates(d_loc, i_loc, group)
-    return merge_fn(cand_d, cand_i, k)
+        recv = torch.empty(world * msg.numel(), dtype=torch.int32, device=q.device)
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(recv, msg, group=group)
+        else:
+            dist.all_gather(list(recv.view(world, -1).unbind(0)), msg, group=group)   # gloo has no tensor form
+        rows = nq
+    out_d, out_i, merged_status = kern.merge(recv, rows, k, world)
+    kern.defer(merged_status)
+    return out_d, out_i
 
 
 def sharded_kmeans(x_shard: torch.Tensor, n_clusters: int, *, max_iters: int = 100, tol: float = 0.0,

@@ -37,7 +37,12 @@ extern "C" {
 
 /* Device status words (int32[FL_STATUS_WORDS]) written by the kNN / assign kernels.     */
 #define FL_STATUS_WORDS     8
-#define FL_STATUS_ERROR     0  /* 0, or FL_ETIMEOUT when a bounded wait expired          */
+#define FL_STATUS_ERROR     0  /* 0; FL_ETIMEOUT when a bounded wait expired (the results
+                                  of that call are invalid); FL_EUNSUPPORTED when the call
+                                  ran with timing-experiment flags (results invalid);
+                                  FL_EWORKSPACE if more rows failed verification than the
+                                  fallback list holds (cannot happen with a workspace of
+                                  fl_knn_workspace_bytes: the list holds every query)     */
 #define FL_STATUS_WHERE     1  /* which wait expired (role << 16 | barrier index)        */
 #define FL_STATUS_FALLBACK  2  /* rows whose candidate pool failed verification and were
                                   recomputed on the exact CUDA-core path                 */
@@ -99,6 +104,44 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
                    float* out_dist, int32_t* out_idx,
                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 
+/* Row-sharded databases (the reference has no sharded kNN; the closest is its multi-GPU   */
+/* k-means, kmeans/large.py:35-280): fl_knn_f32 in two calls, so that the shards can share */
+/* what the threshold-seeding pass found before the scoring pass runs.  k <= 16, tensor-    */
+/* core mode only.                                                                          */
+/*  1. fl_knn_seed_f32 builds the bf16 query plane in `ws` and writes, per query, the 32     */
+/*     class maxima of a strided sample of this shard's rows to seed_cls                     */
+/*     (f32 [fl_knn_seed_floats(nq)], 32 per padded query row; -inf when the shard is too    */
+/*     small to sample).  It clears `status`.                                                */
+/*  2. The caller takes the element-wise maximum of seed_cls over all shards (an all-reduce  */
+/*     with MAX) and, once per database, the maximum over all shards of the f32 at byte       */
+/*     offset fl_knn_plane_maxnorm_offset(m, d) of each shard's plane (largest row norm).     */
+/*  3. fl_knn_seeded_f32, with the SAME ws (untouched in between), q, nq, d, k and plane,     */
+/*     scores this shard from thresholds derived from the combined maxima: k + 6 rows of the  */
+/*     whole database are known to reach them, and they are lowered by twice the scoring     */
+/*     error bound, so a row this shard leaves out cannot be one of the database's k         */
+/*     nearest.  A shard may therefore return fewer than k rows (padded +inf / -1); merging  */
+/*     all shards' lists with fl_topk_merge_f32 gives the exact result.  Rows that can be     */
+/*     neither proven nor ruled out are recomputed exactly, as in fl_knn_f32; status is not   */
+/*     cleared, so an error of step 1 stays visible.                                          */
+int64_t fl_knn_seed_floats(int64_t nq);
+int     fl_knn_seed_f32(const float* q, int64_t nq, int64_t ldq, int d, int k,
+                        const void* plane, int64_t m, float* seed_cls,
+                        void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+int64_t fl_knn_plane_maxnorm_offset(int64_t m, int d);
+int     fl_knn_seeded_f32(const float* q, int64_t nq, int64_t ldq,
+                          const float* db, int64_t m, int64_t ldb, int d, int k,
+                          const void* plane, int64_t row_offset,
+                          const float* seed_cls, const float* global_maxnorm,
+                          float* out_dist, int32_t* out_idx,
+                          void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
+/* Test hook without a counterpart in the reference: experiment flags of the tensor-core  */
+/* scoring kernel (bit values 1..16 leave work out for timing runs and mark the status     */
+/* words FL_EUNSUPPORTED; 32 makes the producer skip one operand load so that a wait runs   */
+/* out) and the limit of its barrier waits in microseconds (0 = the default 2 s).           */
+/* (0, 0) restores normal operation.  Process-wide; not for concurrent use.                 */
+int     fl_debug_tc_experiment(int flags, unsigned wait_us);
+
 /* Test hook without a counterpart in the reference: runs only the tensor-core scoring    */
 /* pass for nq <= 128 queries and writes scores[i][j] = <q_i, x_j> - ||x_j||^2/2 (bf16      */
 /* products, fp32 accumulation) for every database row j; ld_scores >= m rounded up to 256. */
@@ -122,6 +165,27 @@ int     fl_knn_resolve_mode(int64_t nq, int64_t m, int d, int k);
 /* Entries with idx < 0 are ignored.                                                    */
 int fl_topk_merge_f32(const float* cand_dist, const int32_t* cand_idx, int64_t nq, int ncand,
                       int k, float* out_dist, int32_t* out_idx, void* stream);
+
+/* Exchange format of the row-sharded kNN (no counterpart in the reference).              */
+/* fl_knn_pack_f32 writes this rank's (nq, k) candidates as int32 messages, laid end to   */
+/* end in `out` (fl_knn_pack_ints elements): owner != 0 -> one message per destination    */
+/* rank r holding the query rows [r*base + min(r, rem), ...) of an even split of nq over  */
+/* `world` ranks (the first nq % world ranks get one more); owner == 0 -> one message     */
+/* with all rows.  A message is rows x [k distance bit patterns | k row ids] followed by  */
+/* the FL_STATUS_WORDS status words of the call that produced the candidates (zeros when   */
+/* status is NULL).  fl_knn_merge_packed_f32 takes `world` received messages of `rows`     */
+/* rows each, stored back to back, and writes the k best (distance, id) per row, ascending */
+/* (ids < 0 are padding), plus the folded status: first error word in sender order, sum   */
+/* of the fallback counts.                                                                */
+int64_t fl_knn_pack_ints(int64_t nq, int k, int world, int owner);
+int     fl_knn_pack_f32(const float* dist, const int32_t* idx, int64_t nq, int k, int world, int owner,
+                        const int32_t* status, int32_t* out, void* stream);
+int     fl_knn_merge_packed_f32(const int32_t* msgs, int64_t rows, int k, int world,
+                                float* out_dist, int32_t* out_idx, int32_t* status, void* stream);
+/* fp32 -> bf16 rounded toward -inf and back: halves the bytes of the seeding maxima that  */
+/* the shards exchange; a threshold rounded down stays valid.                              */
+int     fl_f32_to_bf16_down(const float* in, void* out, int64_t n, void* stream);
+int     fl_bf16_to_f32(const void* in, float* out, int64_t n, void* stream);
 
 /* ---------------------------------------------------------------------------------- */
 /* Exact gather distances.  Replaces triton_knn_gather_sqdist                           */
@@ -194,6 +258,20 @@ int     fl_ivf_fine_scan_f32(const float* q, int64_t nq, int64_t ldq,
                              const int32_t* probed, int nprobe, int k,
                              const float* data_hnorm,
                              float* out_dist, int32_t* out_pos,
+                             void* ws, int64_t ws_bytes, void* stream);
+
+/* Cell-contiguous index layout from per-row list labels.  Replaces the torch glue of      */
+/* ivf_flat_build_triton (ivf_flat/triton/build.py:59-95: bincount, cumsum, stable argsort,  */
+/* index_select, .item()) with device work and no host synchronisation.                     */
+/* labels [m] int32 in [0, nlist) (what fl_kmeans_assign_* returns for the coarse centroids).*/
+/* data [m][d] receives the rows grouped by list, rows of one list in their original order   */
+/* (a stable partition); ids [m] int64 the original row of every stored row; list_offsets   */
+/* [nlist+1] int64 the exclusive scan of the list lengths; *max_list_len (device int32, may  */
+/* be NULL) the longest list.                                                               */
+int64_t fl_ivf_build_workspace_bytes(int64_t m, int nlist);
+int     fl_ivf_build_csr_f32(const float* x, int64_t m, int64_t ldx, int d,
+                             const int32_t* labels, int nlist,
+                             float* data, int64_t* ids, int64_t* list_offsets, int32_t* max_list_len,
                              void* ws, int64_t ws_bytes, void* stream);
 
 /* The same fine scan on the tensor cores (k <= 16, d <= 128), the counterpart of the     */

@@ -8,8 +8,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_reference_arm_prints_the_contract_line():
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks: the arm must not run single-threaded
+    env = dict(os.environ, OMP_NUM_THREADS="1")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
-                          "--warmup", "0"], cwd=ROOT, capture_output=True, text=True, timeout=600)
+                          "--warmup", "0"], cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1, out.stdout
@@ -22,3 +24,6 @@ def test_reference_arm_prints_the_contract_line():
     assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in line["config"] and "model" not in line["config"]
+    # the same config keys as the GPU arm's line (both come from bench.config_dict)
+    assert set(line["config"]) == {"workload", "db_rows", "dim", "k", "queries_per_step", "sharding", "mode", "l2"}
+    assert line["cpu_baseline"]["cores"] == (os.cpu_count() or 1)

@@ -155,3 +155,50 @@ def test_row_sharded_index_merges_to_the_unsharded_result():
     mv, mi = topk_merge(cd, ci, 10)
     torch.testing.assert_close(mv, wv, rtol=1e-5, atol=1e-5)
     assert (mi.long() == wi).float().mean().item() > 0.999
+
+
+def test_device_side_build_matches_the_reference_layout():
+    """index_from_centroids (histogram + scan + stable partition on the device) against the
+    reference-built fixture: same offsets, same row order, same stored rows -- the check of
+    tests/test_oracle_golden.py::test_ivf_layout_matches_reference, on the CUDA path."""
+    from flashlib_b200.ivf_flat import _pad_features, index_from_centroids
+    d, _ = golden_index()
+    X = torch.from_numpy(d["x"]).cuda()
+    cents = torch.from_numpy(d["centroids"]).cuda()
+    Xp = _pad_features(X, d["data"].shape[1]).contiguous()
+    idx = index_from_centroids(Xp, cents, D=X.shape[1], nprobe=4)
+    assert idx.list_offsets.dtype == torch.int64 and idx.ids.dtype == torch.int64
+    assert np.array_equal(idx.list_offsets.cpu().numpy(), d["list_offsets"])
+    assert np.array_equal(idx.ids.cpu().numpy(), d["ids"])
+    assert np.array_equal(idx.data.cpu().numpy(), d["data"])
+    lens = np.diff(d["list_offsets"])
+    assert idx.max_list_len == int(lens.max()) and isinstance(idx.max_list_len, int)
+
+
+@pytest.mark.parametrize("m,dim,nlist", [(1, 16, 1), (33, 16, 7), (5000, 24, 300), (300_000, 32, 1024), (70_000, 128, 5000)])
+def test_device_side_build_is_a_stable_partition(m, dim, nlist):
+    """Labels straight into fl_ivf_build_csr_f32: the layout must equal numpy's stable argsort by
+    label, with empty lists (more lists than labels used) and units that end mid-warp."""
+    from flashlib_b200 import _lib
+    from flashlib_b200.knn import _stream_ptr
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(m + nlist)
+    x = torch.randn(m, dim, generator=g).cuda()
+    used = max(1, nlist - nlist // 3)
+    lab = torch.randint(0, used, (m,), generator=g, dtype=torch.int32)
+    labd = lab.cuda()
+    data = torch.empty_like(x)
+    ids = torch.empty(m, dtype=torch.int64, device="cuda")
+    offs = torch.empty(nlist + 1, dtype=torch.int64, device="cuda")
+    longest = torch.empty(1, dtype=torch.int32, device="cuda")
+    ws_bytes = lib.fl_ivf_build_workspace_bytes(m, nlist)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    _lib.check(lib.fl_ivf_build_csr_f32(x.data_ptr(), m, x.stride(0), dim, labd.data_ptr(), nlist, data.data_ptr(),
+                                        ids.data_ptr(), offs.data_ptr(), longest.data_ptr(), ws.data_ptr(), ws_bytes,
+                                        _stream_ptr(x.device)))
+    order = np.argsort(lab.numpy(), kind="stable")
+    counts = np.bincount(lab.numpy(), minlength=nlist)
+    assert np.array_equal(offs.cpu().numpy(), np.concatenate([[0], np.cumsum(counts)]))
+    assert np.array_equal(ids.cpu().numpy(), order)
+    assert torch.equal(data.cpu(), x.cpu()[torch.from_numpy(order)])
+    assert int(longest.item()) == int(counts.max())

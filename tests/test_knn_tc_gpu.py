@@ -160,3 +160,65 @@ def test_cta_pair_variant_in_a_subprocess():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "pair ok" in out.stdout, out.stdout + out.stderr
+
+
+def test_every_query_can_take_the_exact_path():
+    """A large common offset makes the scoring error bound swamp every gap: all 9,000 queries fail
+    their proof, more than the fallback list once held, and every one must come back exact."""
+    g = torch.Generator().manual_seed(17)
+    db = (torch.randn(40_000, 64, generator=g) + 30.0).cuda()
+    q = (torch.randn(9_000, 64, generator=g) + 30.0).cuda()
+    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)
+    assert info["status"][_lib.FL_STATUS_ERROR].item() == 0
+    assert info["fallback_rows"] > 8_000, info["fallback_rows"]
+    qd, dbd = q.double(), db.double()
+    d64 = (qd * qd).sum(-1, keepdim=True) + (dbd * dbd).sum(-1)[None, :] - 2.0 * qd @ dbd.T
+    ref_i = d64.topk(10, dim=1, largest=False).indices.cpu().numpy()
+    res = parity.knn_parity(q.cpu().numpy(), db.cpu().numpy(), d_tc.cpu().numpy(), i_tc.cpu().numpy(), ref_i)
+    assert res["ok"], res
+
+
+def test_bounded_wait_runs_out_and_the_gpu_stays_usable():
+    """The producer leaves out one operand load (experiment flag 32) and the wait limit is 1 ms:
+    the MMA lane's wait for that load runs out, the kernel ends by itself, the status words say
+    where, the Python mirror raises -- and the next ordinary call returns correct neighbours."""
+    from flashlib_b200.knn import _raise_on_status
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(23)
+    db = torch.randn(100_000, 128, generator=g).cuda()
+    q = torch.randn(512, 128, generator=g).cuda()
+    try:
+        _lib.check(lib.fl_debug_tc_experiment(32, 1000))
+        _, _, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, check_status=False)
+        torch.cuda.synchronize()
+        st = info["status"].tolist()
+    finally:
+        _lib.check(lib.fl_debug_tc_experiment(0, 0))
+    assert st[_lib.FL_STATUS_ERROR] == _lib.FL_ETIMEOUT, st
+    assert st[_lib.FL_STATUS_WHERE] >> 16 == 5, hex(st[_lib.FL_STATUS_WHERE])      # role 5: the MMA lane
+    with pytest.raises(_lib.FlashlibError):
+        _raise_on_status(st)
+    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)
+    d_ex, i_ex, _ = knn_f32(q, db, 10, mode=_lib.FL_KNN_EXACT_SIMT)
+    assert info["status"][_lib.FL_STATUS_ERROR].item() == 0
+    torch.testing.assert_close(d_tc, d_ex, rtol=1e-4, atol=1e-4)
+    assert (i_tc == i_ex).float().mean().item() > 0.999
+
+
+def test_timing_experiment_flags_invalidate_the_status():
+    """A launch that leaves work out for a timing run says so in its status words."""
+    from flashlib_b200.knn import _raise_on_status
+    lib = _lib.load()
+    g = torch.Generator().manual_seed(24)
+    db = torch.randn(100_000, 64, generator=g).cuda()
+    q = torch.randn(256, 64, generator=g).cuda()
+    try:
+        _lib.check(lib.fl_debug_tc_experiment(1, 0))
+        _, _, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, check_status=False)
+        torch.cuda.synchronize()
+        st = info["status"].tolist()
+    finally:
+        _lib.check(lib.fl_debug_tc_experiment(0, 0))
+    assert st[_lib.FL_STATUS_ERROR] == _lib.FL_EUNSUPPORTED, st
+    with pytest.raises(_lib.FlashlibError):
+        _raise_on_status(st)
