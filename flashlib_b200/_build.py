@@ -28,6 +28,7 @@ NVCC_FLAGS = [
     "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
+    *os.environ.get("FLASHLIB_B200_NVCC_FLAGS", "").split(),     # e.g. -DFL_TC_PROF (per-role cycle counters)
 ]
 
 

@@ -21,14 +21,24 @@ static int g_profile_on = 0;
 static int g_profile_n = 0;
 static cudaEvent_t g_ev_begin[PROFILE_SLOTS];
 static cudaEvent_t g_ev_end[PROFILE_SLOTS];
+static cudaEvent_t g_ev_end_own[PROFILE_SLOTS];
 static bool g_ev_made = false;
 
+// Mode 2 (fl_profile_enable(2)): instead of one bracket per call, every profile_mark() along an
+// entry point's launch sequence records an event; sample i is the time from mark i to mark i + 1.
+void profile_mark(cudaStream_t st) {
+    if (g_profile_on != 2 || g_profile_n >= PROFILE_SLOTS) return;
+    cudaEventRecord(g_ev_begin[g_profile_n], st);
+    if (g_profile_n > 0) g_ev_end[g_profile_n - 1] = g_ev_begin[g_profile_n];
+    ++g_profile_n;
+}
+
 void profile_begin(cudaStream_t st) {
-    if (!g_profile_on || g_profile_n >= PROFILE_SLOTS) return;
+    if (g_profile_on != 1 || g_profile_n >= PROFILE_SLOTS) return;
     cudaEventRecord(g_ev_begin[g_profile_n], st);
 }
 void profile_end(cudaStream_t st) {
-    if (!g_profile_on || g_profile_n >= PROFILE_SLOTS) return;
+    if (g_profile_on != 1 || g_profile_n >= PROFILE_SLOTS) return;
     cudaEventRecord(g_ev_end[g_profile_n], st);
     ++g_profile_n;
 }
@@ -86,10 +96,15 @@ extern "C" int fl_profile_enable(int on) {
         for (int i = 0; i < PROFILE_SLOTS; ++i) {
             FL_CHECK_CUDA(cudaEventCreate(&g_ev_begin[i]));
             FL_CHECK_CUDA(cudaEventCreate(&g_ev_end[i]));
+            g_ev_end_own[i] = g_ev_end[i];
         }
         g_ev_made = true;
     }
-    g_profile_on = on ? 1 : 0;
+    if (g_ev_made && g_profile_on == 2) {
+        // mode 2 aliased the end events to the following marks: give every slot its own event back
+        for (int i = 0; i < PROFILE_SLOTS; ++i) g_ev_end[i] = g_ev_end_own[i];
+    }
+    g_profile_on = on == 2 ? 2 : (on ? 1 : 0);
     g_profile_n = 0;
     return FL_OK;
 }
@@ -98,7 +113,7 @@ extern "C" int fl_profile_count(void) { return fl::g_profile_n; }
 
 extern "C" int fl_profile_read_ms(int i, float* ms) {
     using namespace fl;
-    FL_CHECK_ARG(ms && i >= 0 && i < g_profile_n, "fl_profile_read_ms: no such sample %d", i);
+    FL_CHECK_ARG(ms && i >= 0 && i < (g_profile_on == 2 ? g_profile_n - 1 : g_profile_n), "fl_profile_read_ms: no such sample %d", i);
     FL_CHECK_CUDA(cudaEventSynchronize(g_ev_end[i]));
     FL_CHECK_CUDA(cudaEventElapsedTime(ms, g_ev_begin[i], g_ev_end[i]));
     return FL_OK;

@@ -19,6 +19,8 @@ void count_launch();
 // kernel of an entry point with CUDA events recorded on the caller's stream.
 void profile_begin(cudaStream_t st);
 void profile_end(cudaStream_t st);
+// fl_profile_enable(2): one event per mark along an entry point's launch sequence.
+void profile_mark(cudaStream_t st);
 
 #define FL_CHECK_ARG(cond, ...)                                                         \
     do {                                                                                \

@@ -168,6 +168,305 @@ __global__ void ivf_tc_gather_kernel(const float* __restrict__ q, int64_t ldq, i
     }
 }
 
+// Starting threshold of every query from the seeding pass.  The pass left, for every gathered row
+// (= one (query, probed list) pair), the 32 class maxima of the first tiles of that list: disjoint
+// sets of rows, and the lists of one query are disjoint too.  One warp per query folds its pairs'
+// maxima into the 32 largest and takes the `rank`-th: at least `rank` >= k rows of the probed
+// lists score that much.  The threshold is that score lowered by twice the scoring error bound
+// (plus the fp32 slack): the k best exact distances then lie below the bound the finalisation
+// derives from the threshold, so its proof holds for every query whose pools never overflow --
+// a threshold without the margin would cut closer to the k-th neighbour than the proof can see.
+__global__ void __launch_bounds__(128) ivf_tc_seed_select_kernel(const float* __restrict__ seed_cls,
+                                                                 const int* __restrict__ pair_row, int64_t nq, int nprobe,
+                                                                 int rank, const float* __restrict__ q, int64_t ldq, int d,
+                                                                 const float* __restrict__ maxnorm, float eps_rel,
+                                                                 float* __restrict__ tau_q) {
+    const int lane = threadIdx.x & 31;
+    const int64_t qi = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (qi >= nq) return;
+    float pick;
+    if (nprobe <= 16) {
+        // lane = class: every lane holds its class maximum of up to 16 pairs; `rank` rounds each
+        // take the largest value left in the warp away from the lane that holds it
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int r = j < nprobe ? __ldg(pair_row + qi * nprobe + j) : -1;
+            v[j] = r >= 0 ? __ldg(seed_cls + (int64_t)r * 32 + lane) : neg_inf();
+        }
+        pick = neg_inf();
+        for (int round = 0; round < rank; ++round) {
+            float m = v[0];
+#pragma unroll
+            for (int j = 1; j < 16; ++j) m = fmaxf(m, v[j]);
+            float wmax = m;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(FULL_MASK, wmax, o));
+            pick = wmax;
+            if (!(wmax > neg_inf())) break;            // fewer than `rank` rows were sampled
+            const unsigned owners = __ballot_sync(FULL_MASK, m == wmax);
+            if (lane == __ffs(owners) - 1) {
+                bool gone = false;                     // one copy only: equal scores are different rows
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const bool hit = !gone && v[j] == wmax;
+                    v[j] = hit ? neg_inf() : v[j];
+                    gone = gone || hit;
+                }
+            }
+        }
+    } else {
+        float key[1] = {neg_inf()};
+        uint32_t id[1] = {0};
+        for (int j = 0; j < nprobe; ++j) {
+            const int r = __ldg(pair_row + qi * nprobe + j);
+            if (r < 0) continue;                       // the list has no rows (no work item, no maxima)
+            float kin[1] = {__ldg(seed_cls + (int64_t)r * 32 + lane)};
+            uint32_t iin[1] = {0};
+            warp_sort_desc<1, false>(kin, iin);
+            warp_merge_desc<1, false>(key, id, kin, iin);
+        }
+        pick = __shfl_sync(FULL_MASK, key[0], rank - 1);     // -inf while fewer than `rank` rows were sampled
+    }
+    float qsq = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(q + qi * ldq + c); qsq += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
+    const float mn = __ldg(maxnorm);
+    if (pick > neg_inf()) pick -= 2.f * eps_rel * sqrtf(qsq) * mn + 1e-5f * (qsq + mn * mn);
+    if (lane == 0) tau_q[qi] = pick;
+}
+
+// Finalisation of the inverted-file scan: one warp per query.
+//
+// The scoring pass left, per gathered row (= (query, probed list) pair) and warpgroup, a pool of up
+// to IVF_POOL (score, plane row) pairs in global memory with its entry count and final threshold;
+// every row of the query's probed lists that is in no pool scored at most u = the largest of those
+// thresholds.  The warp collects the entries above u, sorts them by score, re-scores them in that
+// order with exact fp32 sum (q - x)^2 and stops once k exact distances lie below the lower bound that
+// the next score puts on everything not yet re-scored; the result is the k rows of least exact
+// distance, ordered by (distance, row).  When more than IVF_LIST entries lie above u a floor keeps
+// the best few dozen (what it drops counts as not re-scored).  A query whose proof fails, or whose
+// pools hold more than IVF_GATHER entries, is queued for the exact scan.
+constexpr int IVF_POOL = 64, IVF_LIST = 256, IVF_GATHER = 1024;
+
+template <int NPL>
+__device__ __forceinline__ void ivf_rerank(const float* __restrict__ s_sc, const uint32_t* __restrict__ s_id, int total,
+                                           const float* __restrict__ qp, const float* __restrict__ data, int64_t ldd, int d,
+                                           int vec, int k, float u, float qsq, float eps, float slack, float* out_dist,
+                                           int32_t* out_pos, bool& proven) {
+    const int lane = threadIdx.x & 31;
+    float key[NPL];
+    uint32_t id[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const int e = (r << 5) | lane;
+        key[r] = e < total ? s_sc[e] : neg_inf();
+        id[r] = e < total ? s_id[e] : INVALID_ID;
+    }
+    warp_sort_desc<NPL, false>(key, id);
+    float bound = u;
+    bool stop = false;
+    float dist[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) dist[r] = pos_inf();
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        for (int l0 = 0; l0 < 32; l0 += 4) {
+            if (stop || (r << 5) + l0 >= total) break;
+            if ((l0 & 7) == 0 && (r << 5) + l0 >= ((k + 7) & ~7)) {
+                const float nxt = __shfl_sync(FULL_MASK, key[r], l0);
+                const float T = qsq - 2.f * (fmaxf(nxt, u) + eps) - slack;
+                int below = 0;
+#pragma unroll
+                for (int rr = 0; rr < NPL; ++rr) below += __popc(__ballot_sync(FULL_MASK, dist[rr] < T));
+                if (below >= k) { stop = true; bound = fmaxf(u, nxt); break; }
+            }
+            uint32_t cid[4];
+            float a[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                cid[t] = __shfl_sync(FULL_MASK, id[r], l0 + t);
+                a[t] = 0.f;
+            }
+            if (vec) {
+                for (int c = lane * 4; c < d; c += 128) {
+                    const float4 qv = __ldg(reinterpret_cast<const float4*>(qp + c));
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (cid[t] != INVALID_ID) {
+                            const float4 xv = __ldg(reinterpret_cast<const float4*>(data + (int64_t)cid[t] * ldd + c));
+                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
+                            a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                        }
+                    }
+                }
+            } else {
+                for (int c = lane; c < d; c += 32) {
+                    const float qv = __ldg(qp + c);
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        if (cid[t] != INVALID_ID) {
+                            const float df = qv - __ldg(data + (int64_t)cid[t] * ldd + c);
+                            a[t] += df * df;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
+                if (lane == l0 + t && cid[t] != INVALID_ID) dist[r] = a[t];
+            }
+        }
+    }
+    float k2[NPL];
+    uint32_t id2[NPL];
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const bool ok = dist[r] < pos_inf();
+        k2[r] = ok ? -dist[r] : neg_inf();
+        id2[r] = ok ? id[r] : INVALID_ID;
+    }
+    warp_sort_desc<NPL, true>(k2, id2);
+    float dk = pos_inf();
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        if (((k - 1) >> 5) == r) {
+            const float v = __shfl_sync(FULL_MASK, k2[r], (k - 1) & 31);
+            dk = (v > neg_inf()) ? -v : pos_inf();
+        }
+    }
+    // every row that was not re-scored has a score <= bound: its distance is at least qsq - 2 (bound + eps)
+    proven = bound == neg_inf() || dk < qsq - 2.f * (bound + eps) - slack;
+#pragma unroll
+    for (int r = 0; r < NPL; ++r) {
+        const int e = (r << 5) | lane;
+        if (e < k) {
+            const bool ok = id2[r] != INVALID_ID;
+            out_dist[e] = ok ? -k2[r] : pos_inf();
+            out_pos[e] = ok ? (int32_t)id2[r] : -1;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) ivf_tc_finalize_kernel(
+    const float* __restrict__ q, int64_t nq, int64_t ldq, int d, int vec, const float* __restrict__ data, int64_t ldd,
+    const int* __restrict__ pair_row, int nprobe, const float2* __restrict__ pools, const int* __restrict__ pool_cnt,
+    const float* __restrict__ pool_tau, const int* __restrict__ row_map, int64_t rows_max, int k, float eps_rel,
+    const float* __restrict__ maxnorm, float* __restrict__ out_dist, int32_t* __restrict__ out_pos, int* fb_count,
+    int* fb_list) {
+    __shared__ float s_sc[4][IVF_GATHER];
+    __shared__ uint32_t s_id[4][IVF_GATHER];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int64_t qi = (int64_t)blockIdx.x * 4 + w;
+    if (qi >= nq) return;
+    const float* qp = q + qi * ldq;
+    float qsq = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(qp + c); qsq += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
+    const float mn = __ldg(maxnorm);
+    const float eps = eps_rel * sqrtf(qsq) * mn;
+    const float slack = 1e-5f * (qsq + mn * mn);
+
+    // Gather: 32 pools at a time, one pool per lane for the bookkeeping (gathered row, entry count,
+    // threshold: independent loads), then the pools' entries are copied to the warp's list at
+    // the offsets a prefix sum of the counts gives -- no load waits for another.
+    float u = neg_inf();
+    int total = 0;
+    bool overflow = false;
+    for (int base = 0; base < 2 * nprobe; base += 32) {
+        const int pi = base + lane;
+        int r = -1, n = 0;
+        if (pi < 2 * nprobe) r = __ldg(pair_row + qi * nprobe + (pi >> 1));
+        if (r >= 0) {
+            n = __ldg(pool_cnt + (int64_t)r * 2 + (pi & 1));
+            n = n < IVF_POOL ? n : IVF_POOL;
+            u = fmaxf(u, __ldg(pool_tau + (int64_t)r * 2 + (pi & 1)));
+        }
+        int off = n;                                  // inclusive prefix sum of the counts
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(FULL_MASK, off, o);
+            if (lane >= o) off += t;
+        }
+        const int chunk_total = __shfl_sync(FULL_MASK, off, 31);
+        off += total - n;                             // exclusive, from the list's start
+        if (total + chunk_total > IVF_GATHER) { overflow = true; break; }
+#pragma unroll 4
+        for (int pl = 0; pl < 32; ++pl) {
+            const int np = __shfl_sync(FULL_MASK, n, pl);
+            const int op = __shfl_sync(FULL_MASK, off, pl);
+            const int rp = __shfl_sync(FULL_MASK, r, pl);
+            if (np == 0) continue;
+            const float2* pool = pools + ((int64_t)rp * 2 + ((base + pl) & 1)) * IVF_POOL;
+            for (int e = lane; e < np; e += 32) {
+                const float2 v = pool[e];
+                s_sc[w][op + e] = v.x;
+                s_id[w][op + e] = __float_as_uint(v.y);
+            }
+        }
+        total += chunk_total;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
+    __syncwarp();
+    bool proven = false;
+    float* od = out_dist + qi * k;
+    int32_t* op = out_pos + qi * k;
+    if (!overflow) {
+        // plane rows -> data rows (padding rows and entries at or below u drop out), and, when more
+        // than IVF_LIST entries are left, a floor f0 that keeps about the best (k + 14) x a few:
+        // the (k+14)-th largest of the 32 lane maxima, as in the kNN finalisation
+        float lmax = neg_inf();
+        for (int e = lane; e < total; e += 32) {
+            const uint32_t raw = s_id[w][e];
+            int mapped = -1;
+            if (s_sc[w][e] > u && raw < (uint32_t)rows_max) mapped = __ldg(row_map + raw);
+            s_id[w][e] = mapped >= 0 ? (uint32_t)mapped : INVALID_ID;
+            if (mapped < 0) s_sc[w][e] = neg_inf(); else lmax = fmaxf(lmax, s_sc[w][e]);
+        }
+        __syncwarp();
+        float cut = u;
+        if (total > IVF_LIST) {
+            int rank = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float o = __shfl_sync(FULL_MASK, lmax, j);
+                rank += (o > lmax || (o == lmax && j < lane)) ? 1 : 0;
+            }
+            const int want = k + 14 < 32 ? k + 14 : 32;
+            const unsigned sel = __ballot_sync(FULL_MASK, rank == want - 1);
+            cut = fmaxf(u, __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1));
+        }
+        // compact the list in place to the entries above the cut (cut == u: drops only the invalid ones)
+        const unsigned lt = (1u << lane) - 1u;
+        int kept = 0;
+        for (int e0 = 0; e0 < total; e0 += 32) {
+            const int e = e0 + lane;
+            float sc = neg_inf();
+            uint32_t id = INVALID_ID;
+            if (e < total) { sc = s_sc[w][e]; id = s_id[w][e]; }
+            const bool keep = id != INVALID_ID && (cut == u ? true : sc >= cut);
+            const unsigned mask = __ballot_sync(FULL_MASK, keep);
+            __syncwarp();
+            if (keep) { const int pos = kept + __popc(mask & lt); s_sc[w][pos] = sc; s_id[w][pos] = id; }   // pos <= e
+            kept += __popc(mask);
+            __syncwarp();
+        }
+        if (kept <= IVF_LIST) {
+            // rows dropped by the floor scored below it: they count as "not re-scored"
+            const float bound0 = cut;
+            if (kept <= 64) ivf_rerank<2>(s_sc[w], s_id[w], kept, qp, data, ldd, d, vec, k, bound0, qsq, eps, slack, od, op, proven);
+            else if (kept <= 128) ivf_rerank<4>(s_sc[w], s_id[w], kept, qp, data, ldd, d, vec, k, bound0, qsq, eps, slack, od, op, proven);
+            else ivf_rerank<8>(s_sc[w], s_id[w], kept, qp, data, ldd, d, vec, k, bound0, qsq, eps, slack, od, op, proven);
+        }
+    }
+    if (!proven && lane == 0) fb_list[atomicAdd(fb_count, 1)] = (int)qi;      // the list holds every query
+}
+
 // Exact scan for the queries the proof rejected: one block per listed query walks the rows of the
 // query's probed lists (one warp per row, fp32 sum (q - x)^2 with the summation order of the
 // finalisation kernel), collects rows closer than the running k-th distance and compacts the
@@ -251,7 +550,7 @@ __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
 struct IvfTcWs {
     int64_t npairs, max_items, cap_rows; int d_pad, pitch;
     int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_pair_row, off_item_t0, off_item_t1,
-        off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_part_sc, off_part_id, off_part_tau, off_fblist, bytes;
+        off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_seed_cls, off_pools, off_part_cnt, off_part_tau, off_fblist, bytes;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -268,7 +567,6 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
     w.d_pad = (int)round_up(d, 64);
     w.pitch = w.d_pad + PLANE_AUG_COLS;
     (void)k;
-    const int plen = tc_deep_partial_len();
     int64_t cur = 0;
     w.off_cnt = take(cur, (int64_t)(nlist + 1) * 4);
     w.off_pair_off = take(cur, (int64_t)(nlist + 1) * 4);
@@ -284,8 +582,9 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
     w.off_counters = take(cur, 1024);
     w.off_qplane = take(cur, w.cap_rows * w.pitch * 2);
     w.off_tau = take(cur, w.cap_rows * 4);
-    w.off_part_sc = take(cur, w.cap_rows * plen * 4);
-    w.off_part_id = take(cur, w.cap_rows * plen * 4);
+    w.off_seed_cls = take(cur, w.cap_rows * 32 * 4);
+    w.off_pools = take(cur, w.cap_rows * tc_taus_per_range() * tc_pair_pool_cap() * 8);
+    w.off_part_cnt = take(cur, w.cap_rows * tc_taus_per_range() * 4);
     w.off_part_tau = take(cur, w.cap_rows * tc_taus_per_range() * 4);
     w.off_fblist = take(cur, nq * 4);
     w.bytes = cur;
@@ -381,58 +680,73 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     FL_CHECK_CUDA(cudaMemsetAsync(counters, 0, 1024, st));
     FL_CHECK_CUDA(cudaMemsetAsync(pair_row, 0xFF, (size_t)w.npairs * 4, st));
 
+    profile_mark(st);      // 0: grouping
     // group the pairs by list, cut every list's pairs into query tiles
     int rc = launch_ivf_group(probed, w.npairs, nlist, IVF_TC_BQ, list_offsets, cnt, pair_off, item_off, cursor,
                               sorted_pair, st);
     if (rc != FL_OK) return rc;
+    profile_mark(st);      // 1: item table
     ivf_tc_items_kernel<<<(unsigned)nlist, 128, 0, st>>>(cnt, pair_off, item_off, sorted_pair, tile_off, nlist, item_t0,
                                                         item_t1, grow, pair_row, live_rows);
     FL_CHECK_LAUNCH();
+    profile_mark(st);      // 2: gathered query plane
     ivf_tc_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(
         q, ldq, d, nprobe, grow, live_rows, reinterpret_cast<__nv_bfloat16*>(base + w.off_qplane), tau,
         reinterpret_cast<int*>(base + w.off_row_query), w.d_pad);
     FL_CHECK_LAUNCH();
     float* tau_q = reinterpret_cast<float*>(base + w.off_tau_q);
-    rc = launch_fill_f32(tau_q, nq, -INFINITY, st);
-    if (rc != FL_OK) return rc;
 
     TcKnnParams tp{};
     tp.qplane = base + w.off_qplane; tp.nq = w.cap_rows; tp.nq_pad = w.cap_rows;
     tp.dbrows = pl + L.pl.off_rows; tp.hnorm = reinterpret_cast<const float*>(pl + L.pl.off_hnorm);
     tp.m = L.rows_max; tp.m_pad = L.pl.m_pad; tp.d_pad = L.pl.d_pad; tp.K1 = tc_deep_pool_size();
-    tp.deep_pools = 1;     // a query has two pools per probed list only
+    tp.deep_pools = 0;
     tp.nsplit = 1; tp.tiles_per_split = L.pl.m_pad / IVF_TC_TILE;
-    tp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
-    tp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    tp.pair_pools = base + w.off_pools;                    // pools in global memory, four ring slots
+    tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
     tp.tau = tau; tp.status = status;
     tp.part_tau = reinterpret_cast<float*>(base + w.off_part_tau);
     tp.k = k;
     tp.nq_dev = live_rows; tp.item_t0 = item_t0; tp.item_t1 = item_t1;
     tp.row_query = reinterpret_cast<const int*>(base + w.off_row_query); tp.tau_q = tau_q;
     profile_begin(st);
+    profile_mark(st);      // 3: seeding pass
+    // Seeding: the first tile of every (list, query group) item with the branch-free class-maxima
+    // epilogue, then one threshold per query that k + 6 rows of its probed lists reach.  Without it
+    // every pool starts cold and most of the scan is spent inserting and compacting.
+    {
+        TcKnnParams sd = tp;
+        sd.seed_cls = reinterpret_cast<float*>(base + w.off_seed_cls);
+        sd.item_tile_cap = 1;
+        rc = launch_knn_tc_seed(sd, st);
+        if (rc != FL_OK) return rc;
+        const int rank = k + 6 < 32 ? k + 6 : 32;
+        profile_mark(st);  // 4: threshold selection
+        ivf_tc_seed_select_kernel<<<(unsigned)ceil_div(nq, 4), 128, 0, st>>>(
+            sd.seed_cls, pair_row, nq, nprobe, rank, q, ldq, d, reinterpret_cast<const float*>(pl + L.pl.off_meta), 0.004f, tau_q);
+        FL_CHECK_LAUNCH();
+    }
+    profile_mark(st);      // 5: scoring pass
     rc = launch_knn_tc(tp, st);
     profile_end(st);
+    profile_mark(st);      // 6: finalisation
     if (rc != FL_OK) return rc;
 
     const int vecq = (ldq % 4 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
     const int vecd = (ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(data) & 15) == 0);
-    FinalizeParams fp{};
-    fp.q = q; fp.ldq = ldq; fp.count = nq; fp.db = data; fp.m = m; fp.ldb = ldd; fp.d = d;
-    fp.vec = vecq && vecd && (d % 4 == 0);
-    fp.part_sc = tp.part_sc; fp.part_id = tp.part_id; fp.nsplit = nprobe; fp.K1 = tc_deep_partial_len();
-    fp.k = k; fp.rerank = fp.K1; fp.row_offset = 0;
-    fp.part_tau = tp.part_tau; fp.ntau = nprobe * tc_taus_per_range();
-    fp.out_dist = out_dist; fp.out_idx = out_pos;
-    fp.verify = 1; fp.eps_rel = 0.004f;
-    fp.maxnorm = reinterpret_cast<const float*>(pl + L.pl.off_meta);
-    fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = (int)nq;
-    fp.pool_row = pair_row; fp.id_map = row_map; fp.id_bound = L.rows_max;
-    rc = launch_knn_finalize(fp, nq, st);
-    if (rc != FL_OK) return rc;
+    static_assert(IVF_POOL == 64, "pool geometry of the scoring kernel's global-pool mode");
+    const int vec = vecq && vecd && (d % 4 == 0);
+    ivf_tc_finalize_kernel<<<(unsigned)ceil_div(nq, 4), 128, 0, st>>>(
+        q, nq, ldq, d, vec, data, ldd, pair_row, nprobe, reinterpret_cast<const float2*>(base + w.off_pools), tp.part_cnt,
+        tp.part_tau, row_map, L.rows_max, k, 0.004f, reinterpret_cast<const float*>(pl + L.pl.off_meta), out_dist, out_pos,
+        fb_count, fb_list);
+    FL_CHECK_LAUNCH();
+    profile_mark(st);      // 7: exact pass for unproven queries
     rc = launch_fallback_fixup(fb_count, (int)nq, status, tc_deep_pool_size(), st);
     if (rc != FL_OK) return rc;
     ivf_exact_query_kernel<<<(unsigned)(2 * sm_count()), IVFX_THREADS, 0, st>>>(
-        q, ldq, data, ldd, d, fp.vec, list_offsets, nlist, probed, nprobe, k, fb_list, fb_count, out_dist, out_pos);
+        q, ldq, data, ldd, d, vec, list_offsets, nlist, probed, nprobe, k, fb_list, fb_count, out_dist, out_pos);
     FL_CHECK_LAUNCH();
+    profile_mark(st);      // 8: end
     return FL_OK;
 }

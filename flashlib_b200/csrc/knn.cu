@@ -331,6 +331,9 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     TcSeedMargin mg{};
     if (gmaxnorm != nullptr) {
         mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.maxnorm = gmaxnorm; mg.eps_rel = 0.004f; mg.cert_out = cert;
+    } else if (tc_seed_dense(L.m_pad, k)) {
+        mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.eps_rel = 0.004f; mg.cert_out = nullptr;
+        mg.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
     }
     rc = launch_knn_tc_seed_select(tp, mg, st);
     if (rc != FL_OK) return rc;

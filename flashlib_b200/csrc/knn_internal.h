@@ -109,6 +109,10 @@ struct TcKnnParams {
     float* tau_q;            //   per query (f32, -inf initialised) shared by the rows of that query
     const int* item_t0;      // optional, with nsplit == 1: database tile range [item_t0[t], item_t1[t]) of
     const int* item_t1;      //   query tile t instead of one uniform range (inverted-file scan)
+    int item_tile_cap;       // seeding pass over item tables: tiles of every item's range it samples
+    void* pair_pools;        // optional (k <= 16): pools kept in global memory as (score f32, row u32) pairs,
+                             //   [nq_pad][nsplit][tc_taus_per_range][tc_pair_pool_cap]; entry counts go to
+                             //   part_cnt, thresholds to part_tau, part_sc / part_id are not used
     int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)
     int32_t* status;
 };
@@ -124,6 +128,8 @@ int tc_use_deep_pools(int k, int d_pad, int nsplit, int64_t nq_pad);
 int tc_deep_partial_len();
 // Thresholds the tensor-core pass publishes per (query, range).
 int tc_taus_per_range();
+// Slots of a (query row, warpgroup) pool in the global pair-pool mode.
+int tc_pair_pool_cap();
 // 1 when FL_KNN_AUTO should take the tensor-core path for this shape.
 int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
 // Margin applied by the threshold selection when the class maxima cover more than this shard's rows
@@ -139,6 +145,8 @@ struct TcSeedMargin {
 int launch_knn_tc_seed(const TcKnnParams& p, cudaStream_t st);
 int launch_knn_tc_seed_select(const TcKnnParams& p, const TcSeedMargin& mg, cudaStream_t st);
 int launch_knn_tc_scoring(const TcKnnParams& p, cudaStream_t st);
+// 1 when thresholds seeded for this shape need the proof's margin (sample = a large share of the rows).
+int tc_seed_dense(int64_t m_pad, int k);
 // Experiment flags of the scoring kernel and the limit of its barrier waits (0: default).
 void tc_debug_set(int flags, unsigned wait_us);
 // Same as launch_knn_tc, additionally dumping the scores of query tile 0 to dbg[128][dbg_ld].

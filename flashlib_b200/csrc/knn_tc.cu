@@ -79,8 +79,16 @@ static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_P
 // free accumulator, [3] epilogue waiting for an accumulator, [4] cycles in the epilogue's
 // second pass, [5] column groups revisited there, [6] pool compactions, [7] scores appended
 // (warp 0 / lane 0 views), [8] kernel cycles, [9] tiles.
+// The counters cost registers in the epilogue warps, so they are compiled in only with -DFL_TC_PROF
+// (FLASHLIB_B200_NVCC_FLAGS=-DFL_TC_PROF python -m flashlib_b200._build --force); otherwise
+// fl_debug_tc_prof_read returns zeros.
 constexpr int TC_PROF_WORDS = 16;
 __device__ unsigned long long g_tc_prof[160 * TC_PROF_WORDS];
+#ifdef FL_TC_PROF
+#define TC_PROF(...) __VA_ARGS__
+#else
+#define TC_PROF(...)
+#endif
 
 struct TcKernelParams {
     int n_qtiles, n_tiles, nsplit, tiles_per_split, nkc, nstage;
@@ -95,7 +103,9 @@ struct TcKernelParams {
     float* tau_q;            //   a running threshold per query shared by all rows of that query
     const int* item_t0;      // optional (one range per query tile): first / one-past-last database
     const int* item_t1;      //   tile of query tile `it`, instead of the uniform ranges
+    int item_tile_cap;       // > 0: at most this many tiles of every table range (seeding over item tables)
     float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
+    float2* gpool;           // global-pool mode: (score, row) pairs, [nq_pad][nsplit][TC_NWG][TC_GP_CAP]
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
     int32_t* status;
     uint32_t wait_hint_ns;   // suspend-time hint of the barrier waits
@@ -112,6 +122,19 @@ struct TcKernelParams {
     float* dbg_scores;       // optional: [128][n_tiles*256] scores of query tile 0
     int64_t dbg_ld;
 };
+
+// Database tiles [t0, t1) of work item `it`: a uniform range of the whole plane, or the item's own
+// range from the tables (cut to item_tile_cap tiles when that is set).
+__device__ __forceinline__ void tc_item_range(const TcKernelParams& p, int it, int split, int& t0, int& t1) {
+    if (p.item_t0 != nullptr) {
+        t0 = __ldg(p.item_t0 + it);
+        t1 = __ldg(p.item_t1 + it);
+        if (p.item_tile_cap > 0) t1 = min(t1, t0 + p.item_tile_cap);
+    } else {
+        t0 = split * p.tiles_per_split;
+        t1 = min(p.n_tiles, t0 + p.tiles_per_split);
+    }
+}
 
 __device__ __forceinline__ void tc_report_timeout(int32_t* status, int role, int which) {
     if (status) {
@@ -137,6 +160,40 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
     return make_float2(__int_as_float(cnt), tau);
 }
 
+// Same for pools stored as (score, row) pairs of 8 bytes (the deep-pool mode), `stride` pairs apart.
+template <int CAP, int K1>
+static __device__ __noinline__ float2 tc_compact_rows_pairs(unsigned need, float2* warp_pool, int stride, int cnt, float tau) {
+    constexpr int NPL = (CAP + 31) / 32;
+    const int lane = threadIdx.x & 31;
+    __syncwarp();
+    while (need) {
+        const int src = __ffs(need) - 1;
+        need &= need - 1;
+        const int n = __shfl_sync(FULL_MASK, cnt, src);
+        float2* pool = warp_pool + src * stride;
+        float key[NPL];
+        uint32_t id[NPL];
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+            const int e = (r << 5) | lane;
+            const float2 v = e < n ? pool[e] : make_float2(neg_inf(), __uint_as_float(INVALID_ID));
+            key[r] = v.x;
+            id[r] = __float_as_uint(v.y);
+        }
+        warp_sort_desc<NPL, false>(key, id);
+        float thr = neg_inf();
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+            const int e = (r << 5) | lane;
+            if (e < K1) pool[e] = make_float2(key[r], __uint_as_float(id[r]));
+            if (((K1 - 1) >> 5) == r) thr = __shfl_sync(FULL_MASK, key[r], (K1 - 1) & 31);
+        }
+        __syncwarp();
+        if (lane == src) { cnt = min(n, K1); tau = fmaxf(tau, n >= K1 ? thr : neg_inf()); }
+    }
+    return make_float2(__int_as_float(cnt), tau);
+}
+
 // MODE 1 (TC_MODE_SEED) turns the kernel into the threshold-seeding pass: it scans a strided sample of
 // the database tiles and, instead of pools, keeps 16 running maxima per query row over
 // disjoint column classes; their minimum is a score that 16 distinct rows reach, i.e. a valid
@@ -153,8 +210,21 @@ static __device__ __noinline__ float2 tc_compact_rows(unsigned need, float* warp
 // count is published with it.
 //
 // MODE 4 (TC_MODE_KNN_MID) is MODE 0 with deeper pools in shared memory (24 of 48 kept, 64
-// published): for callers whose queries have only a few pools each.
-constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3, TC_MODE_KNN_MID = 4;
+// published): for callers whose queries have only a few pools each (a small database scored as
+// one range; the inverted-file scan, where a query row meets only the tiles of one list).  There a
+// row has a candidate in most tiles, which the screen-then-revisit epilogue of MODE 0 handles
+// badly (every group of columns ends up revisited, one latency-bound step each); this mode
+// compares every score against the row's threshold and appends the passing ones with predicated
+// 8-byte stores -- three instructions per score, no branch, no second pass.
+//
+// MODE 5 (TC_MODE_KNN_GPOOL) is MODE 4 with the pools in global memory, as (score, row) pairs in
+// the buffer the finalisation reads (64 slots per (query row, warpgroup), 24 kept at a
+// compaction, entry counts published): no pool takes shared memory, so the TMA ring is four
+// slots deep -- two whole tiles, where MODE 4 has room for one and stalls on every load -- and
+// nothing is copied out when an item ends.  The inverted-file scan runs in this mode.
+constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3, TC_MODE_KNN_MID = 4,
+              TC_MODE_KNN_GPOOL = 5;
+constexpr int TC_GP_K1 = 24, TC_GP_CAP = 64;
 //
 // PAIR: two CTAs of a cluster work as one (tcgen05 cta_group::2).  CTA r of the pair owns query
 // tile 2 i + r of pair-item i, loads its own query tile and rows 128 r .. 128 r + 127 of every
@@ -242,7 +312,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t fill = 0;     // database chunks issued so far
             uint32_t item_no = 0;
             bool ok = true;
-            long long prof_a = 0;
+            TC_PROF(long long prof_a = 0;)
             // loads of a pair are credited to the leader's barrier, which expects both CTAs' bytes
             auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
                 if (PAIR) tma_load_2d_pair(dst, map, c0, c1, bar); else tma_load_2d(dst, map, c0, c1, bar);
@@ -250,8 +320,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
                 const int split = it / n_units, unit = it - split * n_units;
                 const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
-                const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
-                const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
+                int t0, t1;
+                tc_item_range(p, it, split, t0, t1);
                 if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
                 }
@@ -268,11 +338,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     for (int kc = 0; kc < p.nkc; ++kc, ++fill) {
                         const int s = fill % p.nstage;
                         const uint32_t ph = (fill / p.nstage) & 1;
-                        const long long c0 = clock64();
+                        TC_PROF(const long long c0 = clock64();)
                         if (!mbar_wait(BAR(B_EMPTY + s), ph ^ 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 4, B_EMPTY + s); ok = false; break;
                         }
-                        prof_a += clock64() - c0;
+                        TC_PROF(prof_a += clock64() - c0;)
                         const bool last = (kc == p.nkc - 1);
                         const int row0 = t * p.tile_stride * TC_BN + (int)cta_rank * B_ROWS;
                         if (DBG && (p.dbg_flags & 32) && fill == 3) continue;   // this slot never fills
@@ -282,7 +352,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     }
                 }
             }
-            if (blockIdx.x < 160) g_tc_prof[blockIdx.x * TC_PROF_WORDS + 0] = prof_a;
+            TC_PROF(if (blockIdx.x < 160) g_tc_prof[blockIdx.x * TC_PROF_WORDS + 0] = prof_a;)
             if (!ok) {
                 // give copies already in flight a bounded time to land before the CTA exits
                 const uint64_t t_start = globaltimer_ns();
@@ -302,31 +372,31 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             uint32_t tile_no = 0;  // tiles issued so far (accumulator ring position)
             uint32_t item_no = 0;
             bool ok = true;
-            long long prof_full = 0, prof_tempty = 0;
+            TC_PROF(long long prof_full = 0; long long prof_tempty = 0;)
             for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
                 const int split = it / n_units;
-                const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
-                const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
+                int t0, t1;
+                tc_item_range(p, it, split, t0, t1);
                 if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 5, B_AFULL); ok = false; break;
                 }
                 for (int t = t0; t < t1 && ok; ++t, ++tile_no) {
                     const int b = tile_no & 1;
-                    const long long c0 = clock64();
+                    TC_PROF(const long long c0 = clock64();)
                     if (!mbar_wait(BAR(B_TEMPTY + b), ((tile_no >> 1) & 1) ^ 1, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                         tc_report_timeout(p.status, 5, B_TEMPTY + b); ok = false; break;
                     }
-                    prof_tempty += clock64() - c0;
+                    TC_PROF(prof_tempty += clock64() - c0;)
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + b * TC_BN;
                     for (int kc = 0; kc < p.nkc; ++kc, ++use) {
                         const int s = use % p.nstage;
                         const uint32_t ph = (use / p.nstage) & 1;
-                        const long long c1 = clock64();
+                        TC_PROF(const long long c1 = clock64();)
                         if (!mbar_wait(BAR(B_FULL + s), ph, abort_flag, p.wait_ns, p.wait_hint_ns)) {
                             tc_report_timeout(p.status, 5, B_FULL + s); ok = false; break;
                         }
-                        prof_full += clock64() - c1;
+                        TC_PROF(prof_full += clock64() - c1;)
                         tc_fence_after_sync();
                         const uint64_t da = umma_desc(a_addr + kc * TC_A_CHUNK);
                         const uint64_t db = umma_desc(b_addr + s * SLOT_BYTES);
@@ -345,10 +415,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 }
                 if (ok) commit(BAR(B_AEMPTY));       // query tile reusable
             }
-            if (blockIdx.x < 160) {
+            TC_PROF(if (blockIdx.x < 160) {
                 g_tc_prof[blockIdx.x * TC_PROF_WORDS + 1] = prof_full;
                 g_tc_prof[blockIdx.x * TC_PROF_WORDS + 2] = prof_tempty;
-            }
+            })
         }
     } else {
         // ------------------------------ epilogue warps --------------------------------------
@@ -357,8 +427,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const int wg = warp >> 2, quarter = warp & 3;
         constexpr bool BIG = (MODE == TC_MODE_KNN_BIG);
         constexpr bool MID = (MODE == TC_MODE_KNN_MID);
-        constexpr int CAP = BIG ? TC_BIG_CAP : MID ? TC_MID_CAP : TC_CAP;
-        constexpr int K1 = BIG ? TC_BIG_K1 : MID ? TC_MID_K1 : TC_K1;
+        constexpr bool GP = (MODE == TC_MODE_KNN_GPOOL);
+        constexpr int CAP = BIG ? TC_BIG_CAP : MID ? TC_MID_CAP : GP ? TC_GP_CAP : TC_CAP;
+        constexpr int K1 = BIG ? TC_BIG_K1 : MID ? TC_MID_K1 : GP ? TC_GP_K1 : TC_K1;
         constexpr int PSTR = CAP + 1;                    // shared pools: padded stride, slot CAP is scratch
         constexpr int PUB = BIG ? TC_BIG_CAP : MID ? TC_MID_PUB : TC_CAP;   // published entries per pool
         // pool of lane 0's row and distance (elements) between the pools of consecutive rows
@@ -370,9 +441,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const uint32_t lane_taddr = tmem_base + (uint32_t(quarter * 32) << 16);
         uint32_t tile_no = 0;
         bool ok = true;
-        long long prof_tfull = 0, prof_rare = 0, prof_cc = 0;
-        unsigned prof_groups = 0, prof_compact = 0, prof_append = 0;
-        const long long prof_t0 = clock64();
+        TC_PROF(long long prof_tfull = 0; long long prof_rare = 0; long long prof_cc = 0;
+                unsigned prof_groups = 0; unsigned prof_compact = 0; unsigned prof_append = 0;
+                const long long prof_t0 = clock64();)
         // hands accumulator b back to the MMA lane (of the leader, for a pair)
         auto release_acc = [&](int b) {
             if (PAIR) mbar_arrive_cluster(BAR(B_TEMPTY + b), 0u); else mbar_arrive(BAR(B_TEMPTY + b));
@@ -380,8 +451,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         for (int it = it_first; it < n_items && ok; it += it_step) {
             const int split = it / n_units, unit = it - split * n_units;
             const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
-            const int t0 = p.item_t0 ? __ldg(p.item_t0 + it) : split * p.tiles_per_split;
-            const int t1 = p.item_t0 ? __ldg(p.item_t1 + it) : min(p.n_tiles, t0 + p.tiles_per_split);
+            int t0, t1;
+            tc_item_range(p, it, split, t0, t1);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
             float tau_in = __ldcg(p.tau + qrow);
             int qidx = -1;
@@ -411,13 +482,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             for (int i = 0; i < nt; ++i, ++tile_no) {
                 const int t = t0 + (i + rot < nt ? i + rot : i + rot - nt);
                 const int b = tile_no & 1;
-                const long long c0 = clock64();
+                TC_PROF(const long long c0 = clock64();)
                 if (!__all_sync(FULL_MASK, mbar_wait(BAR(B_TFULL + b), (tile_no >> 1) & 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns))) {
                     if (lane == 0) tc_report_timeout(p.status, warp, B_TFULL + b);
                     ok = false;
                     break;
                 }
-                prof_tfull += clock64() - c0;
+                TC_PROF(prof_tfull += clock64() - c0;)
                 tc_fence_after_sync();
                 // this warpgroup's half of the accumulator columns / of the tile's database rows
                 const uint32_t tile_taddr = lane_taddr + b * TC_BN + wg * (TC_BN / TC_NWG);
@@ -487,6 +558,113 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     fold(vd);
                     continue;
                 }
+                if (GP) {
+                    // this row's pool in global memory and the address of its next free slot
+                    float2* warp_pool = p.gpool + (((int64_t)(qt * TC_BM + quarter * 32) * p.nsplit + split) * TC_NWG + wg) * CAP;
+                    const int gstride = p.nsplit * TC_NWG * CAP;      // pairs between the pools of consecutive rows
+                    const uint64_t my_addr = reinterpret_cast<uint64_t>(warp_pool + (int64_t)lane * gstride);
+                    uint64_t waddr = my_addr + 8ull * (uint64_t)cnt;
+                    const uint64_t lim = my_addr + 8ull * (uint64_t)(CAP - 8);
+                    tmem_ld_32x32b_x32(tile_taddr, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 32, vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 64, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 96, vd);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) release_acc(b);
+                    auto dense = [&](uint32_t (&v)[32], int slice) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (__any_sync(FULL_MASK, waddr > lim)) {
+                                cnt = (int)((waddr - my_addr) >> 3);
+                                const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
+                                TC_PROF(prof_compact += __popc(need);)
+                                const float2 cr = tc_compact_rows_pairs<CAP, K1>(need, warp_pool, gstride, cnt, tau);
+                                cnt = __float_as_int(cr.x);
+                                tau = cr.y;
+                                waddr = my_addr + 8ull * (uint64_t)cnt;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t id = row_base + slice * 32 + g * 8 + j;
+                                asm volatile(
+                                    "{\n\t.reg .pred p;\n\t"
+                                    "setp.gt.f32 p, %1, %2;\n\t"
+                                    "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
+                                    "@p add.u64 %0, %0, 8;\n\t}"
+                                    : "+l"(waddr)
+                                    : "f"(__uint_as_float(v[g * 8 + j])), "f"(tau), "r"(v[g * 8 + j]), "r"(id)
+                                    : "memory");
+                            }
+                        }
+                    };
+                    dense(va, 0);
+                    dense(vb, 1);
+                    dense(vc, 2);
+                    dense(vd, 3);
+                    TC_PROF(prof_append += (int)((waddr - my_addr) >> 3) - cnt;)
+                    cnt = (int)((waddr - my_addr) >> 3);
+                    continue;
+                }
+                if (MID) {
+                    // pools of this mode hold (score, row) pairs; `waddr` is the shared-memory address
+                    // of this row's next free slot
+                    float2* warp_pool = reinterpret_cast<float2*>(pool_sc) + warp * 32 * PSTR;
+                    const uint32_t my_addr = smem_u32(warp_pool + lane * PSTR);
+                    uint32_t waddr = my_addr + 8u * (uint32_t)cnt;
+                    const uint32_t lim = my_addr + 8u * (uint32_t)(CAP - 8);
+                    tmem_ld_32x32b_x32(tile_taddr, va);
+                    tmem_ld_32x32b_x32(tile_taddr + 32, vb);
+                    tmem_ld_32x32b_x32(tile_taddr + 64, vc);
+                    tmem_ld_32x32b_x32(tile_taddr + 96, vd);
+                    tmem_ld_wait();
+                    reg_fence32(va);
+                    reg_fence32(vb);
+                    reg_fence32(vc);
+                    reg_fence32(vd);
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) release_acc(b);
+                    auto dense = [&](uint32_t (&v)[32], int slice) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            // every lane's pool has room for the 8 scores of the group
+                            if (__any_sync(FULL_MASK, waddr > lim)) {
+                                cnt = (int)((waddr - my_addr) >> 3);
+                                const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
+                                TC_PROF(prof_compact += __popc(need);)
+                                const float2 cr = tc_compact_rows_pairs<CAP, K1>(need, warp_pool, PSTR, cnt, tau);
+                                cnt = __float_as_int(cr.x);
+                                tau = cr.y;
+                                waddr = my_addr + 8u * (uint32_t)cnt;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t id = row_base + slice * 32 + g * 8 + j;
+                                asm volatile(
+                                    "{\n\t.reg .pred p;\n\t"
+                                    "setp.gt.f32 p, %1, %2;\n\t"
+                                    "@p st.shared.v2.b32 [%0], {%3, %4};\n\t"
+                                    "@p add.u32 %0, %0, 8;\n\t}"
+                                    : "+r"(waddr)
+                                    : "f"(__uint_as_float(v[g * 8 + j])), "f"(tau), "r"(v[g * 8 + j]), "r"(id)
+                                    : "memory");
+                            }
+                        }
+                    };
+                    dense(va, 0);
+                    dense(vb, 1);
+                    dense(vc, 2);
+                    dense(vd, 3);
+                    TC_PROF(prof_append += ((waddr - my_addr) >> 3) - cnt;)
+                    cnt = (int)((waddr - my_addr) >> 3);
+                    continue;
+                }
                 unsigned hits = 0;
                 auto scan = [&](uint32_t (&v)[32], int slice) {
 #pragma unroll
@@ -534,7 +712,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 // flagged groups of the same lane ("late") are handled one by one before (b).
                 unsigned wm = __reduce_or_sync(FULL_MASK, hits);
                 if (wm) {
-                    const long long cr0 = clock64();
+                    TC_PROF(const long long cr0 = clock64();)
                     float sv[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) sv[j] = neg_inf();
@@ -568,7 +746,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                             scb = take ? row_base + gs[k] * 8 : scb;
                             late |= (mine && have) ? (1u << gs[k]) : 0u;
                             have = have || mine;
-                            prof_groups += live[k] ? 1 : 0;
+                            TC_PROF(prof_groups += live[k] ? 1 : 0;)
                         }
                     } while (wm);
                     unsigned wl = __reduce_or_sync(FULL_MASK, late);
@@ -578,7 +756,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         wl &= wl - 1;
                         const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
                         if (need) {
-                            prof_compact += __popc(need);
+                            TC_PROF(prof_compact += __popc(need);)
                             const float2 cr = tc_compact_rows<CAP, K1>(need, warp_sc, warp_id, pstride, cnt, tau);
                             cnt = __float_as_int(cr.x);
                             tau = cr.y;
@@ -601,7 +779,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                             }
                         }
                         cnt += __popc(pm);
-                        prof_append += __popc(pm);
+                        TC_PROF(prof_append += __popc(pm);)
                     }
                     // every flagged score is in registers or in a pool: hand the accumulator back
                     tc_fence_before_sync();
@@ -610,10 +788,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                     // (b) all lanes at once
                     const unsigned need = __ballot_sync(FULL_MASK, cnt > CAP - 8);
                     if (need) {
-                        prof_compact += __popc(need);
-                        const long long cc0 = clock64();
+                        TC_PROF(prof_compact += __popc(need); const long long cc0 = clock64();)
                         const float2 cr = tc_compact_rows<CAP, K1>(need, warp_sc, warp_id, pstride, cnt, tau);
-                        prof_cc += clock64() - cc0;
+                        TC_PROF(prof_cc += clock64() - cc0;)
                         cnt = __float_as_int(cr.x);
                         tau = cr.y;
                     }
@@ -641,8 +818,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         }
                     }
                     cnt += np;
-                    prof_append += np;
-                    prof_rare += clock64() - cr0;
+                    TC_PROF(prof_append += np;)
+                    TC_PROF(prof_rare += clock64() - cr0;)
                 } else {
                     // nothing flagged: hand the accumulator back right away
                     tc_fence_before_sync();
@@ -674,7 +851,34 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (tau > tau_in) __stcg(p.tau + qrow, tau);
                 continue;
             }
+            if (GP) {
+                // the pools already are the published buffers
+                p.part_cnt[(qrow * p.nsplit + split) * TC_NWG + wg] = cnt;
+                p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
+                if (tau > tau_in) __stcg(p.tau + qrow, tau);
+                if (qidx >= 0 && tau > tau_in) atomic_max_f32(p.tau_q + qidx, tau);
+                continue;
+            }
             __syncwarp();
+            if (MID) {
+                const float2* warp_pool = reinterpret_cast<const float2*>(pool_sc) + warp * 32 * PSTR;
+#pragma unroll 1
+                for (int src = 0; src < 32; ++src) {
+                    const int n = __shfl_sync(FULL_MASK, cnt, src);
+                    const float2* row = warp_pool + src * PSTR;
+                    const int64_t q = (int64_t)qt * TC_BM + quarter * 32 + src;
+                    const int64_t o = ((q * p.nsplit + split) * TC_NWG + wg) * PUB;
+#pragma unroll
+                    for (int e = lane; e < PUB; e += 32) {
+                        const float2 v = e < n ? row[e] : make_float2(neg_inf(), __uint_as_float(INVALID_ID));
+                        p.part_sc[o + e] = v.x;
+                        p.part_id[o + e] = __float_as_uint(v.y);
+                    }
+                }
+                p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
+                if (tau > tau_in) __stcg(p.tau + qrow, tau);
+                if (qidx >= 0 && tau > tau_in) atomic_max_f32(p.tau_q + qidx, tau);
+            } else {
 #pragma unroll 1
             for (int src = 0; src < 32; ++src) {
                 const int n = __shfl_sync(FULL_MASK, cnt, src);
@@ -691,13 +895,16 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
             if (tau > tau_in) __stcg(p.tau + qrow, tau);
             if (qidx >= 0 && tau > tau_in) atomic_max_f32(p.tau_q + qidx, tau);
+            }
         }
+        TC_PROF(
         if (warp == 0 && lane == 0 && blockIdx.x < 160) {
             unsigned long long* pr = g_tc_prof + blockIdx.x * TC_PROF_WORDS;
             pr[3] = prof_tfull; pr[4] = prof_rare; pr[5] = prof_groups; pr[6] = prof_compact; pr[7] = prof_append;
             pr[8] = clock64() - prof_t0; pr[9] = tile_no;
             pr[10] = 0; pr[11] = prof_cc;
         }
+        )
     }
 
     // ------------------------------ common exit ----------------------------------------------
@@ -802,6 +1009,7 @@ int tc_use_deep_pools(int k, int d_pad, int nsplit, int64_t nq_pad) {
 int tc_deep_pool_size() { return TC_MID_K1; }
 int tc_deep_partial_len() { return TC_NWG * TC_MID_PUB; }
 int tc_taus_per_range() { return TC_NWG; }
+int tc_pair_pool_cap() { return TC_GP_CAP; }
 
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k) {
     if (nq < 1 || m < 1) return FL_EUNSUPPORTED;
@@ -933,7 +1141,7 @@ static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch
     if (rc == FL_OK) rc = cached_map_bf16(&L->map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
     FL_CHECK_ARG(!(L->mid && (L->big || dbg)), "tensor-core kNN launch: deep pools go with k <= 16");
-    L->sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), L->big ? 0 : L->mid ? TC_MID_CAP + 1 : TC_PSTR);
+    L->sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), (L->big || p.pair_pools != nullptr) ? 0 : L->mid ? TC_MID_CAP + 1 : TC_PSTR);
     if (L->sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     const TcExperiment& ex = tc_experiment();
     TcKernelParams& kp = L->kp;
@@ -948,6 +1156,7 @@ static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch
     kp.nq_pad = p.nq_pad; kp.part_sc = p.part_sc; kp.part_id = p.part_id;
     kp.tau = p.tau; kp.part_tau = p.part_tau; kp.status = p.status; kp.dbg_scores = dbg; kp.dbg_ld = dbg_ld;
     kp.part_cnt = p.part_cnt;
+    kp.gpool = reinterpret_cast<float2*>(p.pair_pools);
     kp.seed_cls = p.seed_cls;
     kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1;
     kp.row_query = p.row_query; kp.tau_q = p.tau_q;
@@ -983,11 +1192,25 @@ int tc_seed_tiles(int64_t m_pad, int k) {
         const double sample_rank = k >= 64 ? 22.2 : 9.2;
         seed_tiles = (int)((double)n_tiles * sample_rank / (6.0 * k));
         if (seed_tiles > n_tiles / 8) seed_tiles = n_tiles / 8;
+        if (seed_tiles > n_tiles / 2) seed_tiles = n_tiles / 2;
+        if (seed_tiles < 16) seed_tiles = 0;
+    } else if (n_tiles < 256) {
+        // Small databases (k <= 16): a cold pool costs a fixed few dozen insertions and compactions
+        // per query row, which dwarfs the scoring of a handful of tiles (the coarse probe of an
+        // inverted-file search scores 4).  Sample 16 tiles, or simply all of them: the threshold
+        // is then tight, so the selection lowers it by the proof's margin (tc_seed_dense).
+        seed_tiles = n_tiles < 16 ? n_tiles : 16;
     }
-    if (ex.seed_tiles >= 0) seed_tiles = ex.seed_tiles;
-    if (seed_tiles > n_tiles / 2) seed_tiles = n_tiles / 2;
-    if (seed_tiles < 16 || ex.noseed) seed_tiles = 0;
+    if (ex.seed_tiles >= 0) seed_tiles = ex.seed_tiles < n_tiles ? ex.seed_tiles : n_tiles;
+    if (ex.noseed) seed_tiles = 0;
     return seed_tiles;
+}
+// 1 when the seeding sample is a large share of the database: a threshold that k + 6 sampled rows
+// reach then cuts close to the k-th neighbour, and must be lowered by twice the scoring error bound
+// for the finalisation's proof to hold (see tc_seed_select_kernel).
+int tc_seed_dense(int64_t m_pad, int k) {
+    const int n_tiles = (int)(m_pad / TC_BN);
+    return !tc_knn_big(k) && n_tiles < 256 && tc_seed_tiles(m_pad, k) > 0;
 }
 
 // Seeding pass: class maxima of a strided sample of the database tiles into p.seed_cls
@@ -997,14 +1220,21 @@ int launch_knn_tc_seed(const TcKnnParams& p, cudaStream_t st) {
     TcLaunch L;
     int rc = tc_prepare(p, nullptr, 0, &L);
     if (rc != FL_OK) return rc;
-    if (L.seed_tiles == 0) return launch_fill_f32(p.seed_cls, p.nq_pad * (TC_NWG * 16), -INFINITY, st);
     TcKernelParams sk = L.kp;
-    sk.nsplit = 1;
-    sk.tiles_per_split = L.seed_tiles;
-    sk.tile_stride = L.kp.n_tiles / L.seed_tiles;
-    sk.n_tiles = L.seed_tiles;
     sk.dbg_scores = nullptr;
-    sk.item_t0 = sk.item_t1 = nullptr; sk.nq_dev = nullptr; sk.row_query = nullptr; sk.tau_q = nullptr;
+    sk.row_query = nullptr; sk.tau_q = nullptr;
+    if (p.item_t0 != nullptr) {
+        // item tables (inverted-file scan): the first item_tile_cap tiles of every item's own range
+        FL_CHECK_ARG(p.item_tile_cap > 0 && p.nsplit == 1, "tensor-core seeding over item tables needs a tile cap");
+        sk.item_tile_cap = p.item_tile_cap;
+    } else {
+        if (L.seed_tiles == 0) return launch_fill_f32(p.seed_cls, p.nq_pad * (TC_NWG * 16), -INFINITY, st);
+        sk.nsplit = 1;
+        sk.tiles_per_split = L.seed_tiles;
+        sk.tile_stride = L.kp.n_tiles / L.seed_tiles;
+        sk.n_tiles = L.seed_tiles;
+        sk.nq_dev = nullptr;
+    }
     // the seeding kernel keeps no pools: the ring gets the shared memory the pools would take
     const TcSmemPlan sp = L.sp;
     const int sgrid = sk.n_qtiles < sm_count() ? sk.n_qtiles : sm_count();
@@ -1028,11 +1258,13 @@ int launch_knn_tc_seed_select(const TcKnnParams& p, const TcSeedMargin& mg, cuda
 
 // Main scoring launch (thresholds in p.tau as they stand).
 static int launch_tc_main(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cudaStream_t st) {
-    FL_CHECK_ARG(p.part_sc && p.part_id && p.part_tau, "tensor-core kNN launch with a null buffer");
+    const bool gp = p.pair_pools != nullptr;
+    FL_CHECK_ARG(p.part_tau && (gp ? p.part_cnt != nullptr : (p.part_sc && p.part_id)), "tensor-core kNN launch with a null buffer");
     TcLaunch L;
     int rc = tc_prepare(p, dbg, dbg_ld, &L);
     if (rc != FL_OK) return rc;
     const bool big = L.big, mid = L.mid;
+    FL_CHECK_ARG(!gp || (!big && !dbg && p.k <= 16), "tensor-core kNN launch: global pair pools go with k <= 16");
     FL_CHECK_ARG(!big || (p.part_cnt && !dbg), "tensor-core kNN launch (large k) without a count buffer");
     FL_CHECK_ARG((p.row_query == nullptr) == (p.tau_q == nullptr), "tensor-core kNN launch: row_query and tau_q go together");
     FL_CHECK_ARG((p.item_t0 == nullptr) == (p.item_t1 == nullptr) && (p.item_t0 == nullptr || (p.nsplit == 1 && !big)),
@@ -1044,9 +1276,12 @@ static int launch_tc_main(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     const int grid = items < sm_count() ? items : sm_count();
     // CTA pairs (cta_group::2): plain k <= 16 scoring over uniform ranges, an even number of query
     // tiles, at least one pair-item per cluster of a full grid.  FLASHLIB_B200_TC_PAIR=0/1 overrides.
-    const bool pair = !mid && dbg == nullptr && p.item_t0 == nullptr && p.nq_dev == nullptr &&
+    const bool pair = !gp && !mid && dbg == nullptr && p.item_t0 == nullptr && p.nq_dev == nullptr &&
                       tc_pair_enabled(p.nq_pad, p.k);
-    if (pair) {
+    if (gp) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_GPOOL>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_KNN_GPOOL><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
+    } else if (pair) {
         CUtensorMap map_db_h, map_db_aug_h;
         rc = cached_map_bf16(&map_db_h, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN / 2);
         if (rc == FL_OK) rc = cached_map_bf16(&map_db_aug_h, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN / 2);

@@ -230,9 +230,13 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     if not (1 <= k <= index.M):
         raise ValueError(f"k must be in [1, M={index.M}] (got {k})")
     Qp = _pad_features(Q.to(index.data.dtype), index.Dp).contiguous()
-    # coarse probe in the exact-rank mode: near-tied centroids must rank as in fp32
+    # Coarse probe: near-tied centroids must rank as in fp32, which both kNN modes guarantee (the
+    # tensor-core mode proves every row's list of centroids or recomputes it exactly); large
+    # batches take the tensor cores, where the 2 nq nlist D contraction costs next to nothing.
+    coarse = "bf16" if (Q.shape[0] * index.nlist >= (1 << 22) and nprobe <= 16 and index.Dp <= 256
+                        and index.centroids.dtype == torch.float32) else "exact"
     probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
-                       return_distances=False, mode="exact")[0]
+                       return_distances=False, mode=coarse)[0]
     mode = {"auto": None, "elementwise": "exact", "gemm": "bf16"}[variant]
     if mode == "bf16" and (k > 10 or index.Dp > 128):
         mode = "exact"

@@ -59,7 +59,9 @@ int         fl_device_ok(void);
 /* it was loaded.  fl_profile_enable(1) makes fl_knn_f32 / fl_kmeans_assign_f32 /        */
 /* fl_ivf_fine_scan_f32 bracket their dominant (scoring) kernel with CUDA events on the  */
 /* caller's stream, up to 256 samples; fl_profile_read_ms waits for sample i and returns */
-/* its duration.  Not thread-safe; meant for one benchmarking thread.                    */
+/* its duration.  fl_profile_enable(2) instead records an event at every step of         */
+/* fl_ivf_fine_scan_tc_f32's launch sequence; sample i is then the time between steps i    */
+/* and i + 1.  Not thread-safe; meant for one benchmarking thread.                        */
 unsigned long long fl_launch_count(void);
 int         fl_profile_enable(int on);
 int         fl_profile_count(void);

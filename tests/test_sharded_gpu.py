@@ -35,7 +35,8 @@ def run_shards(X, Q, k, world, owner=False, wire_bf16=True):
 
 @pytest.mark.parametrize("skew", [False, True])
 def test_seeded_shards_merge_to_the_exact_result(skew):
-    X, Q = synthetic.mixture(160_000, 128, 256, 7, nq=700, clamp=True)
+    # shards of 80,000 rows: large enough for the seeding pass to sample them (>= 256 tiles of 256 rows)
+    X, Q = synthetic.mixture(320_000, 128, 256, 7, nq=700, clamp=True)
     if skew:
         # rows ordered by distance to the first query: its neighbours, and those of similar queries,
         # all sit in the first shard
@@ -52,7 +53,9 @@ def test_seeded_shards_merge_to_the_exact_result(skew):
     # shards return short lists where their rows cannot matter, and few queries need the exact pass
     short = sum(int((o[1] < 0).any(dim=1).sum()) for o in outs)
     fallbacks = sum(int(o[2][_lib.FL_STATUS_FALLBACK]) for o in outs)
-    assert short > 0, "no shard ever returned fewer than k rows: the shared thresholds did not bite"
+    if skew:
+        # the far shards have nothing above the shared thresholds for most queries
+        assert short > 0, "no shard ever returned fewer than k rows: the shared thresholds did not bite"
     assert fallbacks <= world * Q.shape[0] // 20, fallbacks
     assert st[_lib.FL_STATUS_FALLBACK].item() == fallbacks
 
