@@ -57,6 +57,18 @@ class KMeans:
         B, x_b = self._as_batch(data)
         torch.manual_seed(self.seed)
         torch.cuda.manual_seed_all(self.seed)
+        if data.device.type == "cpu" and x_b.shape[1] > self.chunk_size_data_cpu:
+            # host-resident data too large to copy in one piece: streamed in blocks, as the reference
+            # does (applications/kmeans.py:139-156)
+            if B is not None:
+                raise AssertionError("Batched data with large N on CPU is not supported yet.")
+            from .kmeans_large import kmeans_largeN
+            ids, cents = kmeans_largeN(x_b[0], self.k, max_iters=self.niter, tol=self.tol, verbose=self.verbose,
+                                       dtype=self.dtype, BLOCK_N=self.chunk_size_data_cpu, device=self.device)
+            self.centroids_b = cents.unsqueeze(0)
+            self.cluster_ids_b = ids.unsqueeze(0)
+            self._batch_size = B
+            return
         x_b = x_b.to(device=self.device, dtype=self.dtype or x_b.dtype)
         ids, cents, _ = batch_kmeans_Euclid(x_b, self.k, max_iters=self.niter, tol=self.tol,
                                             init_centroids=None, verbose=self.verbose)
@@ -75,6 +87,12 @@ class KMeans:
         if B != self._batch_size:
             raise ValueError(f"Model was trained with batch size B={self._batch_size}, "
                              f"but predict received B={B}. Provide matching batch size.")
+        if data.device.type == "cpu" and x_b.shape[1] > self.chunk_size_data_cpu:
+            if B is not None:
+                raise AssertionError("Batched data with large N on CPU is not supported yet.")
+            from .kmeans_large import kmeans_largeN_assign
+            return kmeans_largeN_assign(x_b[0], self.centroids_b[0], BLOCK_N=self.chunk_size_data_cpu,
+                                        device=self.device)
         x_b = x_b.to(device=self.device, dtype=self.dtype or x_b.dtype)
         labels = euclid_assign_triton(x_b, self.centroids_b.to(x_b.dtype))
         return labels.squeeze(0) if B is None else labels

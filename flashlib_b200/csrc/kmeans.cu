@@ -24,13 +24,18 @@ __global__ void kmeans_halfnorm_kernel(const float* __restrict__ x, int n, int d
 template <int TQ>
 __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
     const float* __restrict__ x, int64_t n, int64_t ldx, const float* __restrict__ c, int K, int64_t ldc,
-    int d, const float* __restrict__ hnorm, int32_t* __restrict__ labels, int vecx, int vecc) {
+    int d, const float* __restrict__ hnorm, int32_t* __restrict__ labels, int vecx, int vecc, int64_t xbs, int64_t cbs) {
     using T = SimtTile<TQ>;
     constexpr int BQ = T::BQ;
     extern __shared__ __align__(16) float smem[];
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int64_t row0 = (int64_t)blockIdx.x * BQ;
+    // batch item blockIdx.y: its own rows, centroids, half norms and labels
+    x += (int64_t)blockIdx.y * xbs;
+    c += (int64_t)blockIdx.y * cbs;
+    hnorm += (int64_t)blockIdx.y * K;
+    labels += (int64_t)blockIdx.y * n;
 
     const float* qrow[T::QL];
 #pragma unroll
@@ -84,7 +89,7 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
 template <int DPL>
 __global__ void kmeans_update_kernel(const float* __restrict__ x, int64_t n, int64_t ldx, int d,
                                      const int32_t* __restrict__ labels, int K, float* __restrict__ sums,
-                                     int32_t* __restrict__ cnts, int rows_per_warp, int dbase) {
+                                     int32_t* __restrict__ cnts, int rows_per_warp, int dbase, int64_t nb, int Kb) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t r0 = w * rows_per_warp;
@@ -95,7 +100,8 @@ __global__ void kmeans_update_kernel(const float* __restrict__ x, int64_t n, int
     for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
     int cur = -1, run = 0;
     for (int64_t r = r0; r < r1; ++r) {
-        const int lab = __ldg(labels + r);
+        int lab = __ldg(labels + r);
+        if (lab >= 0 && lab < Kb) lab += (int)(r / nb) * Kb; else lab = -1;
         if (lab != cur) {
             if (cur >= 0 && cur < K) {
 #pragma unroll
@@ -134,7 +140,7 @@ __global__ void kmeans_update_kernel(const float* __restrict__ x, int64_t n, int
 template <int V>
 __global__ void kmeans_update_vec_kernel(const float* __restrict__ x, int64_t n, int64_t ldx, int d,
                                          const int32_t* __restrict__ labels, int K, float* __restrict__ sums,
-                                         int32_t* __restrict__ cnts, int rows_per_warp) {
+                                         int32_t* __restrict__ cnts, int rows_per_warp, int64_t nb, int Kb) {
     const int lane = threadIdx.x & 31;
     const int64_t w = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t r0 = w * rows_per_warp;
@@ -160,8 +166,13 @@ __global__ void kmeans_update_vec_kernel(const float* __restrict__ x, int64_t n,
     };
 #pragma unroll
     for (int i = 0; i < V; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    // label of row r in the stacked problem: batch item r / nb owns clusters [item * Kb, (item + 1) * Kb)
+    auto label_of = [&](int64_t r) {
+        const int l = __ldg(labels + r);
+        return (l >= 0 && l < Kb) ? l + (int)(r / nb) * Kb : -1;
+    };
     int cur = -1, run = 0;
-    int lab_n = __ldg(labels + r0);
+    int lab_n = label_of(r0);
     load_row(r0, nxt);
     for (int64_t r = r0; r < r1; ++r) {
         const int lab = lab_n;
@@ -169,7 +180,7 @@ __global__ void kmeans_update_vec_kernel(const float* __restrict__ x, int64_t n,
 #pragma unroll
         for (int i = 0; i < V; ++i) v[i] = nxt[i];
         if (r + 1 < r1) {
-            lab_n = __ldg(labels + r + 1);
+            lab_n = label_of(r + 1);
             load_row(r + 1, nxt);
         }
         if (lab != cur) {
@@ -243,7 +254,7 @@ extern "C" int fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx, cons
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     profile_begin(st);
     kmeans_assign_simt_kernel<TQ><<<(unsigned)ceil_div(n, SimtTile<TQ>::BQ), 256, smem, st>>>(
-        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc);
+        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc, 0, 0);
     profile_end(st);
     FL_CHECK_LAUNCH();
     return FL_OK;
@@ -306,16 +317,15 @@ extern "C" int fl_kmeans_assign_noalloc_f32(const float* x, int64_t n, int64_t l
     FL_CHECK_CUDA(cudaFuncSetAttribute(kmeans_assign_simt_kernel<TQ>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kmeans_assign_simt_kernel<TQ><<<(unsigned)ceil_div(n, SimtTile<TQ>::BQ), 256, smem, st>>>(
-        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc);
+        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc, 0, 0);
     FL_CHECK_LAUNCH();
     return FL_OK;
 }
 
-extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels,
-                                    int K, float* sums, int32_t* cnts, void* stream) {
-    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_f32: bad shape");
-    FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_f32: null pointer");
-    cudaStream_t st = (cudaStream_t)stream;
+// Sums / counts of `n` stacked rows: batch item i owns rows [i nb, (i + 1) nb) and clusters
+// [i Kb, (i + 1) Kb) of the K = items x Kb stacked clusters (one item: nb = n, Kb = K).
+static int kmeans_update_impl(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels, int K, float* sums,
+                              int32_t* cnts, int64_t nb, int Kb, cudaStream_t st) {
     FL_CHECK_CUDA(cudaMemsetAsync(sums, 0, sizeof(float) * (size_t)K * d, st));
     FL_CHECK_CUDA(cudaMemsetAsync(cnts, 0, sizeof(int32_t) * (size_t)K, st));
     if (n == 0) return FL_OK;
@@ -326,24 +336,74 @@ extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int 
     const bool vec = d % 4 == 0 && ldx % 4 == 0 && d <= 512 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(sums) & 15) == 0);
     if (vec) {
-        if (d <= 128) kmeans_update_vec_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
-        else if (d <= 256) kmeans_update_vec_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
-        else kmeans_update_vec_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp);
+        if (d <= 128) kmeans_update_vec_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, nb, Kb);
+        else if (d <= 256) kmeans_update_vec_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, nb, Kb);
+        else kmeans_update_vec_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, nb, Kb);
         FL_CHECK_LAUNCH();
         return FL_OK;
     }
     for (int dbase = 0; dbase < d; dbase += 256) {
         const int rem = d - dbase;
         if (rem <= 32)
-            kmeans_update_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+            kmeans_update_kernel<1><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase, nb, Kb);
         else if (rem <= 64)
-            kmeans_update_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+            kmeans_update_kernel<2><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase, nb, Kb);
         else if (rem <= 128)
-            kmeans_update_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+            kmeans_update_kernel<4><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase, nb, Kb);
         else
-            kmeans_update_kernel<8><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase);
+            kmeans_update_kernel<8><<<grid, 256, 0, st>>>(x, n, ldx, d, labels, K, sums, cnts, rows_per_warp, dbase, nb, Kb);
         FL_CHECK_LAUNCH();
     }
+    return FL_OK;
+}
+
+extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels,
+                                    int K, float* sums, int32_t* cnts, void* stream) {
+    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_f32: bad shape");
+    FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_f32: null pointer");
+    return kmeans_update_impl(x, n, ldx, d, labels, K, sums, cnts, n > 0 ? n : 1, K, (cudaStream_t)stream);
+}
+
+extern "C" int fl_kmeans_update_batch_f32(const float* x, int batch, int64_t n, int64_t ldx, int d, const int32_t* labels,
+                                          int K, float* sums, int32_t* cnts, void* stream) {
+    FL_CHECK_ARG(batch >= 1 && n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_batch_f32: bad shape");
+    FL_CHECK_ARG((int64_t)batch * K < (1ll << 31) && (int64_t)batch * n < (1ll << 40), "fl_kmeans_update_batch_f32: too large");
+    FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_batch_f32: null pointer");
+    return kmeans_update_impl(x, (int64_t)batch * n, ldx, d, labels, batch * K, sums, cnts, n > 0 ? n : 1, K, (cudaStream_t)stream);
+}
+
+extern "C" int64_t fl_kmeans_assign_batch_workspace_bytes(int batch, int64_t n, int K, int d) {
+    (void)n; (void)d;
+    if (batch < 1 || K < 1) return 0;
+    return round_up((int64_t)batch * K * 4, 1024);
+}
+
+extern "C" int fl_kmeans_assign_batch_f32(const float* x, int batch, int64_t n, int64_t ldx, int64_t x_batch_stride,
+                                          const float* c, int K, int64_t ldc, int64_t c_batch_stride, int d,
+                                          int32_t* labels, void* ws, int64_t ws_bytes, void* stream) {
+    FL_CHECK_ARG(batch >= 1 && batch <= 65535 && n >= 0 && K >= 1 && d >= 1 && ldx >= d && ldc >= d,
+                 "fl_kmeans_assign_batch_f32: bad shape");
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && c && labels && ws, "fl_kmeans_assign_batch_f32: null pointer");
+    FL_CHECK_ARG(c_batch_stride == (int64_t)K * ldc, "fl_kmeans_assign_batch_f32: the centroid sets must lie back to back");
+    if (ws_bytes < fl_kmeans_assign_batch_workspace_bytes(batch, n, K, d)) {
+        set_error("fl_kmeans_assign_batch_f32: workspace too small");
+        return FL_EWORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* hnorm = static_cast<float*>(ws);
+    // the centroid sets are contiguous: one pass gives the half norms of all batch items
+    kmeans_halfnorm_kernel<<<(unsigned)ceil_div((int64_t)batch * K, 8), 256, 0, st>>>(c, batch * K, d, ldc, hnorm);
+    FL_CHECK_LAUNCH();
+    const int vecx = (ldx % 4 == 0) && (x_batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    const int vecc = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
+    constexpr int TQ = 4;
+    const size_t smem = sizeof(float) * SimtTile<TQ>::SLAB_FLOATS;
+    FL_CHECK_CUDA(cudaFuncSetAttribute(kmeans_assign_simt_kernel<TQ>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kmeans_assign_simt_kernel<TQ><<<dim3((unsigned)ceil_div(n, SimtTile<TQ>::BQ), (unsigned)batch), 256, smem, st>>>(
+        x, n, ldx, c, K, ldc, d, hnorm, labels, vecx, vecc, x_batch_stride, c_batch_stride);
+    FL_CHECK_LAUNCH();
     return FL_OK;
 }
 

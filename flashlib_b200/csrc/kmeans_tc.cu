@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(128) assign_finalize_kernel(
     int vec, const float* __restrict__ asg_sc, const uint32_t* __restrict__ asg_id, float eps_rel,
     const float* __restrict__ maxnorm, int32_t* __restrict__ labels, const int* __restrict__ rows,
     const int* __restrict__ rows_count, int* __restrict__ next_count, int* __restrict__ next_list, int next_cap,
-    int* __restrict__ fb_count, int* __restrict__ fb_list, int fb_cap) {
+    int* __restrict__ fb_count, int* __restrict__ fb_list, int fb_cap, int scores_by_point) {
     const int sl = threadIdx.x & 7;
     int64_t live = n;
     if (rows_count != nullptr) { const int64_t cnt = *rows_count; live = cnt < n ? cnt : n; }
@@ -111,8 +111,11 @@ __global__ void __launch_bounds__(128) assign_finalize_kernel(
         const bool alive = r_raw < live;
         const int64_t r = alive ? r_raw : live - 1;          // idle groups shadow the last row
         const int64_t pt = rows != nullptr ? (int64_t)rows[r] : r;
-        const float4 sc = __ldg(reinterpret_cast<const float4*>(asg_sc + r * 4));   // b1_0, b2_0, b1_1, b2_1
-        const uint2 ids = __ldg(reinterpret_cast<const uint2*>(asg_id + r * 2));
+        // the scores sit at the scoring row: the list position (points gathered for their own scoring
+        // pass) or the point itself (a list of points that were scored in place)
+        const int64_t sr = scores_by_point ? pt : r;
+        const float4 sc = __ldg(reinterpret_cast<const float4*>(asg_sc + sr * 4));   // b1_0, b2_0, b1_1, b2_1
+        const uint2 ids = __ldg(reinterpret_cast<const uint2*>(asg_id + sr * 2));
         const bool v0 = ids.x < (uint32_t)K && sc.x > -1e37f;   // false: no real centroid in that half
         const bool v1 = ids.y < (uint32_t)K && sc.z > -1e37f;
         const float* xp = x + pt * ldx;
@@ -174,13 +177,69 @@ __global__ void __launch_bounds__(128) assign_finalize_kernel(
     }
 }
 
+// ||x||^2 of every sample row (one warp per row); the scoring error bound of a point needs it.
+__global__ void rowsq_kernel(const float* __restrict__ x, int64_t n, int d, int64_t ld, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n) return;
+    const float* p = x + row * ld;
+    float s = 0.f;
+    for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
+    if (lane == 0) out[row] = s;
+}
+
+// First-stage proof from the scores alone, one thread per point: the best-scoring centroid is the
+// nearest one if its score leads the runner-up's by more than twice the scoring error bound (every
+// score is within eps of the exact <x,c> - ||c||^2/2, so the exact scores keep that order).  No
+// sample row and no centroid is read -- 28 bytes per point instead of its 4 d -- at the price of a
+// lead of 2 eps where the exact re-scoring of assign_finalize_kernel needs eps; what the lead does
+// not decide goes to the `next` list (the second stage, whose bound is a hundred times smaller).
+__global__ void __launch_bounds__(256) assign_by_lead_kernel(
+    int64_t n, int K, const float* __restrict__ asg_sc, const uint32_t* __restrict__ asg_id, const float* __restrict__ xsq,
+    float eps_rel, const float* __restrict__ maxnorm, int32_t* __restrict__ labels, int* __restrict__ next_count,
+    int* __restrict__ next_list, int next_cap, int* __restrict__ fb_count, int* __restrict__ fb_list, int fb_cap) {
+    const int64_t pt = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pt >= n) return;
+    const float4 sc = __ldg(reinterpret_cast<const float4*>(asg_sc + pt * 4));   // b1_0, b2_0, b1_1, b2_1
+    const uint2 ids = __ldg(reinterpret_cast<const uint2*>(asg_id + pt * 2));
+    const bool v0 = ids.x < (uint32_t)K && sc.x > -1e37f;   // false: no real centroid in that half
+    const bool v1 = ids.y < (uint32_t)K && sc.z > -1e37f;
+    const bool first = v0 && (!v1 || sc.x >= sc.z);
+    const float best = first ? sc.x : sc.z;
+    const uint32_t best_i = first ? ids.x : ids.y;
+    float second = first ? sc.y : sc.w;                      // runner-up of the winner's half ...
+    if (v0 && v1) second = fmaxf(second, first ? sc.z : sc.x);   // ... or the other half's best
+    bool ok = v0 || v1;
+    if (ok && second > -1e37f) {
+        const float q2 = __ldg(xsq + pt), mn = __ldg(maxnorm);
+        const float eps = eps_rel * sqrtf(q2) * mn;
+        // the column index rides in the low mantissa bits of both scores: 2^-15 relative each
+        const float lead = (best - fabsf(best) * 3.1e-5f) - (second + fabsf(second) * 3.1e-5f);
+        ok = lead > 2.f * eps + 1e-5f * (q2 + mn * mn);
+    }
+    labels[pt] = ok ? (int32_t)best_i : 0;
+    if (!ok) {
+        bool queued = false;
+        if (next_count != nullptr) {
+            const int i = atomicAdd(next_count, 1);
+            if (i < next_cap) { next_list[i] = (int)pt; queued = true; }
+        }
+        if (!queued) {
+            const int i = atomicAdd(fb_count, 1);
+            if (i < fb_cap) fb_list[i] = (int)pt;
+        }
+    }
+}
+
 struct AssignTcWs {
     int64_t n_pad; int d_pad, pitch; int fb_cap;
     int split;          // 1: a second stage with split (hi/lo) operand planes of 3 d_pad columns
     int l1_cap; int64_t l1_pad; int pitch3;
     int nsplit_fb; int64_t rows_per_split_fb; int fb_bq, fb_blocks;
     PlaneLayout cl, cl3;
-    int64_t off_cplane, off_cplane3, off_xplane, off_xsplit, off_asg_sc, off_asg_id, off_tau, off_cnt, off_l1list,
+    int64_t off_cplane, off_cplane3, off_xplane, off_xsq, off_xsplit, off_asg_sc, off_asg_id, off_tau, off_cnt, off_l0list, off_l1list,
         off_fblist, off_fbpart_sc, off_fbpart_id, off_fbdist, bytes;
 };
 
@@ -218,11 +277,13 @@ static AssignTcWs assign_tc_plan(int64_t n, int K, int d, int have_xplane) {
     w.off_cplane = take(cur, w.cl.bytes);
     w.off_cplane3 = w.split ? take(cur, w.cl3.bytes) : -1;
     w.off_xplane = have_xplane ? -1 : take(cur, w.n_pad * w.pitch * 2);
+    w.off_xsq = have_xplane ? -1 : take(cur, w.n_pad * 4);
     w.off_xsplit = w.split ? take(cur, w.l1_pad * w.pitch3 * 2) : -1;
     w.off_asg_sc = take(cur, w.n_pad * 4 * 4);
     w.off_asg_id = take(cur, w.n_pad * 2 * 4);
     w.off_tau = take(cur, w.n_pad * 4);
     w.off_cnt = take(cur, 1024);
+    w.off_l0list = take(cur, (w.split ? n : 1) * 4);
     w.off_l1list = take(cur, (int64_t)(w.l1_cap > 0 ? w.l1_cap : 1) * 4);
     w.off_fblist = take(cur, (int64_t)w.fb_cap * 4);
     w.off_fbpart_sc = take(cur, fb_pools * 32 * 4);
@@ -243,14 +304,21 @@ using namespace fl;
 
 extern "C" int64_t fl_kmeans_xplane_bytes(int64_t n, int d) {
     if (n < 1 || d < 1) return 0;
-    return round_up(n, 128) * (round_up(d, 64) + PLANE_AUG_COLS) * 2;
+    // the bf16 rows, then ||x||^2 of every row (f32 [n_pad])
+    return round_up(round_up(n, 128) * (round_up(d, 64) + PLANE_AUG_COLS) * 2, 1024) + round_up(n, 128) * 4;
 }
 
 extern "C" int fl_kmeans_prepare_x_f32(const float* x, int64_t n, int d, int64_t ldx, void* xplane,
                                        int64_t xplane_bytes, void* stream) {
     FL_CHECK_ARG(x && xplane && n >= 1 && d >= 1 && ldx >= d, "fl_kmeans_prepare_x_f32: bad arguments");
     if (xplane_bytes < fl_kmeans_xplane_bytes(n, d)) { set_error("fl_kmeans_prepare_x_f32: plane buffer too small"); return FL_EWORKSPACE; }
-    return launch_query_plane(x, n, ldx, d, xplane, round_up(n, 128), (int)round_up(d, 64), (cudaStream_t)stream);
+    const int64_t n_pad = round_up(n, 128);
+    const int rc = launch_query_plane(x, n, ldx, d, xplane, n_pad, (int)round_up(d, 64), (cudaStream_t)stream);
+    if (rc != FL_OK) return rc;
+    float* xsq = reinterpret_cast<float*>(static_cast<char*>(xplane) + round_up(n_pad * (round_up(d, 64) + PLANE_AUG_COLS) * 2, 1024));
+    rowsq_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, (cudaStream_t)stream>>>(x, n, d, ldx, xsq);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
 }
 
 extern "C" int64_t fl_kmeans_assign_tc_workspace_bytes(int64_t n, int K, int d, int have_xplane) {
@@ -294,16 +362,25 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     }
     // sample plane (query side)
     const char* xpl = static_cast<const char*>(xplane);
+    const float* xsq;
     if (!xpl) {
         rc = launch_query_plane(x, n, ldx, d, base + w.off_xplane, w.n_pad, w.d_pad, st);
         if (rc != FL_OK) return rc;
         xpl = base + w.off_xplane;
+        float* xs = reinterpret_cast<float*>(base + w.off_xsq);
+        rowsq_kernel<<<(unsigned)ceil_div(n, 8), 256, 0, st>>>(x, n, d, ldx, xs);
+        FL_CHECK_LAUNCH();
+        xsq = xs;
+    } else {
+        xsq = reinterpret_cast<const float*>(xpl + round_up(w.n_pad * w.pitch * 2, 1024));
     }
     int* counters = reinterpret_cast<int*>(base + w.off_cnt);
     int* fb_count = counters;          // points for the exact path
     int* l1_count = counters + 64;     // points for the second stage
     int* fb_list = reinterpret_cast<int*>(base + w.off_fblist);
     int* l1_list = reinterpret_cast<int*>(base + w.off_l1list);
+    int* l0_count = counters + 128;    // points the scores' lead did not decide
+    int* l0_list = reinterpret_cast<int*>(base + w.off_l0list);
     FL_CHECK_CUDA(cudaMemsetAsync(counters, 0, 1024, st));
     const int vecx = (ldx % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     const int vecc = (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
@@ -328,9 +405,22 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
         profile_end(st);
         if (rc != FL_OK) return rc;
         // scoring error relative to ||x|| max||c||: 2^-8 for plain bf16 operands, rounded up
-        assign_finalize_kernel<<<fin_grid, 128, 0, st>>>(
-            x, n, ldx, c, K, ldc, d, vec, asg_sc, asg_id, 0.004f, maxnorm, labels, nullptr, nullptr,
-            w.split ? l1_count : nullptr, l1_list, w.l1_cap, fb_count, fb_list, w.fb_cap);
+        if (w.split) {
+            // a second, far more precise stage follows: decide what the scores' lead decides
+            // without touching the rows
+            assign_by_lead_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(
+                n, K, asg_sc, asg_id, xsq, 0.004f, maxnorm, labels, l0_count, l0_list, (int)n, fb_count, fb_list, w.fb_cap);
+            FL_CHECK_LAUNCH();
+            // ... then, for the undecided ones only, the exact distances to the two half-winners, which
+            // need half the lead; what is still open goes to the second stage
+            assign_finalize_kernel<<<fin_grid, 128, 0, st>>>(
+                x, n, ldx, c, K, ldc, d, vec, asg_sc, asg_id, 0.004f, maxnorm, labels, l0_list, l0_count,
+                l1_count, l1_list, w.l1_cap, fb_count, fb_list, w.fb_cap, 1);
+        } else {
+            assign_finalize_kernel<<<fin_grid, 128, 0, st>>>(
+                x, n, ldx, c, K, ldc, d, vec, asg_sc, asg_id, 0.004f, maxnorm, labels, nullptr, nullptr,
+                nullptr, l1_list, w.l1_cap, fb_count, fb_list, w.fb_cap, 0);
+        }
         FL_CHECK_LAUNCH();
     }
     // ---- stage 2: split planes for the unproven points --------------------------------------
@@ -348,7 +438,7 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
         // split operands: 3 * 2^-18 from the dropped terms plus the fp32 accumulation of 400 products
         assign_finalize_kernel<<<fin_grid, 128, 0, st>>>(
             x, w.l1_cap, ldx, c, K, ldc, d, vec, asg_sc, asg_id, 4e-5f, maxnorm, labels, l1_list, l1_count,
-            nullptr, nullptr, 0, fb_count, fb_list, w.fb_cap);
+            nullptr, nullptr, 0, fb_count, fb_list, w.fb_cap, 0);
         FL_CHECK_LAUNCH();
     }
     rc = launch_fallback_fixup(fb_count, w.fb_cap, status, tc_pool_size(1), st);

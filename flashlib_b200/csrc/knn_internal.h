@@ -45,7 +45,11 @@ __host__ __device__ inline SimtDynSplit simt_dyn_split(int64_t count, int bq, in
     const int64_t nqb = (count + bq - 1) / bq;
     int64_t ns = nqb > 0 ? blocks / nqb : 1;
     const int64_t tiles = (m + 127) / 128;
-    if (ns > tiles / 4) ns = tiles / 4;
+    // ranges of at least four tiles -- or, for a database of a few tiles (k-means centroids), of one:
+    // a handful of slots is then still spread over eight times as many blocks
+    int64_t lim = tiles / 4;
+    if (lim < 8) lim = tiles < 8 ? tiles : 8;
+    if (ns > lim) ns = lim;
     if (ns > 296) ns = 296;     // two blocks per SM when a single query block is live
     if (ns < 1) ns = 1;
     const int64_t rps = ((m + ns - 1) / ns + 127) / 128 * 128;

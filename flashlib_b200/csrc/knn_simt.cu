@@ -11,12 +11,12 @@ namespace fl {
 // streams its split of the database in tiles of 128 rows, scores every pair with
 // score = <q,x> - ||x||^2/2 in fp32 FFMA and feeds the per-row pools.
 // ------------------------------------------------------------------------------------
+// One block's work: virtual block (vbx, vby) of the launch geometry described above.
 template <int TQ>
-__global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
+__device__ __forceinline__ void knn_simt_block(const SimtKnnParams& p, const int vbx, const int vby, float* smem) {
     using T = SimtTile<TQ>;
     constexpr int BQ = T::BQ;
     constexpr int SSTR = 129;
-    extern __shared__ __align__(16) float smem[];
     float* slab = smem;
     float* pool_sc = smem + T::SLAB_FLOATS;
     uint32_t* pool_id = reinterpret_cast<uint32_t*>(pool_sc + BQ * p.cap);
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
     int split;
     int nsplit = p.nsplit;
     if (p.ivf) {
-        const int b = blockIdx.x;
+        const int b = vbx;
         if (b >= p.item_off[p.nlist]) return;
         int lo = 0, hi = p.nlist;  // largest c with item_off[c] <= b
         while (hi - lo > 1) {
@@ -62,13 +62,13 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
             nsplit = ds.nsplit;
             rps = ds.rows_per_split;
             const int64_t nqb = (count + BQ - 1) / BQ;
-            slot0 = ((int64_t)blockIdx.x % nqb) * BQ;
-            split = (int)((int64_t)blockIdx.x / nqb);
+            slot0 = ((int64_t)vbx % nqb) * BQ;
+            split = (int)((int64_t)vbx / nqb);
             if (split >= nsplit) return;
         } else {
-            slot0 = (int64_t)blockIdx.x * BQ;
+            slot0 = (int64_t)vbx * BQ;
             if (slot0 >= count) return;
-            split = blockIdx.y;
+            split = vby;
         }
         row_begin = (int64_t)split * rps;
         row_end = min(p.m, row_begin + rps);
@@ -165,6 +165,27 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
     }
 }
 
+// The kernel proper.  Static geometries: one virtual block per block.  Dynamic mode (slot count on
+// the device): the launch has a fixed, modest number of blocks and each walks the virtual blocks
+// that the live slot count calls for -- a grid sized for the largest possible count would spend
+// most of its time launching blocks that find nothing to do.
+template <int TQ>
+__global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
+    extern __shared__ __align__(16) float smem[];
+    if (p.dyn_blocks <= 0 || p.ivf) {
+        knn_simt_block<TQ>(p, blockIdx.x, blockIdx.y, smem);
+        return;
+    }
+    const int64_t count = p.count_dev ? (int64_t)(*p.count_dev) : p.count;
+    if (count <= 0) return;
+    const int64_t nqb = (count + SimtTile<TQ>::BQ - 1) / SimtTile<TQ>::BQ;
+    const int64_t live = nqb * simt_dyn_split(count, SimtTile<TQ>::BQ, p.dyn_blocks, p.m).nsplit;
+    for (int64_t vb = blockIdx.x; vb < live; vb += gridDim.x) {
+        knn_simt_block<TQ>(p, (int)vb, 0, smem);
+        __syncthreads();
+    }
+}
+
 template <int TQ>
 static size_t simt_smem_bytes(int cap) {
     using T = SimtTile<TQ>;
@@ -209,7 +230,9 @@ static int launch_simt_t(const SimtKnnParams& p, int64_t max_slots, cudaStream_t
             set_error("dynamic split: plan made for %d queries per block, kernel uses %d", p.dyn_bq, SimtTile<TQ>::BQ);
             return FL_EINVAL;
         }
-        grid = dim3((unsigned)p.dyn_blocks, 1);
+        // (p.dyn_blocks stays the figure the range split and the pool storage are planned with)
+        const int launched = 4 * sm_count();
+        grid = dim3((unsigned)(p.dyn_blocks < launched ? p.dyn_blocks : launched), 1);
     }
     knn_simt_kernel<TQ><<<grid, 256, smem, st>>>(p);
     FL_CHECK_LAUNCH();

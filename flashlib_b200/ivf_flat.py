@@ -63,6 +63,40 @@ class IvfFlatIndex:
         return self._hnorm
 
 
+_INDEX_FORMAT = "flashlib_b200.IvfFlatIndex/1"
+
+
+def save_ivf_flat_index(index: IvfFlatIndex, path) -> None:
+    """Writes the index to ``path`` with ``torch.save``: the reference's ``IvfFlatIndex`` fields
+    (``ivf_flat/index.py:27-55``; the reference itself defines no on-disk format) as CPU tensors
+    plus a format tag.  Derived data -- the half norms and the tensor-core operand plane -- is
+    not stored: it is rebuilt from ``data`` on first use after loading."""
+    torch.save({"format": _INDEX_FORMAT,
+                "centroids": index.centroids.cpu(), "data": index.data.cpu(), "ids": index.ids.cpu(),
+                "list_offsets": index.list_offsets.cpu(), "metric": index.metric, "D": int(index.D),
+                "Dp": int(index.Dp), "nlist": int(index.nlist), "nprobe": int(index.nprobe),
+                "max_list_len": int(index.max_list_len)}, path)
+
+
+def load_ivf_flat_index(path, device=None) -> IvfFlatIndex:
+    """Reads an index written by :func:`save_ivf_flat_index` and moves it to ``device`` (default:
+    the tensors stay on the CPU; searching needs a CUDA device)."""
+    blob = torch.load(path, map_location="cpu", weights_only=True)
+    if not isinstance(blob, dict) or blob.get("format") != _INDEX_FORMAT:
+        raise ValueError(f"{path!s} is not a flashlib_b200 IVF-Flat index (format tag {blob.get('format') if isinstance(blob, dict) else None!r})")
+    t = {k: (blob[k].to(device) if device is not None else blob[k]) for k in ("centroids", "data", "ids", "list_offsets")}
+    if t["data"].shape[0] != t["ids"].shape[0] or t["list_offsets"].shape[0] != blob["nlist"] + 1 \
+            or int(t["list_offsets"][-1]) != t["data"].shape[0]:
+        raise ValueError(f"{path!s}: inconsistent index (rows, ids and list offsets do not agree)")
+    return IvfFlatIndex(centroids=t["centroids"], data=t["data"], ids=t["ids"], list_offsets=t["list_offsets"],
+                        metric=blob["metric"], D=blob["D"], Dp=blob["Dp"], nlist=blob["nlist"], nprobe=blob["nprobe"],
+                        max_list_len=blob["max_list_len"])
+
+
+IvfFlatIndex.save = save_ivf_flat_index
+IvfFlatIndex.load = staticmethod(load_ivf_flat_index)
+
+
 def _get_max_list_len(self) -> int:
     v = self.__dict__.get("_max_list_len", 0)
     if isinstance(v, torch.Tensor):

@@ -97,7 +97,21 @@ def euclid_assign_triton(x: torch.Tensor, centroids: torch.Tensor, out: Optional
         out = torch.empty((B, N), device=x.device, dtype=torch.int32)
     else:
         assert out.shape == (B, N) and out.dtype == torch.int32 and out.is_contiguous()
+    if mode is None:
+        mode = os.environ.get("FLASHLIB_B200_ASSIGN_MODE") or None
     with torch.cuda.device(x.device):
+        if B > 1 and not _use_tensor_cores(N, K, D, mode):
+            # many small problems (IVF-PQ's sub-quantisers: a few features, 256 centroids each):
+            # one launch with the batch on a grid axis instead of 2 B launches
+            lib = _lib.load()
+            xb = x.float().contiguous()
+            cb = centroids.float().contiguous()
+            ws_bytes = lib.fl_kmeans_assign_batch_workspace_bytes(B, N, K, D)
+            ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+            _lib.check(lib.fl_kmeans_assign_batch_f32(xb.data_ptr(), B, N, xb.stride(1), xb.stride(0), cb.data_ptr(), K,
+                                                      cb.stride(1), cb.stride(0), D, out.data_ptr(), ws.data_ptr(),
+                                                      ws_bytes, _stream_ptr(x.device)))
+            return out
         for b in range(B):
             _assign_2d(_as_f32_rows(x[b]), _as_f32_rows(centroids[b]), out[b], mode)
     return out
@@ -120,13 +134,19 @@ def triton_centroid_update_euclid(x: torch.Tensor, cluster_ids: torch.Tensor, ol
         centroid_cnts = torch.empty((B, K), device=x.device, dtype=torch.int32)
     assert centroid_sums.is_contiguous() and centroid_cnts.is_contiguous()
     with torch.cuda.device(x.device):
-        for b in range(B):
-            xb = _as_f32_rows(x[b])
-            lab = cluster_ids[b]
+        if B > 1:
+            xb = x.float().contiguous()
+            lab = cluster_ids.to(torch.int32).contiguous()
+            _lib.check(lib.fl_kmeans_update_batch_f32(xb.data_ptr(), B, N, xb.stride(1), D, lab.data_ptr(), K,
+                                                      centroid_sums.data_ptr(), centroid_cnts.data_ptr(),
+                                                      _stream_ptr(x.device)))
+        else:
+            xb = _as_f32_rows(x[0])
+            lab = cluster_ids[0]
             if lab.dtype != torch.int32 or not lab.is_contiguous():
                 lab = lab.to(torch.int32).contiguous()
             _lib.check(lib.fl_kmeans_update_f32(xb.data_ptr(), N, xb.stride(0), D, lab.data_ptr(), K,
-                                                centroid_sums[b].data_ptr(), centroid_cnts[b].data_ptr(),
+                                                centroid_sums[0].data_ptr(), centroid_cnts[0].data_ptr(),
                                                 _stream_ptr(x.device)))
     if not calculate_new:
         return centroid_sums, centroid_cnts
@@ -156,11 +176,11 @@ def triton_centroid_finalize(sums: torch.Tensor, cnts: torch.Tensor, old_centroi
         shift = torch.empty((B, K), device=sums.device, dtype=torch.float32)
     sums = sums.contiguous()
     cnts = cnts.contiguous()
+    assert shift.is_contiguous() and new32.is_contiguous()
     with torch.cuda.device(sums.device):
-        for b in range(B):
-            _lib.check(lib.fl_kmeans_finalize_f32(sums[b].data_ptr(), cnts[b].data_ptr(), old32[b].data_ptr(),
-                                                  new32[b].data_ptr(), shift[b].data_ptr(), K, D,
-                                                  _stream_ptr(sums.device)))
+        # the (B, K, D) arrays are contiguous: the batch is K * B centroids to the kernel
+        _lib.check(lib.fl_kmeans_finalize_f32(sums.data_ptr(), cnts.data_ptr(), old32.data_ptr(), new32.data_ptr(),
+                                              shift.data_ptr(), K * B, D, _stream_ptr(sums.device)))
     if direct:
         return out, shift
     if out is None:

@@ -213,8 +213,9 @@ int     fl_kmeans_assign_f32(const float* x, int64_t n, int64_t ldx,
 /* Tensor-core assignment (tcgen05 bf16 candidates, exact fp32 re-score, proven or recomputed */
 /* on the exact path; d <= 256).  Replaces the Blackwell assign kernels of                    */
 /* kmeans/cutedsl/blackwell_assign.py:77-2289 for fp32 inputs.  `xplane` is the bf16 operand   */
-/* plane of the sample rows built once per data set by fl_kmeans_prepare_x_f32 (NULL: built   */
-/* in the workspace on every call).  Labels are identical to fl_kmeans_assign_f32's.          */
+/* plane of the sample rows followed by their squared norms, built once per data set by       */
+/* fl_kmeans_prepare_x_f32 (NULL: both are built in the workspace on every call).  Labels are  */
+/* identical to fl_kmeans_assign_f32's.                                                       */
 int64_t fl_kmeans_xplane_bytes(int64_t n, int d);
 int     fl_kmeans_prepare_x_f32(const float* x, int64_t n, int d, int64_t ldx,
                                 void* xplane, int64_t xplane_bytes, void* stream);
@@ -239,6 +240,21 @@ int     fl_kmeans_assign_noalloc_f32(const float* x, int64_t n, int64_t ldx,
 int     fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d,
                              const int32_t* labels, int K,
                              float* sums, int32_t* cnts, void* stream);
+/* Batched forms for many small problems at once (the reference's kernels take the batch  */
+/* on a grid axis, kmeans/triton/assign.py:1028-1129; its IVF-PQ build runs B = m           */
+/* sub-quantisers of 2-8 features each, ivf_pq/triton/build.py:41-70): `batch` problems of  */
+/* n rows and K centroids each in one launch.  x is [batch][n][ldx] with x_batch_stride      */
+/* elements between items, c [batch][K][ldc] back to back, labels [batch][n], sums           */
+/* [batch][K][d], cnts [batch][K].  The exact CUDA-core kernels; results per item are those  */
+/* of the single-problem entry points.  fl_kmeans_finalize_f32 serves a batch as K * batch   */
+/* centroids (the arrays are contiguous).                                                   */
+int64_t fl_kmeans_assign_batch_workspace_bytes(int batch, int64_t n, int K, int d);
+int     fl_kmeans_assign_batch_f32(const float* x, int batch, int64_t n, int64_t ldx, int64_t x_batch_stride,
+                                   const float* c, int K, int64_t ldc, int64_t c_batch_stride, int d,
+                                   int32_t* labels, void* ws, int64_t ws_bytes, void* stream);
+int     fl_kmeans_update_batch_f32(const float* x, int batch, int64_t n, int64_t ldx, int d,
+                                   const int32_t* labels, int K,
+                                   float* sums, int32_t* cnts, void* stream);
 /* new_c = cnt ? sums/cnt : old_c ; shift[j] = ||new_c[j] - old_c[j]||_2.               */
 int     fl_kmeans_finalize_f32(const float* sums, const int32_t* cnts, const float* old_c,
                                float* new_c, float* shift, int K, int d, void* stream);

@@ -78,3 +78,54 @@ def test_large_kmeans_block_partition():
     assert [block_range(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
     assert [block_range(2, 4, r) for r in range(4)] == [(0, 1), (1, 2), (2, 2), (2, 2)]
     assert block_range(7, 1, 0) == (0, 7)
+
+
+def test_kmeans_class_routes_large_host_data_to_the_streaming_path(monkeypatch):
+    """CPU-resident data with more rows than chunk_size_data_cpu goes to kmeans_largeN /
+    kmeans_largeN_assign with that block size (flashlib/applications/kmeans.py:139-156, 229-240),
+    not to one whole-tensor copy."""
+    import torch
+    import flashlib_b200.kmeans_large as large
+    from flashlib_b200.applications import KMeans
+    calls = {}
+
+    def fake_fit(x, k, **kw):
+        calls["fit"] = (tuple(x.shape), k, kw["BLOCK_N"], kw["max_iters"])
+        return torch.zeros(x.shape[0], dtype=torch.int32), torch.zeros(k, x.shape[1])
+
+    def fake_assign(x, c, **kw):
+        calls["assign"] = (tuple(x.shape), tuple(c.shape), kw["BLOCK_N"])
+        return torch.zeros(x.shape[0], dtype=torch.int32)
+
+    monkeypatch.setattr(large, "kmeans_largeN", fake_fit)
+    monkeypatch.setattr(large, "kmeans_largeN_assign", fake_assign)
+    km = KMeans(d=4, k=3, niter=2, chunk_size_data_cpu=100, device="cpu")
+    x = torch.randn(250, 4)
+    assert km.fit_predict(x).shape == (250,)
+    assert calls["fit"] == ((250, 4), 3, 100, 2)
+    assert km.predict(x).shape == (250,)
+    assert calls["assign"] == ((250, 4), (3, 4), 100)
+
+
+def test_ivf_index_save_and_load_round_trip(tmp_path):
+    """Index persistence (torch.save of the reference's IvfFlatIndex fields): every field comes
+    back, caches are left to be rebuilt, a foreign file is refused."""
+    import torch
+    from flashlib_b200.ivf_flat import IvfFlatIndex, load_ivf_flat_index
+    g = torch.Generator().manual_seed(0)
+    idx = IvfFlatIndex(centroids=torch.randn(3, 16, generator=g), data=torch.randn(10, 16, generator=g),
+                       ids=torch.randperm(10, generator=g), list_offsets=torch.tensor([0, 4, 4, 10]), metric="l2",
+                       D=12, Dp=16, nlist=3, nprobe=2, max_list_len=torch.tensor([6], dtype=torch.int32))
+    path = tmp_path / "index.pt"
+    idx.save(path)
+    back = load_ivf_flat_index(path)
+    for f in ("centroids", "data", "ids", "list_offsets"):
+        assert torch.equal(getattr(back, f), getattr(idx, f))
+    assert (back.metric, back.D, back.Dp, back.nlist, back.nprobe, back.max_list_len) == ("l2", 12, 16, 3, 2, 6)
+    assert back._tc_plane is None and back._hnorm is None
+    assert isinstance(IvfFlatIndex.load(path), IvfFlatIndex)
+    other = tmp_path / "other.pt"
+    torch.save({"format": "something else"}, other)
+    import pytest
+    with pytest.raises(ValueError):
+        load_ivf_flat_index(other)

@@ -151,3 +151,31 @@ def test_large_n_streaming_matches_resident_kmeans():
     again = fl.kmeans_largeN_assign(X, cent_l, BLOCK_N=64_000)
     direct = fl.euclid_assign_triton(Xd[None], cent_l.float()[None])[0].cpu()
     assert torch.equal(again, direct)
+
+
+@pytest.mark.parametrize("B,n,d,K", [(16, 3000, 2, 256), (16, 2500, 8, 256), (5, 777, 3, 17), (3, 4000, 128, 40)])
+def test_batched_small_problems_match_the_oracle_per_item(B, n, d, K):
+    """Many small problems in one launch (the sub-quantiser regime of the reference's IVF-PQ build,
+    ivf_pq/triton/build.py:41-70): assignment, update and finalisation per batch item against the
+    oracle, and the batched Lloyd loop end to end."""
+    g = torch.Generator().manual_seed(B * 1000 + d)
+    x = torch.randn(B, n, d, generator=g)
+    c = x[:, :K].clone() + 0.01 * torch.randn(B, K, d, generator=g)
+    xd, cd = x.cuda(), c.cuda()
+    lab = fl.euclid_assign_triton(xd, cd)
+    assert lab.shape == (B, n) and lab.dtype == torch.int32
+    sums, cnts = fl.triton_centroid_update_euclid(xd, lab, cd, calculate_new=False)
+    new, shift = fl.triton_centroid_finalize(sums, cnts, cd)
+    for b in range(B):
+        ref = oracle.kmeans_assign(x[b].numpy(), c[b].numpy())
+        assert parity.label_parity(x[b].numpy(), c[b].numpy(), lab[b].cpu().numpy(), ref)["ok"], b
+        new_ref, sums_ref, cnts_ref = oracle.kmeans_update(x[b].numpy(), lab[b].cpu().numpy().astype(np.int64), c[b].numpy())
+        assert np.array_equal(cnts[b].cpu().numpy(), cnts_ref)
+        assert parity.rel_close(sums[b].cpu().numpy(), sums_ref, rel=1e-4, atol=1e-4)
+        assert parity.rel_close(new[b].cpu().numpy(), new_ref, rel=1e-4, atol=1e-5)
+        assert np.allclose(shift[b].cpu().numpy(), np.sqrt(((new_ref - c[b].numpy()) ** 2).sum(-1)), rtol=1e-4, atol=1e-5)
+    ids, cents, n_iter = fl.flash_kmeans(xd, K, max_iters=3, init_centroids=cd)
+    for b in (0, B - 1):
+        rl, rc, _ = oracle.kmeans(x[b].numpy(), K, max_iters=3, init_centroids=c[b].numpy())
+        assert (ids[b].cpu().numpy() == rl).mean() > 0.999
+        assert parity.rel_close(cents[b].cpu().numpy(), rc, rel=1e-3, atol=1e-4)
