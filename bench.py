@@ -163,7 +163,7 @@ def config_dict(world: int, result: str, resolved_tc: bool, nq: int) -> dict:
             if world > 1 else "single GPU",
             "mode": ("tcgen05 bf16 candidates + exact fp32 re-rank + verified fallback" if resolved_tc else
                      "exact fp32 CUDA-core scoring + exact re-rank"),
-            "l2": ("a 256 MB buffer is overwritten before every step (inside the timed region): a rank's "
+            "l2": ("a 160 MB buffer (larger than the 126 MB L2) is overwritten before every step (inside the timed region): a rank's "
                    f"operand plane is {plane_bytes >> 20} MB" if flushes else
                    f"no flush needed: each step streams the rank's operand plane ({plane_bytes >> 20} MB), "
                    "larger than the 126 MB L2")}
@@ -244,6 +244,80 @@ def run_reference(args, rank: int, world: int):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def _reference_gpu_child(dtype_name: str, backend):
+    """One measurement of the UNMODIFIED reference's GPU kernels (installed under baseline/_ref by
+    `python -m pip install --no-index --no-build-isolation --no-deps --target baseline/_ref
+    <reference tree>`) through its public `flashlib.flash_knn`, on the headline shape, in a process
+    of its own.  Prints one JSON line: time per 10,000 queries and recall@10 against this library's
+    exact result."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    out = {"impl": "reference-gpu", "dtype": dtype_name, "backend": backend or "auto"}
+    if not os.path.isdir(os.path.join(ref_dir, "flashlib")):
+        out["unavailable"] = "baseline/_ref holds no installed reference"
+        print(json.dumps(out), flush=True)
+        return
+    from flashlib_b200 import flash_knn as ours, synthetic
+    sys.path.insert(0, ref_dir)
+    try:
+        import flashlib                      # noqa: F401  (the reference)
+        from flashlib import flash_knn as theirs
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"import of the reference failed: {type(e).__name__}: {e}"[:300]
+        print(json.dumps(out), flush=True)
+        return
+    X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
+    Xd, Qd = X.cuda(), Q.cuda()
+    _, exact_i = ours(Qd, Xd, K_NEIGHBOURS)
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+    xq, xc = Qd.to(dt), Xd.to(dt)
+    try:
+        t0 = time.perf_counter()
+        vals, idxs = theirs(xq, xc, K_NEIGHBOURS, backend=backend)
+        torch.cuda.synchronize()
+        out["first_call_s"] = time.perf_counter() - t0           # includes the JIT compilation
+        ms = _time_steps(lambda: theirs(xq, xc, K_NEIGHBOURS, backend=backend), 10, 3)
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"the reference's kernel did not run: {type(e).__name__}: {e}"[:300]
+        print(json.dumps(out), flush=True)
+        return
+    a, b = idxs.cpu().numpy(), exact_i.cpu().numpy()
+    recall = float(np.mean([len(set(r.tolist()) & set(t.tolist())) / K_NEIGHBOURS for r, t in zip(a, b)]))
+    same_rows = float(np.mean([set(r.tolist()) == set(t.tolist()) for r, t in zip(a, b)]))
+    out.update({"ms_per_step": ms, "value": QUERIES_PER_GPU / (ms * 1e-3), "unit": UNIT,
+                "tensor_tflops_algorithmic": 2.0 * QUERIES_PER_GPU * DB_ROWS * DIM / (ms * 1e-3) / 1e12,
+                "recall_at_10_vs_exact": recall, "rows_with_the_exact_set": same_rows,
+                "note": "exact = this library's result for the fp32 inputs; the bf16 legs search the bf16-rounded data"})
+    print(json.dumps(out), flush=True)
+
+
+def run_reference_gpu(args):
+    """The reference's own GPU kernels on this box, beside ours: every leg in a child process with a
+    time limit (a leg that does not come back is reported, not retried)."""
+    legs = [("fp32", "triton"), ("bf16", "triton"), ("bf16", None)]
+    if args.ref_leg:
+        d_, b_ = args.ref_leg.split(":")
+        _reference_gpu_child(d_, None if b_ == "auto" else b_)
+        return
+    for d_, b_ in legs:
+        cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--ref-leg", f"{d_}:{b_ or 'auto'}"]
+        try:
+            res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=420)
+            lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+            print(lines[-1] if lines else json.dumps({"impl": "reference-gpu", "dtype": d_, "backend": b_ or "auto",
+                                                      "unavailable": (res.stderr or "no output")[-300:]}), flush=True)
+        except subprocess.TimeoutExpired:
+            print(json.dumps({"impl": "reference-gpu", "dtype": d_, "backend": b_ or "auto",
+                              "unavailable": "no result within 420 s"}), flush=True)
+    # ours, same process layout, for the table
+    import flashlib_b200 as fl
+    from flashlib_b200 import synthetic
+    X, Q = synthetic.mixture(DB_ROWS, DIM, N_COMP, SEED, nq=QUERIES_PER_GPU, clamp=True)
+    Xd, Qd = X.cuda(), Q.cuda()
+    ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, K_NEIGHBOURS), 10, 3)
+    print(json.dumps({"impl": "ours", "dtype": "fp32 in, exact fp32 out", "ms_per_step": ms,
+                      "value": QUERIES_PER_GPU / (ms * 1e-3), "unit": UNIT, "recall_at_10_vs_exact": 1.0}), flush=True)
 
 
 def _time_steps(fn, steps, warmup):
@@ -411,7 +485,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="reference: the reference's CPU path (oracle port) on the host cores; reference-gpu: the "
+                         "unmodified reference's own GPU kernels from baseline/_ref, one GPU, for the comparison table")
+    ap.add_argument("--ref-leg", default=None, help="internal: one leg of --impl reference-gpu, 'dtype:backend'")
     ap.add_argument("--mode", default=None, help="kNN scoring mode: exact | bf16 | None (auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="N = 1: skip the k-means / IVF-Flat / k=100 legs")
@@ -446,6 +523,10 @@ def main():
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    if args.impl == "reference-gpu":
+        if rank == 0:
+            run_reference_gpu(args)
+        return
     if args.workload not in ("knn_1m", "knn_100m"):
         run_secondary(args)
         return
@@ -478,10 +559,10 @@ def main():
     torch.cuda.synchronize()
 
     # Timing hygiene: when this rank's operand plane is not well above the 126 MB L2 it would stay
-    # cache-resident from step to step, so a 256 MB buffer is overwritten before every step
+    # cache-resident from step to step, so a 160 MB buffer (larger than the L2) is overwritten before every step
     # (inside the timed region).
     plane_bytes = db.shape[0] * (((DIM + 63) // 64) * 64 + 16) * 2
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if plane_bytes < (256 << 20) else None
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev) if plane_bytes < (256 << 20) else None
 
     def step_device():
         if flush is not None:

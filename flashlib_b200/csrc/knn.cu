@@ -461,8 +461,8 @@ extern "C" int fl_knn_seed_f32(const float* q, int64_t nq, int64_t ldq, int d, i
         set_error("fl_knn_seed_f32: shape (nq=%lld m=%lld d=%d) outside the tensor-core kernel's range", (long long)nq, (long long)m, d);
         return FL_EUNSUPPORTED;
     }
-    return knn_tc_phases(TC_PREP | TC_SEED, q, nq, ldq, nullptr, m, d, d, k, plane, 0, seed_cls, nullptr, nullptr, nullptr,
-                         ws, ws_bytes, status, (cudaStream_t)stream);
+    return knn_tc_phases(TC_PREP | TC_SEED, q, nq, ldq, nullptr, m, d, d, k, plane, 0, seed_cls, nullptr, nullptr,
+                         nullptr, ws, ws_bytes, status, (cudaStream_t)stream);
 }
 
 extern "C" int fl_knn_seeded_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb,

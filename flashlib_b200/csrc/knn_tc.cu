@@ -589,18 +589,29 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                 tau = cr.y;
                                 waddr = my_addr + 8ull * (uint64_t)cnt;
                             }
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const uint32_t id = row_base + slice * 32 + g * 8 + j;
-                                asm volatile(
-                                    "{\n\t.reg .pred p;\n\t"
-                                    "setp.gt.f32 p, %1, %2;\n\t"
-                                    "@p st.global.v2.b32 [%0], {%3, %4};\n\t"
-                                    "@p add.u64 %0, %0, 8;\n\t}"
-                                    : "+l"(waddr)
-                                    : "f"(__uint_as_float(v[g * 8 + j])), "f"(tau), "r"(v[g * 8 + j]), "r"(id)
-                                    : "memory");
-                            }
+                            // the 8 comparisons first (independent), then the predicated stores: only
+                            // the address increments form a chain
+                            const uint32_t col0 = row_base + slice * 32 + g * 8;
+                            const uint32_t* x = v + g * 8;
+                            asm volatile(
+                                "{\n\t.reg .pred p0, p1, p2, p3, p4, p5, p6, p7;\n\t.reg .b32 c;\n\t"
+                                "setp.gt.f32 p0, %3, %1;\n\tsetp.gt.f32 p1, %4, %1;\n\tsetp.gt.f32 p2, %5, %1;\n\tsetp.gt.f32 p3, %6, %1;\n\t"
+                                "setp.gt.f32 p4, %7, %1;\n\tsetp.gt.f32 p5, %8, %1;\n\tsetp.gt.f32 p6, %9, %1;\n\tsetp.gt.f32 p7, %10, %1;\n\t"
+                                "@p0 st.global.v2.b32 [%0], {%11, %2};\n\t@p0 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 1;\n\t"
+                                "@p1 st.global.v2.b32 [%0], {%12, c};\n\t@p1 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 2;\n\t"
+                                "@p2 st.global.v2.b32 [%0], {%13, c};\n\t@p2 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 3;\n\t"
+                                "@p3 st.global.v2.b32 [%0], {%14, c};\n\t@p3 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 4;\n\t"
+                                "@p4 st.global.v2.b32 [%0], {%15, c};\n\t@p4 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 5;\n\t"
+                                "@p5 st.global.v2.b32 [%0], {%16, c};\n\t@p5 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 6;\n\t"
+                                "@p6 st.global.v2.b32 [%0], {%17, c};\n\t@p6 add.u64 %0, %0, 8;\n\tadd.u32 c, %2, 7;\n\t"
+                                "@p7 st.global.v2.b32 [%0], {%18, c};\n\t@p7 add.u64 %0, %0, 8;\n\t}"
+                                : "+l"(waddr)
+                                : "f"(tau), "r"(col0),
+                                  "f"(__uint_as_float(x[0])), "f"(__uint_as_float(x[1])), "f"(__uint_as_float(x[2])),
+                                  "f"(__uint_as_float(x[3])), "f"(__uint_as_float(x[4])), "f"(__uint_as_float(x[5])),
+                                  "f"(__uint_as_float(x[6])), "f"(__uint_as_float(x[7])),
+                                  "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7])
+                                : "memory");
                         }
                     };
                     dense(va, 0);
@@ -643,18 +654,27 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                                 tau = cr.y;
                                 waddr = my_addr + 8u * (uint32_t)cnt;
                             }
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const uint32_t id = row_base + slice * 32 + g * 8 + j;
-                                asm volatile(
-                                    "{\n\t.reg .pred p;\n\t"
-                                    "setp.gt.f32 p, %1, %2;\n\t"
-                                    "@p st.shared.v2.b32 [%0], {%3, %4};\n\t"
-                                    "@p add.u32 %0, %0, 8;\n\t}"
-                                    : "+r"(waddr)
-                                    : "f"(__uint_as_float(v[g * 8 + j])), "f"(tau), "r"(v[g * 8 + j]), "r"(id)
-                                    : "memory");
-                            }
+                            const uint32_t col0 = row_base + slice * 32 + g * 8;
+                            const uint32_t* x = v + g * 8;
+                            asm volatile(
+                                "{\n\t.reg .pred p0, p1, p2, p3, p4, p5, p6, p7;\n\t.reg .b32 c;\n\t"
+                                "setp.gt.f32 p0, %3, %1;\n\tsetp.gt.f32 p1, %4, %1;\n\tsetp.gt.f32 p2, %5, %1;\n\tsetp.gt.f32 p3, %6, %1;\n\t"
+                                "setp.gt.f32 p4, %7, %1;\n\tsetp.gt.f32 p5, %8, %1;\n\tsetp.gt.f32 p6, %9, %1;\n\tsetp.gt.f32 p7, %10, %1;\n\t"
+                                "@p0 st.shared.v2.b32 [%0], {%11, %2};\n\t@p0 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 1;\n\t"
+                                "@p1 st.shared.v2.b32 [%0], {%12, c};\n\t@p1 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 2;\n\t"
+                                "@p2 st.shared.v2.b32 [%0], {%13, c};\n\t@p2 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 3;\n\t"
+                                "@p3 st.shared.v2.b32 [%0], {%14, c};\n\t@p3 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 4;\n\t"
+                                "@p4 st.shared.v2.b32 [%0], {%15, c};\n\t@p4 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 5;\n\t"
+                                "@p5 st.shared.v2.b32 [%0], {%16, c};\n\t@p5 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 6;\n\t"
+                                "@p6 st.shared.v2.b32 [%0], {%17, c};\n\t@p6 add.u32 %0, %0, 8;\n\tadd.u32 c, %2, 7;\n\t"
+                                "@p7 st.shared.v2.b32 [%0], {%18, c};\n\t@p7 add.u32 %0, %0, 8;\n\t}"
+                                : "+r"(waddr)
+                                : "f"(tau), "r"(col0),
+                                  "f"(__uint_as_float(x[0])), "f"(__uint_as_float(x[1])), "f"(__uint_as_float(x[2])),
+                                  "f"(__uint_as_float(x[3])), "f"(__uint_as_float(x[4])), "f"(__uint_as_float(x[5])),
+                                  "f"(__uint_as_float(x[6])), "f"(__uint_as_float(x[7])),
+                                  "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7])
+                                : "memory");
                         }
                     };
                     dense(va, 0);
@@ -1188,6 +1208,7 @@ int tc_seed_tiles(int64_t m_pad, int k) {
     const int n_tiles = (int)(m_pad / TC_BN);
     const TcExperiment& ex = tc_experiment();
     int seed_tiles = n_tiles >= 1024 ? 64 : n_tiles / 16;
+
     if (tc_knn_big(k)) {
         const double sample_rank = k >= 64 ? 22.2 : 9.2;
         seed_tiles = (int)((double)n_tiles * sample_rank / (6.0 * k));
