@@ -28,6 +28,7 @@ FL_STATUS_ERROR = 0
 FL_STATUS_WHERE = 1
 FL_STATUS_FALLBACK = 2
 FL_STATUS_POOL = 3
+FL_STATUS_STAGE2 = 4
 
 # name -> (restype, argtypes); mirrors include/flashlib_b200.h one to one.
 SIGNATURES = {
@@ -44,6 +45,11 @@ SIGNATURES = {
     "fl_knn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int, c_int]),
     "fl_knn_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_knn_split_plane_bytes": (c_int64, [c_int64, c_int]),
+    "fl_knn_prepare_split_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
+    "fl_knn_staged_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int]),
+    "fl_knn_staged_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
+                                  c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_knn_seed_floats": (c_int64, [c_int64]),
     "fl_knn_seed_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p,
                                 c_void_p, c_int64, c_void_p, c_void_p]),

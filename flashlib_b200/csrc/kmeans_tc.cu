@@ -64,25 +64,52 @@ __global__ void split_c_plane_kernel(const float* __restrict__ c, int64_t m, int
 
 // Sample side of the second stage: the points listed in `rows` (live count on the device, at most
 // `cap`), one warp per row in a grid-stride loop, written as split rows [hi | lo | hi | ones].
+// With `tau_out` (kNN second stage) row r also gets its starting threshold: the exact k-th distance
+// d_k found so far (prev_dist [point][k]) bounds the true one from above, so every true neighbour
+// scores at least (||x||^2 - d_k) / 2 exactly and at most eps = eps_rel ||x|| *maxnorm less in
+// this stage; the threshold sits 2 eps and the proof's slack below that, so that a pool that never
+// overflowed proves its row.
 __global__ void split_x_gather_kernel(const float* __restrict__ x, int64_t ldx, int d, const int* __restrict__ rows,
                                       const int* __restrict__ rows_count, int cap, __nv_bfloat16* __restrict__ out,
-                                      int d_pad) {
+                                      int d_pad, const float* __restrict__ prev_dist, int k,
+                                      const float* __restrict__ maxnorm, float eps_rel, float* __restrict__ tau_out) {
     const int lane = threadIdx.x & 31;
     const int pitch = 3 * d_pad + PLANE_AUG_COLS;
     int count = *rows_count;
     count = count < cap ? count : cap;
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    if (tau_out != nullptr) {
+        // rows of the last live tile beyond the list's end hold stale memory: they must never append
+        const int tile_end = (count + 127) & ~127;
+        for (int r = count + blockIdx.x * blockDim.x + threadIdx.x; r < tile_end; r += gridDim.x * blockDim.x) tau_out[r] = pos_inf();
+    }
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < count; r += nwarps) {
-        const float* src = x + (int64_t)rows[r] * ldx;
+        const int64_t pt = rows[r];
+        const float* src = x + pt * ldx;
         __nv_bfloat16* o = out + (int64_t)r * pitch;
+        float qsq = 0.f;
         for (int t = lane; t < d_pad; t += 32) {
             __nv_bfloat16 hi, lo;
-            bf16_split(t < d ? __ldg(src + t) : 0.f, hi, lo);
+            const float v = t < d ? __ldg(src + t) : 0.f;
+            qsq += v * v;
+            bf16_split(v, hi, lo);
             o[t] = hi;
             o[d_pad + t] = lo;
             o[2 * d_pad + t] = hi;
         }
         if (lane < PLANE_AUG_COLS) o[3 * d_pad + lane] = __float2bfloat16_rn(lane < 3 ? 1.f : 0.f);
+        if (tau_out != nullptr) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, off);
+            if (lane == 0) {
+                const float dk = prev_dist[pt * k + (k - 1)];
+                const float mn = __ldg(maxnorm);
+                float tau = neg_inf();
+                if (dk < pos_inf())
+                    tau = 0.5f * (qsq - dk) - 2.f * eps_rel * sqrtf(qsq) * mn - 1e-5f * (qsq + mn * mn);
+                tau_out[r] = tau;
+            }
+        }
     }
 }
 
@@ -293,6 +320,32 @@ static AssignTcWs assign_tc_plan(int64_t n, int K, int d, int have_xplane) {
     return w;
 }
 
+int split_plane_supported(int d) { return assign_tc_split(d); }
+
+// Split database plane [hi | hi | lo | norm terms] in the layout plane_layout(m, 3 d_pad).
+int launch_split_db_plane(const float* c, int64_t m, int d, int64_t ldc, void* plane, cudaStream_t st) {
+    const int d_pad = (int)round_up(d, 64);
+    const PlaneLayout L = plane_layout(m, 3 * d_pad);
+    char* pl = static_cast<char*>(plane);
+    FL_CHECK_CUDA(cudaMemsetAsync(pl + L.off_meta, 0, 1024, st));
+    const int wpb = 8;
+    split_c_plane_kernel<<<(unsigned)ceil_div(L.m_pad, wpb), wpb * 32, 0, st>>>(
+        c, m, d, ldc, reinterpret_cast<__nv_bfloat16*>(pl + L.off_rows), reinterpret_cast<float*>(pl + L.off_hnorm),
+        reinterpret_cast<unsigned int*>(pl + L.off_meta), L.m_pad, d_pad);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
+int launch_split_query_gather(const float* x, int64_t ldx, int d, const int* rows, const int* rows_count, int cap,
+                              void* out, int d_pad, const float* prev_dist, int k, const float* maxnorm, float eps_rel,
+                              float* tau_out, cudaStream_t st) {
+    split_x_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(x, ldx, d, rows, rows_count, cap,
+                                                                     static_cast<__nv_bfloat16*>(out), d_pad, prev_dist, k,
+                                                                     maxnorm, eps_rel, tau_out);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 int assign_tc_supported(int64_t n, int K, int d) {
     if (n < 1 || K < 1 || d > 256) return 0;
     return 1;
@@ -352,13 +405,8 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     char* cpl3 = nullptr;
     if (w.split) {
         cpl3 = base + w.off_cplane3;
-        FL_CHECK_CUDA(cudaMemsetAsync(cpl3 + w.cl3.off_meta, 0, 1024, st));
-        const int wpb = 8;
-        split_c_plane_kernel<<<(unsigned)ceil_div(w.cl3.m_pad, wpb), wpb * 32, 0, st>>>(
-            c, K, d, ldc, reinterpret_cast<__nv_bfloat16*>(cpl3 + w.cl3.off_rows),
-            reinterpret_cast<float*>(cpl3 + w.cl3.off_hnorm), reinterpret_cast<unsigned int*>(cpl3 + w.cl3.off_meta),
-            w.cl3.m_pad, w.d_pad);
-        FL_CHECK_LAUNCH();
+        rc = launch_split_db_plane(c, K, d, ldc, cpl3, st);
+        if (rc != FL_OK) return rc;
     }
     // sample plane (query side)
     const char* xpl = static_cast<const char*>(xplane);
@@ -426,7 +474,8 @@ extern "C" int fl_kmeans_assign_tc_f32(const float* x, int64_t n, int64_t ldx, c
     // ---- stage 2: split planes for the unproven points --------------------------------------
     if (w.split) {
         __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(base + w.off_xsplit);
-        split_x_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(x, ldx, d, l1_list, l1_count, w.l1_cap, xs, w.d_pad);
+        split_x_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(x, ldx, d, l1_list, l1_count, w.l1_cap, xs, w.d_pad,
+                                                                         nullptr, 0, nullptr, 0.f, nullptr);
         FL_CHECK_LAUNCH();
         TcKnnParams tp{};
         tp.qplane = xs; tp.nq = w.l1_cap; tp.nq_pad = w.l1_pad;

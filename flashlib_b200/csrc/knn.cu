@@ -7,8 +7,9 @@
 namespace fl {
 
 // out[i] = ||x_i||^2 / 2
+// ||x||^2 / 2 per row and (maxnorm_bits, zero-initialised) the largest row norm.
 __global__ void halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, int64_t ld,
-                                float* __restrict__ out) {
+                                float* __restrict__ out, unsigned int* __restrict__ maxnorm_bits) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n) return;
@@ -17,8 +18,16 @@ __global__ void halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, i
     for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
-    if (lane == 0) out[row] = 0.5f * s;
+    if (lane == 0) {
+        out[row] = 0.5f * s;
+        atomicMax(maxnorm_bits, __float_as_uint(sqrtf(s)));    // norms are >= 0: their bit patterns order like the values
+    }
 }
+
+// Relative bound (of ||q|| max||x||) on the error of an fp32 score <q,x> - ||x||^2/2 accumulated on
+// the CUDA cores: the exact re-rank walks past the k + 8 best scores while rows that close could
+// still change the answer.
+constexpr float SIMT_EPS_REL = 4e-6f;
 
 // bf16 query plane [nq_pad][d_pad + 16]: the features, zero padding, and ones in the three
 // columns that meet the database plane's split -||x||^2/2 terms.
@@ -52,9 +61,12 @@ __global__ void fill_f32_kernel(float* p, int64_t n, float v) {
     if (i < n) p[i] = v;
 }
 
-// Clamps the fallback count to the list capacity and publishes it in the status words.
-__global__ void fallback_fixup_kernel(int* fb_count, int fb_cap, int32_t* status, int K1) {
+// Clamps the fallback count to the list capacity and publishes it (and the number of rows the
+// split-plane stage took) in the status words.
+__global__ void fallback_fixup_kernel(int* fb_count, int fb_cap, int32_t* status, int K1, const int* s2_count = nullptr,
+                                      int s2_cap = 0) {
     int c = *fb_count;
+    if (status && s2_count) { const int c2 = *s2_count; status[FL_STATUS_STAGE2] = c2 < s2_cap ? c2 : s2_cap; }
     if (status) {
         status[FL_STATUS_FALLBACK] = c;
         status[FL_STATUS_POOL] = K1;
@@ -83,6 +95,11 @@ struct KnnWs {
     int64_t nq_pad; int d_pad; int fb_cap; int fb_bq, fb_blocks;
     int64_t off_hnorm, off_qplane, off_part_sc, off_part_id, off_part_tau, off_part_cnt, off_seed_cls, off_tau, off_cert, off_cnt, off_fblist,
         off_fbpart_sc, off_fbpart_id, bytes;
+    // second stage (split hi/lo planes) for the rows the first proof rejects
+    int s2;                                    // 1: planned
+    int s2_cap; int64_t s2_pad;                // rows the stage takes (the rest go to the exact path), padded to tiles
+    int s2_nsplit; int64_t s2_tiles_per_split; int s2_plen;
+    int64_t off_s2_list, off_s2_qplane, off_s2_tau, off_s2_part_sc, off_s2_part_id, off_s2_part_tau, off_s2_part_cnt;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -91,7 +108,14 @@ static int64_t take(int64_t& cur, int64_t bytes) {
     return o;
 }
 
-static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
+// Rows the split-plane stage takes: a quarter of the queries, all of them below 4096.
+static int knn_stage2_rows(int64_t nq) {
+    int64_t c = nq / 4;
+    if (c < 4096) c = nq < 4096 ? nq : 4096;
+    return (int)c;
+}
+
+static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode, int staged = 0) {
     KnnWs w{};
     w.mode = mode;
     int64_t cur = 0;
@@ -139,6 +163,29 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode) {
         const int64_t fb_pools = (int64_t)w.fb_blocks * (w.fb_bq > 0 ? w.fb_bq : 1);
         w.off_fbpart_sc = take(cur, fb_pools * w.K1f * 4);
         w.off_fbpart_id = take(cur, fb_pools * w.K1f * 4);
+        if (staged && split_plane_supported(d)) {
+            w.s2 = 1;
+            w.s2_cap = knn_stage2_rows(nq);
+            w.s2_pad = round_up(w.s2_cap, 128);
+            w.s2_plen = tc_partial_len(17);            // the large global-memory pools
+            // Ranges: the live row count is only known on the device and is usually a small part of
+            // the capacity, so plan for an eighth of it (more ranges keep the SMs busy when few query
+            // tiles are live), within 256 MB of pools.
+            int64_t plan_rows = round_up(ceil_div(w.s2_cap, 8), 128);
+            tc_split_plan(plan_rows, m_pad, 17, &w.s2_nsplit, &w.s2_tiles_per_split);
+            const int64_t n_tiles = m_pad / 256;
+            while (w.s2_nsplit > 1 && w.s2_pad * w.s2_nsplit * (int64_t)w.s2_plen * 8 > (256ll << 20)) {
+                w.s2_tiles_per_split = ceil_div(n_tiles, w.s2_nsplit - 1);
+                w.s2_nsplit = (int)ceil_div(n_tiles, w.s2_tiles_per_split);
+            }
+            w.off_s2_list = take(cur, (int64_t)w.s2_cap * 4);
+            w.off_s2_qplane = take(cur, w.s2_pad * (3 * w.d_pad + PLANE_AUG_COLS) * 2);
+            w.off_s2_tau = take(cur, w.s2_pad * 4);
+            w.off_s2_part_sc = take(cur, w.s2_pad * w.s2_nsplit * (int64_t)w.s2_plen * 4);
+            w.off_s2_part_id = take(cur, w.s2_pad * w.s2_nsplit * (int64_t)w.s2_plen * 4);
+            w.off_s2_part_tau = take(cur, w.s2_pad * w.s2_nsplit * tc_taus_per_range() * 4);
+            w.off_s2_part_cnt = take(cur, w.s2_pad * w.s2_nsplit * tc_taus_per_range() * 4);
+        }
     } else {
         w.K1 = simt_pool_size(k);
         w.K1f = w.K1;
@@ -275,8 +322,8 @@ enum { TC_PREP = 1, TC_SEED = 2, TC_SCORE = 4 };
 static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb,
                          int d, int k, const void* plane, int64_t row_offset, float* seed_cls, const float* gmaxnorm,
                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status,
-                         cudaStream_t st) {
-    const KnnWs w = knn_ws_plan(nq, m, d, k, FL_KNN_BF16_RERANK);
+                         cudaStream_t st, const void* split_plane = nullptr) {
+    const KnnWs w = knn_ws_plan(nq, m, d, k, FL_KNN_BF16_RERANK, split_plane != nullptr);
     if (ws_bytes < w.bytes) {
         set_error("fl_knn: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
         return FL_EWORKSPACE;
@@ -356,9 +403,46 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     fp.cert_tau = gmaxnorm != nullptr ? cert : nullptr;
     fp.fb_count = fb_count; fp.fb_list = fb_list; fp.fb_cap = w.fb_cap;
     fp.part_cnt = tp.part_cnt;
+    int* s2_count = fb_count + 64;
+    int* s2_list = w.s2 ? reinterpret_cast<int*>(base + w.off_s2_list) : nullptr;
+    if (w.s2) { fp.next_count = s2_count; fp.next_list = s2_list; fp.next_cap = w.s2_cap; }
     rc = tc_knn_big(k) ? launch_knn_finalize_big(fp, nq, st) : launch_knn_finalize(fp, nq, st);
     if (rc != FL_OK) return rc;
-    fallback_fixup_kernel<<<1, 1, 0, st>>>(fb_count, w.fb_cap, status, w.K1);
+
+    // Second stage: the rejected rows are scored again with split (hi/lo) operands -- an error
+    // bound a hundred times smaller -- against the split database plane, each starting from the
+    // threshold its k-th distance so far implies; the same proof then accepts nearly all of them.
+    if (w.s2) {
+        const PlaneLayout L3 = plane_layout(m, 3 * w.d_pad);
+        const char* pl3 = static_cast<const char*>(split_plane);
+        const float* maxnorm3 = reinterpret_cast<const float*>(pl3 + L3.off_meta);
+        const float eps2 = 4e-5f;   // 3 * 2^-18 from the dropped lo.lo and rounded lo terms, plus fp32 accumulation
+        float* tau2 = reinterpret_cast<float*>(base + w.off_s2_tau);
+        rc = launch_split_query_gather(q, ldq, d, s2_list, s2_count, w.s2_cap, base + w.off_s2_qplane, w.d_pad, out_dist, k,
+                                       maxnorm3, eps2, tau2, st);
+        if (rc != FL_OK) return rc;
+        TcKnnParams t2{};
+        t2.qplane = base + w.off_s2_qplane; t2.nq = w.s2_cap; t2.nq_pad = w.s2_pad;
+        t2.dbrows = pl3 + L3.off_rows; t2.hnorm = reinterpret_cast<const float*>(pl3 + L3.off_hnorm);
+        t2.m = m; t2.m_pad = L3.m_pad; t2.d_pad = L3.d_pad; t2.K1 = tc_pool_size(17);
+        t2.nsplit = w.s2_nsplit; t2.tiles_per_split = w.s2_tiles_per_split;
+        t2.part_sc = reinterpret_cast<float*>(base + w.off_s2_part_sc);
+        t2.part_id = reinterpret_cast<uint32_t*>(base + w.off_s2_part_id);
+        t2.part_tau = reinterpret_cast<float*>(base + w.off_s2_part_tau);
+        t2.part_cnt = reinterpret_cast<int*>(base + w.off_s2_part_cnt);
+        t2.tau = tau2; t2.status = status; t2.k = k; t2.big_pools = 1; t2.nq_dev = s2_count;
+        rc = launch_knn_tc_scoring(t2, st);
+        if (rc != FL_OK) return rc;
+        FinalizeParams f2 = fp;
+        f2.qlist = s2_list; f2.count_dev = s2_count; f2.count = w.s2_cap;
+        f2.part_sc = t2.part_sc; f2.part_id = t2.part_id; f2.nsplit = w.s2_nsplit; f2.K1 = w.s2_plen;
+        f2.rerank = f2.K1; f2.part_tau = t2.part_tau; f2.ntau = w.s2_nsplit * tc_taus_per_range();
+        f2.part_cnt = t2.part_cnt; f2.eps_rel = eps2; f2.maxnorm = maxnorm3; f2.cert_tau = nullptr;
+        f2.next_count = nullptr; f2.next_list = nullptr; f2.next_cap = 0;
+        rc = launch_knn_finalize_big(f2, w.s2_cap, st);
+        if (rc != FL_OK) return rc;
+    }
+    fallback_fixup_kernel<<<1, 1, 0, st>>>(fb_count, w.fb_cap, status, w.K1, w.s2 ? s2_count : nullptr, w.s2_cap);
     FL_CHECK_LAUNCH();
 
     // Rows whose pool could not be proven complete: exact CUDA-core pass over the list.
@@ -377,8 +461,11 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     FinalizeParams ff = fp;
     ff.qlist = fb_list; ff.count_dev = fb_count; ff.count = 0;
     ff.part_sc = sp.part_sc; ff.part_id = sp.part_id; ff.nsplit = w.nsplit_fb; ff.K1 = w.K1f;
-    ff.rerank = (k + 8 < w.K1f) ? k + 8 : w.K1f; ff.verify = 0; ff.part_tau = nullptr; ff.ntau = 0;
+    // as in the exact mode: walk until k distances are safe against the fp32 scoring error; last pass
+    ff.rerank = simt_pool_keep(w.K1f, k); ff.verify = 1; ff.eps_rel = SIMT_EPS_REL; ff.part_tau = nullptr; ff.ntau = 0;
+    ff.fb_count = nullptr; ff.fb_list = nullptr; ff.fb_cap = 0;
     ff.cert_tau = nullptr;
+    ff.next_count = nullptr; ff.next_list = nullptr; ff.next_cap = 0;
     ff.dyn_blocks = w.fb_blocks; ff.dyn_bq = w.fb_bq;
     return launch_knn_finalize(ff, w.fb_cap, st);
 }
@@ -406,14 +493,18 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
     FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
     const float* hnorm;
+    const float* maxnorm;
     if (plane) {
         const PlaneLayout L = plane_layout(m, d);
         hnorm = reinterpret_cast<const float*>(static_cast<const char*>(plane) + L.off_hnorm);
+        maxnorm = reinterpret_cast<const float*>(static_cast<const char*>(plane) + L.off_meta);
     } else {
         float* h = reinterpret_cast<float*>(base + w.off_hnorm);
-        halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h);
+        unsigned int* mx = reinterpret_cast<unsigned int*>(base + w.off_cnt) + 128;    // cleared above
+        halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h, mx);
         FL_CHECK_LAUNCH();
         hnorm = h;
+        maxnorm = reinterpret_cast<const float*>(mx);
     }
     SimtKnnParams sp{};
     sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
@@ -432,8 +523,13 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
     fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
     fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
-    fp.k = k; fp.rerank = (k + 8 < w.K1) ? k + 8 : w.K1; fp.row_offset = row_offset;
-    fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 0;
+    // The walk over the merged pool (best score first) ends once k exact distances lie below what the
+    // next score allows, the fp32 scoring error included -- usually after k + 8 entries, further where
+    // many rows sit within that error of the k-th neighbour.  Nothing is queued: this is the last pass.
+    // (The scan's compactions keep simt_pool_keep entries per pool: down to that depth the merged list
+    // misses no row that scored above its entries, so that is how far the walk may go.)
+    fp.k = k; fp.rerank = simt_pool_keep(w.K1, k); fp.row_offset = row_offset;
+    fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 1; fp.eps_rel = SIMT_EPS_REL; fp.maxnorm = maxnorm;
     rc = launch_knn_finalize(fp, nq, st);
     if (rc != FL_OK) return rc;
     if (status) {
@@ -523,6 +619,45 @@ extern "C" int fl_gather_l2sq_f32(const float* x, int64_t n, int64_t ldx, const 
                                                           static_cast<const int32_t*>(idx), k, out);
     FL_CHECK_LAUNCH();
     return FL_OK;
+}
+
+extern "C" int64_t fl_knn_split_plane_bytes(int64_t m, int d) {
+    if (m < 1 || d < 1 || !split_plane_supported(d)) return 0;
+    return plane_layout(m, 3 * (int)round_up(d, 64)).bytes;
+}
+
+extern "C" int fl_knn_prepare_split_f32(const float* db, int64_t m, int d, int64_t ld, void* split_plane,
+                                        int64_t split_plane_bytes, void* stream) {
+    FL_CHECK_ARG(m >= 1 && d >= 1 && ld >= d, "fl_knn_prepare_split_f32: bad shape m=%lld d=%d ld=%lld", (long long)m, d,
+                 (long long)ld);
+    FL_CHECK_ARG(db && split_plane, "fl_knn_prepare_split_f32: null pointer");
+    FL_CHECK_ARG((reinterpret_cast<uintptr_t>(split_plane) & 255) == 0, "fl_knn_prepare_split_f32: plane must be 256-byte aligned");
+    const int64_t need = fl_knn_split_plane_bytes(m, d);
+    if (need == 0) { set_error("fl_knn_prepare_split_f32: d=%d > 128 has no split plane", d); return FL_EUNSUPPORTED; }
+    if (split_plane_bytes < need) {
+        set_error("fl_knn_prepare_split_f32: plane buffer %lld < %lld bytes", (long long)split_plane_bytes, (long long)need);
+        return FL_EWORKSPACE;
+    }
+    return launch_split_db_plane(db, m, d, ld, split_plane, (cudaStream_t)stream);
+}
+
+extern "C" int64_t fl_knn_staged_workspace_bytes(int64_t nq, int64_t m, int d, int k) {
+    if (nq < 1 || m < 1 || d < 1 || k < 1 || tc_knn_supported(nq, m, d, k) != FL_OK) return 0;
+    return knn_ws_plan(nq, m, d, k, FL_KNN_BF16_RERANK, 1).bytes;
+}
+
+extern "C" int fl_knn_staged_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb, int d,
+                                 int k, const void* plane, const void* split_plane, int64_t row_offset, float* out_dist,
+                                 int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
+    int mode = FL_KNN_BF16_RERANK;
+    int rc = knn_check_args("fl_knn_staged_f32", q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
+    if (rc != FL_OK || nq == 0) return rc;
+    if (split_plane != nullptr) {
+        FL_CHECK_ARG(split_plane_supported(d), "fl_knn_staged_f32: d=%d > 128 has no split plane", d);
+        FL_CHECK_ARG((reinterpret_cast<uintptr_t>(split_plane) & 255) == 0, "fl_knn_staged_f32: split plane must be 256-byte aligned");
+    }
+    return knn_tc_phases(TC_PREP | TC_SEED | TC_SCORE, q, nq, ldq, db, m, ldb, d, k, plane, row_offset, nullptr, nullptr,
+                         out_dist, out_idx, ws, ws_bytes, status, (cudaStream_t)stream, split_plane);
 }
 
 // Test hook: runs only the tensor-core scoring pass for up to 128 queries and writes the

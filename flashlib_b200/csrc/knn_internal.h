@@ -87,6 +87,9 @@ struct FinalizeParams {
     // query as k rows known to exist somewhere in the database, so this shard's list may be short
     const float* cert_tau;
     int* fb_count; int* fb_list; int fb_cap;
+    // Optional: unproven queries go to this list first (the split-plane stage), and to the exact-path
+    // list only when it is absent or full
+    int* next_count; int* next_list; int next_cap;
 };
 // Finalisation of the large-k tensor-core pools (one block per query).
 int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);
@@ -118,6 +121,8 @@ struct TcKnnParams {
                              //   [nq_pad][nsplit][tc_taus_per_range][tc_pair_pool_cap]; entry counts go to
                              //   part_cnt, thresholds to part_tau, part_sc / part_id are not used
     int k;                   // neighbours wanted: selects the pool geometry (tc_knn_big)
+    int big_pools;           // 1: the large global-memory pools whatever k is (no pool in shared memory:
+                             //    room for a query tile of up to 384 feature columns)
     int32_t* status;
 };
 // 1 when k takes the large pools (256 entries per (query, range, warpgroup), kept in global memory).
@@ -167,6 +172,18 @@ int launch_knn_tc(const TcKnnParams& p, cudaStream_t st);
 // m_pad/d_pad, tau (scratch) and status of `p` are used.
 // nq_dev (optional): device-resident count of live rows; query tiles beyond it are skipped.
 int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, const int* nq_dev, cudaStream_t st);
+
+// Split (hi/lo) operand planes of the second, more precise tensor-core stage (kmeans_tc.cu).
+// Database side: rows [m_pad][3 d_pad + 16] = [hi | hi | lo | norm terms] laid out by
+// plane_layout(m, 3 d_pad).  Query side: the rows listed in `rows` (live count on the device, at
+// most `cap`) as [hi | lo | hi | ones]; with `tau_out` the kernel also derives each listed row's
+// starting threshold from the k-th distance found so far (`prev_dist` [nq][k]):
+// (||q||^2 - d_k) / 2 lowered by 2 eps_rel ||q|| *maxnorm and the proof's slack.
+int split_plane_supported(int d);
+int launch_split_db_plane(const float* c, int64_t m, int d, int64_t ldc, void* plane, cudaStream_t st);
+int launch_split_query_gather(const float* x, int64_t ldx, int d, const int* rows, const int* rows_count, int cap,
+                              void* out, int d_pad, const float* prev_dist, int k, const float* maxnorm, float eps_rel,
+                              float* tau_out, cudaStream_t st);
 
 // bf16 query plane [nq_pad][d_pad + 16] (features zero padded, ones in the norm columns) from fp32 queries.
 int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,

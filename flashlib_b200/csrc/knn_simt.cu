@@ -517,9 +517,16 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
                 p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)id2[r] + p.row_offset) : -1;
             }
         }
-        if (!proven && lane == 0) {
-            const int i = atomicAdd(p.fb_count, 1);
-            if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+        if (!proven && lane == 0 && p.fb_count != nullptr) {
+            bool queued = false;
+            if (p.next_count != nullptr) {
+                const int i = atomicAdd(p.next_count, 1);
+                if (i < p.next_cap) { p.next_list[i] = (int)qi; queued = true; }
+            }
+            if (!queued) {
+                const int i = atomicAdd(p.fb_count, 1);
+                if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+            }
         }
         break;
     }
@@ -592,16 +599,14 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
 // ------------------------------------------------------------------------------------
 constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 256;
 
-__global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeParams p) {
+static __device__ __forceinline__ void finalize_big_slot(const FinalizeParams& p, const int64_t slot) {
     __shared__ float s_key[BIG_CAND];
     __shared__ uint32_t s_id[BIG_CAND];
     __shared__ float s_q[256];
     __shared__ float s_red[BIG_THREADS / 32];
     __shared__ int s_n;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t slot = blockIdx.x;
-    if (slot >= p.count) return;
-    const int64_t qi = slot;
+    const int64_t qi = p.qlist != nullptr ? (int64_t)p.qlist[slot] : slot;
     const float* qp = p.q + qi * p.ldq;
 
     // u and ||q||^2
@@ -750,9 +755,27 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
             proven = dk < qsq - 2.f * (bound + eps) - slack;
         }
         if (!proven) {
-            const int i = atomicAdd(p.fb_count, 1);
-            if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+            bool queued = false;
+            if (p.next_count != nullptr) {
+                const int i = atomicAdd(p.next_count, 1);
+                if (i < p.next_cap) { p.next_list[i] = (int)qi; queued = true; }
+            }
+            if (!queued) {
+                const int i = atomicAdd(p.fb_count, 1);
+                if (i < p.fb_cap) p.fb_list[i] = (int)qi;
+            }
         }
+    }
+}
+
+// One block per slot; with a device-side slot count (capped by p.count) the blocks of a modest grid
+// stride over the live slots instead.
+__global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeParams p) {
+    int64_t count = p.count;
+    if (p.count_dev != nullptr) { const int64_t c = *p.count_dev; count = c < count ? c : count; }
+    for (int64_t slot = blockIdx.x; slot < count; slot += gridDim.x) {
+        finalize_big_slot(p, slot);
+        __syncthreads();
     }
 }
 
@@ -760,7 +783,9 @@ int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStre
     if (max_slots <= 0) return FL_OK;
     FL_CHECK_ARG(p.part_cnt && p.part_tau && p.K1 == 2 * BIG_POOL && p.d <= 256 && p.k <= BIG_RERANK && p.count == max_slots,
                  "large-k finalisation: bad parameters");
-    knn_finalize_big_kernel<<<(unsigned)max_slots, BIG_THREADS, 0, st>>>(p);
+    int64_t grid = max_slots;
+    if (p.count_dev != nullptr && grid > (int64_t)sm_count() * 4) grid = (int64_t)sm_count() * 4;
+    knn_finalize_big_kernel<<<(unsigned)grid, BIG_THREADS, 0, st>>>(p);
     FL_CHECK_LAUNCH();
     return FL_OK;
 }

@@ -1152,7 +1152,7 @@ struct TcLaunch {
 // the seeding sample.
 static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch* L) {
     FL_CHECK_ARG(p.qplane && p.dbrows && p.tau, "tensor-core kNN launch with a null buffer");
-    L->big = tc_knn_big(p.k) != 0;
+    L->big = tc_knn_big(p.k) != 0 || p.big_pools != 0;
     L->mid = p.deep_pools != 0;
     const int pitch = p.d_pad + PLANE_AUG_COLS;
     int rc = cached_map_bf16(&L->map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);

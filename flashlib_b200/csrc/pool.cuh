@@ -20,9 +20,11 @@ static __device__ __noinline__ float pool_compact_dyn(float* sc, uint32_t* idv, 
     }
 }
 
-// Pool size (a power of two >= 32) used for k neighbours on the exact CUDA-core path.
+// Pool size (a power of two >= 32) used for k neighbours on the exact CUDA-core path: room for the
+// k wanted and at least 8 more, which the exact re-rank needs where fp32 scores of rows that close
+// to the k-th neighbour come out in the wrong order (k > 504: what 512 entries leave).
 static inline int simt_pool_size(int k) {
-    int p = pow2_ceil(k);
+    int p = pow2_ceil(k + 8 < 512 ? k + 8 : 512);
     return p < 32 ? 32 : p;
 }
 

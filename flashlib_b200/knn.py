@@ -59,10 +59,36 @@ class DbPlane:
         _lib.check(lib.fl_knn_prepare_db_f32(db.data_ptr(), m, d, db.stride(0), self.buf.data_ptr(),
                                              nbytes, _stream_ptr(db.device)))
         self.key = _plane_key(db)
+        self.split_buf = None
 
     @property
     def ptr(self) -> int:
         return self.buf.data_ptr()
+
+    def split_ptr(self, db: torch.Tensor):
+        """Address of the split (hi/lo bf16) plane of the same database, built on first use; ``None``
+        when the shape has none (d > 128) or it would exceed the size limit."""
+        if self.split_buf is None:
+            lib = _lib.load()
+            m, d = db.shape
+            nbytes = lib.fl_knn_split_plane_bytes(m, d)
+            if nbytes == 0 or nbytes > _split_plane_limit():
+                self.split_buf = False
+            else:
+                self.split_buf = torch.empty(nbytes, dtype=torch.uint8, device=db.device)
+                _lib.check(lib.fl_knn_prepare_split_f32(db.data_ptr(), m, d, db.stride(0), self.split_buf.data_ptr(),
+                                                        nbytes, _stream_ptr(db.device)))
+        return self.split_buf.data_ptr() if self.split_buf is not False else None
+
+
+def _split_plane_limit() -> int:
+    """Largest split plane (bytes) built without being asked for: it takes 6.25x the fp32 rows'
+    memory at d = 128 -> on for databases of a few million rows, off for the 100M-row shards."""
+    return int(os.environ.get("FLASHLIB_B200_SPLIT_MAX_MB", "4096")) << 20
+
+
+def _second_stage_default() -> bool:
+    return os.environ.get("FLASHLIB_B200_KNN_STAGE2", "1") != "0"
 
 
 def _plane_key(db: torch.Tensor):
@@ -145,11 +171,16 @@ def _defer_status_check(status: torch.Tensor) -> None:
 
 
 def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KNN_AUTO,
-            row_offset: int = 0, plane: Optional[DbPlane] = None, check_status=True):
-    """One 2-D problem through ``fl_knn_f32``: returns ``(dist fp32 (nq,k), idx int32 (nq,k), info)``.
+            row_offset: int = 0, plane: Optional[DbPlane] = None, check_status=True,
+            second_stage: Optional[bool] = None):
+    """One 2-D problem through ``fl_knn_f32`` / ``fl_knn_staged_f32``: returns
+    ``(dist fp32 (nq,k), idx int32 (nq,k), info)``.
     ``check_status=True`` reads the kernel's status words before returning (one host/device
-    round trip; ``info["fallback_rows"]`` is filled), ``"deferred"`` leaves that to a later call
-    or to ``check_pending()``, ``False`` skips it."""
+    round trip; ``info["fallback_rows"]`` and ``info["stage2_rows"]`` are filled), ``"deferred"``
+    leaves that to a later call or to ``check_pending()``, ``False`` skips it.
+    ``second_stage`` (tensor-core mode): rows the bf16 proof rejects are scored again on the
+    tensor cores with split hi/lo operands before anything takes the exact CUDA-core pass;
+    ``None`` = when the database's split plane exists or is small enough to build."""
     lib = _lib.load()
     _lib.require_device()
     nq, d = q.shape
@@ -160,20 +191,34 @@ def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KN
         plane = get_plane(db)
     out_d = torch.empty((nq, k), dtype=torch.float32, device=dev)
     out_i = torch.empty((nq, k), dtype=torch.int32, device=dev)
-    ws_bytes = lib.fl_knn_workspace_bytes(max(nq, 1), m, d, k, resolved)
-    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    split = None
+    if resolved == _lib.FL_KNN_BF16_RERANK and nq > 0:
+        if second_stage is None:
+            second_stage = _second_stage_default()
+        if second_stage:
+            split = plane.split_ptr(db)
     status = torch.zeros(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=dev)
-    rc = lib.fl_knn_f32(q.data_ptr(), nq, q.stride(0) if nq else d, db.data_ptr(), m, db.stride(0), d, k,
-                        resolved, plane.ptr if plane is not None else None, row_offset,
-                        out_d.data_ptr(), out_i.data_ptr(), ws.data_ptr(), ws_bytes,
-                        status.data_ptr(), _stream_ptr(dev))
+    if split is not None:
+        ws_bytes = lib.fl_knn_staged_workspace_bytes(nq, m, d, k)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        rc = lib.fl_knn_staged_f32(q.data_ptr(), nq, q.stride(0), db.data_ptr(), m, db.stride(0), d, k,
+                                   plane.ptr, split, row_offset, out_d.data_ptr(), out_i.data_ptr(),
+                                   ws.data_ptr(), ws_bytes, status.data_ptr(), _stream_ptr(dev))
+    else:
+        ws_bytes = lib.fl_knn_workspace_bytes(max(nq, 1), m, d, k, resolved)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        rc = lib.fl_knn_f32(q.data_ptr(), nq, q.stride(0) if nq else d, db.data_ptr(), m, db.stride(0), d, k,
+                            resolved, plane.ptr if plane is not None else None, row_offset,
+                            out_d.data_ptr(), out_i.data_ptr(), ws.data_ptr(), ws_bytes,
+                            status.data_ptr(), _stream_ptr(dev))
     _lib.check(rc)
-    info = {"mode": resolved, "status": status}
+    info = {"mode": resolved, "status": status, "second_stage": split is not None}
     if check_status == "deferred" and resolved == _lib.FL_KNN_BF16_RERANK:
         _defer_status_check(status)
     elif check_status and resolved == _lib.FL_KNN_BF16_RERANK:
         st = status.tolist()
         info["fallback_rows"] = st[_lib.FL_STATUS_FALLBACK]
+        info["stage2_rows"] = st[_lib.FL_STATUS_STAGE2]
         _raise_on_status(st)
     return out_d, out_i, info
 

@@ -47,6 +47,8 @@ extern "C" {
 #define FL_STATUS_FALLBACK  2  /* rows whose candidate pool failed verification and were
                                   recomputed on the exact CUDA-core path                 */
 #define FL_STATUS_POOL      3  /* candidate-pool size per row used by the last call      */
+#define FL_STATUS_STAGE2    4  /* fl_knn_staged_f32: rows the first proof rejected and the
+                                  split-plane tensor-core stage scored again             */
 
 int         fl_version(void);
 const char* fl_last_error(void);
@@ -105,6 +107,28 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
                    const void* plane, int64_t row_offset,
                    float* out_dist, int32_t* out_idx,
                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
+/* fl_knn_f32 (tensor-core mode) with a second tensor-core stage between the bf16 pass and  */
+/* the exact CUDA-core pass.  Rows whose bf16 candidate pool cannot be proven complete are  */
+/* scored again with every fp32 operand carried as two bf16 values (hi = bf16(v),           */
+/* lo = bf16(v - hi); one product over [hi|lo|hi] x [hi|hi|lo] columns gives                */
+/* hi.hi + lo.hi + hi.lo), the error-compensated split the reference uses for fp32-exact    */
+/* ranking on tensor cores (linalg/gemm/bf16_x3.py:1-22 with bf16 halves, the lo.lo product  */
+/* dropped and one fp32 accumulator across the three products; linalg/gemm/tf32_x3.py:9-31, */
+/* linalg/gemm/triton/fused_kernels.py:222-294 with TF32 halves).  The scoring error drops from 2^-8 to about 2^-16 of          */
+/* ||q|| max||x||, so the same proof accepts nearly every row; what is left takes the exact  */
+/* pass as before (status[FL_STATUS_STAGE2] / [FL_STATUS_FALLBACK] count the two).  d <= 128.*/
+/* `split_plane` is filled once per database by fl_knn_prepare_split_f32                    */
+/* (fl_knn_split_plane_bytes = 0: no split plane for this d); NULL = no second stage.       */
+int64_t fl_knn_split_plane_bytes(int64_t m, int d);
+int     fl_knn_prepare_split_f32(const float* db, int64_t m, int d, int64_t ld,
+                                 void* split_plane, int64_t split_plane_bytes, void* stream);
+int64_t fl_knn_staged_workspace_bytes(int64_t nq, int64_t m, int d, int k);
+int     fl_knn_staged_f32(const float* q, int64_t nq, int64_t ldq,
+                          const float* db, int64_t m, int64_t ldb, int d, int k,
+                          const void* plane, const void* split_plane, int64_t row_offset,
+                          float* out_dist, int32_t* out_idx,
+                          void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 
 /* Row-sharded databases (the reference has no sharded kNN; the closest is its multi-GPU   */
 /* k-means, kmeans/large.py:35-280): fl_knn_f32 in two calls, so that the shards can share */

@@ -66,7 +66,7 @@ def test_bf16_mode_equals_exact_mode_and_reports_fallbacks():
     base = torch.randn(200, 128, generator=g)
     db = (base[torch.randint(0, 200, (60_000,), generator=g)] + 0.1 * torch.randn(60_000, 128, generator=g)).cuda()
     q = (base[torch.randint(0, 200, (512,), generator=g)] + 0.1 * torch.randn(512, 128, generator=g)).cuda()
-    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)
+    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=False)
     d_ex, i_ex, _ = knn_f32(q, db, 10, mode=_lib.FL_KNN_EXACT_SIMT)
     # Neighbours here are ~2.5 apart from the query at norms ~128, where the fp32 expansion the
     # oracle uses is itself only good to ~1e-5 relative; the yardstick is fp64 brute force.
@@ -78,6 +78,72 @@ def test_bf16_mode_equals_exact_mode_and_reports_fallbacks():
     assert info["fallback_rows"] > 0
     same = (i_tc == i_ex).all(dim=1).float().mean().item()
     assert same > 0.99, same
+
+
+def _near_duplicates(m, nq, d, seed, spread=0.1, centres=200):
+    g = torch.Generator().manual_seed(seed)
+    base = torch.randn(centres, d, generator=g)
+    db = base[torch.randint(0, centres, (m,), generator=g)] + spread * torch.randn(m, d, generator=g)
+    q = base[torch.randint(0, centres, (nq,), generator=g)] + spread * torch.randn(nq, d, generator=g)
+    return q.cuda(), db.cuda()
+
+
+def _fp64_neighbours(q, db, k):
+    qd, dbd = q.double(), db.double()
+    d64 = (qd * qd).sum(-1, keepdim=True) + (dbd * dbd).sum(-1)[None, :] - 2.0 * qd @ dbd.T
+    return d64.topk(k, dim=1, largest=False).indices.cpu().numpy()
+
+
+@pytest.mark.parametrize("m,nq,d,k", [(60_000, 512, 128, 10), (90_000, 700, 64, 5), (50_000, 300, 100, 32),
+                                      (150_000, 2000, 128, 16)])
+def test_second_stage_proves_what_the_bf16_pass_cannot(m, nq, d, k):
+    """Near-duplicate data: the bf16 proof rejects many rows; the split-plane tensor-core stage
+    (error bound a hundred times smaller) proves nearly all of them, the exact CUDA-core pass
+    takes what is left, and the neighbours equal fp64 brute force either way."""
+    q, db = _near_duplicates(m, nq, d, seed=m + k)
+    d_1, i_1, info1 = knn_f32(q, db, k, mode=_lib.FL_KNN_BF16_RERANK, second_stage=False)
+    d_2, i_2, info2 = knn_f32(q, db, k, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
+    assert info2["second_stage"] and not info1["second_stage"]
+    ref_i = _fp64_neighbours(q, db, k)
+    for d_, i_ in ((d_1, i_1), (d_2, i_2)):
+        res = parity.knn_parity(q.cpu().numpy(), db.cpu().numpy(), d_.cpu().numpy(), i_.cpu().numpy(), ref_i)
+        assert res["ok"], res
+    assert info1["fallback_rows"] > 0, "the generator no longer defeats the bf16 proof"
+    assert info2["stage2_rows"] == info1["fallback_rows"]
+    assert info2["fallback_rows"] <= max(1, info1["fallback_rows"] // 50), (info1, info2)
+
+
+def test_second_stage_overflow_goes_to_the_exact_pass():
+    """More rejected rows than the second stage holds (a quarter of the queries, at least 4096):
+    the surplus takes the exact pass directly and every row is still correct."""
+    q, db = _near_duplicates(40_000, 6000, 128, seed=77)
+    d_2, i_2, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
+    assert info["stage2_rows"] == 4096, info
+    assert info["fallback_rows"] > 0
+    ref_i = _fp64_neighbours(q, db, 10)
+    res = parity.knn_parity(q.cpu().numpy(), db.cpu().numpy(), d_2.cpu().numpy(), i_2.cpu().numpy(), ref_i)
+    assert res["ok"], res
+
+
+def test_second_stage_idle_on_well_separated_data():
+    g = torch.Generator().manual_seed(5)
+    db = torch.randn(100_000, 128, generator=g).cuda()
+    q = torch.randn(400, 128, generator=g).cuda()
+    d_1, i_1, _ = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=False)
+    d_2, i_2, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
+    assert info["stage2_rows"] == 0 and info["fallback_rows"] == 0
+    assert torch.equal(i_1, i_2) and torch.equal(d_1, d_2)
+
+
+def test_no_split_plane_beyond_128_features():
+    lib = _lib.load()
+    assert lib.fl_knn_split_plane_bytes(1000, 129) == 0
+    assert lib.fl_knn_split_plane_bytes(1000, 128) > 0
+    g = torch.Generator().manual_seed(6)
+    db = torch.randn(30_000, 200, generator=g).cuda()
+    q = torch.randn(600, 200, generator=g).cuda()
+    _, _, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
+    assert not info["second_stage"]
 
 
 BIG_K_SHAPES = [(64, 3000, 64, 17), (129, 20_000, 128, 32), (300, 60_000, 128, 100), (500, 150_000, 64, 64),
@@ -168,7 +234,7 @@ def test_every_query_can_take_the_exact_path():
     g = torch.Generator().manual_seed(17)
     db = (torch.randn(40_000, 64, generator=g) + 30.0).cuda()
     q = (torch.randn(9_000, 64, generator=g) + 30.0).cuda()
-    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK)
+    d_tc, i_tc, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=False)
     assert info["status"][_lib.FL_STATUS_ERROR].item() == 0
     assert info["fallback_rows"] > 8_000, info["fallback_rows"]
     qd, dbd = q.double(), db.double()
