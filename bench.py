@@ -454,6 +454,39 @@ def run_secondary(args):
                 "algorithmic_tflops": 2.0 * DB_ROWS * DB_ROWS * DIM / (ms * 1e-3) / 1e12,
                 "config": {"rows": DB_ROWS, "dim": DIM, "k": K_NEIGHBOURS, "mode": int(info["mode"]),
                            "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+    elif args.workload == "knn_neardup":
+        # Near-duplicate data (200 centres, every row and query a centre plus N(0, 0.1^2) noise): rows
+        # of one centre lie within the bf16 scoring error of each other, so the bf16 proof rejects
+        # most queries and the split-plane stage (or, without it, the exact CUDA-core pass) decides.
+        g = torch.Generator().manual_seed(9)
+        base = torch.randn(200, DIM, generator=g)
+        X = base[torch.randint(0, 200, (DB_ROWS,), generator=g)] + 0.1 * torch.randn(DB_ROWS, DIM, generator=g)
+        Q = base[torch.randint(0, 200, (QUERIES_PER_GPU,), generator=g)] + 0.1 * torch.randn(QUERIES_PER_GPU, DIM, generator=g)
+        Xd, Qd = X.cuda(), Q.cuda()
+        from flashlib_b200.knn import _mode_from, knn_f32
+        from tests import parity
+        mode = _mode_from(args.mode or "bf16")
+        ms = _time_steps(lambda: knn_f32(Qd, Xd, K_NEIGHBOURS, mode=mode, check_status=False), steps, warm)
+        d_, i_, info = knn_f32(Qd, Xd, K_NEIGHBOURS, mode=mode)
+        ms1 = _time_steps(lambda: knn_f32(Qd, Xd, K_NEIGHBOURS, mode=mode, check_status=False, second_stage=False), 1, 1)
+        _, _, info1 = knn_f32(Qd, Xd, K_NEIGHBOURS, mode=mode, second_stage=False)
+        # yardstick: fp64 brute force on the device for a sample (the fp32 expansion of the CPU
+        # restatement is itself only good to about 1e-5 relative on such data)
+        n_chk = 128
+        qd, xd = Qd[:n_chk].double(), Xd.double()
+        d64 = (qd * qd).sum(-1, keepdim=True) + (xd * xd).sum(-1)[None, :] - 2.0 * qd @ xd.T
+        ref_i = d64.topk(K_NEIGHBOURS, dim=1, largest=False).indices.cpu().numpy()
+        res = parity.knn_parity(Q[:n_chk].numpy(), X.numpy(), d_[:n_chk].cpu().numpy(), i_[:n_chk].cpu().numpy(), ref_i)
+        nq = QUERIES_PER_GPU
+        line = {"workload": "knn_neardup", "metric": "exact_knn_queries_per_sec", "value": nq / (ms * 1e-3),
+                "unit": "queries/s", "ms_per_step": ms,
+                "parity_ok": bool(res["ok"]), "parity": {"rows": n_chk, "bad_rows": len(res["bad_rows"]), "against": "fp64 brute force"},
+                "rows_rejected_by_the_bf16_proof": int(info.get("stage2_rows", 0)) + (0 if info["second_stage"] else int(info["fallback_rows"])),
+                "rows_on_the_split_plane_stage": int(info.get("stage2_rows", 0)),
+                "rows_on_the_exact_cuda_core_pass": int(info.get("fallback_rows", 0)),
+                "without_second_stage": {"ms_per_step": ms1, "rows_on_the_exact_cuda_core_pass": int(info1.get("fallback_rows", 0))},
+                "config": {"rows": DB_ROWS, "dim": DIM, "queries": nq, "k": K_NEIGHBOURS, "centres": 200, "spread": 0.1,
+                           "mode": int(info["mode"]), "second_stage": bool(info["second_stage"])}}
     elif args.workload == "knn_100m_shard":
         # One GPU's share of the sharded configuration: 12.5M of the 100M rows x 96 features
         # ~ N(0,1), all 100,000 queries, k = 100 (drawn on the device: 4.8 GB of rows).
@@ -495,7 +528,7 @@ def main():
     ap.add_argument("--result", default="owner", choices=["owner", "replicated"],
                     help="N > 1: 'owner' = all-to-all, every rank merges and returns its own slice of the step's queries; "
                          "'replicated' = all-gather, every rank merges and returns all of them")
-    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_self_1m", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
+    ap.add_argument("--workload", default="knn_1m", choices=["knn_1m", "knn_100m", "knn_1m_k100", "knn_self_1m", "knn_neardup", "knn_100m_shard", "kmeans_1m", "ivf_1m"],
                     help="knn_1m is the headline benchmark; the others time the remaining configurations on one GPU "
                          "and print a shorter JSON line")
     ap.add_argument("--db-rows", type=int, default=None, help="with --profile-case: database rows")

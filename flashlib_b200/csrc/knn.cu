@@ -108,10 +108,13 @@ static int64_t take(int64_t& cur, int64_t bytes) {
     return o;
 }
 
-// Rows the split-plane stage takes: a quarter of the queries, all of them below 4096.
+// Rows the split-plane stage takes: every query up to 65 536 (near-duplicate data can fail the bf16
+// proof for all of them), a quarter of the queries beyond that, at most 262 144 (1 GB of pools).
 static int knn_stage2_rows(int64_t nq) {
+    if (nq <= 65536) return (int)nq;
     int64_t c = nq / 4;
-    if (c < 4096) c = nq < 4096 ? nq : 4096;
+    if (c < 65536) c = 65536;
+    if (c > 262144) c = 262144;
     return (int)c;
 }
 

@@ -114,14 +114,15 @@ def test_second_stage_proves_what_the_bf16_pass_cannot(m, nq, d, k):
 
 
 def test_second_stage_overflow_goes_to_the_exact_pass():
-    """More rejected rows than the second stage holds (a quarter of the queries, at least 4096):
-    the surplus takes the exact pass directly and every row is still correct."""
-    q, db = _near_duplicates(40_000, 6000, 128, seed=77)
-    d_2, i_2, info = knn_f32(q, db, 10, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
-    assert info["stage2_rows"] == 4096, info
+    """More rejected rows than the second stage holds (every query up to 65 536, a quarter of them
+    beyond): the surplus takes the exact pass directly and every row is still correct."""
+    q, db = _near_duplicates(20_000, 70_000, 64, seed=77, centres=20)
+    d_2, i_2, info = knn_f32(q, db, 5, mode=_lib.FL_KNN_BF16_RERANK, second_stage=True)
+    assert info["stage2_rows"] == 65_536, info
     assert info["fallback_rows"] > 0
-    ref_i = _fp64_neighbours(q, db, 10)
-    res = parity.knn_parity(q.cpu().numpy(), db.cpu().numpy(), d_2.cpu().numpy(), i_2.cpu().numpy(), ref_i)
+    sub = torch.arange(0, 70_000, 35, device="cuda")
+    ref_i = _fp64_neighbours(q[sub], db, 5)
+    res = parity.knn_parity(q[sub].cpu().numpy(), db.cpu().numpy(), d_2[sub].cpu().numpy(), i_2[sub].cpu().numpy(), ref_i)
     assert res["ok"], res
 
 
