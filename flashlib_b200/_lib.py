@@ -29,6 +29,7 @@ FL_STATUS_WHERE = 1
 FL_STATUS_FALLBACK = 2
 FL_STATUS_POOL = 3
 FL_STATUS_STAGE2 = 4
+FL_DTYPE_F32, FL_DTYPE_BF16, FL_DTYPE_F16 = 0, 1, 2
 
 # name -> (restype, argtypes); mirrors include/flashlib_b200.h one to one.
 SIGNATURES = {
@@ -45,6 +46,9 @@ SIGNATURES = {
     "fl_knn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int, c_int]),
     "fl_knn_f32": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int,
                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_knn_prepare_db_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
+    "fl_knn_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
+                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     "fl_knn_split_plane_bytes": (c_int64, [c_int64, c_int]),
     "fl_knn_prepare_split_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
     "fl_knn_staged_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int]),

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -61,10 +62,41 @@ int smem_optin_bytes();
 constexpr unsigned FULL_MASK = 0xffffffffu;
 constexpr uint32_t INVALID_ID = 0xffffffffu;
 
+// Element types of the caller's rows (FL_DTYPE_* of the C ABI): fp32, or 16-bit storage that is
+// widened to fp32 on load (exactly: every bf16 / fp16 value is an fp32 value).
+constexpr int DT_F32 = FL_DTYPE_F32, DT_BF16 = FL_DTYPE_BF16, DT_F16 = FL_DTYPE_F16;
+static inline int dt_size(int dt) { return dt == DT_F32 ? 4 : 2; }
+// Four consecutive elements can be fetched with one load: 16 bytes of fp32, 8 bytes of 16-bit values.
+static inline bool dt_vec_ok(const void* p, int64_t ld, int dt) {
+    return (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(p) & (dt == DT_F32 ? 15 : 7)) == 0);
+}
+
 #if defined(__CUDACC__)
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 __device__ __forceinline__ float pos_inf() { return __int_as_float(0x7f800000); }
+
+__device__ __forceinline__ float f16_bits_to_f32(unsigned short h) { return __half2float(__ushort_as_half(h)); }
+// Element i of a row array of type dt, as fp32.
+__device__ __forceinline__ float ld_elem(const void* base, int64_t i, int dt) {
+    if (dt == DT_F32) return __ldg(static_cast<const float*>(base) + i);
+    const unsigned short h = __ldg(static_cast<const unsigned short*>(base) + i);
+    return dt == DT_BF16 ? __uint_as_float((uint32_t)h << 16) : f16_bits_to_f32(h);
+}
+// Elements i .. i+3 (the address must allow one load: see dt_vec_ok).
+__device__ __forceinline__ float4 ld_elem4(const void* base, int64_t i, int dt) {
+    if (dt == DT_F32) return __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(base) + i));
+    const uint2 w = __ldg(reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(base) + i));
+    if (dt == DT_BF16)
+        return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                           __uint_as_float(w.y & 0xffff0000u));
+    return make_float4(f16_bits_to_f32((unsigned short)(w.x & 0xffffu)), f16_bits_to_f32((unsigned short)(w.x >> 16)),
+                       f16_bits_to_f32((unsigned short)(w.y & 0xffffu)), f16_bits_to_f32((unsigned short)(w.y >> 16)));
+}
+// Address of row r (ld in elements).
+__host__ __device__ __forceinline__ const void* row_at(const void* base, int64_t r, int64_t ld, int dt) {
+    return static_cast<const char*>(base) + r * ld * (dt == DT_F32 ? 4 : 2);
+}
 
 // Bitonic sorting network over NPL*32 (key, id) pairs held NPL per lane; the element at
 // register r of lane l has position r*32 + l.  Sorts by DESCENDING key.  With TIEBREAK,

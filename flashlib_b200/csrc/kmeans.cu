@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
     hnorm += (int64_t)blockIdx.y * K;
     labels += (int64_t)blockIdx.y * n;
 
-    const float* qrow[T::QL];
+    const void* qrow[T::QL];
 #pragma unroll
     for (int i = 0; i < T::QL; ++i) {
         const int r = (i * 256 + tid) >> 3;
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
     for (int i = 0; i < TQ; ++i) { best[i] = neg_inf(); bidx[i] = 0x7fffffff; }
 
     for (int tile = 0; tile < K; tile += 128) {
-        const float* drow[4];
+        const void* drow[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int gr = tile + ((i * 256 + tid) >> 3);

@@ -8,14 +8,14 @@ namespace fl {
 
 // out[i] = ||x_i||^2 / 2
 // ||x||^2 / 2 per row and (maxnorm_bits, zero-initialised) the largest row norm.
-__global__ void halfnorm_kernel(const float* __restrict__ x, int64_t n, int d, int64_t ld,
-                                float* __restrict__ out, unsigned int* __restrict__ maxnorm_bits) {
+__global__ void halfnorm_kernel(const void* __restrict__ x, int64_t n, int d, int64_t ld,
+                                float* __restrict__ out, unsigned int* __restrict__ maxnorm_bits, int dt) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n) return;
-    const float* p = x + row * ld;
+    const void* p = row_at(x, row, ld, dt);
     float s = 0.f;
-    for (int c = lane; c < d; c += 32) { const float v = __ldg(p + c); s += v * v; }
+    for (int c = lane; c < d; c += 32) { const float v = ld_elem(p, c, dt); s += v * v; }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FULL_MASK, s, o);
     if (lane == 0) {
@@ -31,8 +31,8 @@ constexpr float SIMT_EPS_REL = 4e-6f;
 
 // bf16 query plane [nq_pad][d_pad + 16]: the features, zero padding, and ones in the three
 // columns that meet the database plane's split -||x||^2/2 terms.
-__global__ void query_plane_kernel(const float* __restrict__ q, int64_t nq, int64_t ldq, int d,
-                                   __nv_bfloat16* __restrict__ out, int64_t nq_pad, int d_pad) {
+__global__ void query_plane_kernel(const void* __restrict__ q, int64_t nq, int64_t ldq, int d,
+                                   __nv_bfloat16* __restrict__ out, int64_t nq_pad, int d_pad, int dt) {
     const int pitch = d_pad + PLANE_AUG_COLS;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t total = nq_pad * pitch;
@@ -41,17 +41,17 @@ __global__ void query_plane_kernel(const float* __restrict__ q, int64_t nq, int6
     const int c = (int)(i - r * pitch);
     float v = 0.f;
     if (r < nq) {
-        if (c < d) v = __ldg(q + r * ldq + c);
+        if (c < d) v = ld_elem(row_at(q, r, ldq, dt), c, dt);
         else if (c >= d_pad && c < d_pad + 3) v = 1.f;
     }
     out[i] = __float2bfloat16_rn(v);
 }
 
-int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
-                       int d_pad, cudaStream_t st) {
+int launch_query_plane(const void* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
+                       int d_pad, cudaStream_t st, int dt) {
     const int64_t total = nq_pad * (d_pad + PLANE_AUG_COLS);
     query_plane_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(
-        q, nq, ldq, d, reinterpret_cast<__nv_bfloat16*>(qplane), nq_pad, d_pad);
+        q, nq, ldq, d, reinterpret_cast<__nv_bfloat16*>(qplane), nq_pad, d_pad, dt);
     FL_CHECK_LAUNCH();
     return FL_OK;
 }
@@ -202,7 +202,6 @@ static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode, int stag
     return w;
 }
 
-static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int resolve_mode(int64_t nq, int64_t m, int d, int k, int mode) {
     if (mode == FL_KNN_AUTO) return tc_knn_auto(nq, m, d, k) ? FL_KNN_BF16_RERANK : FL_KNN_EXACT_SIMT;
@@ -285,7 +284,7 @@ extern "C" int64_t fl_knn_workspace_bytes(int64_t nq, int64_t m, int d, int k, i
 }
 
 // Argument checks shared by the kNN entry points; resolves FL_KNN_AUTO.
-static int knn_check_args(const char* who, const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
+static int knn_check_args(const char* who, const void* q, int64_t nq, int64_t ldq, const void* db, int64_t m,
                           int64_t ldb, int d, int k, int* mode, const void* plane, int64_t row_offset,
                           const float* out_dist, const int32_t* out_idx, const void* ws) {
     FL_CHECK_ARG(nq >= 0 && m >= 1 && d >= 1, "%s: bad shape nq=%lld m=%lld d=%d", who, (long long)nq, (long long)m, d);
@@ -322,18 +321,18 @@ static int knn_check_args(const char* who, const float* q, int64_t nq, int64_t l
 //              given), scoring pass, finalisation, exact pass for what could not be proven
 enum { TC_PREP = 1, TC_SEED = 2, TC_SCORE = 4 };
 
-static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb,
+static int knn_tc_phases(int phases, const void* q, int64_t nq, int64_t ldq, const void* db, int64_t m, int64_t ldb,
                          int d, int k, const void* plane, int64_t row_offset, float* seed_cls, const float* gmaxnorm,
                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status,
-                         cudaStream_t st, const void* split_plane = nullptr) {
+                         cudaStream_t st, const void* split_plane = nullptr, int dt = DT_F32) {
     const KnnWs w = knn_ws_plan(nq, m, d, k, FL_KNN_BF16_RERANK, split_plane != nullptr);
     if (ws_bytes < w.bytes) {
         set_error("fl_knn: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
         return FL_EWORKSPACE;
     }
     char* base = static_cast<char*>(ws);
-    const int vecq = (ldq % 4 == 0) && aligned16(q);
-    const int vecd = (ldb % 4 == 0) && aligned16(db);
+    const int vecq = dt_vec_ok(q, ldq, dt);
+    const int vecd = dt_vec_ok(db, ldb, dt);
     const int vec = vecq && vecd && (d % 4 == 0);
     const PlaneLayout L = plane_layout(m, d);
     const char* pl = static_cast<const char*>(plane);
@@ -363,7 +362,7 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
         if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
         rc = launch_fill_f32(tau, w.nq_pad, -INFINITY, st);
         if (rc != FL_OK) return rc;
-        rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st);
+        rc = launch_query_plane(q, nq, ldq, d, base + w.off_qplane, w.nq_pad, w.d_pad, st, dt);
         if (rc != FL_OK) return rc;
     }
     if (phases & TC_SEED) {
@@ -379,6 +378,7 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     }
     if (!(phases & TC_SEED)) profile_begin(st);
     TcSeedMargin mg{};
+    mg.dt = dt;
     if (gmaxnorm != nullptr) {
         mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.maxnorm = gmaxnorm; mg.eps_rel = 0.004f; mg.cert_out = cert;
     } else if (tc_seed_dense(L.m_pad, k)) {
@@ -392,6 +392,7 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     if (rc != FL_OK) return rc;
 
     FinalizeParams fp{};
+    fp.dt = dt;
     fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
     fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
     // Re-rank the tc_partial_len best scores of the union of the published pools; what the
@@ -421,7 +422,7 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
         const float* maxnorm3 = reinterpret_cast<const float*>(pl3 + L3.off_meta);
         const float eps2 = 4e-5f;   // 3 * 2^-18 from the dropped lo.lo and rounded lo terms, plus fp32 accumulation
         float* tau2 = reinterpret_cast<float*>(base + w.off_s2_tau);
-        rc = launch_split_query_gather(q, ldq, d, s2_list, s2_count, w.s2_cap, base + w.off_s2_qplane, w.d_pad, out_dist, k,
+        rc = launch_split_query_gather(static_cast<const float*>(q), ldq, d, s2_list, s2_count, w.s2_cap, base + w.off_s2_qplane, w.d_pad, out_dist, k,
                                        maxnorm3, eps2, tau2, st);
         if (rc != FL_OK) return rc;
         TcKnnParams t2{};
@@ -450,6 +451,7 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
 
     // Rows whose pool could not be proven complete: exact CUDA-core pass over the list.
     SimtKnnParams sp{};
+    sp.dt = dt;
     sp.q = q; sp.ldq = ldq; sp.qlist = fb_list; sp.count_dev = fb_count; sp.count = 0;
     sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d;
     sp.hnorm = reinterpret_cast<const float*>(pl + L.off_hnorm);
@@ -473,25 +475,31 @@ static int knn_tc_phases(int phases, const float* q, int64_t nq, int64_t ldq, co
     return launch_knn_finalize(ff, w.fb_cap, st);
 }
 
-extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
-                          int64_t ldb, int d, int k, int mode, const void* plane, int64_t row_offset,
-                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes,
-                          int32_t* status, void* stream) {
-    int rc = knn_check_args("fl_knn_f32", q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
+// Every dtype and both stages behind one body: fl_knn_f32 / fl_knn_staged_f32 / fl_knn_rows.
+static int knn_rows_impl(const char* who, const void* q, int64_t nq, int64_t ldq, const void* db, int64_t m, int64_t ldb,
+                         int d, int k, int dt, int mode, const void* plane, const void* split_plane, int64_t row_offset,
+                         float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
+    FL_CHECK_ARG(dt == DT_F32 || dt == DT_BF16 || dt == DT_F16, "%s: unknown dtype %d", who, dt);
+    int rc = knn_check_args(who, q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
     if (rc != FL_OK || nq == 0) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+    if (split_plane != nullptr) {
+        FL_CHECK_ARG(mode == FL_KNN_BF16_RERANK && dt == DT_F32, "%s: the split-plane stage goes with fp32 rows and the tensor-core mode", who);
+        FL_CHECK_ARG(split_plane_supported(d), "%s: d=%d > 128 has no split plane", who, d);
+        FL_CHECK_ARG((reinterpret_cast<uintptr_t>(split_plane) & 255) == 0, "%s: split plane must be 256-byte aligned", who);
+    }
     if (mode == FL_KNN_BF16_RERANK)
         return knn_tc_phases(TC_PREP | TC_SEED | TC_SCORE, q, nq, ldq, db, m, ldb, d, k, plane, row_offset, nullptr,
-                             nullptr, out_dist, out_idx, ws, ws_bytes, status, st);
+                             nullptr, out_dist, out_idx, ws, ws_bytes, status, st, split_plane, dt);
 
     const KnnWs w = knn_ws_plan(nq, m, d, k, mode);
     if (ws_bytes < w.bytes) {
-        set_error("fl_knn_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes);
+        set_error("%s: workspace %lld < %lld bytes", who, (long long)ws_bytes, (long long)w.bytes);
         return FL_EWORKSPACE;
     }
     char* base = static_cast<char*>(ws);
-    const int vecq = (ldq % 4 == 0) && aligned16(q);
-    const int vecd = (ldb % 4 == 0) && aligned16(db);
+    const int vecq = dt_vec_ok(q, ldq, dt);
+    const int vecd = dt_vec_ok(db, ldb, dt);
     const int vec = vecq && vecd && (d % 4 == 0);
     if (status) FL_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t) * FL_STATUS_WORDS, st));
     FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
@@ -504,12 +512,13 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     } else {
         float* h = reinterpret_cast<float*>(base + w.off_hnorm);
         unsigned int* mx = reinterpret_cast<unsigned int*>(base + w.off_cnt) + 128;    // cleared above
-        halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h, mx);
+        halfnorm_kernel<<<(unsigned)ceil_div(m, 8), 256, 0, st>>>(db, m, d, ldb, h, mx, dt);
         FL_CHECK_LAUNCH();
         hnorm = h;
         maxnorm = reinterpret_cast<const float*>(mx);
     }
     SimtKnnParams sp{};
+    sp.dt = dt;
     sp.q = q; sp.ldq = ldq; sp.qlist = nullptr; sp.count_dev = nullptr; sp.count = nq;
     sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
     sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k);
@@ -523,6 +532,7 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
     if (rc != FL_OK) return rc;
 
     FinalizeParams fp{};
+    fp.dt = dt;
     fp.q = q; fp.ldq = ldq; fp.qlist = nullptr; fp.count_dev = nullptr; fp.count = nq;
     fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
     fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
@@ -541,6 +551,21 @@ extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* 
         FL_CHECK_LAUNCH();
     }
     return FL_OK;
+}
+
+extern "C" int fl_knn_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m,
+                          int64_t ldb, int d, int k, int mode, const void* plane, int64_t row_offset,
+                          float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes,
+                          int32_t* status, void* stream) {
+    return knn_rows_impl("fl_knn_f32", q, nq, ldq, db, m, ldb, d, k, DT_F32, mode, plane, nullptr, row_offset, out_dist,
+                         out_idx, ws, ws_bytes, status, stream);
+}
+
+extern "C" int fl_knn_rows(const void* q, int64_t nq, int64_t ldq, const void* db, int64_t m, int64_t ldb, int d, int k,
+                           int dtype, int mode, const void* plane, int64_t row_offset, float* out_dist, int32_t* out_idx,
+                           void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
+    return knn_rows_impl("fl_knn_rows", q, nq, ldq, db, m, ldb, d, k, dtype, mode, plane, nullptr, row_offset, out_dist,
+                         out_idx, ws, ws_bytes, status, stream);
 }
 
 extern "C" int64_t fl_knn_seed_floats(int64_t nq) {
@@ -652,15 +677,8 @@ extern "C" int64_t fl_knn_staged_workspace_bytes(int64_t nq, int64_t m, int d, i
 extern "C" int fl_knn_staged_f32(const float* q, int64_t nq, int64_t ldq, const float* db, int64_t m, int64_t ldb, int d,
                                  int k, const void* plane, const void* split_plane, int64_t row_offset, float* out_dist,
                                  int32_t* out_idx, void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
-    int mode = FL_KNN_BF16_RERANK;
-    int rc = knn_check_args("fl_knn_staged_f32", q, nq, ldq, db, m, ldb, d, k, &mode, plane, row_offset, out_dist, out_idx, ws);
-    if (rc != FL_OK || nq == 0) return rc;
-    if (split_plane != nullptr) {
-        FL_CHECK_ARG(split_plane_supported(d), "fl_knn_staged_f32: d=%d > 128 has no split plane", d);
-        FL_CHECK_ARG((reinterpret_cast<uintptr_t>(split_plane) & 255) == 0, "fl_knn_staged_f32: split plane must be 256-byte aligned");
-    }
-    return knn_tc_phases(TC_PREP | TC_SEED | TC_SCORE, q, nq, ldq, db, m, ldb, d, k, plane, row_offset, nullptr, nullptr,
-                         out_dist, out_idx, ws, ws_bytes, status, (cudaStream_t)stream, split_plane);
+    return knn_rows_impl("fl_knn_staged_f32", q, nq, ldq, db, m, ldb, d, k, DT_F32, FL_KNN_BF16_RERANK, plane, split_plane,
+                         row_offset, out_dist, out_idx, ws, ws_bytes, status, stream);
 }
 
 // Test hook: runs only the tensor-core scoring pass for up to 128 queries and writes the

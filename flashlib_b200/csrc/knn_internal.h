@@ -8,11 +8,12 @@ namespace fl {
 // Exact CUDA-core scoring pass: every (slot, split) pair gets a descending pool of K1
 // (score, row) entries at part[(slot*nsplit + split)*K1].
 struct SimtKnnParams {
-    const float* q; int64_t ldq;
+    int dt;                 // element type of the q and db rows (DT_*; leading dimensions in elements)
+    const void* q; int64_t ldq;
     const int* qlist;       // optional slot -> query row map
     const int* count_dev;   // optional device-resident slot count
     int64_t count;          // slot count when count_dev is null
-    const float* db; int64_t m; int64_t ldb; int d;
+    const void* db; int64_t m; int64_t ldb; int d;
     const float* hnorm;     // ||x||^2 / 2 per database row
     int K1, cap, npl;       // published entries per pool, pool capacity, capacity / 32
     int keep;               // entries kept at a compaction inside the scan (<= K1; 0: K1)
@@ -66,9 +67,10 @@ int simt_block_queries(int K1);
 // Merge of the per-split pools, exact fp32 re-rank, top-k selection and (optionally)
 // verification of the candidate pool against the scoring error bound.
 struct FinalizeParams {
-    const float* q; int64_t ldq;
+    int dt;                  // element type of the q and db rows (DT_*)
+    const void* q; int64_t ldq;
     const int* qlist; const int* count_dev; int64_t count;
-    const float* db; int64_t m; int64_t ldb; int d; int vec;
+    const void* db; int64_t m; int64_t ldb; int d; int vec;
     const float* part_sc; const uint32_t* part_id; int nsplit; int K1;
     int k; int rerank; int64_t row_offset;
     float* out_dist; int32_t* out_idx;
@@ -145,7 +147,7 @@ int tc_knn_auto(int64_t nq, int64_t m, int d, int k);
 // (q == nullptr: none): the threshold is lowered by 2 eps_rel ||q|| *maxnorm + slack and copied to
 // cert_out (f32 [nq_pad], may be null).
 struct TcSeedMargin {
-    const float* q; int64_t ldq; int d; int64_t nq;
+    const void* q; int dt; int64_t ldq; int d; int64_t nq;
     const float* maxnorm; float eps_rel;
     float* cert_out;
 };
@@ -186,11 +188,11 @@ int launch_split_query_gather(const float* x, int64_t ldx, int d, const int* row
                               float* tau_out, cudaStream_t st);
 
 // bf16 query plane [nq_pad][d_pad + 16] (features zero padded, ones in the norm columns) from fp32 queries.
-int launch_query_plane(const float* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
-                       int d_pad, cudaStream_t st);
+int launch_query_plane(const void* q, int64_t nq, int64_t ldq, int d, void* qplane, int64_t nq_pad,
+                       int d_pad, cudaStream_t st, int dt = DT_F32);
 
 // Small helpers shared by the entry points.
-int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st);
+int launch_plane_build(const void* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st, int dt = DT_F32);
 int launch_fill_f32(float* p, int64_t n, float v, cudaStream_t st);
 int launch_ivf_group(const int32_t* probed, int64_t npairs, int nlist, int bq, const int64_t* list_offsets, int* cnt,
                      int* pair_off, int* item_off, int* cursor, int* sorted_pair, cudaStream_t st);

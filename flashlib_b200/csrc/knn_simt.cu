@@ -1,5 +1,4 @@
-// Exact CUDA-core kNN scoring pass and the pool finalisation (merge + exact re-rank +
-// top-k + verification) shared by both kNN modes.
+// Exact CUDA-core kNN scoring pass (the pools it publishes are finalised in knn_finalize.cu).
 #include "knn_internal.h"
 #include "pool.cuh"
 #include "simt_tile.cuh"
@@ -82,24 +81,24 @@ __device__ __forceinline__ void knn_simt_block(const SimtKnnParams& p, const int
     }
     __syncthreads();
 
-    const float* qrow[T::QL];
+    const void* qrow[T::QL];
 #pragma unroll
     for (int i = 0; i < T::QL; ++i) {
         const int r = (i * 256 + tid) >> 3;
-        qrow[i] = (r < BQ && qmap[r] >= 0) ? p.q + (int64_t)qmap[r] * p.ldq : nullptr;
+        qrow[i] = (r < BQ && qmap[r] >= 0) ? row_at(p.q, qmap[r], p.ldq, p.dt) : nullptr;
     }
 
     constexpr int RPW = BQ / 8;  // rows per warp in the pool phase
     const int keep = p.keep > 0 ? p.keep : p.K1;
     for (int64_t tile_row = row_begin; tile_row < row_end; tile_row += 128) {
-        const float* drow[4];
+        const void* drow[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int64_t gr = tile_row + ((i * 256 + tid) >> 3);
-            drow[i] = gr < row_end ? p.db + gr * p.ldb : nullptr;
+            drow[i] = gr < row_end ? row_at(p.db, gr, p.ldb, p.dt) : nullptr;
         }
         float acc[TQ][8];
-        simt_cross_tile<TQ>(qrow, drow, p.d, p.vecq != 0, p.vecd != 0, slab, acc);
+        simt_cross_tile<TQ>(qrow, drow, p.d, p.vecq != 0, p.vecd != 0, slab, acc, p.dt, p.dt);
 
         // Scores into the tile buffer (it aliases the operand slabs, which are idle now).
         float* S = slab;
@@ -253,541 +252,6 @@ int launch_knn_simt(const SimtKnnParams& p, int64_t max_slots, cudaStream_t st) 
     if (tq == 4) return launch_simt_t<4>(p, max_slots, st);
     if (tq == 2) return launch_simt_t<2>(p, max_slots, st);
     return launch_simt_t<1>(p, max_slots, st);
-}
-
-// ------------------------------------------------------------------------------------
-// Finalisation: one warp per query slot.
-//
-// Input: `nsplit` published pools of K1 (score, row) entries per slot, and (tensor-core path)
-// the thresholds of the scoring pass: every row it did not publish scored at most u = the
-// largest threshold.  Output: the k rows of least exact fp32 distance among the candidates,
-// ordered by (distance, row).  With verification on, the result is accepted only when the k-th
-// exact distance lies below qsq - 2 (bound + eps), where `bound` is an upper bound on the
-// score of every row that was not re-scored exactly; otherwise the slot is queued for the
-// exact path.
-//
-// Candidates are taken in two attempts.  The first keeps only scores above u (entries at or
-// below u can never satisfy the proof) and at or above a floor f0 chosen so that a few dozen
-// entries survive, which are sorted once; dropped entries scored at most max(u, f0).  If that
-// set cannot be proven (or overflows), the second attempt sorts every pool and merges the K1
-// best, with bound = max(u, K1-th best).
-// ------------------------------------------------------------------------------------
-template <int NPL1, bool INDIRECT, bool DYN>
-__device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int64_t slot, const int64_t count) {
-    const int lane = threadIdx.x & 31;
-    const int64_t qi = p.qlist ? (int64_t)p.qlist[slot] : slot;
-    const int K1 = p.K1;
-    const int nsplit = DYN ? simt_dyn_split(count, p.dyn_bq, p.dyn_blocks, p.m).nsplit : p.nsplit;
-    // pool s of this slot: offset of its first entry (negative: the pool does not exist)
-    auto pool_base = [&](int s) -> int64_t {
-        if (!INDIRECT) return (slot * nsplit + s) * (int64_t)K1;
-        const int row = __ldg(p.pool_row + slot * nsplit + s);
-        return row >= 0 ? (int64_t)row * K1 : -1;
-    };
-    // published id -> database row, INVALID_ID for padding rows of the operand plane
-    auto real_id = [&](uint32_t raw) -> uint32_t {
-        if (!INDIRECT) return raw < (uint32_t)p.m ? raw : INVALID_ID;
-        if (raw >= (uint32_t)p.id_bound) return INVALID_ID;
-        const int mapped = __ldg(p.id_map + raw);
-        return mapped >= 0 ? (uint32_t)mapped : INVALID_ID;
-    };
-    const float* psc = p.part_sc;
-    const uint32_t* pid = p.part_id;
-
-    float u = neg_inf();
-    if (p.part_tau != nullptr) {
-        const int per_pool = p.ntau / nsplit;
-        for (int i = lane; i < p.ntau; i += 32) {
-            int64_t t = slot * p.ntau + i;
-            if (INDIRECT) {
-                const int row = __ldg(p.pool_row + slot * nsplit + i / per_pool);
-                t = row >= 0 ? (int64_t)row * per_pool + i % per_pool : -1;
-            }
-            if (t >= 0) u = fmaxf(u, p.part_tau[t]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
-    }
-
-    const float* qp = p.q + qi * p.ldq;
-    float qsq = 0.f;
-    if (p.vec) {
-        for (int c = lane * 4; c < p.d; c += 128) {
-            const float4 v = __ldg(reinterpret_cast<const float4*>(qp + c));
-            qsq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-    } else {
-        for (int c = lane; c < p.d; c += 32) { const float v = __ldg(qp + c); qsq += v * v; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);
-    float eps = 0.f, slack = 0.f;
-    if (p.verify) {
-        const float mn = __ldg(p.maxnorm);
-        eps = p.eps_rel * sqrtf(qsq) * mn;
-        slack = 1e-5f * (qsq + mn * mn);
-    }
-
-    constexpr bool HAS_FILTER = NPL1 <= 4;
-    __shared__ float s_sc[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
-    __shared__ uint32_t s_id[HAS_FILTER ? 4 : 1][HAS_FILTER ? 32 * NPL1 : 1];
-    const bool try_filter = HAS_FILTER && p.verify && p.part_tau != nullptr && u > neg_inf();
-
-    for (int attempt = try_filter ? 0 : 1; attempt < 2; ++attempt) {
-        float key[NPL1];
-        uint32_t id[NPL1];
-        float bound;
-        if (attempt == 0) {
-            // Each lane notes the best score it meets; the (k+14)-th largest of the 32 lane maxima
-            // is a floor with at least k+14 entries at or above it and, scores being spread evenly
-            // over the lanes, rarely more than fit the list.  Pool slots are ordered (best kept
-            // entries first), so the slot a lane reads rotates from pool to pool.
-            float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
-            uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
-            float lmax = neg_inf();
-            for (int s = 0; s < nsplit; ++s) {
-                const int64_t pb = pool_base(s);
-                if (pb < 0) continue;
-#pragma unroll
-                for (int r = 0; r < NPL1; ++r) {
-                    const int e = (r << 5) | ((lane + 5 * s + 16 * r) & 31);
-                    const float sc = psc[pb + e];
-                    // (padding rows of an operand plane score -3e38: no need to look their ids up)
-                    if (pid[pb + e] != INVALID_ID) lmax = fmaxf(lmax, sc);
-                }
-            }
-            int rank = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const float o = __shfl_sync(FULL_MASK, lmax, j);
-                rank += (o > lmax || (o == lmax && j < lane)) ? 1 : 0;
-            }
-            const int want = p.k + 14 < 32 ? p.k + 14 : 32;
-            const unsigned sel = __ballot_sync(FULL_MASK, rank == want - 1);
-            const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
-            const unsigned lt = (1u << lane) - 1u;
-            int total = 0;
-            for (int s = 0; s < nsplit; ++s) {
-                const int64_t pb = pool_base(s);
-                if (pb < 0) continue;
-#pragma unroll
-                for (int r = 0; r < NPL1; ++r) {
-                    const int e = (r << 5) | lane;
-                    const float sc = psc[pb + e];
-                    const bool pass = sc > u && sc >= f0;
-                    const uint32_t cid = pass ? real_id(pid[pb + e]) : INVALID_ID;
-                    const bool keep = pass && cid != INVALID_ID;
-                    const unsigned mask = __ballot_sync(FULL_MASK, keep);
-                    const int pos = total + __popc(mask & lt);
-                    if (keep && pos < 32 * NPL1) { wsc[pos] = sc; wid[pos] = cid; }
-                    total += __popc(mask);
-                }
-            }
-            __syncwarp();
-            if (total > 32 * NPL1) continue;
-#pragma unroll
-            for (int r = 0; r < NPL1; ++r) {
-                const int e = (r << 5) | lane;
-                key[r] = e < total ? wsc[e] : neg_inf();
-                id[r] = e < total ? wid[e] : INVALID_ID;
-            }
-            __syncwarp();
-            warp_sort_desc<NPL1, false>(key, id);
-            bound = fmaxf(u, f0);
-        } else {
-            // Every pool is sorted on its own and merged into the running list with one bitonic
-            // merge step.  The K1-th kept score covers what this merge dropped.
-            float kin[NPL1];
-            uint32_t iin[NPL1];
-#pragma unroll
-            for (int r = 0; r < NPL1; ++r) { key[r] = neg_inf(); id[r] = INVALID_ID; }
-            for (int s = 0; s < nsplit; ++s) {
-                const int64_t pb = pool_base(s);
-                if (pb < 0) continue;
-#pragma unroll
-                for (int r = 0; r < NPL1; ++r) {
-                    const int e = (r << 5) | lane;
-                    const uint32_t cid = real_id(pid[pb + e]);
-                    const bool real = cid != INVALID_ID;   // padding rows of the operand plane never count
-                    kin[r] = real ? psc[pb + e] : neg_inf();
-                    iin[r] = real ? cid : INVALID_ID;
-                }
-                warp_sort_desc<NPL1, false>(kin, iin);
-                warp_merge_desc<NPL1, false>(key, id, kin, iin);
-            }
-            bound = __shfl_sync(FULL_MASK, id[NPL1 - 1], 31) != INVALID_ID
-                        ? __shfl_sync(FULL_MASK, key[NPL1 - 1], 31) : neg_inf();
-            bound = fmaxf(bound, u);
-        }
-
-        // Exact fp32 distances of the first `rerank` entries, best score first.  With
-        // verification on, the walk stops as soon as k of the exact distances seen so far lie
-        // below the lower bound that the next entry's score (and `bound`) puts on every row not
-        // yet re-scored.
-        bool stop = false;
-        float dist[NPL1];
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) dist[r] = pos_inf();
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) {
-            for (int l0 = 0; l0 < 32; l0 += 4) {
-                if (stop || (r << 5) + l0 >= p.rerank) break;
-                if (p.verify && (l0 & 7) == 0 && (r << 5) + l0 >= ((p.k + 7) & ~7)) {
-                    const float nxt = __shfl_sync(FULL_MASK, key[r], l0);
-                    const float T = qsq - 2.f * (fmaxf(nxt, bound) + eps) - slack;
-                    int cnt = 0;
-#pragma unroll
-                    for (int rr = 0; rr < NPL1; ++rr) cnt += __popc(__ballot_sync(FULL_MASK, dist[rr] < T));
-                    if (cnt >= p.k) { stop = true; bound = fmaxf(bound, nxt); break; }
-                }
-                uint32_t cid[4];
-                float a[4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    cid[t] = __shfl_sync(FULL_MASK, id[r], l0 + t);
-                    if ((r << 5) + l0 + t >= p.rerank) cid[t] = INVALID_ID;
-                    a[t] = 0.f;
-                }
-                if (p.vec) {
-                    for (int c = lane * 4; c < p.d; c += 128) {
-                        const float4 qv = __ldg(reinterpret_cast<const float4*>(qp + c));
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            if (cid[t] != INVALID_ID) {
-                                const float4 xv = __ldg(
-                                    reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
-                                const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z,
-                                            d3 = qv.w - xv.w;
-                                a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
-                            }
-                        }
-                    }
-                } else {
-                    for (int c = lane; c < p.d; c += 32) {
-                        const float qv = __ldg(qp + c);
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            if (cid[t] != INVALID_ID) {
-                                const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
-                                a[t] += df * df;
-                            }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
-                    if (lane == l0 + t && cid[t] != INVALID_ID) dist[r] = a[t];
-                }
-            }
-        }
-
-        // Order by (exact distance, row) ascending.
-        float k2[NPL1];
-        uint32_t id2[NPL1];
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) {
-            const bool ok = dist[r] < pos_inf();
-            k2[r] = ok ? -dist[r] : neg_inf();
-            id2[r] = ok ? id[r] : INVALID_ID;
-        }
-        warp_sort_desc<NPL1, true>(k2, id2);
-        float dk = pos_inf();
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) {
-            if (((p.k - 1) >> 5) == r) {
-                const float v = __shfl_sync(FULL_MASK, k2[r], (p.k - 1) & 31);
-                dk = (v > neg_inf()) ? -v : pos_inf();
-            }
-        }
-
-        // Verification: every row that was not re-scored has a score <= bound, so its exact
-        // distance is at least qsq - 2 (bound + eps).
-        bool proven = true;
-        if (p.verify && bound > neg_inf()) proven = dk < qsq - 2.f * (bound + eps) - slack;
-        if (!proven && p.cert_tau != nullptr) proven = bound <= __ldg(p.cert_tau + qi);
-        if (!proven && attempt == 0) continue;
-#pragma unroll
-        for (int r = 0; r < NPL1; ++r) {
-            const int e = (r << 5) | lane;
-            if (e < p.k) {
-                const bool ok = id2[r] != INVALID_ID;
-                p.out_dist[qi * p.k + e] = ok ? -k2[r] : pos_inf();
-                p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)id2[r] + p.row_offset) : -1;
-            }
-        }
-        if (!proven && lane == 0 && p.fb_count != nullptr) {
-            bool queued = false;
-            if (p.next_count != nullptr) {
-                const int i = atomicAdd(p.next_count, 1);
-                if (i < p.next_cap) { p.next_list[i] = (int)qi; queued = true; }
-            }
-            if (!queued) {
-                const int i = atomicAdd(p.fb_count, 1);
-                if (i < p.fb_cap) p.fb_list[i] = (int)qi;
-            }
-        }
-        break;
-    }
-}
-
-// One warp per slot, grid-stride: the slot count may only be known on the device, and a grid
-// sized for the largest possible count would mostly launch blocks that have nothing to do.
-template <int NPL1, bool INDIRECT, bool DYN>
-__global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
-    if (p.count_dev == nullptr) {
-        // slot count known at launch: one slot per warp
-        const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-        if (slot < p.count) finalize_slot<NPL1, INDIRECT, DYN>(p, slot, p.count);
-        return;
-    }
-    const int64_t count = (int64_t)(*p.count_dev);
-    for (int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5); slot < count; slot += (int64_t)gridDim.x * 4) {
-        finalize_slot<NPL1, INDIRECT, DYN>(p, slot, count);
-        __syncwarp();
-    }
-}
-
-int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
-    if (max_slots <= 0) return FL_OK;
-    int64_t blocks = ceil_div(max_slots, 4);
-    if (p.count_dev != nullptr && blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
-    const unsigned grid = (unsigned)blocks;
-    const bool indirect = p.pool_row != nullptr;
-    if (indirect && (p.id_map == nullptr || p.K1 != 128)) {
-        set_error("finalisation: pool indirection goes with an id map and 128 published entries per pool");
-        return FL_EINVAL;
-    }
-    if (!indirect && p.id_map != nullptr) { set_error("finalisation: id map without pool indirection"); return FL_EINVAL; }
-    const bool dyn = p.dyn_blocks > 0;
-    if (dyn && (indirect || p.count_dev == nullptr)) { set_error("finalisation: dynamic split goes with a device-side count"); return FL_EINVAL; }
-#define FL_FINALIZE_CASE(N)                                                                   \
-    case N:                                                                                   \
-        if (dyn) knn_finalize_kernel<N, false, true><<<grid, 128, 0, st>>>(p);                \
-        else knn_finalize_kernel<N, false, false><<<grid, 128, 0, st>>>(p);                   \
-        break;
-    switch (p.K1 / 32) {
-        FL_FINALIZE_CASE(1)
-        FL_FINALIZE_CASE(2)
-        case 4:
-            if (indirect) knn_finalize_kernel<4, true, false><<<grid, 128, 0, st>>>(p);
-            else if (dyn) knn_finalize_kernel<4, false, true><<<grid, 128, 0, st>>>(p);
-            else knn_finalize_kernel<4, false, false><<<grid, 128, 0, st>>>(p);
-            break;
-        FL_FINALIZE_CASE(8)
-        FL_FINALIZE_CASE(16)
-        default:
-            set_error("unsupported pool size %d", p.K1);
-            return FL_EUNSUPPORTED;
-    }
-#undef FL_FINALIZE_CASE
-    FL_CHECK_LAUNCH();
-    return FL_OK;
-}
-
-// ------------------------------------------------------------------------------------
-// Finalisation of the large-k tensor-core pools: one block per query.
-//
-// The scoring pass published, per (query, range, warpgroup), a pool of up to 256 (score, row)
-// entries with its entry count and final threshold; every row it did not publish scored at most
-// u = the largest threshold.  The block gathers the entries scoring above u (the others can
-// never satisfy the proof), sorts them by score, re-scores the best BIG_RERANK with exact fp32
-// sum (q - x)^2, sorts those by (distance, row) and accepts the first k when the k-th distance
-// lies below qsq - 2 (bound + eps), bound = max(u, best score that was not re-scored).
-// Otherwise (or when more than BIG_CAND entries survive) the query is queued for the exact path.
-// ------------------------------------------------------------------------------------
-constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 256;
-
-static __device__ __forceinline__ void finalize_big_slot(const FinalizeParams& p, const int64_t slot) {
-    __shared__ float s_key[BIG_CAND];
-    __shared__ uint32_t s_id[BIG_CAND];
-    __shared__ float s_q[256];
-    __shared__ float s_red[BIG_THREADS / 32];
-    __shared__ int s_n;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t qi = p.qlist != nullptr ? (int64_t)p.qlist[slot] : slot;
-    const float* qp = p.q + qi * p.ldq;
-
-    // u and ||q||^2
-    float u = neg_inf(), qs = 0.f;
-    for (int i = tid; i < p.ntau; i += BIG_THREADS) u = fmaxf(u, p.part_tau[slot * p.ntau + i]);
-    for (int c = tid; c < p.d; c += BIG_THREADS) { const float v = __ldg(qp + c); s_q[c] = v; qs += v * v; }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        u = fmaxf(u, __shfl_xor_sync(FULL_MASK, u, o));
-        qs += __shfl_xor_sync(FULL_MASK, qs, o);
-    }
-    if (lane == 0) s_red[warp] = u;
-    if (tid == 0) s_n = 0;
-    __syncthreads();
-    u = s_red[0];
-#pragma unroll
-    for (int w = 1; w < BIG_THREADS / 32; ++w) u = fmaxf(u, s_red[w]);
-    __syncthreads();
-    if (lane == 0) s_red[warp] = qs;
-    __syncthreads();
-    float qsq = 0.f;
-#pragma unroll
-    for (int w = 0; w < BIG_THREADS / 32; ++w) qsq += s_red[w];
-
-    // Gather the survivors (score above `cut`), one pool per warp at a time.  If more than
-    // BIG_CAND survive (a loose starting threshold), the BIG_CAND that were stored -- an
-    // arbitrary subset -- are sorted, the cut moves up to the score at their first quarter and
-    // the gather is repeated; everything below the cut is covered by `bound`.
-    float cut = u;
-    int total = 0;
-    for (int round = 0; round < 4; ++round) {
-        __syncthreads();
-        if (tid == 0) s_n = 0;
-        __syncthreads();
-        for (int pi = warp; pi < p.ntau; pi += BIG_THREADS / 32) {
-            int cnt = p.part_cnt[slot * p.ntau + pi];
-            cnt = cnt < BIG_POOL ? cnt : BIG_POOL;
-            const float* psc = p.part_sc + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
-            const uint32_t* pid = p.part_id + (slot * p.ntau + pi) * (int64_t)BIG_POOL;
-            for (int e0 = 0; e0 < cnt; e0 += 32) {
-                const int e = e0 + lane;
-                float sc = neg_inf();
-                uint32_t cid = INVALID_ID;
-                if (e < cnt) { sc = psc[e]; cid = pid[e]; }
-                const bool keep = sc > cut && cid < (uint32_t)p.m;
-                const unsigned mask = __ballot_sync(FULL_MASK, keep);
-                if (mask) {
-                    int base = 0;
-                    if (lane == 0) base = atomicAdd(&s_n, __popc(mask));
-                    base = __shfl_sync(FULL_MASK, base, 0);
-                    const int pos = base + __popc(mask & ((1u << lane) - 1u));
-                    if (keep && pos < BIG_CAND) { s_key[pos] = sc; s_id[pos] = cid; }
-                }
-            }
-        }
-        __syncthreads();
-        total = s_n;
-        if (total <= BIG_CAND) break;
-        block_sort_desc<BIG_THREADS>(s_key, s_id, BIG_CAND);
-        cut = fmaxf(cut, s_key[BIG_CAND / 4 - 1]);
-    }
-    const bool overflow = total > BIG_CAND;
-    const int n = overflow ? BIG_CAND : total;
-    int P = BIG_RERANK;
-    while (P < n) P <<= 1;
-    for (int i = n + tid; i < P; i += BIG_THREADS) { s_key[i] = neg_inf(); s_id[i] = INVALID_ID; }
-    block_sort_desc<BIG_THREADS>(s_key, s_id, P);
-
-    // Exact distances in rounds of 64 candidates, best scores first.  After a round the walk stops
-    // when k of the exact distances seen so far lie below the lower bound that the next
-    // candidate's score (and the cut) puts on every row not yet re-scored; at most BIG_RERANK.
-    __shared__ float s_dist[BIG_RERANK];
-    const float mn = __ldg(p.maxnorm);
-    const float eps = p.eps_rel * sqrtf(qsq) * mn;
-    const float slack = 1e-5f * (qsq + mn * mn);
-    const int n_rr = n < BIG_RERANK ? n : BIG_RERANK;
-    float bound = cut;
-    int done = 0;
-    __syncthreads();
-    for (int r0 = 0; r0 < n_rr; r0 += 64) {
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-            const int c0 = r0 + warp * 8 + h * 4;
-            uint32_t cid[4];
-            float a[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) { cid[t] = s_id[c0 + t]; a[t] = 0.f; }
-            if (p.vec) {
-                for (int c = lane * 4; c < p.d; c += 128) {
-                    const float4 qv = *reinterpret_cast<const float4*>(s_q + c);
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        if (cid[t] != INVALID_ID) {
-                            const float4 xv = __ldg(reinterpret_cast<const float4*>(p.db + (int64_t)cid[t] * p.ldb + c));
-                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
-                            a[t] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
-                        }
-                    }
-                }
-            } else {
-                for (int c = lane; c < p.d; c += 32) {
-                    const float qv = s_q[c];
-#pragma unroll
-                    for (int t = 0; t < 4; ++t) {
-                        if (cid[t] != INVALID_ID) {
-                            const float df = qv - __ldg(p.db + (int64_t)cid[t] * p.ldb + c);
-                            a[t] += df * df;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) a[t] += __shfl_xor_sync(FULL_MASK, a[t], o);
-                if (lane == 0) s_dist[c0 + t] = cid[t] != INVALID_ID ? a[t] : pos_inf();
-            }
-        }
-        done = r0 + 64;
-        // everything from position `done` on scored at most s_key[done] (sorted) or the cut
-        const float nxt = done < n ? s_key[done] : neg_inf();
-        bound = fmaxf(cut, nxt);
-        const float T = qsq - 2.f * (bound + eps) - slack;
-        __syncthreads();                                   // this round's distances are written
-        const int below = __syncthreads_count(tid < done && s_dist[tid] < T);
-        if (done >= p.k && below >= p.k) break;
-    }
-    // order the re-scored candidates by (distance, row)
-    __syncthreads();
-    for (int i = tid; i < BIG_RERANK; i += BIG_THREADS) {
-        const bool have = i < done && i < n_rr && s_id[i] != INVALID_ID;
-        s_key[i] = have ? -s_dist[i] : neg_inf();
-        if (!have) s_id[i] = INVALID_ID;
-    }
-    block_sort_desc<BIG_THREADS>(s_key, s_id, BIG_RERANK);
-
-    for (int e = tid; e < p.k; e += BIG_THREADS) {
-        const bool ok = s_id[e] != INVALID_ID;
-        p.out_dist[qi * p.k + e] = ok ? -s_key[e] : pos_inf();
-        p.out_idx[qi * p.k + e] = ok ? (int32_t)((int64_t)s_id[e] + p.row_offset) : -1;
-    }
-    if (tid == 0) {
-        bool proven = !overflow;
-        if (proven && bound > neg_inf()) {
-            const float dk = s_id[p.k - 1] != INVALID_ID ? -s_key[p.k - 1] : pos_inf();
-            proven = dk < qsq - 2.f * (bound + eps) - slack;
-        }
-        if (!proven) {
-            bool queued = false;
-            if (p.next_count != nullptr) {
-                const int i = atomicAdd(p.next_count, 1);
-                if (i < p.next_cap) { p.next_list[i] = (int)qi; queued = true; }
-            }
-            if (!queued) {
-                const int i = atomicAdd(p.fb_count, 1);
-                if (i < p.fb_cap) p.fb_list[i] = (int)qi;
-            }
-        }
-    }
-}
-
-// One block per slot; with a device-side slot count (capped by p.count) the blocks of a modest grid
-// stride over the live slots instead.
-__global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeParams p) {
-    int64_t count = p.count;
-    if (p.count_dev != nullptr) { const int64_t c = *p.count_dev; count = c < count ? c : count; }
-    for (int64_t slot = blockIdx.x; slot < count; slot += gridDim.x) {
-        finalize_big_slot(p, slot);
-        __syncthreads();
-    }
-}
-
-int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
-    if (max_slots <= 0) return FL_OK;
-    FL_CHECK_ARG(p.part_cnt && p.part_tau && p.K1 == 2 * BIG_POOL && p.d <= 256 && p.k <= BIG_RERANK && p.count == max_slots,
-                 "large-k finalisation: bad parameters");
-    int64_t grid = max_slots;
-    if (p.count_dev != nullptr && grid > (int64_t)sm_count() * 4) grid = (int64_t)sm_count() * 4;
-    knn_finalize_big_kernel<<<(unsigned)grid, BIG_THREADS, 0, st>>>(p);
-    FL_CHECK_LAUNCH();
-    return FL_OK;
 }
 
 }  // namespace fl

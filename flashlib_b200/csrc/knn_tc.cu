@@ -967,8 +967,8 @@ __global__ void __launch_bounds__(256) tc_seed_select_kernel(const float* __rest
     if (mg.q != nullptr) {
         float qsq = 0.f;
         if (row < mg.nq) {
-            const float* qp = mg.q + row * mg.ldq;
-            for (int c = lane; c < mg.d; c += 32) { const float x = __ldg(qp + c); qsq += x * x; }
+            const void* qp = row_at(mg.q, row, mg.ldq, mg.dt);
+            for (int c = lane; c < mg.d; c += 32) { const float x = ld_elem(qp, c, mg.dt); qsq += x * x; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) qsq += __shfl_xor_sync(FULL_MASK, qsq, o);

@@ -38,9 +38,11 @@ __global__ void rownorm_kernel(const float* __restrict__ x, int64_t n, int d, in
 // to 2^-24 relative); multiplied by the ones the query plane holds in the same columns they
 // make the tensor-core product come out as <q,x> - ||x||^2/2.  Padding rows carry a huge
 // negative value there so they can never rank.
-__global__ void plane_build_kernel(const float* __restrict__ db, int64_t m, int d, int64_t ld,
+// Rows of 16-bit storage (dt): bf16 values enter the plane as they are, fp16 values are rounded to
+// bf16 like fp32 ones; the norms are those of the stored values.
+__global__ void plane_build_kernel(const void* __restrict__ db, int64_t m, int d, int64_t ld,
                                    __nv_bfloat16* __restrict__ rows, float* __restrict__ hnorm,
-                                   unsigned int* __restrict__ maxnorm_bits, int64_t m_pad, int d_pad) {
+                                   unsigned int* __restrict__ maxnorm_bits, int64_t m_pad, int d_pad, int dt) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= m_pad) return;
@@ -51,10 +53,10 @@ __global__ void plane_build_kernel(const float* __restrict__ db, int64_t m, int 
         if (lane == 0) hnorm[row] = pos_inf();
         return;
     }
-    const float* p = db + row * ld;
+    const void* p = row_at(db, row, ld, dt);
     float s = 0.f;
     for (int c = lane; c < d_pad; c += 32) {
-        const float v = (c < d) ? __ldg(p + c) : 0.f;
+        const float v = (c < d) ? ld_elem(p, c, dt) : 0.f;
         s += v * v;
         o[c] = __float2bfloat16_rn(v);
     }
@@ -88,7 +90,7 @@ PlaneLayout plane_layout(int64_t m, int d) {
 }
 
 // Fills `plane` (layout plane_layout(m, d)) for the fp32 rows of db.
-int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st) {
+int launch_plane_build(const void* db, int64_t m, int d, int64_t ld, void* plane, cudaStream_t st, int dt) {
     const PlaneLayout L = plane_layout(m, d);
     char* base = static_cast<char*>(plane);
     FL_CHECK_CUDA(cudaMemsetAsync(base + L.off_meta, 0, 1024, st));
@@ -96,7 +98,7 @@ int launch_plane_build(const float* db, int64_t m, int d, int64_t ld, void* plan
     plane_build_kernel<<<(unsigned)ceil_div(L.m_pad, wpb), wpb * 32, 0, st>>>(
         db, m, d, ld, reinterpret_cast<__nv_bfloat16*>(base + L.off_rows),
         reinterpret_cast<float*>(base + L.off_hnorm), reinterpret_cast<unsigned int*>(base + L.off_meta),
-        L.m_pad, L.d_pad);
+        L.m_pad, L.d_pad, dt);
     FL_CHECK_LAUNCH();
     return FL_OK;
 }
@@ -121,18 +123,24 @@ extern "C" int64_t fl_knn_plane_bytes(int64_t m, int d) {
     return plane_layout(m, d).bytes;
 }
 
-extern "C" int fl_knn_prepare_db_f32(const float* db, int64_t m, int d, int64_t ld, void* plane,
-                                     int64_t plane_bytes, void* stream) {
-    FL_CHECK_ARG(m >= 1 && d >= 1 && ld >= d, "fl_knn_prepare_db_f32: bad shape m=%lld d=%d ld=%lld",
+extern "C" int fl_knn_prepare_db_rows(const void* db, int dtype, int64_t m, int d, int64_t ld, void* plane,
+                                      int64_t plane_bytes, void* stream) {
+    FL_CHECK_ARG(m >= 1 && d >= 1 && ld >= d, "fl_knn_prepare_db: bad shape m=%lld d=%d ld=%lld",
                  (long long)m, d, (long long)ld);
-    FL_CHECK_ARG(db && plane, "fl_knn_prepare_db_f32: null pointer");
+    FL_CHECK_ARG(dtype == DT_F32 || dtype == DT_BF16 || dtype == DT_F16, "fl_knn_prepare_db: unknown dtype %d", dtype);
+    FL_CHECK_ARG(db && plane, "fl_knn_prepare_db: null pointer");
     FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0,
-                 "fl_knn_prepare_db_f32: plane must be 256-byte aligned");
+                 "fl_knn_prepare_db: plane must be 256-byte aligned");
     const PlaneLayout L = plane_layout(m, d);
     if (plane_bytes < L.bytes) {
-        set_error("fl_knn_prepare_db_f32: plane buffer %lld < %lld bytes", (long long)plane_bytes,
+        set_error("fl_knn_prepare_db: plane buffer %lld < %lld bytes", (long long)plane_bytes,
                   (long long)L.bytes);
         return FL_EWORKSPACE;
     }
-    return launch_plane_build(db, m, d, ld, plane, (cudaStream_t)stream);
+    return launch_plane_build(db, m, d, ld, plane, (cudaStream_t)stream, dtype);
+}
+
+extern "C" int fl_knn_prepare_db_f32(const float* db, int64_t m, int d, int64_t ld, void* plane,
+                                     int64_t plane_bytes, void* stream) {
+    return fl_knn_prepare_db_rows(db, DT_F32, m, d, ld, plane, plane_bytes, stream);
 }

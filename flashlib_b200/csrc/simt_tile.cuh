@@ -18,14 +18,14 @@ struct SimtTile {
     static constexpr int SLAB_FLOATS = 2 * KS * (QSTR + DSTR);
 };
 
-__device__ __forceinline__ float4 load4_guard(const float* row, int kb, int d, bool vec) {
+__device__ __forceinline__ float4 load4_guard(const void* row, int kb, int d, bool vec, int dt) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (row == nullptr) return v;
-    if (vec && kb + 3 < d) return __ldg(reinterpret_cast<const float4*>(row + kb));
-    if (kb < d) v.x = __ldg(row + kb);
-    if (kb + 1 < d) v.y = __ldg(row + kb + 1);
-    if (kb + 2 < d) v.z = __ldg(row + kb + 2);
-    if (kb + 3 < d) v.w = __ldg(row + kb + 3);
+    if (vec && kb + 3 < d) return ld_elem4(row, kb, dt);
+    if (kb < d) v.x = ld_elem(row, kb, dt);
+    if (kb + 1 < d) v.y = ld_elem(row, kb + 1, dt);
+    if (kb + 2 < d) v.z = ld_elem(row, kb + 2, dt);
+    if (kb + 3 < d) v.w = ld_elem(row, kb + 3, dt);
     return v;
 }
 
@@ -33,10 +33,12 @@ __device__ __forceinline__ float4 load4_guard(const float* row, int kb, int d, b
 // float4 groups this thread stages: group g = i*256 + tid covers row g/8, features
 // (g%8)*4 .. +3 of each slab.  acc[i][j] receives <q[ty*TQ+i], x[col(j)]> with
 // col(j) = tx*4 + j for j < 4 and 64 + tx*4 + (j-4) otherwise (tx = tid%16, ty = tid/16).
+// dtq / dtd: element types of the query and database rows (DT_*), widened to fp32 on load.
 template <int TQ>
-__device__ __forceinline__ void simt_cross_tile(const float* const (&qrow)[SimtTile<TQ>::QL],
-                                                const float* const (&drow)[4], int d, bool vecq,
-                                                bool vecd, float* smem, float (&acc)[TQ][8]) {
+__device__ __forceinline__ void simt_cross_tile(const void* const (&qrow)[SimtTile<TQ>::QL],
+                                                const void* const (&drow)[4], int d, bool vecq,
+                                                bool vecd, float* smem, float (&acc)[TQ][8], int dtq = DT_F32,
+                                                int dtd = DT_F32) {
     using T = SimtTile<TQ>;
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
@@ -54,9 +56,9 @@ __device__ __forceinline__ void simt_cross_tile(const float* const (&qrow)[SimtT
     auto fetch = [&](int slab) {
         const int kb = slab * T::KS + kq;
 #pragma unroll
-        for (int i = 0; i < T::QL; ++i) rq[i] = load4_guard(qrow[i], kb, d, vecq);
+        for (int i = 0; i < T::QL; ++i) rq[i] = load4_guard(qrow[i], kb, d, vecq, dtq);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) rd[i] = load4_guard(drow[i], kb, d, vecd);
+        for (int i = 0; i < 4; ++i) rd[i] = load4_guard(drow[i], kb, d, vecd, dtd);
     };
     auto stash = [&](int buf) {
         float* qs = Qs + buf * T::KS * T::QSTR;

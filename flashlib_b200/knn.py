@@ -36,6 +36,55 @@ def _as_f32_rows(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+_DTYPE_CODES = {torch.float32: _lib.FL_DTYPE_F32, torch.bfloat16: _lib.FL_DTYPE_BF16, torch.float16: _lib.FL_DTYPE_F16}
+
+
+def _as_rows(t: torch.Tensor) -> torch.Tensor:
+    """Rows the kernels read as they are: fp32, bf16 or fp16 (anything else is converted to fp32),
+    last dimension contiguous."""
+    if t.dtype not in _DTYPE_CODES:
+        t = t.float()
+    if t.stride(-1) != 1 or (t.dim() == 2 and t.stride(0) < t.shape[1]):
+        t = t.contiguous()
+    return t
+
+
+# Restatement of the reference's tol -> storage dtype rule (flashlib/linalg/gemm/__init__.py:114-207):
+# among the GEMM variants whose declared residual is <= tol the one with the highest listed throughput
+# is chosen, and only "fp16" / "bf16" name a storage dtype.  fp16 (residual 4e-4, 892 TF) beats bf16
+# (3e-3, 816 TF) whenever both qualify, and tf32 (3e-4, 386 TF) qualifies alone below 4e-4.
+_TOL_VARIANTS = (("fp16", 4e-4, 892.0, torch.float16), ("bf16", 3e-3, 816.0, torch.bfloat16), ("tf32", 3e-4, 386.0, None))
+
+
+def storage_dtype_for(tol: Optional[float]):
+    """16-bit dtype the inputs may be stored in for this ``tol`` (``None``: keep them as given)."""
+    if tol is None or tol <= 0:
+        return None
+    ok = [v for v in _TOL_VARIANTS if v[1] <= tol]
+    if not ok:
+        return None
+    return max(ok, key=lambda v: v[2])[3]
+
+
+_CAST_CACHE: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
+
+
+def _cast_rows_cached(c: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``c.to(dtype)``, kept while ``c`` is alive and unchanged: the database is stored in 16 bits once,
+    and its operand plane is found again on the next call."""
+    key = _plane_key(c) + (dtype,)
+    hit = _CAST_CACHE.get(key)
+    if hit is not None:
+        _CAST_CACHE.move_to_end(key)
+        return hit
+    out = c.to(dtype)
+    _CAST_CACHE[key] = out
+    _evict_when_freed(_CAST_CACHE, key, c)
+    while len(_CAST_CACHE) > _PLANE_CACHE_SIZE:
+        _CAST_CACHE.popitem(last=False)
+    return out
+
+
 def _mode_from(mode: Optional[str]) -> int:
     if mode is None:
         mode = os.environ.get("FLASHLIB_B200_KNN_MODE") or None
@@ -56,8 +105,8 @@ class DbPlane:
         m, d = db.shape
         nbytes = lib.fl_knn_plane_bytes(m, d)
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=db.device)
-        _lib.check(lib.fl_knn_prepare_db_f32(db.data_ptr(), m, d, db.stride(0), self.buf.data_ptr(),
-                                             nbytes, _stream_ptr(db.device)))
+        _lib.check(lib.fl_knn_prepare_db_rows(db.data_ptr(), _DTYPE_CODES[db.dtype], m, d, db.stride(0),
+                                              self.buf.data_ptr(), nbytes, _stream_ptr(db.device)))
         self.key = _plane_key(db)
         self.split_buf = None
 
@@ -71,7 +120,7 @@ class DbPlane:
         if self.split_buf is None:
             lib = _lib.load()
             m, d = db.shape
-            nbytes = lib.fl_knn_split_plane_bytes(m, d)
+            nbytes = lib.fl_knn_split_plane_bytes(m, d) if db.dtype == torch.float32 else 0
             if nbytes == 0 or nbytes > _split_plane_limit():
                 self.split_buf = False
             else:
@@ -92,7 +141,7 @@ def _second_stage_default() -> bool:
 
 
 def _plane_key(db: torch.Tensor):
-    return (db.data_ptr(), tuple(db.shape), db.stride(0), db._version, db.device.index)
+    return (db.data_ptr(), tuple(db.shape), db.stride(0), db._version, db.device.index, db.dtype)
 
 
 def _evict_when_freed(cache, key, t: torch.Tensor) -> None:
@@ -173,8 +222,8 @@ def _defer_status_check(status: torch.Tensor) -> None:
 def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KNN_AUTO,
             row_offset: int = 0, plane: Optional[DbPlane] = None, check_status=True,
             second_stage: Optional[bool] = None):
-    """One 2-D problem through ``fl_knn_f32`` / ``fl_knn_staged_f32``: returns
-    ``(dist fp32 (nq,k), idx int32 (nq,k), info)``.
+    """One 2-D problem through ``fl_knn_f32`` / ``fl_knn_staged_f32`` (fp32 rows) or ``fl_knn_rows``
+    (bf16 / fp16 rows, read as stored): returns ``(dist fp32 (nq,k), idx int32 (nq,k), info)``.
     ``check_status=True`` reads the kernel's status words before returning (one host/device
     round trip; ``info["fallback_rows"]`` and ``info["stage2_rows"]`` are filled), ``"deferred"``
     leaves that to a later call or to ``check_pending()``, ``False`` skips it.
@@ -186,6 +235,8 @@ def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KN
     nq, d = q.shape
     m = db.shape[0]
     dev = q.device
+    if q.dtype != db.dtype or db.dtype not in _DTYPE_CODES:
+        raise TypeError(f"knn_f32 takes q and db of one dtype out of fp32 / bf16 / fp16, got {q.dtype} and {db.dtype}")
     resolved = lib.fl_knn_resolve_mode(nq, m, d, k) if mode == _lib.FL_KNN_AUTO else mode
     if resolved == _lib.FL_KNN_BF16_RERANK and plane is None:
         plane = get_plane(db)
@@ -207,10 +258,10 @@ def knn_f32(q: torch.Tensor, db: torch.Tensor, k: int, *, mode: int = _lib.FL_KN
     else:
         ws_bytes = lib.fl_knn_workspace_bytes(max(nq, 1), m, d, k, resolved)
         ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
-        rc = lib.fl_knn_f32(q.data_ptr(), nq, q.stride(0) if nq else d, db.data_ptr(), m, db.stride(0), d, k,
-                            resolved, plane.ptr if plane is not None else None, row_offset,
-                            out_d.data_ptr(), out_i.data_ptr(), ws.data_ptr(), ws_bytes,
-                            status.data_ptr(), _stream_ptr(dev))
+        rc = lib.fl_knn_rows(q.data_ptr(), nq, q.stride(0) if nq else d, db.data_ptr(), m, db.stride(0), d, k,
+                             _DTYPE_CODES[db.dtype], resolved, plane.ptr if plane is not None else None, row_offset,
+                             out_d.data_ptr(), out_i.data_ptr(), ws.data_ptr(), ws_bytes,
+                             status.data_ptr(), _stream_ptr(dev))
     _lib.check(rc)
     info = {"mode": resolved, "status": status, "second_stage": split is not None}
     if check_status == "deferred" and resolved == _lib.FL_KNN_BF16_RERANK:
@@ -230,9 +281,12 @@ def flash_knn_dispatch(x: torch.Tensor, c: torch.Tensor, k: int, *, tol: Optiona
 
     Parameters follow ``flashlib/primitives/knn/impl.py:199-247``: ``x`` is ``(B, N, D)`` or
     ``(N, D)``, ``c`` has the same rank and dtype, ``backend`` may be ``None`` or one of the
-    reference's names (validated, then ignored: there is one implementation), ``tol`` is
-    accepted for compatibility (fp32 is kept: results are exact either way).  ``mode``
-    (``"exact"`` | ``"bf16"`` | ``None`` = auto) picks the scoring kernel.
+    reference's names (validated, then ignored: there is one implementation).  bf16 / fp16
+    inputs are read as stored (no fp32 copy); ``tol`` follows the reference's rule
+    (``storage_dtype_for``): when it allows 16-bit storage, fp32 inputs are cast to it -- the
+    database once, cached -- and the result is the exact kNN of the stored values, as in the
+    reference (``knn/impl.py:257-261``).  ``mode`` (``"exact"`` | ``"bf16"`` | ``None`` = auto)
+    picks the scoring kernel.
 
     Returns ``(vals, idxs)`` -- fp32 true squared distances ascending and int32 indices --
     or just ``idxs`` with ``return_distances=False``.
@@ -259,10 +313,13 @@ def flash_knn_dispatch(x: torch.Tensor, c: torch.Tensor, k: int, *, tol: Optiona
     m = _mode_from(mode)
     vals = torch.empty((B, N, k), dtype=torch.float32, device=x.device)
     idxs = torch.empty((B, N, k), dtype=torch.int32, device=x.device)
+    target = storage_dtype_for(tol)
     with torch.cuda.device(x.device):
         for b in range(B):
-            qb = _as_f32_rows(x[b])
-            cb = _as_f32_rows(c[b])
+            qb, cb = x[b], c[b]
+            if target is not None and qb.dtype != target:
+                qb, cb = qb.to(target), _cast_rows_cached(cb, target)
+            qb, cb = _as_rows(qb), _as_rows(cb)
             d_b, i_b, _ = knn_f32(qb, cb, k, mode=m, check_status="deferred")
             vals[b] = d_b
             idxs[b] = i_b

@@ -30,6 +30,11 @@ extern "C" {
 #define FL_ETIMEOUT     -4   /* a bounded device-side wait gave up (see status words)    */
 #define FL_EWORKSPACE   -5   /* workspace or plane buffer too small                      */
 
+/* Element types of the caller's rows (argument `dtype` of fl_knn_rows and its helpers). */
+#define FL_DTYPE_F32   0
+#define FL_DTYPE_BF16  1
+#define FL_DTYPE_F16   2
+
 /* kNN modes (argument `mode` of fl_knn_f32 / fl_knn_workspace_bytes). */
 #define FL_KNN_AUTO        -1  /* tensor-core path when supported, else CUDA-core path   */
 #define FL_KNN_EXACT_SIMT   0  /* fp32 CUDA-core scoring + exact re-rank                 */
@@ -107,6 +112,23 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
                    const void* plane, int64_t row_offset,
                    float* out_dist, int32_t* out_idx,
                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
+
+/* fl_knn_f32 for rows stored as fp32, bf16 or fp16 (`dtype` = FL_DTYPE_*, the same for q and */
+/* db; leading dimensions in elements).  The reference runs its kernels on 16-bit inputs as    */
+/* they are, and casts fp32 inputs to 16-bit storage when the caller's `tol` allows it          */
+/* (knn/impl.py:257-261, linalg/gemm/__init__.py:163-183): the database then takes half the     */
+/* memory.  Here the bf16 operand plane is built straight from the 16-bit rows                  */
+/* (fl_knn_prepare_db_rows; bf16 values enter it unrounded), no fp32 copy exists, and the exact */
+/* re-rank and the exact pass widen the stored values to fp32 on load -- which is exact, so the */
+/* result is the exact kNN of the values as stored, distances in fp32.  Workspace as for        */
+/* fl_knn_f32.  No split-plane stage for 16-bit rows.                                           */
+int     fl_knn_prepare_db_rows(const void* db, int dtype, int64_t m, int d, int64_t ld,
+                               void* plane, int64_t plane_bytes, void* stream);
+int     fl_knn_rows(const void* q, int64_t nq, int64_t ldq,
+                    const void* db, int64_t m, int64_t ldb, int d, int k, int dtype, int mode,
+                    const void* plane, int64_t row_offset,
+                    float* out_dist, int32_t* out_idx,
+                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 
 /* fl_knn_f32 (tensor-core mode) with a second tensor-core stage between the bf16 pass and  */
 /* the exact CUDA-core pass.  Rows whose bf16 candidate pool cannot be proven complete are  */

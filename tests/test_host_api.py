@@ -129,3 +129,15 @@ def test_ivf_index_save_and_load_round_trip(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         load_ivf_flat_index(other)
+
+
+def test_tol_to_storage_dtype_follows_the_reference_rule():
+    """Pairs recorded from the reference's ``storage_dtype_for`` (flashlib/linalg/gemm/__init__.py:163-207):
+    fp16 from its declared residual 4e-4 upwards (it out-ranks bf16 by listed throughput wherever both
+    qualify), nothing below (tf32 alone qualifies from 3e-4 and names no storage dtype)."""
+    import torch
+    from flashlib_b200.knn import storage_dtype_for
+    recorded = [(None, None), (0, None), (-1, None), (1e-8, None), (1e-6, None), (2e-4, None), (3e-4, None), (3.5e-4, None),
+                (4e-4, torch.float16), (1e-3, torch.float16), (3e-3, torch.float16), (1e-2, torch.float16), (1.0, torch.float16)]
+    for tol, want in recorded:
+        assert storage_dtype_for(tol) is want, (tol, want)

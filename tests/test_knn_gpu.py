@@ -159,3 +159,41 @@ def test_full_size_properties():
         ref_v, ref_i = oracle.knn_chunked(Q[sub].numpy(), X.numpy(), k, chunk_size=8192)
         res = parity.knn_parity(Q[sub].numpy(), X.numpy(), vals[sub].cpu().numpy(), idxs[sub].cpu().numpy(), ref_i)
         assert res["ok"], res
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("nq,m,d,k,mode", [(300, 70_000, 128, 10, "bf16"), (64, 5_000, 96, 10, "exact"), (200, 90_000, 64, 32, "bf16"),
+                                           (129, 30_001, 100, 5, "bf16"), (33, 2_000, 200, 50, "exact"), (500, 40_000, 128, 10, None)])
+def test_sixteen_bit_rows_are_read_as_stored(dtype, nq, m, d, k, mode):
+    """bf16 / fp16 inputs: no fp32 copy is made; the result is the exact kNN of the stored values
+    (fp64 brute force on them), distances in fp32."""
+    g = torch.Generator().manual_seed(nq + m + d)
+    db = torch.randn(m, d, generator=g).to(dtype).cuda()
+    q = torch.randn(nq, d, generator=g).to(dtype).cuda()
+    vals, idxs = fl.flash_knn(q, db, k, mode=mode)
+    assert vals.dtype == torch.float32 and idxs.dtype == torch.int32
+    qd, dbd = q.double(), db.double()
+    d64 = (qd * qd).sum(-1, keepdim=True) + (dbd * dbd).sum(-1)[None, :] - 2.0 * qd @ dbd.T
+    ref_i = d64.topk(k, dim=1, largest=False).indices.cpu().numpy()
+    res = parity.knn_parity(q.float().cpu().numpy(), db.float().cpu().numpy(), vals.cpu().numpy(), idxs.cpu().numpy(), ref_i)
+    assert res["ok"], res
+    fl.check_pending()
+
+
+def test_tol_stores_the_inputs_in_sixteen_bits():
+    """``tol`` >= 4e-4 selects fp16 storage (the reference's rule): same result as passing fp16 inputs,
+    and the cast database is made once."""
+    from flashlib_b200 import knn as knn_mod
+    g = torch.Generator().manual_seed(3)
+    db = torch.randn(80_000, 128, generator=g).cuda()
+    q = torch.randn(400, 128, generator=g).cuda()
+    v_tol, i_tol = fl.flash_knn(q, db, 10, tol=1e-3)
+    v_16, i_16 = fl.flash_knn(q.half(), db.half(), 10)
+    assert torch.equal(i_tol, i_16) and torch.equal(v_tol, v_16)
+    n_cached = len(knn_mod._CAST_CACHE)
+    fl.flash_knn(q, db, 10, tol=1e-3)
+    assert len(knn_mod._CAST_CACHE) == n_cached
+    v_32, i_32 = fl.flash_knn(q, db, 10, tol=1e-5)      # too tight for 16-bit storage: fp32 kept
+    v_ex, i_ex = fl.flash_knn(q, db, 10)
+    assert torch.equal(i_32, i_ex) and torch.equal(v_32, v_ex)
+    fl.check_pending()
