@@ -49,6 +49,9 @@ SIGNATURES = {
     "fl_knn_prepare_db_rows": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
     "fl_knn_rows": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_int,
                             c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "fl_knn_batch_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int, c_int]),
+    "fl_knn_batch_f32": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "fl_knn_split_plane_bytes": (c_int64, [c_int64, c_int]),
     "fl_knn_prepare_split_f32": (c_int, [c_void_p, c_int64, c_int, c_int64, c_void_p, c_int64, c_void_p]),
     "fl_knn_staged_workspace_bytes": (c_int64, [c_int64, c_int64, c_int, c_int]),

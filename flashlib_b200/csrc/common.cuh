@@ -93,6 +93,7 @@ __device__ __forceinline__ float4 ld_elem4(const void* base, int64_t i, int dt) 
     return make_float4(f16_bits_to_f32((unsigned short)(w.x & 0xffffu)), f16_bits_to_f32((unsigned short)(w.x >> 16)),
                        f16_bits_to_f32((unsigned short)(w.y & 0xffffu)), f16_bits_to_f32((unsigned short)(w.y >> 16)));
 }
+__device__ __forceinline__ int dt_size_dev(int dt) { return dt == DT_F32 ? 4 : 2; }
 // Address of row r (ld in elements).
 __host__ __device__ __forceinline__ const void* row_at(const void* base, int64_t r, int64_t ld, int dt) {
     return static_cast<const char*>(base) + r * ld * (dt == DT_F32 ? 4 : 2);

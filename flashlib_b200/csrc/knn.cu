@@ -8,11 +8,15 @@ namespace fl {
 
 // out[i] = ||x_i||^2 / 2
 // ||x||^2 / 2 per row and (maxnorm_bits, zero-initialised) the largest row norm.
+// (blockIdx.y: problem of a batch, rows bstride elements further, norms n further.)
 __global__ void halfnorm_kernel(const void* __restrict__ x, int64_t n, int d, int64_t ld,
-                                float* __restrict__ out, unsigned int* __restrict__ maxnorm_bits, int dt) {
+                                float* __restrict__ out, unsigned int* __restrict__ maxnorm_bits, int dt,
+                                int64_t bstride = 0) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= n) return;
+    x = static_cast<const char*>(x) + (int64_t)blockIdx.y * bstride * dt_size_dev(dt);
+    out += (int64_t)blockIdx.y * n;
     const void* p = row_at(x, row, ld, dt);
     float s = 0.f;
     for (int c = lane; c < d; c += 32) { const float v = ld_elem(p, c, dt); s += v * v; }
@@ -566,6 +570,70 @@ extern "C" int fl_knn_rows(const void* q, int64_t nq, int64_t ldq, const void* d
                            void* ws, int64_t ws_bytes, int32_t* status, void* stream) {
     return knn_rows_impl("fl_knn_rows", q, nq, ldq, db, m, ldb, d, k, dtype, mode, plane, nullptr, row_offset, out_dist,
                          out_idx, ws, ws_bytes, status, stream);
+}
+
+// ---- batch of small problems, exact mode ---------------------------------------------------
+struct KnnBatchWs { int K1, nsplit; int64_t rows_per_split; int64_t off_hnorm, off_part_sc, off_part_id, off_cnt, bytes; };
+
+static KnnBatchWs knn_batch_plan(int batch, int64_t nq, int64_t m, int d, int k) {
+    KnnBatchWs w{};
+    w.K1 = simt_pool_size(k);
+    // the batch fills the GPU: ranges only as far as one problem alone would want them divided by the batch
+    simt_split_plan(nq * batch, m, w.K1, d, &w.nsplit, &w.rows_per_split);
+    int64_t cur = 0;
+    w.off_hnorm = take(cur, (int64_t)batch * m * 4);
+    w.off_part_sc = take(cur, (int64_t)batch * nq * w.nsplit * w.K1 * 4);
+    w.off_part_id = take(cur, (int64_t)batch * nq * w.nsplit * w.K1 * 4);
+    w.off_cnt = take(cur, 1024);
+    w.bytes = cur;
+    return w;
+}
+
+extern "C" int64_t fl_knn_batch_workspace_bytes(int batch, int64_t nq, int64_t m, int d, int k) {
+    if (batch < 1 || nq < 1 || m < 1 || d < 1 || k < 1 || k > 512) return 0;
+    return knn_batch_plan(batch, nq, m, d, k).bytes;
+}
+
+extern "C" int fl_knn_batch_f32(const float* q, int batch, int64_t nq, int64_t ldq, int64_t q_bstride, const float* db,
+                                int64_t m, int64_t ldb, int64_t db_bstride, int d, int k, float* out_dist, int32_t* out_idx,
+                                void* ws, int64_t ws_bytes, void* stream) {
+    FL_CHECK_ARG(batch >= 1 && batch <= 65535, "fl_knn_batch_f32: batch must be in [1, 65535] (got %d)", batch);
+    int mode = FL_KNN_EXACT_SIMT;
+    int rc = knn_check_args("fl_knn_batch_f32", q, nq, ldq, db, m, ldb, d, k, &mode, nullptr, 0, out_dist, out_idx, ws);
+    if (rc != FL_OK || nq == 0) return rc;
+    FL_CHECK_ARG(q_bstride >= 0 && db_bstride >= 0, "fl_knn_batch_f32: negative batch stride");
+    const KnnBatchWs w = knn_batch_plan(batch, nq, m, d, k);
+    if (ws_bytes < w.bytes) { set_error("fl_knn_batch_f32: workspace %lld < %lld bytes", (long long)ws_bytes, (long long)w.bytes); return FL_EWORKSPACE; }
+    cudaStream_t st = (cudaStream_t)stream;
+    char* base = static_cast<char*>(ws);
+    const int vecq = dt_vec_ok(q, ldq, DT_F32) && q_bstride % 4 == 0;
+    const int vecd = dt_vec_ok(db, ldb, DT_F32) && db_bstride % 4 == 0;
+    const int vec = vecq && vecd && (d % 4 == 0);
+    FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_cnt, 0, 1024, st));
+    float* hnorm = reinterpret_cast<float*>(base + w.off_hnorm);
+    unsigned int* mx = reinterpret_cast<unsigned int*>(base + w.off_cnt) + 128;     // largest row norm of the whole batch
+    halfnorm_kernel<<<dim3((unsigned)ceil_div(m, 8), (unsigned)batch), 256, 0, st>>>(db, m, d, ldb, hnorm, mx, DT_F32, db_bstride);
+    FL_CHECK_LAUNCH();
+    SimtKnnParams sp{};
+    sp.dt = DT_F32;
+    sp.q = q; sp.ldq = ldq; sp.count = nq; sp.db = db; sp.m = m; sp.ldb = ldb; sp.d = d; sp.hnorm = hnorm;
+    sp.K1 = w.K1; sp.cap = simt_pool_cap(w.K1); sp.npl = sp.cap / 32; sp.keep = simt_pool_keep(w.K1, k);
+    sp.nsplit = w.nsplit; sp.rows_per_split = w.rows_per_split;
+    sp.part_sc = reinterpret_cast<float*>(base + w.off_part_sc);
+    sp.part_id = reinterpret_cast<uint32_t*>(base + w.off_part_id);
+    sp.vecq = vecq; sp.vecd = vecd;
+    sp.batch = batch; sp.q_bstride = q_bstride; sp.db_bstride = db_bstride;
+    rc = launch_knn_simt(sp, nq, st);
+    if (rc != FL_OK) return rc;
+    FinalizeParams fp{};
+    fp.dt = DT_F32;
+    fp.q = q; fp.ldq = ldq; fp.count = nq; fp.db = db; fp.m = m; fp.ldb = ldb; fp.d = d; fp.vec = vec;
+    fp.part_sc = sp.part_sc; fp.part_id = sp.part_id; fp.nsplit = w.nsplit; fp.K1 = w.K1;
+    fp.k = k; fp.rerank = simt_pool_keep(w.K1, k); fp.row_offset = 0;
+    fp.out_dist = out_dist; fp.out_idx = out_idx; fp.verify = 1; fp.eps_rel = SIMT_EPS_REL;
+    fp.maxnorm = reinterpret_cast<const float*>(mx);
+    fp.batch = batch; fp.q_bstride = q_bstride; fp.db_bstride = db_bstride;
+    return launch_knn_finalize(fp, nq, st);
 }
 
 extern "C" int64_t fl_knn_seed_floats(int64_t nq) {

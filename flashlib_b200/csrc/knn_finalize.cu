@@ -300,12 +300,46 @@ __global__ void __launch_bounds__(128) knn_finalize_kernel(FinalizeParams p) {
     }
 }
 
+// Batch of independent problems (plain pools of a static scan, fp32 or 16-bit rows): problem
+// blockIdx.y runs the same code on shifted operands, pools and outputs.
+template <int NPL1>
+__global__ void __launch_bounds__(128) knn_finalize_batch_kernel(FinalizeParams p) {
+    const int64_t b = blockIdx.y;
+    p.q = static_cast<const char*>(p.q) + b * p.q_bstride * dt_size_dev(p.dt);
+    p.db = static_cast<const char*>(p.db) + b * p.db_bstride * dt_size_dev(p.dt);
+    const int64_t pools = p.count * p.nsplit * (int64_t)p.K1;
+    p.part_sc += b * pools;
+    p.part_id += b * pools;
+    p.out_dist += b * p.count * p.k;
+    p.out_idx += b * p.count * p.k;
+    const int64_t slot = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (slot < p.count) finalize_slot<NPL1, false, false, false>(p, slot, p.count);
+}
+
 int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
     if (max_slots <= 0) return FL_OK;
     int64_t blocks = ceil_div(max_slots, 4);
     if (p.count_dev != nullptr && blocks > (int64_t)sm_count() * 32) blocks = (int64_t)sm_count() * 32;
     const unsigned grid = (unsigned)blocks;
     const bool indirect = p.pool_row != nullptr;
+    if (p.batch > 1) {
+        if (p.count_dev != nullptr || p.qlist != nullptr || indirect || p.part_tau != nullptr || p.fb_count != nullptr ||
+            p.dyn_blocks > 0 || p.batch > 65535) {
+            set_error("batched finalisation: plain pools of a static scan only, at most 65535 problems");
+            return FL_EINVAL;
+        }
+        const dim3 bgrid((unsigned)blocks, (unsigned)p.batch);
+        switch (p.K1 / 32) {
+            case 1: knn_finalize_batch_kernel<1><<<bgrid, 128, 0, st>>>(p); break;
+            case 2: knn_finalize_batch_kernel<2><<<bgrid, 128, 0, st>>>(p); break;
+            case 4: knn_finalize_batch_kernel<4><<<bgrid, 128, 0, st>>>(p); break;
+            case 8: knn_finalize_batch_kernel<8><<<bgrid, 128, 0, st>>>(p); break;
+            case 16: knn_finalize_batch_kernel<16><<<bgrid, 128, 0, st>>>(p); break;
+            default: set_error("unsupported pool size %d", p.K1); return FL_EUNSUPPORTED;
+        }
+        FL_CHECK_LAUNCH();
+        return FL_OK;
+    }
     if (indirect && (p.id_map == nullptr || p.K1 != 128)) {
         set_error("finalisation: pool indirection goes with an id map and 128 published entries per pool");
         return FL_EINVAL;

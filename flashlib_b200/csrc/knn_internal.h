@@ -33,6 +33,10 @@ struct SimtKnnParams {
     int ivf; int nlist; int nprobe; int bq_items;
     const int* item_off; const int* pair_off; const int* sorted_pair;
     const int64_t* list_offsets;
+    // batch > 1 (static geometry only): grid.z walks `batch` independent problems of the same shape;
+    // problem b reads q + b * q_bstride and db + b * db_bstride (elements), hnorm + b * m, and
+    // writes the pools of its `count` slots after those of problem b - 1.
+    int batch; int64_t q_bstride, db_bstride;
     // Optional f32 [queries], -inf initialised: running threshold of every query, shared by the
     // blocks that scan its probed lists.  A block starts from it and raises it to its own
     // pool's threshold when it ends, so lists scanned later start warm.
@@ -92,6 +96,10 @@ struct FinalizeParams {
     // Optional: unproven queries go to this list first (the split-plane stage), and to the exact-path
     // list only when it is absent or full
     int* next_count; int* next_list; int next_cap;
+    // batch > 1 (slot count known at launch, no lists): grid.y walks `batch` independent problems of
+    // `count` slots each; problem b reads q + b * q_bstride and db + b * db_bstride (elements), its
+    // pools and its outputs follow those of problem b - 1.
+    int batch; int64_t q_bstride, db_bstride;
 };
 // Finalisation of the large-k tensor-core pools (one block per query).
 int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st);

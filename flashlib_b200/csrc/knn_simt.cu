@@ -185,6 +185,21 @@ __global__ void __launch_bounds__(256) knn_simt_kernel(SimtKnnParams p) {
     }
 }
 
+// Batch of independent problems of one shape (static geometry): problem blockIdx.z runs the same
+// code on shifted operands and pools.
+template <int TQ>
+__global__ void __launch_bounds__(256) knn_simt_batch_kernel(SimtKnnParams p) {
+    extern __shared__ __align__(16) float smem[];
+    const int64_t b = blockIdx.z;
+    p.q = static_cast<const char*>(p.q) + b * p.q_bstride * dt_size_dev(p.dt);
+    p.db = static_cast<const char*>(p.db) + b * p.db_bstride * dt_size_dev(p.dt);
+    p.hnorm += b * p.m;
+    const int64_t pools = p.count * p.nsplit * (int64_t)p.K1;
+    p.part_sc += b * pools;
+    p.part_id += b * pools;
+    knn_simt_block<TQ>(p, blockIdx.x, blockIdx.y, smem);
+}
+
 template <int TQ>
 static size_t simt_smem_bytes(int cap) {
     using T = SimtTile<TQ>;
@@ -223,7 +238,11 @@ static int launch_simt_t(const SimtKnnParams& p, int64_t max_slots, cudaStream_t
     FL_CHECK_CUDA(cudaFuncSetAttribute(knn_simt_kernel<TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     dim3 grid(p.ivf ? (unsigned)max_slots : (unsigned)ceil_div(max_slots, SimtTile<TQ>::BQ),
-              (unsigned)p.nsplit);
+              (unsigned)p.nsplit, (unsigned)(p.batch > 1 ? p.batch : 1));
+    if (p.batch > 1 && (p.ivf || p.dyn_blocks > 0 || p.count_dev != nullptr || p.qlist != nullptr || p.batch > 65535)) {
+        set_error("batched CUDA-core scan: static geometry only, at most 65535 problems");
+        return FL_EINVAL;
+    }
     if (p.dyn_blocks > 0) {
         if (p.ivf || p.dyn_bq != SimtTile<TQ>::BQ || p.count_dev == nullptr) {
             set_error("dynamic split: plan made for %d queries per block, kernel uses %d", p.dyn_bq, SimtTile<TQ>::BQ);
@@ -232,6 +251,12 @@ static int launch_simt_t(const SimtKnnParams& p, int64_t max_slots, cudaStream_t
         // (p.dyn_blocks stays the figure the range split and the pool storage are planned with)
         const int launched = 4 * sm_count();
         grid = dim3((unsigned)(p.dyn_blocks < launched ? p.dyn_blocks : launched), 1);
+    }
+    if (p.batch > 1) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_simt_batch_kernel<TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        knn_simt_batch_kernel<TQ><<<grid, 256, smem, st>>>(p);
+        FL_CHECK_LAUNCH();
+        return FL_OK;
     }
     knn_simt_kernel<TQ><<<grid, 256, smem, st>>>(p);
     FL_CHECK_LAUNCH();

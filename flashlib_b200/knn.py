@@ -314,6 +314,22 @@ def flash_knn_dispatch(x: torch.Tensor, c: torch.Tensor, k: int, *, tol: Optiona
     vals = torch.empty((B, N, k), dtype=torch.float32, device=x.device)
     idxs = torch.empty((B, N, k), dtype=torch.int32, device=x.device)
     target = storage_dtype_for(tol)
+    lib = _lib.load()
+    batched = (B > 1 and N > 0 and target is None and x.dtype == torch.float32 and m != _lib.FL_KNN_BF16_RERANK
+               and lib.fl_knn_resolve_mode(N, M, D, k) == _lib.FL_KNN_EXACT_SIMT
+               and x.stride(2) == 1 and c.stride(2) == 1 and x.stride(1) >= D and c.stride(1) >= D)
+    if batched:
+        # many small problems: one launch sequence for the whole batch
+        _lib.require_device()
+        with torch.cuda.device(x.device):
+            ws_bytes = lib.fl_knn_batch_workspace_bytes(B, N, M, D, k)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+            _lib.check(lib.fl_knn_batch_f32(x.data_ptr(), B, N, x.stride(1), x.stride(0), c.data_ptr(), M, c.stride(1),
+                                            c.stride(0), D, k, vals.data_ptr(), idxs.data_ptr(), ws.data_ptr(), ws_bytes,
+                                            _stream_ptr(x.device)))
+        if not return_distances:
+            return idxs
+        return vals, idxs
     with torch.cuda.device(x.device):
         for b in range(B):
             qb, cb = x[b], c[b]

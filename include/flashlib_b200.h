@@ -113,6 +113,16 @@ int     fl_knn_f32(const float* q, int64_t nq, int64_t ldq,
                    float* out_dist, int32_t* out_idx,
                    void* ws, int64_t ws_bytes, int32_t* status, void* stream);
 
+/* A batch of independent problems of one shape in one call (the reference's kernels take  */
+/* the batch on a grid axis, knn/triton/insert.py:49; its callers are many small problems, */
+/* where a launch per problem is the whole cost).  Problem b reads q + b * q_bstride and    */
+/* db + b * db_bstride (elements) and writes out_dist / out_idx [batch][nq][k].  Exact      */
+/* CUDA-core path; large problems are better served by one fl_knn_f32 call each.            */
+int64_t fl_knn_batch_workspace_bytes(int batch, int64_t nq, int64_t m, int d, int k);
+int     fl_knn_batch_f32(const float* q, int batch, int64_t nq, int64_t ldq, int64_t q_bstride,
+                         const float* db, int64_t m, int64_t ldb, int64_t db_bstride, int d, int k,
+                         float* out_dist, int32_t* out_idx, void* ws, int64_t ws_bytes, void* stream);
+
 /* fl_knn_f32 for rows stored as fp32, bf16 or fp16 (`dtype` = FL_DTYPE_*, the same for q and */
 /* db; leading dimensions in elements).  The reference runs its kernels on 16-bit inputs as    */
 /* they are, and casts fp32 inputs to 16-bit storage when the caller's `tol` allows it          */

@@ -197,3 +197,25 @@ def test_tol_stores_the_inputs_in_sixteen_bits():
     v_ex, i_ex = fl.flash_knn(q, db, 10)
     assert torch.equal(i_32, i_ex) and torch.equal(v_32, v_ex)
     fl.check_pending()
+
+
+@pytest.mark.parametrize("B,N,M,d,k", [(16, 200, 300, 2, 5), (16, 257, 1000, 8, 10), (64, 100, 256, 4, 1), (3, 500, 5000, 33, 40)])
+def test_batched_small_problems_in_one_call(B, N, M, d, k):
+    """B > 1: one launch sequence for the whole batch (problem b on grid axis b), each item equal to
+    the oracle on that item alone; strided batches (a slice of a larger tensor) included."""
+    g = torch.Generator().manual_seed(B * 1000 + M)
+    big_c = torch.randn(B, M + 7, d + 4, generator=g).cuda()
+    c = big_c[:, 3:3 + M, :d] if d % 4 == 0 else big_c[:, 3:3 + M, :d].contiguous()
+    x = torch.randn(B, N, d, generator=g).cuda()
+    lib = _lib.load()
+    before = lib.fl_launch_count()
+    vals, idxs = fl.flash_knn(x, c, k)
+    launches = lib.fl_launch_count() - before
+    assert launches <= 4, launches                      # norms, scan, finalisation: not 3 per item
+    assert vals.shape == (B, N, k) and idxs.dtype == torch.int32
+    for b in range(B):
+        _, ref_i = oracle.knn_naive(x[b].cpu().numpy(), c[b].cpu().numpy(), k)
+        res = parity.knn_parity(x[b].cpu().numpy(), c[b].cpu().numpy(), vals[b].cpu().numpy(), idxs[b].cpu().numpy(), ref_i)
+        assert res["ok"], (b, res)
+    only_idx = fl.flash_knn(x, c, k, return_distances=False)
+    assert torch.equal(only_idx, idxs)
