@@ -119,8 +119,8 @@ def kmeans_largeN(x: torch.Tensor, n_clusters: int, max_iters: int = 100, tol: f
             tot_s = sums[0] + sums[1]
             tot_c = cnts[0] + cnts[1]
             if multi:
-                dist.all_reduce(tot_s, op=dist.ReduceOp.SUM, group=group)
-                dist.all_reduce(tot_c, op=dist.ReduceOp.SUM, group=group)
+                from .sharded import all_reduce_sums_counts
+                all_reduce_sums_counts(tot_s, tot_c, group)
             new, shift = km.triton_centroid_finalize(tot_s, tot_c, cur[None])
             cur = new[0].float().contiguous()
             if verbose:

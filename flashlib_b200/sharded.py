@@ -290,12 +290,30 @@ def sharded_knn(q: torch.Tensor, db_shard: Optional[torch.Tensor], k: int, *, ro
     return out_d, out_i
 
 
+def all_reduce_sums_counts(sums: torch.Tensor, cnts: torch.Tensor, group=None) -> None:
+    """Sums ``(..., K, D)`` fp32 and counts ``(..., K)`` int32 over the ranks in ONE all-reduce, in
+    place.  The counts ride in the same fp32 buffer as two columns, ``cnt // 4096`` and
+    ``cnt % 4096``: both stay below 2^24 after the reduction for any int32 count and any world
+    size in use (<= 4096 ranks), so the sum of integers is exact."""
+    assert sums.is_contiguous() and cnts.is_contiguous(), "all_reduce_sums_counts works in place"
+    K, D = sums.shape[-2], sums.shape[-1]
+    flat_s = sums.reshape(-1, K, D)
+    flat_c = cnts.reshape(-1, K)
+    buf = torch.empty((flat_s.shape[0], K, D + 2), dtype=torch.float32, device=sums.device)
+    buf[..., :D] = flat_s
+    buf[..., D] = torch.div(flat_c, 4096, rounding_mode="floor").to(torch.float32)
+    buf[..., D + 1] = (flat_c % 4096).to(torch.float32)
+    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+    flat_s.copy_(buf[..., :D])
+    flat_c.copy_((buf[..., D].to(torch.int64) * 4096 + buf[..., D + 1].to(torch.int64)).to(cnts.dtype))
+
+
 def sharded_kmeans(x_shard: torch.Tensor, n_clusters: int, *, max_iters: int = 100, tol: float = 0.0,
                    init_centroids: torch.Tensor, group=None,
                    assign_fn: Optional[Callable] = None, update_fn: Optional[Callable] = None,
                    finalize_fn: Optional[Callable] = None):
     """Lloyd k-means over row-sharded samples.  ``init_centroids`` ``(K, D)`` must be identical
-    on every rank.  Per iteration: local assignment, local sums/counts, all-reduce of both,
+    on every rank.  Per iteration: local assignment, local sums/counts, one all-reduce of both (a fused buffer),
     identical finalisation on every rank.  Returns ``(labels of this shard int32, centroids,
     iterations)``; the loop and its return convention follow
     ``flashlib/primitives/kmeans/triton/kmeans.py:117-153``."""
@@ -319,8 +337,7 @@ def sharded_kmeans(x_shard: torch.Tensor, n_clusters: int, *, max_iters: int = 1
         labels = assign_fn(x_shard, cur)
         sums, cnts = update_fn(x_shard, labels, cur)
         if multi:
-            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
-            dist.all_reduce(cnts, op=dist.ReduceOp.SUM, group=group)
+            all_reduce_sums_counts(sums, cnts, group)
         new, shift = finalize_fn(sums, cnts, cur)
         cur = new
         if tol > 0.0 and float(shift.max()) < tol:

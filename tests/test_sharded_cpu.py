@@ -233,6 +233,12 @@ def _kmeans_worker(rank, world, port, out):
                                                    assign_fn=assign, update_fn=update, finalize_fn=finalize)
     ref_l, ref_c, ref_n = oracle.kmeans(x.numpy(), 12, max_iters=5, init_centroids=init.numpy())
     ok = n_iter == ref_n and np.array_equal(labels.numpy(), ref_l[s:e]) and np.allclose(cents.numpy(), ref_c, rtol=1e-4, atol=1e-5)
+    # the fused all-reduce carries integer counts exactly, beyond what one fp32 holds (2^24)
+    sums = torch.full((2, 3, 5), float(rank + 1))
+    cnts = torch.tensor([[300_000_007, 16_777_217, 0], [5, 4095, 4096]], dtype=torch.int32) + rank * 700_000_001
+    sharded.all_reduce_sums_counts(sums, cnts, None)
+    want = torch.tensor([[300_000_007, 16_777_217, 0], [5, 4095, 4096]], dtype=torch.int64) * world + 700_000_001 * sum(range(world))
+    ok = ok and torch.equal(cnts.to(torch.int64), want) and torch.all(sums == float(sum(range(1, world + 1)))).item()
     out[rank] = bool(ok)
     dist.destroy_process_group()
 
