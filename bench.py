@@ -292,13 +292,85 @@ def _reference_gpu_child(dtype_name: str, backend):
     print(json.dumps(out), flush=True)
 
 
+def _reference_gpu_child_other(which: str, dtype_name: str):
+    """Same for the other two configurations: `kmeans` = the reference's `flash_kmeans` on 1,000,000 x 128,
+    K = 1024, 20 Lloyd iterations from the first K rows; `ivf` = its `IVFFlat(nlist=1024, nprobe=16,
+    niter=10)` fitted and searched with 10,000 queries, k = 10.  Quality beside the time: inertia
+    against this library's run from the same start; recall@10 against this library's exact kNN."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    out = {"impl": "reference-gpu", "workload": {"kmeans": "kmeans_1m", "ivf": "ivf_1m"}[which], "dtype": dtype_name}
+    if not os.path.isdir(os.path.join(ref_dir, "flashlib")):
+        out["unavailable"] = "baseline/_ref holds no installed reference"
+        print(json.dumps(out), flush=True)
+        return
+    import flashlib_b200 as ours
+    from flashlib_b200 import synthetic
+    sys.path.insert(0, ref_dir)
+    try:
+        import flashlib as theirs
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"import of the reference failed: {type(e).__name__}: {e}"[:300]
+        print(json.dumps(out), flush=True)
+        return
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16}[dtype_name]
+    try:
+        if which == "kmeans":
+            cfg = synthetic.CONFIGS["kmeans_1m"]
+            X, _ = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"])
+            Xd = X.cuda()
+            init = Xd[:cfg["K"]].clone()
+
+            def inertia(c):
+                lab = ours.euclid_assign_triton(Xd[None], c.float().reshape(1, cfg["K"], -1))[0].long()
+                return float(((Xd - c.float().reshape(cfg["K"], -1)[lab]) ** 2).sum())
+            _, c_ours, _ = ours.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init)
+            ms_ours = _time_steps(lambda: ours.flash_kmeans(Xd, cfg["K"], max_iters=cfg["iters"], init_centroids=init), 3, 1)
+            xr, ir = Xd.to(dt), init.to(dt)
+            run = lambda: theirs.flash_kmeans(xr, cfg["K"], max_iters=cfg["iters"], tol=0.0, init_centroids=ir)   # noqa: E731
+            t0 = time.perf_counter()
+            _, c_ref, _ = run()
+            torch.cuda.synchronize()
+            out["first_call_s"] = time.perf_counter() - t0
+            ms = _time_steps(run, 3, 1)
+            out.update({"ms_per_step": ms, "unit": "ms per 20 Lloyd iterations", "ours_ms_per_step": ms_ours,
+                        "inertia_over_ours": inertia(c_ref) / inertia(c_ours)})
+        else:
+            cfg = synthetic.CONFIGS["ivf_1m"]
+            X, Q = synthetic.mixture(cfg["n"], cfg["d"], cfg["n_comp"], cfg["seed"], nq=cfg["nq"], clamp=True)
+            Xd, Qd = X.cuda(), Q.cuda()
+            _, exact_i = ours.flash_knn(Qd[:2000], Xd, cfg["k"])
+            mine = ours.IVFFlat(nlist=cfg["nlist"], nprobe=cfg["nprobe"], niter=10, seed=cfg["seed"]).fit(Xd)
+            ms_ours = _time_steps(lambda: mine.kneighbors(Qd, cfg["k"]), 5, 2)
+            _, i_ours = mine.kneighbors(Qd, cfg["k"])
+            xr, qr = Xd.to(dt), Qd.to(dt)
+            t0 = time.perf_counter()
+            ref = theirs.IVFFlat(nlist=cfg["nlist"], nprobe=cfg["nprobe"], niter=10, seed=cfg["seed"]).fit(xr)
+            torch.cuda.synchronize()
+            out["build_s_first_call"] = time.perf_counter() - t0
+            _, i_ref = ref.kneighbors(qr, cfg["k"])
+            torch.cuda.synchronize()
+            ms = _time_steps(lambda: ref.kneighbors(qr, cfg["k"]), 5, 2)
+
+            def recall(i_):
+                a, b = i_[:2000].cpu().numpy(), exact_i.cpu().numpy()
+                return float(np.mean([len(set(r.tolist()) & set(t.tolist())) / cfg["k"] for r, t in zip(a, b)]))
+            out.update({"ms_per_step": ms, "unit": "ms per 10,000 queries", "ours_ms_per_step": ms_ours,
+                        "recall_at_10_vs_exact": recall(i_ref), "ours_recall_at_10_vs_exact": recall(i_ours)})
+    except Exception as e:  # noqa: BLE001
+        out["unavailable"] = f"the reference did not run: {type(e).__name__}: {e}"[:300]
+    print(json.dumps(out), flush=True)
+
+
 def run_reference_gpu(args):
     """The reference's own GPU kernels on this box, beside ours: every leg in a child process with a
     time limit (a leg that does not come back is reported, not retried)."""
-    legs = [("fp32", "triton"), ("bf16", "triton"), ("bf16", None)]
+    legs = [("fp32", "triton"), ("bf16", "triton"), ("bf16", None), ("fp32", "kmeans"), ("bf16", "kmeans"), ("fp32", "ivf")]
     if args.ref_leg:
         d_, b_ = args.ref_leg.split(":")
-        _reference_gpu_child(d_, None if b_ == "auto" else b_)
+        if b_ in ("kmeans", "ivf"):
+            _reference_gpu_child_other(b_, d_)
+        else:
+            _reference_gpu_child(d_, None if b_ == "auto" else b_)
         return
     for d_, b_ in legs:
         cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--ref-leg", f"{d_}:{b_ or 'auto'}"]

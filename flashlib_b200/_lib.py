@@ -89,6 +89,8 @@ SIGNATURES = {
                                              c_void_p, c_void_p]),
     "fl_kmeans_update_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int,
                                      c_void_p, c_void_p, c_void_p]),
+    "fl_kmeans_update_delta_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_void_p, c_void_p]),
     "fl_kmeans_assign_batch_workspace_bytes": (c_int64, [c_int, c_int64, c_int, c_int]),
     "fl_kmeans_assign_batch_f32": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int, c_int64, c_int64,
                                            c_int, c_void_p, c_void_p, c_int64, c_void_p]),

@@ -197,6 +197,54 @@ __global__ void kmeans_update_vec_kernel(const float* __restrict__ x, int64_t n,
     flush(cur, run);
 }
 
+// Incremental form of the update: sums and counts already hold the result for the labels in `prev`;
+// only the points whose label differs from it are touched -- their row is taken out of the old
+// cluster's sum and added to the new one's -- and `prev` is brought up to date.  One warp per 32
+// consecutive points: the lanes compare the labels, then the warp handles the changed points one
+// by one with all lanes across the row.  After the first Lloyd iterations under 1 % of the points
+// change sides, so this reads the two label arrays and a few rows instead of every row.
+__global__ void kmeans_update_delta_kernel(const float* __restrict__ x, int64_t n, int64_t ldx, int d,
+                                           const int32_t* __restrict__ labels, int32_t* __restrict__ prev, int K,
+                                           float* __restrict__ sums, int32_t* __restrict__ cnts, int vec) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t base = (((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 32; base < n; base += nwarps * 32) {
+        const int64_t r = base + lane;
+        int lab = -1, old = -1;
+        if (r < n) {
+            lab = __ldg(labels + r);
+            old = prev[r];
+            if (lab < 0 || lab >= K) lab = -1;
+            if (old < 0 || old >= K) old = -1;
+            if (lab != old) prev[r] = lab;
+        }
+        unsigned changed = __ballot_sync(FULL_MASK, lab != old);
+        while (changed) {
+            const int src = __ffs(changed) - 1;
+            changed &= changed - 1;
+            const int to = __shfl_sync(FULL_MASK, lab, src), from = __shfl_sync(FULL_MASK, old, src);
+            const float* p = x + (base + src) * ldx;
+            if (vec) {
+                for (int c = lane * 4; c < d; c += 128) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(p + c));
+                    if (from >= 0) atomicAdd(reinterpret_cast<float4*>(sums + (int64_t)from * d + c), make_float4(-v.x, -v.y, -v.z, -v.w));
+                    if (to >= 0) atomicAdd(reinterpret_cast<float4*>(sums + (int64_t)to * d + c), v);
+                }
+            } else {
+                for (int c = lane; c < d; c += 32) {
+                    const float v = __ldg(p + c);
+                    if (from >= 0) atomicAdd(sums + (int64_t)from * d + c, -v);
+                    if (to >= 0) atomicAdd(sums + (int64_t)to * d + c, v);
+                }
+            }
+            if (lane == 0) {
+                if (from >= 0) atomicAdd(cnts + from, -1);
+                if (to >= 0) atomicAdd(cnts + to, 1);
+            }
+        }
+    }
+}
+
 // One block per centroid.
 __global__ void __launch_bounds__(128) kmeans_finalize_kernel(const float* __restrict__ sums,
                                                               const int32_t* __restrict__ cnts,
@@ -362,6 +410,22 @@ extern "C" int fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int 
     FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_f32: bad shape");
     FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_f32: null pointer");
     return kmeans_update_impl(x, n, ldx, d, labels, K, sums, cnts, n > 0 ? n : 1, K, (cudaStream_t)stream);
+}
+
+extern "C" int fl_kmeans_update_delta_f32(const float* x, int64_t n, int64_t ldx, int d, const int32_t* labels,
+                                          int32_t* prev_labels, int K, float* sums, int32_t* cnts, void* stream) {
+    FL_CHECK_ARG(n >= 0 && K >= 1 && d >= 1 && ldx >= d, "fl_kmeans_update_delta_f32: bad shape");
+    FL_CHECK_ARG(sums && cnts, "fl_kmeans_update_delta_f32: null pointer");
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(x && labels && prev_labels, "fl_kmeans_update_delta_f32: null pointer");
+    const int vec = d % 4 == 0 && ldx % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                    ((reinterpret_cast<uintptr_t>(sums) & 15) == 0);
+    int64_t blocks = ceil_div(ceil_div(n, 32), 8);
+    if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+    kmeans_update_delta_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(x, n, ldx, d, labels, prev_labels, K, sums,
+                                                                                  cnts, vec);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
 }
 
 extern "C" int fl_kmeans_update_batch_f32(const float* x, int batch, int64_t n, int64_t ldx, int d, const int32_t* labels,

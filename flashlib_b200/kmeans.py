@@ -189,16 +189,46 @@ def triton_centroid_finalize(sums: torch.Tensor, cnts: torch.Tensor, old_centroi
     return out, shift
 
 
+def centroid_update_delta(x: torch.Tensor, cluster_ids: torch.Tensor, prev_ids: torch.Tensor,
+                          centroid_sums: torch.Tensor, centroid_cnts: torch.Tensor) -> None:
+    """Brings ``centroid_sums (1,K,D)`` / ``centroid_cnts (1,K)`` from the labels in ``prev_ids``
+    to those in ``cluster_ids`` by moving only the rows whose label changed, and copies the labels
+    into ``prev_ids`` (``fl_kmeans_update_delta_f32``).  ``x`` is ``(1, N, D)`` fp32."""
+    lib = _lib.load()
+    xb = x[0]
+    assert xb.dtype == torch.float32 and xb.stride(1) == 1
+    assert cluster_ids.dtype == torch.int32 and prev_ids.dtype == torch.int32
+    assert cluster_ids.is_contiguous() and prev_ids.is_contiguous() and centroid_sums.is_contiguous()
+    K, D = centroid_sums.shape[1], centroid_sums.shape[2]
+    with torch.cuda.device(x.device):
+        _lib.check(lib.fl_kmeans_update_delta_f32(xb.data_ptr(), xb.shape[0], xb.stride(0), D, cluster_ids.data_ptr(),
+                                                  prev_ids.data_ptr(), K, centroid_sums.data_ptr(),
+                                                  centroid_cnts.data_ptr(), _stream_ptr(x.device)))
+
+
+# Lloyd iterations between two full recomputations of the sums when they are maintained
+# incrementally: bounds the rounding drift of adding and taking out rows.
+DELTA_REFRESH = 8
+
+
 def triton_lloyd_centroid_step_euclid(x: torch.Tensor, cluster_ids: torch.Tensor, old_centroids: torch.Tensor,
                                       *, sums_buf: Optional[torch.Tensor] = None,
                                       cnts_buf: Optional[torch.Tensor] = None,
                                       new_buf: Optional[torch.Tensor] = None,
-                                      shift_buf: Optional[torch.Tensor] = None, **_ignored):
+                                      shift_buf: Optional[torch.Tensor] = None,
+                                      prev_ids: Optional[torch.Tensor] = None, refresh: bool = True, **_ignored):
     """One centroid step: sums/counts, finalize, max shift
     (``flashlib/primitives/kmeans/triton/update.py:501-554``).  Returns
-    ``(new_centroids, cluster_ids, max_shift)`` with ``max_shift`` a 0-d device tensor."""
-    sums_buf, cnts_buf = triton_centroid_update_euclid(
-        x, cluster_ids, old_centroids, centroid_sums=sums_buf, centroid_cnts=cnts_buf, calculate_new=False)
+    ``(new_centroids, cluster_ids, max_shift)`` with ``max_shift`` a 0-d device tensor.
+    With ``prev_ids`` (B = 1; the labels ``sums_buf`` / ``cnts_buf`` currently stand for) and
+    ``refresh=False`` the sums are brought up to date from the changed labels only."""
+    if prev_ids is not None and not refresh and x.shape[0] == 1 and x.dtype == torch.float32:
+        centroid_update_delta(x, cluster_ids, prev_ids, sums_buf, cnts_buf)
+    else:
+        sums_buf, cnts_buf = triton_centroid_update_euclid(
+            x, cluster_ids, old_centroids, centroid_sums=sums_buf, centroid_cnts=cnts_buf, calculate_new=False)
+        if prev_ids is not None:
+            prev_ids.copy_(cluster_ids)
     new_centroids, shift_per_k = triton_centroid_finalize(sums_buf, cnts_buf, old_centroids,
                                                           out=new_buf, shift=shift_buf)
     max_shift = shift_per_k.amax(dim=-1).amax()
@@ -231,11 +261,17 @@ def batch_kmeans_Euclid(x: torch.Tensor, n_clusters: int, max_iters: int = 100, 
     cnts_buf = torch.empty((B, K), device=x.device, dtype=torch.int32)
     shift_buf = torch.empty((B, K), device=x.device, dtype=torch.float32)
     cluster_ids = torch.empty((B, N), device=x.device, dtype=torch.int32)
+    # B = 1: the sums are kept from iteration to iteration and only the rows whose label changed are
+    # moved between them (after the first iterations under 1 % of the points); every
+    # DELTA_REFRESH-th iteration recomputes them from all rows
+    incremental = B == 1 and x32.stride(2) == 1 and os.environ.get("FLASHLIB_B200_KMEANS_DELTA", "1") != "0"
+    prev_ids = torch.empty((B, N), device=x.device, dtype=torch.int32) if incremental else None
     it = 0
     for it in range(max_iters):
         euclid_assign_triton(x32, cur, out=cluster_ids)
         _, _, max_shift = triton_lloyd_centroid_step_euclid(
-            x32, cluster_ids, cur, sums_buf=sums_buf, cnts_buf=cnts_buf, new_buf=nxt, shift_buf=shift_buf)
+            x32, cluster_ids, cur, sums_buf=sums_buf, cnts_buf=cnts_buf, new_buf=nxt, shift_buf=shift_buf,
+            prev_ids=prev_ids, refresh=(it % DELTA_REFRESH == 0))
         if verbose:
             print(f"Iter {it}, center shift: {max_shift.item():.6f}")
         cur, nxt = nxt, cur

@@ -296,6 +296,14 @@ int     fl_kmeans_assign_noalloc_f32(const float* x, int64_t n, int64_t ldx,
 int     fl_kmeans_update_f32(const float* x, int64_t n, int64_t ldx, int d,
                              const int32_t* labels, int K,
                              float* sums, int32_t* cnts, void* stream);
+/* Incremental form for the Lloyd loop (no counterpart in the reference, which re-reads x    */
+/* every iteration, kmeans/triton/update.py:313-384): sums / cnts hold the result for the   */
+/* labels in prev_labels [n]; the rows of the points whose label changed are moved from the */
+/* old cluster's sum to the new one's, and prev_labels is brought up to date.  Same sums up */
+/* to fp32 rounding; a caller refreshes them with fl_kmeans_update_f32 now and then.        */
+int     fl_kmeans_update_delta_f32(const float* x, int64_t n, int64_t ldx, int d,
+                                   const int32_t* labels, int32_t* prev_labels, int K,
+                                   float* sums, int32_t* cnts, void* stream);
 /* Batched forms for many small problems at once (the reference's kernels take the batch  */
 /* on a grid axis, kmeans/triton/assign.py:1028-1129; its IVF-PQ build runs B = m           */
 /* sub-quantisers of 2-8 features each, ivf_pq/triton/build.py:41-70): `batch` problems of  */

@@ -179,3 +179,46 @@ def test_batched_small_problems_match_the_oracle_per_item(B, n, d, K):
         rl, rc, _ = oracle.kmeans(x[b].numpy(), K, max_iters=3, init_centroids=c[b].numpy())
         assert (ids[b].cpu().numpy() == rl).mean() > 0.999
         assert parity.rel_close(cents[b].cpu().numpy(), rc, rel=1e-3, atol=1e-4)
+
+
+@pytest.mark.parametrize("n,d,K", [(200_000, 64, 256), (50_001, 100, 37), (30_000, 7, 16)])
+def test_incremental_update_equals_the_full_one(n, d, K):
+    """Sums maintained by moving only the rows whose label changed: counts identical, sums equal to
+    the full recomputation up to fp32 rounding, labels outside [0, K) ignored, prev brought up to date."""
+    from flashlib_b200 import kmeans as km
+    g = torch.Generator().manual_seed(n + K)
+    x = torch.randn(1, n, d, generator=g).cuda()
+    a = torch.randint(0, K, (1, n), generator=g, dtype=torch.int32).cuda()
+    b = a.clone()
+    pick = torch.randperm(n, generator=g)[: n // 20].cuda()
+    b[0, pick] = torch.randint(0, K, (pick.numel(),), generator=g, dtype=torch.int32).cuda()
+    b[0, pick[:5]] = -1                                         # a few points drop out altogether
+    cents = torch.zeros(1, K, d, device="cuda")
+    sums, cnts = km.triton_centroid_update_euclid(x, a, cents, calculate_new=False)
+    prev = a.clone()
+    km.centroid_update_delta(x, b, prev, sums, cnts)
+    want_s, want_c = km.triton_centroid_update_euclid(x, b, cents, calculate_new=False)
+    assert torch.equal(cnts, want_c)
+    scale = want_s.abs().max().item()
+    assert (sums - want_s).abs().max().item() <= 2e-5 * scale
+    assert torch.equal(prev[0, pick[5:]], b[0, pick[5:]]) and torch.all(prev[0, pick[:5]] == -1)
+    keep = torch.ones(n, dtype=torch.bool, device="cuda")
+    keep[pick] = False
+    assert torch.equal(prev[0, keep], a[0, keep])
+
+
+def test_lloyd_loop_with_and_without_incremental_sums(monkeypatch):
+    X, _ = synthetic.mixture(120_000, 64, 64, 4)
+    Xd = X.cuda()
+    init = Xd[:200].clone()
+    l1, c1, n1 = fl.flash_kmeans(Xd, 200, max_iters=20, init_centroids=init)
+    monkeypatch.setenv("FLASHLIB_B200_KMEANS_DELTA", "0")
+    l0, c0, n0 = fl.flash_kmeans(Xd, 200, max_iters=20, init_centroids=init)
+    assert n0 == n1 == 20
+    # Two runs never agree to the last bit (the sums are fp32 atomics in any order, and a boundary point
+    # that changes sides moves its centroids): the yardstick is the objective, as for the oracle.
+    def inertia(lab, c):
+        return float(((Xd - c[lab.long()]) ** 2).sum())
+    i1, i0 = inertia(l1, c1), inertia(l0, c0)
+    assert abs(i1 - i0) <= 1e-3 * i0, (i1, i0)
+    assert (l0 == l1).float().mean().item() > 0.97
