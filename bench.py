@@ -501,6 +501,41 @@ def secondary_ivf(steps, warm, peaks):
             "config": {"nlist": cfg["nlist"], "nprobe": cfg["nprobe"], "k": cfg["k"], "max_list_len": int(lens.max())}}
 
 
+def secondary_knn_100m_shard(steps, warm, mode_name, peaks, rows=None, nq=None):
+    """One GPU's share of the sharded configuration: 12,500,000 of the 100,000,000 rows x 96 features
+    ~ N(0,1) (drawn on the device: 4.8 GB of rows), all 100,000 queries, k = 100.  Parity: the CPU
+    restatement on 16 of the queries against all of this GPU's rows (copied to the host in blocks)."""
+    import flashlib_b200 as fl
+    from flashlib_b200 import synthetic
+    from flashlib_b200.knn import _mode_from, knn_f32
+    from oracle import oracle_torch
+    from tests import parity
+    cfg = synthetic.CONFIGS["knn_sharded_100m"]
+    rows = rows or cfg["m"] // 8
+    nq = nq or cfg["nq"]
+    g = torch.Generator(device="cuda").manual_seed(cfg["seed"])
+    Xd = torch.randn(rows, cfg["d"], generator=g, device="cuda")
+    Qd = torch.randn(nq, cfg["d"], generator=g, device="cuda")
+    ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, cfg["k"], mode=mode_name), steps, warm)
+    d_, i_, info = knn_f32(Qd, Xd, cfg["k"], mode=_mode_from(mode_name))
+    n_chk = 16
+    Xh = torch.empty((rows, cfg["d"]), dtype=torch.float32)
+    for r0 in range(0, rows, 2_000_000):
+        Xh[r0:r0 + 2_000_000] = Xd[r0:r0 + 2_000_000].cpu()
+    Qh = Qd[:n_chk].cpu()
+    _, ref_i = oracle_torch.knn_chunked(Qh, Xh, cfg["k"], chunk_size=65536)
+    res = parity.knn_parity(Qh.numpy(), Xh.numpy(), d_[:n_chk].cpu().numpy(), i_[:n_chk].cpu().numpy(), ref_i.numpy())
+    flop = 2.0 * nq * rows * cfg["d"]
+    del Xd, Xh
+    torch.cuda.empty_cache()
+    return {"workload": "knn_100m_shard", "metric": "exact_knn_queries_per_sec", "value": nq / (ms * 1e-3),
+            "unit": "queries/s", "ms_per_step": ms, "roofline": _roof("tensor", flop, ms, peaks),
+            "parity_ok": bool(res["ok"]), "parity": {"rows": n_chk, "bad_rows": len(res["bad_rows"]),
+                                                     "worst_rel_dist_err": res["worst_rel_dist_err"]},
+            "config": {"rows_on_this_gpu": rows, "of_rows": cfg["m"], "dim": cfg["d"], "queries": nq, "k": cfg["k"],
+                       "mode": int(info["mode"]), "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+
+
 def run_secondary(args):
     """Single-GPU timings of the other configurations (k-means 1M x 128 / K=1024 / 20 Lloyd
     iterations; IVF-Flat search nlist=1024, nprobe=16; exact kNN with k=100)."""
@@ -560,23 +595,7 @@ def run_secondary(args):
                 "config": {"rows": DB_ROWS, "dim": DIM, "queries": nq, "k": K_NEIGHBOURS, "centres": 200, "spread": 0.1,
                            "mode": int(info["mode"]), "second_stage": bool(info["second_stage"])}}
     elif args.workload == "knn_100m_shard":
-        # One GPU's share of the sharded configuration: 12.5M of the 100M rows x 96 features
-        # ~ N(0,1), all 100,000 queries, k = 100 (drawn on the device: 4.8 GB of rows).
-        cfg = synthetic.CONFIGS["knn_sharded_100m"]
-        rows = args.db_rows or cfg["m"] // 8
-        nq = args.queries or cfg["nq"]
-        g = torch.Generator(device="cuda").manual_seed(cfg["seed"])
-        Xd = torch.randn(rows, cfg["d"], generator=g, device="cuda")
-        Qd = torch.randn(nq, cfg["d"], generator=g, device="cuda")
-        from flashlib_b200.knn import _mode_from, knn_f32
-        mode = _mode_from(args.mode)
-        ms = _time_steps(lambda: fl.flash_knn(Qd, Xd, cfg["k"], mode=args.mode), steps, warm)
-        _, _, info = knn_f32(Qd, Xd, cfg["k"], mode=mode)
-        flop = 2.0 * nq * rows * cfg["d"]
-        line = {"workload": "knn_100m_shard", "metric": "exact_knn_queries_per_sec", "value": nq / (ms * 1e-3),
-                "unit": "queries/s", "ms_per_step": ms, "algorithmic_tflops": flop / (ms * 1e-3) / 1e12,
-                "config": {"rows_on_this_gpu": rows, "dim": cfg["d"], "queries": nq, "k": cfg["k"], "mode": int(info["mode"]),
-                           "rows_recomputed_on_exact_path": int(info.get("fallback_rows", 0))}}
+        line = secondary_knn_100m_shard(steps, warm, args.mode, peaks, rows=args.db_rows, nq=args.queries)
     elif args.workload == "kmeans_1m":
         line = secondary_kmeans(steps, warm, peaks)
     else:
@@ -877,6 +896,9 @@ def main():
         secondary["kmeans_1m"] = secondary_kmeans(3, 1, peaks_)
         torch.cuda.empty_cache()
         secondary["ivf_1m"] = secondary_ivf(5, 2, peaks_)
+        torch.cuda.empty_cache()
+        # one GPU's share of the 100M-row sharded configuration (the 8-GPU run of it: --workload knn_100m)
+        secondary["knn_100m_shard"] = secondary_knn_100m_shard(2, 1, args.mode, peaks_)
 
     if rank == 0:
         peaks = load_peaks()
