@@ -93,6 +93,7 @@ int launch_fallback_fixup(int* fb_count, int fb_cap, int32_t* status, int K1, cu
 // ---- workspace layout -----------------------------------------------------------------
 struct KnnWs {
     int mode, K1, K1f;
+    int kg;                                    // k that selects the tensor-core pool geometry (see knn_geometry_k)
     int deep, plen;                            // tensor-core path: deep pools, published entries per (query, range)
     int nsplit; int64_t rows_per_split;        // main pass (SIMT: rows; TC: tiles of 256)
     int nsplit_fb; int64_t rows_per_split_fb;  // fallback pass
@@ -122,13 +123,22 @@ static int knn_stage2_rows(int64_t nq) {
     return (int)c;
 }
 
+// More than 256 features: the resident query tile (up to 132 KB at d = 512) leaves no room for pools
+// in shared memory, so small k takes the large-k geometry too (pools in global memory, block-per-
+// query finalisation, the seeding rule of k = 17).
+static int knn_geometry_k(int d, int k) { return (d > 256 && k < 17) ? 17 : k; }
+
 static KnnWs knn_ws_plan(int64_t nq, int64_t m, int d, int k, int mode, int staged = 0) {
     KnnWs w{};
     w.mode = mode;
+    w.kg = k;
     int64_t cur = 0;
     if (mode == FL_KNN_BF16_RERANK) {
+        const int k_real = k;
+        k = knn_geometry_k(d, k);
+        w.kg = k;
         w.K1 = tc_pool_size(k);
-        w.K1f = simt_pool_size(k);
+        w.K1f = simt_pool_size(k_real);
         w.nq_pad = tc_query_rows_padded(nq);
         w.d_pad = (int)round_up(d, 64);
         const int64_t m_pad = round_up(m, 256);
@@ -358,7 +368,7 @@ static int knn_tc_phases(int phases, const void* q, int64_t nq, int64_t ldq, con
     tp.part_cnt = reinterpret_cast<int*>(base + w.off_part_cnt);
     tp.deep_pools = w.deep;
     tp.seed_cls = seed_cls;
-    tp.k = k;
+    tp.k = w.kg;
     int rc;
 
     if (phases & TC_SCORE) FL_CHECK_CUDA(cudaMemsetAsync(fb_count, 0, 1024, st));
@@ -385,7 +395,7 @@ static int knn_tc_phases(int phases, const void* q, int64_t nq, int64_t ldq, con
     mg.dt = dt;
     if (gmaxnorm != nullptr) {
         mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.maxnorm = gmaxnorm; mg.eps_rel = 0.004f; mg.cert_out = cert;
-    } else if (tc_seed_dense(L.m_pad, k)) {
+    } else if (tc_seed_dense(L.m_pad, w.kg)) {
         mg.q = q; mg.ldq = ldq; mg.d = d; mg.nq = nq; mg.eps_rel = 0.004f; mg.cert_out = nullptr;
         mg.maxnorm = reinterpret_cast<const float*>(pl + L.off_meta);
     }
@@ -414,7 +424,7 @@ static int knn_tc_phases(int phases, const void* q, int64_t nq, int64_t ldq, con
     int* s2_count = fb_count + 64;
     int* s2_list = w.s2 ? reinterpret_cast<int*>(base + w.off_s2_list) : nullptr;
     if (w.s2) { fp.next_count = s2_count; fp.next_list = s2_list; fp.next_cap = w.s2_cap; }
-    rc = tc_knn_big(k) ? launch_knn_finalize_big(fp, nq, st) : launch_knn_finalize(fp, nq, st);
+    rc = tc_knn_big(w.kg) ? launch_knn_finalize_big(fp, nq, st) : launch_knn_finalize(fp, nq, st);
     if (rc != FL_OK) return rc;
 
     // Second stage: the rejected rows are scored again with split (hi/lo) operands -- an error
@@ -756,7 +766,7 @@ extern "C" int fl_debug_knn_tc_scores(const float* q, int64_t nq, int64_t ldq, i
                                       int64_t m, float* scores, int64_t ld_scores, void* ws, int64_t ws_bytes,
                                       int32_t* status, void* stream) {
     FL_CHECK_ARG(q && plane && scores && ws && nq >= 1 && nq <= 128 && m >= 1 && d >= 1, "fl_debug_knn_tc_scores: bad arguments");
-    if (tc_knn_supported(nq, m, d, 10) != FL_OK) { set_error("fl_debug_knn_tc_scores: unsupported shape"); return FL_EUNSUPPORTED; }
+    if (d > 256 || tc_knn_supported(nq, m, d, 10) != FL_OK) { set_error("fl_debug_knn_tc_scores: unsupported shape"); return FL_EUNSUPPORTED; }
     const KnnWs w = knn_ws_plan(nq, m, d, 10, FL_KNN_BF16_RERANK);
     if (ws_bytes < w.bytes) { set_error("fl_debug_knn_tc_scores: workspace too small"); return FL_EWORKSPACE; }
     const PlaneLayout L = plane_layout(m, d);

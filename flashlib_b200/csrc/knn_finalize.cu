@@ -393,7 +393,7 @@ constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 2
 static __device__ __forceinline__ void finalize_big_slot(const FinalizeParams& p, const int64_t slot) {
     __shared__ float s_key[BIG_CAND];
     __shared__ uint32_t s_id[BIG_CAND];
-    __shared__ float s_q[256];
+    __shared__ float s_q[512];
     __shared__ float s_red[BIG_THREADS / 32];
     __shared__ int s_n;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(BIG_THREADS) knn_finalize_big_kernel(FinalizeP
 
 int launch_knn_finalize_big(const FinalizeParams& p, int64_t max_slots, cudaStream_t st) {
     if (max_slots <= 0) return FL_OK;
-    FL_CHECK_ARG(p.part_cnt && p.part_tau && p.K1 == 2 * BIG_POOL && p.d <= 256 && p.k <= BIG_RERANK && p.count == max_slots,
+    FL_CHECK_ARG(p.part_cnt && p.part_tau && p.K1 == 2 * BIG_POOL && p.d <= 512 && p.k <= BIG_RERANK && p.count == max_slots,
                  "large-k finalisation: bad parameters");
     int64_t grid = max_slots;
     if (p.count_dev != nullptr && grid > (int64_t)sm_count() * 4) grid = (int64_t)sm_count() * 4;

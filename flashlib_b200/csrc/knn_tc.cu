@@ -1034,7 +1034,8 @@ int tc_pair_pool_cap() { return TC_GP_CAP; }
 int tc_knn_supported(int64_t nq, int64_t m, int d, int k) {
     if (nq < 1 || m < 1) return FL_EUNSUPPORTED;
     if (k > 112) return FL_EUNSUPPORTED;            // pools keep 12 (k <= 16) or 128 entries: leave the proof a margin
-    if (d > 256) return FL_EUNSUPPORTED;            // resident query tile: up to 4 chunks of 64 features
+    if (d > 512) return FL_EUNSUPPORTED;            // resident query tile: up to 8 chunks of 64 features (beyond 4:
+                                                    // pools in global memory only, two ring slots at d = 512)
     if (round_up(m, 256) / 256 > (1 << 23)) return FL_EUNSUPPORTED;
     return FL_OK;
 }

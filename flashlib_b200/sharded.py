@@ -238,7 +238,7 @@ def sharded_knn(q: torch.Tensor, db_shard: Optional[torch.Tensor], k: int, *, ro
     # every rank must take the same branch (the seeded flow has one more collective): the decision
     # uses only facts that are identical everywhere
     seeded = (multi and index is not None and share_seeds is not False and nq > 0 and k <= 16
-              and q.dtype == torch.float32 and db_shard.dtype == torch.float32
+              and q.dtype == torch.float32 and db_shard.dtype == torch.float32 and d <= 256
               and index.all_tensor_core and index.min_rows >= k
               and (share_seeds is True or kern.tensor_core(nq, index.min_rows, d, k, mode)))
     gmax = index.global_max_norm if index is not None else None

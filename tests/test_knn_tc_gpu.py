@@ -147,6 +147,26 @@ def test_no_split_plane_beyond_128_features():
     assert not info["second_stage"]
 
 
+@pytest.mark.parametrize("nq,m,d,k", [(200, 60_000, 384, 10), (129, 30_000, 512, 10), (100, 20_000, 300, 32), (300, 70_000, 512, 1),
+                                      (64, 9_000, 257, 16)])
+def test_bf16_mode_up_to_512_features(nq, m, d, k):
+    """256 < d <= 512: the resident query tile leaves no room for pools in shared memory, so every k takes
+    the global-memory pools of the large-k mode; same proof, same result as the oracle."""
+    g = torch.Generator().manual_seed(nq + m + d)
+    db = torch.randn(m, d, generator=g)
+    q = torch.randn(nq, d, generator=g)
+    _, ref_i = oracle.knn_naive(q.numpy(), db.numpy(), k)
+    d_tc, i_tc, info = knn_f32(q.cuda(), db.cuda(), k, mode=_lib.FL_KNN_BF16_RERANK)
+    res = parity.knn_parity(q.numpy(), db.numpy(), d_tc.cpu().numpy(), i_tc.cpu().numpy(), ref_i)
+    assert res["ok"], (res, info)
+    assert info["fallback_rows"] <= nq // 10, info
+    lib = _lib.load()
+    assert lib.fl_knn_workspace_bytes(nq, m, 513, k, _lib.FL_KNN_BF16_RERANK) >= 0
+    with pytest.raises(NotImplementedError):
+        knn_f32(q.cuda()[:, :1].expand(nq, 513).contiguous(), db.cuda()[:, :1].expand(m, 513).contiguous(), k,
+                mode=_lib.FL_KNN_BF16_RERANK)
+
+
 BIG_K_SHAPES = [(64, 3000, 64, 17), (129, 20_000, 128, 32), (300, 60_000, 128, 100), (500, 150_000, 64, 64),
                 (100, 400, 96, 112), (257, 300_001, 96, 100), (33, 50_000, 200, 50)]
 
