@@ -593,7 +593,7 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
 
 static int ivf_tc_supported(int64_t nq, int nprobe, int nlist, int64_t m, int d, int k) {
     if (nq < 1 || nprobe < 1 || nlist < 1 || m < 1) return 0;
-    if (k > 16 || d > 128) return 0;      // deep pools + resident query tile + two ring slots: 128 features
+    if (k > 16 || d > 256) return 0;      // resident query tile + ring: four slots up to 128 features, three up to 256
     if (nq * (int64_t)nprobe >= (1ll << 31) / IVF_TC_BQ || m + (int64_t)IVF_TC_TILE * nlist >= (1ll << 31)) return 0;
     return 1;
 }
@@ -603,7 +603,7 @@ static int ivf_tc_supported(int64_t nq, int nprobe, int nlist, int64_t m, int d,
 using namespace fl;
 
 extern "C" int64_t fl_ivf_plane_bytes(int64_t m, int nlist, int d) {
-    if (m < 1 || nlist < 1 || d < 1 || d > 128) return 0;
+    if (m < 1 || nlist < 1 || d < 1 || d > 256) return 0;
     return ivf_plane_layout(m, nlist, d).bytes;
 }
 
@@ -612,7 +612,7 @@ extern "C" int fl_ivf_prepare_f32(const float* data, int64_t m, int64_t ldd, int
     FL_CHECK_ARG(m >= 1 && d >= 1 && nlist >= 1 && ldd >= d, "fl_ivf_prepare_f32: bad shape");
     FL_CHECK_ARG(data && list_offsets && plane, "fl_ivf_prepare_f32: null pointer");
     FL_CHECK_ARG((reinterpret_cast<uintptr_t>(plane) & 255) == 0, "fl_ivf_prepare_f32: plane must be 256-byte aligned");
-    if (d > 128) { set_error("fl_ivf_prepare_f32: d=%d > 128 is not supported", d); return FL_EUNSUPPORTED; }
+    if (d > 256) { set_error("fl_ivf_prepare_f32: d=%d > 256 is not supported", d); return FL_EUNSUPPORTED; }
     const IvfPlaneLayout L = ivf_plane_layout(m, nlist, d);
     if (plane_bytes < L.bytes) { set_error("fl_ivf_prepare_f32: plane buffer %lld < %lld bytes", (long long)plane_bytes, (long long)L.bytes); return FL_EWORKSPACE; }
     cudaStream_t st = (cudaStream_t)stream;
@@ -648,7 +648,7 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     FL_CHECK_ARG(ldq >= d && ldd >= d, "fl_ivf_fine_scan_tc_f32: leading dimensions smaller than d");
     if (nq == 0) return FL_OK;
     if (!ivf_tc_supported(nq, nprobe, nlist, m, d, k)) {
-        set_error("fl_ivf_fine_scan_tc_f32: k=%d / d=%d / sizes outside the tensor-core scan (k <= 16, d <= 128)", k, d);
+        set_error("fl_ivf_fine_scan_tc_f32: k=%d / d=%d / sizes outside the tensor-core scan (k <= 16, d <= 256)", k, d);
         return FL_EUNSUPPORTED;
     }
     FL_CHECK_ARG(q && data && list_offsets && probed && ivf_plane && out_dist && out_pos && ws, "fl_ivf_fine_scan_tc_f32: null pointer");

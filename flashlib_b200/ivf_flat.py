@@ -200,7 +200,7 @@ def _tc_plane(index: IvfFlatIndex, data: torch.Tensor, offs: torch.Tensor) -> to
 def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k: int, mode: Optional[str] = None):
     """Fine scan of the probed lists: ``(vals fp32 (nq,k), pos int32 (nq,k))``, ``+inf`` / ``-1``
     padded when a query's lists hold fewer than ``k`` rows.  ``mode`` ``"exact"`` forces the
-    CUDA-core scan, ``"bf16"`` the tensor-core scan (k <= 16, d <= 128); ``None`` takes the
+    CUDA-core scan, ``"bf16"`` the tensor-core scan (k <= 16, d <= 256); ``None`` takes the
     tensor cores for k <= 10 when the batch has at least 2,048 (query, probe) pairs.  Both
     return the same neighbours."""
     lib = _lib.load()
@@ -219,7 +219,7 @@ def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k
     same_data = data.data_ptr() == index.data.data_ptr()
     tc_bytes = lib.fl_ivf_fine_scan_tc_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k) if same_data else 0
     if mode in ("bf16", "tc") and tc_bytes == 0:
-        raise NotImplementedError("tensor-core fine scan needs k <= 16, d <= 128 and fp32 rows stored in the index")
+        raise NotImplementedError("tensor-core fine scan needs k <= 16, d <= 256 and fp32 rows stored in the index")
     # auto: the candidate pools keep 12 entries per (pair, half list), enough to prove k <= 10
     if nq > 0 and tc_bytes > 0 and (mode in ("bf16", "tc") or
                                     (mode in (None, "auto") and k <= 10 and nq * nprobe >= 2048)):
@@ -252,7 +252,7 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     """``(vals fp32, ids int64)`` of the ``k`` nearest probed rows per query, ``-1`` / ``+inf``
     padded (``ivf_flat/triton/search.py:52-108``).  ``variant`` is validated like the
     reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 10 and
-    d <= 128, where its candidate pools prove nearly every query; the CUDA-core scan
+    d <= 256, where its candidate pools prove nearly every query; the CUDA-core scan
     otherwise), ``"elementwise"`` for the CUDA-core scan, ``"auto"`` picks by batch size.
     All variants return the same neighbours."""
     if variant not in ("auto", "gemm", "elementwise"):
@@ -272,7 +272,7 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
                        return_distances=False, mode=coarse)[0]
     mode = {"auto": None, "elementwise": "exact", "gemm": "bf16"}[variant]
-    if mode == "bf16" and (k > 10 or index.Dp > 128):
+    if mode == "bf16" and (k > 10 or index.Dp > 256):
         mode = "exact"
     vals, pos = ivf_fine_scan(Qp, index, probed, k, mode=mode)
     valid = pos >= 0

@@ -356,7 +356,7 @@ int     fl_ivf_build_csr_f32(const float* x, int64_t m, int64_t ldx, int d,
                              float* data, int64_t* ids, int64_t* list_offsets, int32_t* max_list_len,
                              void* ws, int64_t ws_bytes, void* stream);
 
-/* The same fine scan on the tensor cores (k <= 16, d <= 128), the counterpart of the     */
+/* The same fine scan on the tensor cores (k <= 16, d <= 256), the counterpart of the     */
 /* reference's GEMM variant (ivf_flat/triton/fine_scan_gemm.py:41-272).                   */
 /* fl_ivf_prepare_f32 builds, once per index, the bf16 operand plane of the stored rows    */
 /* (every list padded to whole 256-row tiles) and the map back to stored rows, in a         */

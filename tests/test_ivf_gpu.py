@@ -108,7 +108,8 @@ def test_tensor_core_fine_scan_matches_reference_fixture(k, nprobe):
 
 
 @pytest.mark.parametrize("n,dim,nlist,nprobe,nq,k", [(60_000, 64, 128, 8, 700, 10), (30_000, 96, 37, 5, 1500, 16),
-                                                   (5_000, 128, 300, 20, 64, 3), (100_000, 128, 256, 16, 4000, 10)])
+                                                   (5_000, 128, 300, 20, 64, 3), (100_000, 128, 256, 16, 4000, 10),
+                                                   (40_000, 200, 64, 8, 900, 10), (50_000, 256, 100, 10, 2000, 5)])
 def test_tensor_core_fine_scan_equals_cuda_core_scan(n, dim, nlist, nprobe, nq, k):
     """Same index, same probed lists: both fine scans return the same rows and distances.  Shapes
     cover lists shorter than k, empty lists (more lists than a cluster structure fills), query
