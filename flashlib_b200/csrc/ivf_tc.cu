@@ -467,24 +467,32 @@ __global__ void __launch_bounds__(128) ivf_tc_finalize_kernel(
     if (!proven && lane == 0) fb_list[atomicAdd(fb_count, 1)] = (int)qi;      // the list holds every query
 }
 
-// Exact scan for the queries the proof rejected: one block per listed query walks the rows of the
-// query's probed lists (one warp per row, fp32 sum (q - x)^2 with the summation order of the
-// finalisation kernel), collects rows closer than the running k-th distance and compacts the
-// collection with a block sort whenever it is half full.
+// Exact scan for the queries the proof rejected: a block walks the rows of a listed query's probed
+// lists (four rows per warp and step, fp32 sum (q - x)^2 with the summation order of the finalisation
+// kernel), collects rows closer than the running k-th distance and compacts the collection with a
+// block sort whenever it is half full.  With fewer listed queries than blocks a query's lists are
+// dealt to several blocks (`parts`); each leaves its k best in `scratch` and the last one to finish
+// (a ticket per query in `done`, zeroed by the caller) merges them.
 constexpr int IVFX_THREADS = 256, IVFX_CAP = 4096, IVFX_CHUNK = 2048;
 __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
     const float* __restrict__ q, int64_t ldq, const float* __restrict__ data, int64_t ldd, int d, int vec,
     const int64_t* __restrict__ list_offsets, int nlist, const int32_t* __restrict__ probed, int nprobe, int k,
     const int* __restrict__ fb_list, const int* __restrict__ fb_count, float* __restrict__ out_dist,
-    int32_t* __restrict__ out_pos) {
+    int32_t* __restrict__ out_pos, float2* __restrict__ scratch, int* __restrict__ done) {
     __shared__ float s_key[IVFX_CAP];       // -distance: the block sort puts larger keys first
     __shared__ uint32_t s_id[IVFX_CAP];
     __shared__ __align__(16) float s_q[512];
     __shared__ int s_n;
     __shared__ float s_T;
+    __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int count = *fb_count;
-    for (int slot = blockIdx.x; slot < count; slot += gridDim.x) {
+    const int G = (int)gridDim.x;
+    int parts = 1;
+    if (count > 0 && count < G) { parts = G / count; if (parts > nprobe) parts = nprobe; if (parts > 16) parts = 16; }
+    const int items = count * parts;        // parts > 1: items <= G, one item per block
+    for (int item = blockIdx.x; item < items; item += G) {
+        const int slot = item / parts, part = item - slot * parts;
         const int qi = fb_list[slot];
         __syncthreads();
         for (int c = tid; c < d; c += IVFX_THREADS) s_q[c] = __ldg(q + (int64_t)qi * ldq + c);
@@ -503,32 +511,52 @@ __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
             }
             __syncthreads();
         };
-        for (int j = 0; j < nprobe; ++j) {
+        for (int j = part; j < nprobe; j += parts) {
             const int c = probed[(int64_t)qi * nprobe + j];
             if (c < 0 || c >= nlist) continue;
             const int64_t r0 = list_offsets[c], r1 = list_offsets[c + 1];
             for (int64_t base = r0; base < r1; base += IVFX_CHUNK) {
                 const int64_t end = base + IVFX_CHUNK < r1 ? base + IVFX_CHUNK : r1;
                 const float T = s_T;
-                for (int64_t r = base + warp; r < end; r += IVFX_THREADS / 32) {
-                    const float* xp = data + r * ldd;
-                    float a = 0.f;
+                // four rows per warp and step: a lone block is bound by load latency, so the loads of
+                // four rows are in flight together
+                constexpr int RW = 4;
+                for (int64_t r = base + warp * RW; r < end; r += (IVFX_THREADS / 32) * RW) {
+                    float a[RW];
+#pragma unroll
+                    for (int u = 0; u < RW; ++u) a[u] = 0.f;
                     if (vec) {
                         for (int t = lane * 4; t < d; t += 128) {
                             const float4 qv = *reinterpret_cast<const float4*>(s_q + t);
-                            const float4 xv = __ldg(reinterpret_cast<const float4*>(xp + t));
-                            const float d0 = qv.x - xv.x, d1 = qv.y - xv.y, d2 = qv.z - xv.z, d3 = qv.w - xv.w;
-                            a += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                            float4 xv[RW];
+#pragma unroll
+                            for (int u = 0; u < RW; ++u)
+                                xv[u] = r + u < end ? __ldg(reinterpret_cast<const float4*>(data + (r + u) * ldd + t)) : qv;
+#pragma unroll
+                            for (int u = 0; u < RW; ++u) {
+                                const float d0 = qv.x - xv[u].x, d1 = qv.y - xv[u].y, d2 = qv.z - xv[u].z, d3 = qv.w - xv[u].w;
+                                a[u] += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+                            }
                         }
                     } else {
-                        for (int t = lane; t < d; t += 32) { const float df = s_q[t] - __ldg(xp + t); a += df * df; }
+                        for (int t = lane; t < d; t += 32) {
+                            const float qv = s_q[t];
+                            float xv[RW];
+#pragma unroll
+                            for (int u = 0; u < RW; ++u) xv[u] = r + u < end ? __ldg(data + (r + u) * ldd + t) : qv;
+#pragma unroll
+                            for (int u = 0; u < RW; ++u) { const float df = qv - xv[u]; a[u] += df * df; }
+                        }
                     }
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(FULL_MASK, a, o);
-                    if (lane == 0 && a <= T) {
-                        const int pos = atomicAdd(&s_n, 1);
-                        s_key[pos] = -a;                 // <= IVFX_CHUNK appends per chunk, <= IVFX_CHUNK kept before it
-                        s_id[pos] = (uint32_t)r;
+                    for (int u = 0; u < RW; ++u) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) a[u] += __shfl_xor_sync(FULL_MASK, a[u], o);
+                        if (lane == 0 && r + u < end && a[u] <= T) {
+                            const int pos = atomicAdd(&s_n, 1);
+                            s_key[pos] = -a[u];          // <= IVFX_CHUNK appends per chunk, <= IVFX_CHUNK kept before it
+                            s_id[pos] = (uint32_t)(r + u);
+                        }
                     }
                 }
                 __syncthreads();
@@ -539,10 +567,34 @@ __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
         }
         __syncthreads();
         compact();
+        if (parts > 1) {
+            // leave this part's k best for the merge; the last block of the query does it
+            const int n = s_n;
+            for (int e = tid; e < k; e += IVFX_THREADS)
+                scratch[(int64_t)item * k + e] = e < n ? make_float2(s_key[e], __uint_as_float(s_id[e]))
+                                                       : make_float2(neg_inf(), __uint_as_float(INVALID_ID));
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_last = atomicAdd(done + slot, 1) == parts - 1;
+            __syncthreads();
+            if (!s_last) continue;
+            __threadfence();
+            const int total = parts * k;            // <= 16 * 16
+            for (int e = tid; e < total; e += IVFX_THREADS) {
+                const float2 v = __ldcg(scratch + (int64_t)slot * parts * k + e);
+                s_key[e] = v.x;
+                s_id[e] = __float_as_uint(v.y);
+            }
+            if (tid == 0) s_n = total;
+            __syncthreads();
+            compact();
+            // (padding entries carry -inf keys: they sort last and count as absent below)
+        }
         const int n = s_n;
         for (int e = tid; e < k; e += IVFX_THREADS) {
-            out_dist[(int64_t)qi * k + e] = e < n ? -s_key[e] : pos_inf();
-            out_pos[(int64_t)qi * k + e] = e < n ? (int32_t)s_id[e] : -1;
+            const bool have = e < n && s_id[e] != INVALID_ID;
+            out_dist[(int64_t)qi * k + e] = have ? -s_key[e] : pos_inf();
+            out_pos[(int64_t)qi * k + e] = have ? (int32_t)s_id[e] : -1;
         }
     }
 }
@@ -550,7 +602,8 @@ __global__ void __launch_bounds__(IVFX_THREADS) ivf_exact_query_kernel(
 struct IvfTcWs {
     int64_t npairs, max_items, cap_rows; int d_pad, pitch;
     int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_pair_row, off_item_t0, off_item_t1,
-        off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_seed_cls, off_pools, off_part_cnt, off_part_tau, off_fblist, bytes;
+        off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_seed_cls, off_pools, off_part_cnt, off_part_tau, off_fblist,
+        off_x_scratch, off_x_done, bytes;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -587,6 +640,9 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
     w.off_part_cnt = take(cur, w.cap_rows * tc_taus_per_range() * 4);
     w.off_part_tau = take(cur, w.cap_rows * tc_taus_per_range() * 4);
     w.off_fblist = take(cur, nq * 4);
+    // exact pass over a handful of queries: per-block partial results and a ticket per query
+    w.off_x_scratch = take(cur, (int64_t)2 * sm_count() * 16 * 8);
+    w.off_x_done = take(cur, (int64_t)2 * sm_count() * 4);
     w.bytes = cur;
     return w;
 }
@@ -744,8 +800,10 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     profile_mark(st);      // 7: exact pass for unproven queries
     rc = launch_fallback_fixup(fb_count, (int)nq, status, tc_deep_pool_size(), st);
     if (rc != FL_OK) return rc;
+    FL_CHECK_CUDA(cudaMemsetAsync(base + w.off_x_done, 0, (size_t)2 * sm_count() * 4, st));
     ivf_exact_query_kernel<<<(unsigned)(2 * sm_count()), IVFX_THREADS, 0, st>>>(
-        q, ldq, data, ldd, d, vec, list_offsets, nlist, probed, nprobe, k, fb_list, fb_count, out_dist, out_pos);
+        q, ldq, data, ldd, d, vec, list_offsets, nlist, probed, nprobe, k, fb_list, fb_count, out_dist, out_pos,
+        reinterpret_cast<float2*>(base + w.off_x_scratch), reinterpret_cast<int*>(base + w.off_x_done));
     FL_CHECK_LAUNCH();
     profile_mark(st);      // 8: end
     return FL_OK;

@@ -201,7 +201,7 @@ def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k
     """Fine scan of the probed lists: ``(vals fp32 (nq,k), pos int32 (nq,k))``, ``+inf`` / ``-1``
     padded when a query's lists hold fewer than ``k`` rows.  ``mode`` ``"exact"`` forces the
     CUDA-core scan, ``"bf16"`` the tensor-core scan (k <= 16, d <= 256); ``None`` takes the
-    tensor cores for k <= 10 when the batch has at least 2,048 (query, probe) pairs.  Both
+    tensor cores for k <= 16 when the batch has at least 2,048 (query, probe) pairs.  Both
     return the same neighbours."""
     lib = _lib.load()
     _lib.require_device()
@@ -220,9 +220,10 @@ def ivf_fine_scan(Qp: torch.Tensor, index: IvfFlatIndex, probed: torch.Tensor, k
     tc_bytes = lib.fl_ivf_fine_scan_tc_workspace_bytes(max(nq, 1), nprobe, index.nlist, m, d, k) if same_data else 0
     if mode in ("bf16", "tc") and tc_bytes == 0:
         raise NotImplementedError("tensor-core fine scan needs k <= 16, d <= 256 and fp32 rows stored in the index")
-    # auto: the candidate pools keep 12 entries per (pair, half list), enough to prove k <= 10
+    # auto: every k the tensor-core scan takes (the pools keep 24 entries per (pair, half list): k <= 12
+    # proves every query of the 1M-row benchmark, k = 16 leaves a handful to the exact scan)
     if nq > 0 and tc_bytes > 0 and (mode in ("bf16", "tc") or
-                                    (mode in (None, "auto") and k <= 10 and nq * nprobe >= 2048)):
+                                    (mode in (None, "auto") and k <= 16 and nq * nprobe >= 2048)):
         plane = _tc_plane(index, data, offs)
         ws = torch.empty(tc_bytes, dtype=torch.uint8, device=q.device)
         status = torch.zeros(_lib.FL_STATUS_WORDS, dtype=torch.int32, device=q.device)
@@ -251,7 +252,7 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
                           backend: Optional[str] = None, variant: str = "auto"):
     """``(vals fp32, ids int64)`` of the ``k`` nearest probed rows per query, ``-1`` / ``+inf``
     padded (``ivf_flat/triton/search.py:52-108``).  ``variant`` is validated like the
-    reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 10 and
+    reference's: ``"gemm"`` asks for the tensor-core fine scan (taken when k <= 16 and
     d <= 256, where its candidate pools prove nearly every query; the CUDA-core scan
     otherwise), ``"elementwise"`` for the CUDA-core scan, ``"auto"`` picks by batch size.
     All variants return the same neighbours."""
@@ -272,7 +273,7 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
                        return_distances=False, mode=coarse)[0]
     mode = {"auto": None, "elementwise": "exact", "gemm": "bf16"}[variant]
-    if mode == "bf16" and (k > 10 or index.Dp > 256):
+    if mode == "bf16" and (k > 16 or index.Dp > 256):
         mode = "exact"
     vals, pos = ivf_fine_scan(Qp, index, probed, k, mode=mode)
     valid = pos >= 0
