@@ -216,7 +216,8 @@ def triton_lloyd_centroid_step_euclid(x: torch.Tensor, cluster_ids: torch.Tensor
                                       cnts_buf: Optional[torch.Tensor] = None,
                                       new_buf: Optional[torch.Tensor] = None,
                                       shift_buf: Optional[torch.Tensor] = None,
-                                      prev_ids: Optional[torch.Tensor] = None, refresh: bool = True, **_ignored):
+                                      prev_ids: Optional[torch.Tensor] = None, refresh: bool = True,
+                                      want_shift: bool = True, **_ignored):
     """One centroid step: sums/counts, finalize, max shift
     (``flashlib/primitives/kmeans/triton/update.py:501-554``).  Returns
     ``(new_centroids, cluster_ids, max_shift)`` with ``max_shift`` a 0-d device tensor.
@@ -231,7 +232,8 @@ def triton_lloyd_centroid_step_euclid(x: torch.Tensor, cluster_ids: torch.Tensor
             prev_ids.copy_(cluster_ids)
     new_centroids, shift_per_k = triton_centroid_finalize(sums_buf, cnts_buf, old_centroids,
                                                           out=new_buf, shift=shift_buf)
-    max_shift = shift_per_k.amax(dim=-1).amax()
+    # (a loop that neither tests convergence nor prints the shift spares itself the two reductions)
+    max_shift = shift_per_k.amax(dim=-1).amax() if want_shift else None
     return new_centroids, cluster_ids, max_shift
 
 
@@ -271,7 +273,7 @@ def batch_kmeans_Euclid(x: torch.Tensor, n_clusters: int, max_iters: int = 100, 
         euclid_assign_triton(x32, cur, out=cluster_ids)
         _, _, max_shift = triton_lloyd_centroid_step_euclid(
             x32, cluster_ids, cur, sums_buf=sums_buf, cnts_buf=cnts_buf, new_buf=nxt, shift_buf=shift_buf,
-            prev_ids=prev_ids, refresh=(it % DELTA_REFRESH == 0))
+            prev_ids=prev_ids, refresh=(it % DELTA_REFRESH == 0), want_shift=(tol > 0.0 or verbose))
         if verbose:
             print(f"Iter {it}, center shift: {max_shift.item():.6f}")
         cur, nxt = nxt, cur
