@@ -55,11 +55,12 @@ struct TcSmemPlan {
     int off_a, off_b, off_pool_sc, off_pool_id, off_hbuf, off_bar, bytes;
 };
 
-static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_PSTR, int slot_bytes = TC_B_STAGE) {
+// nabuf: query-tile buffers (2: the next item's tile is loaded while the current item is scored).
+static TcSmemPlan tc_smem_plan(int d_pad, int smem_limit, int pool_stride = TC_PSTR, int slot_bytes = TC_B_STAGE, int nabuf = 1) {
     TcSmemPlan s{};
     s.nkc = d_pad / TC_BK;
     int cur = 0;
-    s.off_a = cur; cur += s.nkc * TC_A_CHUNK + TC_A_AUG;
+    s.off_a = cur; cur += nabuf * (s.nkc * TC_A_CHUNK + TC_A_AUG);
     const int pool = TC_NWG * TC_BM * pool_stride * 4;   // 0: no pools in shared memory
     const int fixed = cur + 2 * pool + 256 + 1024 /* alignment slack */;
     int ns = (smem_limit - fixed) / slot_bytes;
@@ -92,6 +93,7 @@ __device__ unsigned long long g_tc_prof[160 * TC_PROF_WORDS];
 
 struct TcKernelParams {
     int n_qtiles, n_tiles, nsplit, tiles_per_split, nkc, nstage;
+    int nabuf;               // query-tile buffers in shared memory (1 or 2)
     int off_b, off_pool_sc, off_pool_id, off_bar;
     int64_t nq_pad;
     float* part_sc; uint32_t* part_id;
@@ -248,10 +250,18 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     float* pool_sc = reinterpret_cast<float*>(smem + p.off_pool_sc);
     uint32_t* pool_id = reinterpret_cast<uint32_t*>(smem + p.off_pool_id);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
-    // barrier slots: [0, 6) full, [6, 12) empty, 12 a_full, 13 a_empty, 14-15 tmem_full, 16-17 tmem_empty
+    // barrier slots: [0, 6) full, [6, 12) empty, 12 a_full, 13 a_empty, 14-15 tmem_full, 16-17 tmem_empty,
+    // 18 a_full / 19 a_empty of the second query-tile buffer
     const uint32_t bar0 = smem_u32(bars);
     auto BAR = [&](int i) { return bar0 + 8u * i; };
     constexpr int B_FULL = 0, B_EMPTY = 6, B_AFULL = 12, B_AEMPTY = 13, B_TFULL = 14, B_TEMPTY = 16;
+    // Query-tile buffer of item number i of this CTA: buffer i % nabuf, used for the (i / nabuf)-th time.
+    const uint32_t a_stride = (uint32_t)(p.nkc * TC_A_CHUNK + TC_A_AUG);
+    const bool two_a = !PAIR && p.nabuf == 2;
+    auto a_buf = [&](uint32_t item) { return two_a ? (item & 1u) : 0u; };
+    auto a_phase = [&](uint32_t item) { return two_a ? ((item >> 1) & 1u) : (item & 1u); };
+    auto a_full_bar = [&](uint32_t buf) { return BAR(buf ? 18 : B_AFULL); };
+    auto a_empty_bar = [&](uint32_t buf) { return BAR(buf ? 19 : B_AEMPTY); };
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 20);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
 
@@ -273,6 +283,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         for (int i = 0; i < TC_MAX_STAGES; ++i) { mbar_init(BAR(B_FULL + i), 1); mbar_init(BAR(B_EMPTY + i), 1); }
         mbar_init(BAR(B_AFULL), 1);
         mbar_init(BAR(B_AEMPTY), 1);
+        mbar_init(BAR(18), 1);
+        mbar_init(BAR(19), 1);
         for (int i = 0; i < 2; ++i) { mbar_init(BAR(B_TFULL + i), 1); mbar_init(BAR(B_TEMPTY + i), 4 * TC_NWG * OPERAND_CTAS); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -322,13 +334,14 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
                 int t0, t1;
                 tc_item_range(p, it, split, t0, t1);
-                if (!mbar_wait(BAR(B_AEMPTY), (item_no & 1) ^ 1, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
-                    tc_report_timeout(p.status, 4, B_AEMPTY); ok = false; break;
+                const uint32_t ab = a_buf(item_no), a_off = ab * a_stride;
+                if (!mbar_wait(a_empty_bar(ab), a_phase(item_no) ^ 1u, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
+                    tc_report_timeout(p.status, 4, ab ? 19 : B_AEMPTY); ok = false; break;
                 }
-                if (leader) mbar_expect_tx(BAR(B_AFULL), (p.nkc * TC_A_CHUNK + TC_A_AUG) * OPERAND_CTAS);
+                if (leader) mbar_expect_tx(a_full_bar(ab), (p.nkc * TC_A_CHUNK + TC_A_AUG) * OPERAND_CTAS);
                 for (int kc = 0; kc < p.nkc; ++kc)
-                    load(a_addr + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, BAR(B_AFULL));
-                load(a_aug_addr, &map_q_aug, d_pad, qt * TC_BM, BAR(B_AFULL));
+                    load(a_addr + a_off + kc * TC_A_CHUNK, &map_q, kc * TC_BK, qt * TC_BM, a_full_bar(ab));
+                load(a_aug_addr + a_off, &map_q_aug, d_pad, qt * TC_BM, a_full_bar(ab));
                 const int nt = t1 - t0;
                 const int rot = (int)(((int64_t)unit * nt) / n_units);
                 for (int i = 0; i < nt && ok; ++i) {
@@ -377,8 +390,9 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 const int split = it / n_units;
                 int t0, t1;
                 tc_item_range(p, it, split, t0, t1);
-                if (!mbar_wait(BAR(B_AFULL), item_no & 1, abort_flag, p.wait_ns, p.wait_hint_ns)) {
-                    tc_report_timeout(p.status, 5, B_AFULL); ok = false; break;
+                const uint32_t ab = a_buf(item_no), a_off = ab * a_stride;
+                if (!mbar_wait(a_full_bar(ab), a_phase(item_no), abort_flag, p.wait_ns, p.wait_hint_ns)) {
+                    tc_report_timeout(p.status, 5, ab ? 18 : B_AFULL); ok = false; break;
                 }
                 for (int t = t0; t < t1 && ok; ++t, ++tile_no) {
                     const int b = tile_no & 1;
@@ -398,7 +412,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         }
                         TC_PROF(prof_full += clock64() - c1;)
                         tc_fence_after_sync();
-                        const uint64_t da = umma_desc(a_addr + kc * TC_A_CHUNK);
+                        const uint64_t da = umma_desc(a_addr + a_off + kc * TC_A_CHUNK);
                         const uint64_t db = umma_desc(b_addr + s * SLOT_BYTES);
 #pragma unroll
                         for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
@@ -407,13 +421,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         }
                         if (kc == p.nkc - 1 && !(DBG && (p.dbg_flags & 8))) {
                             // norm columns: ones x split(-||x||^2/2), 32-byte rows, 32-byte swizzle
-                            mma(d_tmem, umma_desc_sw32(a_aug_addr), umma_desc_sw32(b_addr + s * SLOT_BYTES + SLOT_CHUNK), 1u);
+                            mma(d_tmem, umma_desc_sw32(a_aug_addr + a_off), umma_desc_sw32(b_addr + s * SLOT_BYTES + SLOT_CHUNK), 1u);
                         }
                         commit(BAR(B_EMPTY + s));   // slot reusable once these MMAs retire
                     }
                     if (ok) commit(BAR(B_TFULL + b));
                 }
-                if (ok) commit(BAR(B_AEMPTY));       // query tile reusable
+                if (ok) commit(a_empty_bar(ab));     // query tile buffer reusable
             }
             TC_PROF(if (blockIdx.x < 160) {
                 g_tc_prof[blockIdx.x * TC_PROF_WORDS + 1] = prof_full;
@@ -1358,6 +1372,13 @@ static int launch_tc_impl(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
 }
 int launch_knn_tc_scoring(const TcKnnParams& p, cudaStream_t st) { return launch_tc_main(p, nullptr, 0, st); }
 
+// FLASHLIB_B200_ASSIGN_SINGLE_A=1: one query-tile buffer in the assignment launches (measurements).
+static int tc_assign_single_a() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("FLASHLIB_B200_ASSIGN_SINGLE_A"); v = (e && atoi(e) != 0) ? 1 : 0; }
+    return v;
+}
+
 int tc_prof_read(unsigned long long* host_out, int words) {
     const size_t n = sizeof(unsigned long long) * (size_t)(words < 160 * TC_PROF_WORDS ? words : 160 * TC_PROF_WORDS);
     FL_CHECK_CUDA(cudaMemcpyFromSymbol(host_out, g_tc_prof, n));
@@ -1375,9 +1396,14 @@ int launch_assign_tc(const TcKnnParams& p, float* asg_sc, uint32_t* asg_id, cons
     if (rc == FL_OK) rc = make_map_bf16(&map_db, p.dbrows, p.m_pad, pitch, TC_BK, TC_BN);
     if (rc == FL_OK) rc = make_map_bf16(&map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
-    const TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), 0);
+    // Items are short here (a query tile against a handful of centroid tiles): with room for a second
+    // query-tile buffer beside a three-slot ring the next item's tile is loaded while this one is scored.
+    TcSmemPlan sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), 0, TC_B_STAGE, 2);
+    int nabuf = 2;
+    if (sp.nstage < 3 || tc_assign_single_a()) { sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), 0); nabuf = 1; }
     if (sp.nstage < 2) { set_error("tensor-core assignment: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     TcKernelParams kp{};
+    kp.nabuf = nabuf;
     kp.n_qtiles = (int)(p.nq_pad / TC_BM);
     kp.n_tiles = (int)(p.m_pad / TC_BN);
     kp.nsplit = 1;
