@@ -224,8 +224,14 @@ static __device__ __noinline__ float2 tc_compact_rows_pairs(unsigned need, float
 // compaction, entry counts published): no pool takes shared memory, so the TMA ring is four
 // slots deep -- two whole tiles, where MODE 4 has room for one and stalls on every load -- and
 // nothing is copied out when an item ends.  The inverted-file scan runs in this mode.
+//
+// MODE 6 (TC_MODE_KNN_GS) is MODE 0 with its small pools (32 slots, 12 kept) in global memory, in
+// place in the published-pool buffers like MODE 3: appends are rare in MODE 0 (about a hundred per
+// query row and launch), so their stores and the compactions' reads can afford the L2, and the
+// 67 KB of shared memory the pools took go to the TMA ring (four slots instead of three at 128
+// features, four instead of two at 256).
 constexpr int TC_MODE_KNN = 0, TC_MODE_SEED = 1, TC_MODE_ASSIGN = 2, TC_MODE_KNN_BIG = 3, TC_MODE_KNN_MID = 4,
-              TC_MODE_KNN_GPOOL = 5;
+              TC_MODE_KNN_GPOOL = 5, TC_MODE_KNN_GS = 6;
 constexpr int TC_GP_K1 = 24, TC_GP_CAP = 64;
 //
 // PAIR: two CTAs of a cluster work as one (tcgen05 cta_group::2).  CTA r of the pair owns query
@@ -440,6 +446,8 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         // every accumulator and keeps its own pool per query row.
         const int wg = warp >> 2, quarter = warp & 3;
         constexpr bool BIG = (MODE == TC_MODE_KNN_BIG);
+        constexpr bool GS = (MODE == TC_MODE_KNN_GS);
+        constexpr bool GLOB = BIG || GS;                 // pools addressed in global memory
         constexpr bool MID = (MODE == TC_MODE_KNN_MID);
         constexpr bool GP = (MODE == TC_MODE_KNN_GPOOL);
         constexpr int CAP = BIG ? TC_BIG_CAP : MID ? TC_MID_CAP : GP ? TC_GP_CAP : TC_CAP;
@@ -476,7 +484,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 qidx = __ldg(p.row_query + qrow);
                 if (qidx >= 0) tau_in = fmaxf(tau_in, __ldcg(p.tau_q + qidx));
             }
-            if (BIG) {
+            if (GLOB) {
                 pstride = (int64_t)p.nsplit * TC_NWG * CAP;
                 const int64_t o = (((int64_t)(qt * TC_BM + quarter * 32) * p.nsplit + split) * TC_NWG + wg) * CAP;
                 warp_sc = p.part_sc + o;
@@ -807,7 +815,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         for (int j = 0; j < 8; ++j) {
                             const bool pass = (pm >> j) & 1u;
                             const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : CAP;
-                            if (!BIG || pass) {       // shared pools: slot CAP is the row's scratch slot
+                            if (!GLOB || pass) {      // shared pools: slot CAP is the row's scratch slot
                                 my_sc[pos] = __uint_as_float(r[j]);
                                 my_id[pos] = row_base + g * 8 + j;
                             }
@@ -836,7 +844,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         // at most one passing score per lane: it is the maximum of the group
                         const float mx = fmaxf(fmax3(sv[0], sv[1], sv[2]), fmax3(fmax3(sv[3], sv[4], sv[5]), sv[6], sv[7]));
                         const int pos = np ? cnt : CAP;
-                        if (!BIG || np) {
+                        if (!GLOB || np) {
                             my_sc[pos] = mx;
                             my_id[pos] = scb + (__ffs(pm) - 1);
                         }
@@ -845,7 +853,7 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                         for (int j = 0; j < 8; ++j) {
                             const bool pass = (pm >> j) & 1u;
                             const int pos = pass ? cnt + __popc(pm & ((1u << j) - 1u)) : CAP;
-                            if (!BIG || pass) {
+                            if (!GLOB || pass) {
                                 my_sc[pos] = sv[j];
                                 my_id[pos] = scb + j;
                             }
@@ -881,6 +889,13 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             if (BIG) {
                 // the pools already are the published buffers
                 p.part_cnt[(qrow * p.nsplit + split) * TC_NWG + wg] = cnt;
+                p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
+                if (tau > tau_in) __stcg(p.tau + qrow, tau);
+                continue;
+            }
+            if (GS) {
+                // the pools already are the published buffers: pad the unused slots
+                for (int e = cnt; e < CAP; ++e) { my_sc[e] = neg_inf(); my_id[e] = INVALID_ID; }
                 p.part_tau[(qrow * p.nsplit + split) * TC_NWG + wg] = tau;
                 if (tau > tau_in) __stcg(p.tau + qrow, tau);
                 continue;
@@ -1160,8 +1175,19 @@ struct TcLaunch {
     TcSmemPlan sp;
     TcKernelParams kp;
     int seed_tiles, seed_rank;
-    bool big, mid;
+    bool big, mid, gs;
 };
+
+// Plain k <= 16 scoring with the small pools in global memory (mode KNN_GS) instead of shared memory.
+// Measured on 1M rows x 10 000 queries: 8 % slower at 128 features (2.86 vs 2.65 ms: the three-slot ring
+// was not what held the kernel back, and compactions through the L2 cost more), 12 % faster at 192 and
+// 21 % faster at 256 features (4.83 vs 5.85 ms), where pools in shared memory leave only two ring
+// slots.  So: beyond 128 features.  FLASHLIB_B200_TC_GS=0/1 overrides.
+static int tc_gs_requested(int d_pad) {
+    static int v = -2;
+    if (v == -2) { const char* e = getenv("FLASHLIB_B200_TC_GS"); v = e ? (atoi(e) != 0 ? 1 : 0) : -1; }
+    return v >= 0 ? v : (d_pad > 128 ? 1 : 0);
+}
 
 // Everything a launch needs: tensor maps, shared-memory plan, kernel parameters and the size of
 // the seeding sample.
@@ -1169,6 +1195,9 @@ static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch
     FL_CHECK_ARG(p.qplane && p.dbrows && p.tau, "tensor-core kNN launch with a null buffer");
     L->big = tc_knn_big(p.k) != 0 || p.big_pools != 0;
     L->mid = p.deep_pools != 0;
+    const TcExperiment& ex0 = tc_experiment();
+    L->gs = !L->big && !L->mid && p.pair_pools == nullptr && dbg == nullptr && ex0.flags == 0 && p.row_query == nullptr &&
+            p.item_t0 == nullptr && !tc_pair_enabled(p.nq_pad, p.k) && tc_gs_requested(p.d_pad) != 0;
     const int pitch = p.d_pad + PLANE_AUG_COLS;
     int rc = cached_map_bf16(&L->map_q, p.qplane, p.nq_pad, pitch, TC_BK, TC_BM);
     if (rc == FL_OK) rc = cached_map_bf16(&L->map_q_aug, p.qplane, p.nq_pad, pitch, PLANE_AUG_COLS, TC_BM);
@@ -1176,7 +1205,7 @@ static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch
     if (rc == FL_OK) rc = cached_map_bf16(&L->map_db_aug, p.dbrows, p.m_pad, pitch, PLANE_AUG_COLS, TC_BN);
     if (rc != FL_OK) return rc;
     FL_CHECK_ARG(!(L->mid && (L->big || dbg)), "tensor-core kNN launch: deep pools go with k <= 16");
-    L->sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), (L->big || p.pair_pools != nullptr) ? 0 : L->mid ? TC_MID_CAP + 1 : TC_PSTR);
+    L->sp = tc_smem_plan(p.d_pad, smem_optin_bytes(), (L->big || L->gs || p.pair_pools != nullptr) ? 0 : L->mid ? TC_MID_CAP + 1 : TC_PSTR);
     if (L->sp.nstage < 2) { set_error("tensor-core kNN: feature dimension %d leaves no room for the TMA ring", p.d_pad); return FL_EUNSUPPORTED; }
     const TcExperiment& ex = tc_experiment();
     TcKernelParams& kp = L->kp;
@@ -1348,6 +1377,9 @@ static int launch_tc_main(const TcKnnParams& p, float* dbg, int64_t dbg_ld, cuda
     } else if (big) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_BIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<false, TC_MODE_KNN_BIG><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
+    } else if (L.gs) {
+        FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<false, TC_MODE_KNN_GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
+        knn_tc_kernel<false, TC_MODE_KNN_GS><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
     } else if (dbg != nullptr || kp.dbg_flags != 0) {
         FL_CHECK_CUDA(cudaFuncSetAttribute(knn_tc_kernel<true, TC_MODE_KNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, sp.bytes));
         knn_tc_kernel<true, TC_MODE_KNN><<<grid, TC_THREADS, sp.bytes, st>>>(L.map_q, L.map_q_aug, L.map_db, L.map_db_aug, kp);
