@@ -525,11 +525,20 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 constexpr bool SEED = (MODE == TC_MODE_SEED);
                 if (MODE == TC_MODE_ASSIGN) {
                     const float b1_before = b1;
+                    // column index into the low 7 mantissa bits: one three-input logic instruction per
+                    // score, (v & mask) | column, with the mask held in a register
+                    uint32_t idx_mask;
+                    asm volatile("mov.u32 %0, 0xFFFFFF80;" : "=r"(idx_mask));
+                    auto pack = [&](uint32_t v, uint32_t col) {
+                        uint32_t r;
+                        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(v), "r"(idx_mask), "r"(col));
+                        return r;
+                    };
                     auto top2 = [&](uint32_t (&v)[32], int slice) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
-                            const float x = __uint_as_float((v[j] & 0xFFFFFF80u) | (uint32_t)(slice * 32 + j));
-                            const float y = __uint_as_float((v[j + 1] & 0xFFFFFF80u) | (uint32_t)(slice * 32 + j + 1));
+                            const float x = __uint_as_float(pack(v[j], (uint32_t)(slice * 32 + j)));
+                            const float y = __uint_as_float(pack(v[j + 1], (uint32_t)(slice * 32 + j + 1)));
                             const float hi = fmaxf(x, y), lo = fminf(x, y);
                             b2 = fmax3(b2, lo, fminf(b1, hi));
                             b1 = fmaxf(b1, hi);
