@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .kmeans import euclid_assign_triton, flash_kmeans
-from .knn import _as_f32_rows, _defer_status_check, _stream_ptr, flash_knn, row_sqnorm
+from .knn import _as_f32_rows, _defer_status_check, _mode_from, _stream_ptr, knn_f32, row_sqnorm
 
 
 @dataclass
@@ -270,8 +270,10 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     # batches take the tensor cores, where the 2 nq nlist D contraction costs next to nothing.
     coarse = "bf16" if (Q.shape[0] * index.nlist >= (1 << 22) and nprobe <= 16 and index.Dp <= 256
                         and index.centroids.dtype == torch.float32) else "exact"
-    probed = flash_knn(Qp.unsqueeze(0), index.centroids.unsqueeze(0), nprobe,
-                       return_distances=False, mode=coarse)[0]
+    # (no second tensor-core stage here: on a database of a few tiles the exact pass for a handful of
+    # unproven rows costs less than the stage's three launches cost every call)
+    _, probed, _ = knn_f32(_as_f32_rows(Qp), _as_f32_rows(index.centroids), nprobe, mode=_mode_from(coarse),
+                           check_status="deferred", second_stage=False)
     mode = {"auto": None, "elementwise": "exact", "gemm": "bf16"}[variant]
     if mode == "bf16" and (k > 16 or index.Dp > 256):
         mode = "exact"
