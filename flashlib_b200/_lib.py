@@ -105,6 +105,7 @@ SIGNATURES = {
     "fl_ivf_build_workspace_bytes": (c_int64, [c_int64, c_int]),
     "fl_ivf_build_csr_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_int64, c_void_p]),
+    "fl_ivf_map_ids": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "fl_ivf_plane_bytes": (c_int64, [c_int64, c_int, c_int]),
     "fl_ivf_prepare_f32": (c_int, [c_void_p, c_int64, c_int64, c_int, c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "fl_ivf_fine_scan_tc_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int64, c_int, c_int]),

@@ -252,6 +252,24 @@ static IvfBuildWs ivf_build_plan(int64_t m, int nlist) {
 
 using namespace fl;
 
+// out[i] = pos[i] >= 0 ? ids[pos[i]] : -1
+__global__ void ivf_map_ids_kernel(const int32_t* __restrict__ pos, const int64_t* __restrict__ ids, int64_t n, int64_t m,
+                                   int64_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int32_t p = pos[i];
+    out[i] = (p >= 0 && p < m) ? __ldg(ids + p) : -1;
+}
+
+extern "C" int fl_ivf_map_ids(const int32_t* pos, const int64_t* ids, int64_t n, int64_t m, int64_t* out, void* stream) {
+    FL_CHECK_ARG(n >= 0 && m >= 0, "fl_ivf_map_ids: bad shape");
+    if (n == 0) return FL_OK;
+    FL_CHECK_ARG(pos && ids && out, "fl_ivf_map_ids: null pointer");
+    ivf_map_ids_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, (cudaStream_t)stream>>>(pos, ids, n, m, out);
+    FL_CHECK_LAUNCH();
+    return FL_OK;
+}
+
 extern "C" int64_t fl_ivf_build_workspace_bytes(int64_t m, int nlist) {
     if (m < 1 || nlist < 1) return 0;
     return ivf_build_plan(m, nlist).bytes;

@@ -278,9 +278,15 @@ def flash_ivf_flat_search(index: IvfFlatIndex, Q: torch.Tensor, k: int, *, nprob
     if mode == "bf16" and (k > 16 or index.Dp > 256):
         mode = "exact"
     vals, pos = ivf_fine_scan(Qp, index, probed, k, mode=mode)
-    valid = pos >= 0
-    pos_safe = pos.clamp_min(0).to(torch.int64)
-    ids = torch.where(valid, index.ids[pos_safe], torch.full_like(pos_safe, -1))
+    if index.ids.dtype == torch.int64 and index.ids.is_contiguous():
+        ids = torch.empty(pos.shape, dtype=torch.int64, device=pos.device)
+        with torch.cuda.device(pos.device):
+            _lib.check(_lib.load().fl_ivf_map_ids(pos.data_ptr(), index.ids.data_ptr(), pos.numel(), index.ids.shape[0],
+                                                  ids.data_ptr(), _stream_ptr(pos.device)))
+    else:
+        valid = pos >= 0
+        pos_safe = pos.clamp_min(0).to(torch.int64)
+        ids = torch.where(valid, index.ids[pos_safe], torch.full_like(pos_safe, -1))
     return vals, ids
 
 

@@ -355,6 +355,11 @@ int     fl_ivf_build_csr_f32(const float* x, int64_t m, int64_t ldx, int d,
                              const int32_t* labels, int nlist,
                              float* data, int64_t* ids, int64_t* list_offsets, int32_t* max_list_len,
                              void* ws, int64_t ws_bytes, void* stream);
+/* Stored positions (the fine scans' out_pos, -1 padded) to the caller's row ids: out[i] =  */
+/* pos[i] >= 0 ? ids[pos[i]] : -1, the last line of the reference's search                  */
+/* (ivf_flat/triton/search.py:104-107).                                                     */
+int     fl_ivf_map_ids(const int32_t* pos, const int64_t* ids, int64_t n, int64_t m,
+                       int64_t* out, void* stream);
 
 /* The same fine scan on the tensor cores (k <= 16, d <= 256), the counterpart of the     */
 /* reference's GEMM variant (ivf_flat/triton/fine_scan_gemm.py:41-272).                   */
