@@ -142,6 +142,26 @@ __global__ void ivf_tc_items_kernel(const int* __restrict__ cnt, const int* __re
     }
 }
 
+// Order in which the scoring kernel deals the items to its CTAs: longest list ranges first, so that the
+// round-robin deal gives every CTA a similar number of tiles (list lengths spread over a factor of
+// five around their mean).  One block sorts (tile count, item) in shared memory; entries past the
+// live items sort last and are never visited.
+constexpr int IVF_ORDER_MAX = 4096;
+__global__ void __launch_bounds__(1024) ivf_tc_item_order_kernel(const int* __restrict__ item_t0, const int* __restrict__ item_t1,
+                                                                 const int* __restrict__ live_rows, int p2, int max_items,
+                                                                 int* __restrict__ order) {
+    __shared__ float s_key[IVF_ORDER_MAX];
+    __shared__ uint32_t s_id[IVF_ORDER_MAX];
+    const int n_items = *live_rows / IVF_TC_BQ;
+    for (int i = threadIdx.x; i < p2; i += 1024) {
+        const bool live = i < n_items && i < max_items;
+        s_key[i] = live ? (float)(item_t1[i] - item_t0[i]) : -1.f;
+        s_id[i] = (uint32_t)i;
+    }
+    block_sort_desc<1024>(s_key, s_id, p2);
+    for (int i = threadIdx.x; i < max_items && i < p2; i += 1024) order[i] = (int)s_id[i];
+}
+
 // One warp per gathered query row (grid-stride over the live rows): the bf16 row of the pair's
 // query with ones in the norm columns and a -inf starting threshold; rows without a pair are
 // zero and get a +inf threshold, so nothing is ever a candidate for them.
@@ -603,7 +623,7 @@ struct IvfTcWs {
     int64_t npairs, max_items, cap_rows; int d_pad, pitch;
     int64_t off_cnt, off_pair_off, off_item_off, off_cursor, off_sorted, off_pair_row, off_item_t0, off_item_t1,
         off_grow, off_row_query, off_tau_q, off_counters, off_qplane, off_tau, off_seed_cls, off_pools, off_part_cnt, off_part_tau, off_fblist,
-        off_x_scratch, off_x_done, bytes;
+        off_x_scratch, off_x_done, off_item_order, bytes;
 };
 
 static int64_t take(int64_t& cur, int64_t bytes) {
@@ -643,6 +663,7 @@ static IvfTcWs ivf_tc_plan(int64_t nq, int nprobe, int nlist, int d, int k) {
     // exact pass over a handful of queries: per-block partial results and a ticket per query
     w.off_x_scratch = take(cur, (int64_t)2 * sm_count() * 16 * 8);
     w.off_x_done = take(cur, (int64_t)2 * sm_count() * 4);
+    w.off_item_order = take(cur, w.max_items * 4);
     w.bytes = cur;
     return w;
 }
@@ -745,6 +766,14 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     ivf_tc_items_kernel<<<(unsigned)nlist, 128, 0, st>>>(cnt, pair_off, item_off, sorted_pair, tile_off, nlist, item_t0,
                                                         item_t1, grow, pair_row, live_rows);
     FL_CHECK_LAUNCH();
+    // item order for the scoring launch (tables of up to 4 096 items; larger ones are dealt in list order)
+    int* item_order = nullptr;
+    if (w.max_items <= IVF_ORDER_MAX) {
+        item_order = reinterpret_cast<int*>(base + w.off_item_order);
+        ivf_tc_item_order_kernel<<<1, 1024, 0, st>>>(item_t0, item_t1, live_rows, pow2_ceil((int)w.max_items), (int)w.max_items,
+                                                    item_order);
+        FL_CHECK_LAUNCH();
+    }
     profile_mark(st);      // 2: gathered query plane
     ivf_tc_gather_kernel<<<(unsigned)(8 * sm_count()), 256, 0, st>>>(
         q, ldq, d, nprobe, grow, live_rows, reinterpret_cast<__nv_bfloat16*>(base + w.off_qplane), tau,
@@ -783,6 +812,7 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
         FL_CHECK_LAUNCH();
     }
     profile_mark(st);      // 5: scoring pass
+    tp.item_order = item_order;
     rc = launch_knn_tc(tp, st);
     profile_end(st);
     profile_mark(st);      // 6: finalisation

@@ -127,6 +127,7 @@ struct TcKnnParams {
     const int* item_t0;      // optional, with nsplit == 1: database tile range [item_t0[t], item_t1[t]) of
     const int* item_t1;      //   query tile t instead of one uniform range (inverted-file scan)
     int item_tile_cap;       // seeding pass over item tables: tiles of every item's range it samples
+    const int* item_order;   // optional, with item tables: order in which the items are dealt to the CTAs
     void* pair_pools;        // optional (k <= 16): pools kept in global memory as (score f32, row u32) pairs,
                              //   [nq_pad][nsplit][tc_taus_per_range][tc_pair_pool_cap]; entry counts go to
                              //   part_cnt, thresholds to part_tau, part_sc / part_id are not used

@@ -106,6 +106,8 @@ struct TcKernelParams {
     const int* item_t0;      // optional (one range per query tile): first / one-past-last database
     const int* item_t1;      //   tile of query tile `it`, instead of the uniform ranges
     int item_tile_cap;       // > 0: at most this many tiles of every table range (seeding over item tables)
+    const int* item_order;   // optional, with item tables: the CTAs walk item item_order[i] in place of item i
+                             //   (longest ranges first, so that the round-robin deal comes out even)
     float* seed_cls;         // seeding output: [nq_pad][TC_NWG][16] class maxima
     float2* gpool;           // global-pool mode: (score, row) pairs, [nq_pad][nsplit][TC_NWG][TC_GP_CAP]
     float* asg_sc; uint32_t* asg_id;   // assignment mode outputs: [rows][TC_NWG] x (best, second) / centroid
@@ -336,10 +338,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                 if (PAIR) tma_load_2d_pair(dst, map, c0, c1, bar); else tma_load_2d(dst, map, c0, c1, bar);
             };
             for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
-                const int split = it / n_units, unit = it - split * n_units;
+                const int itp = p.item_order != nullptr ? __ldg(p.item_order + it) : it;
+                const int split = itp / n_units, unit = itp - split * n_units;
                 const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
                 int t0, t1;
-                tc_item_range(p, it, split, t0, t1);
+                tc_item_range(p, itp, split, t0, t1);
                 const uint32_t ab = a_buf(item_no), a_off = ab * a_stride;
                 if (!mbar_wait(a_empty_bar(ab), a_phase(item_no) ^ 1u, abort_flag, 2 * p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 4, ab ? 19 : B_AEMPTY); ok = false; break;
@@ -393,9 +396,10 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             bool ok = true;
             TC_PROF(long long prof_full = 0; long long prof_tempty = 0;)
             for (int it = it_first; it < n_items && ok; it += it_step, ++item_no) {
-                const int split = it / n_units;
+                const int itp = p.item_order != nullptr ? __ldg(p.item_order + it) : it;
+                const int split = itp / n_units;
                 int t0, t1;
-                tc_item_range(p, it, split, t0, t1);
+                tc_item_range(p, itp, split, t0, t1);
                 const uint32_t ab = a_buf(item_no), a_off = ab * a_stride;
                 if (!mbar_wait(a_full_bar(ab), a_phase(item_no), abort_flag, p.wait_ns, p.wait_hint_ns)) {
                     tc_report_timeout(p.status, 5, ab ? 18 : B_AFULL); ok = false; break;
@@ -471,10 +475,11 @@ knn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             if (PAIR) mbar_arrive_cluster(BAR(B_TEMPTY + b), 0u); else mbar_arrive(BAR(B_TEMPTY + b));
         };
         for (int it = it_first; it < n_items && ok; it += it_step) {
-            const int split = it / n_units, unit = it - split * n_units;
+            const int itp = p.item_order != nullptr ? __ldg(p.item_order + it) : it;
+            const int split = itp / n_units, unit = itp - split * n_units;
             const int qt = PAIR ? 2 * unit + (int)cta_rank : unit;
             int t0, t1;
-            tc_item_range(p, it, split, t0, t1);
+            tc_item_range(p, itp, split, t0, t1);
             const int64_t qrow = (int64_t)qt * TC_BM + quarter * 32 + lane;
             float tau_in = __ldcg(p.tau + qrow);
             int qidx = -1;
@@ -1231,7 +1236,7 @@ static int tc_prepare(const TcKnnParams& p, float* dbg, int64_t dbg_ld, TcLaunch
     kp.part_cnt = p.part_cnt;
     kp.gpool = reinterpret_cast<float2*>(p.pair_pools);
     kp.seed_cls = p.seed_cls;
-    kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1;
+    kp.nq_dev = p.nq_dev; kp.item_t0 = p.item_t0; kp.item_t1 = p.item_t1; kp.item_order = p.item_order;
     kp.row_query = p.row_query; kp.tau_q = p.tau_q;
     kp.dbg_flags = ex.flags;
     kp.wait_hint_ns = ex.hint_ns;
