@@ -19,8 +19,11 @@ __global__ void kmeans_halfnorm_kernel(const float* __restrict__ x, int n, int d
 }
 
 // Exact fp32 assignment: 64 points per block against all centroids in tiles of 128.
-// The winner maximises <x,c> - ||c||^2/2, i.e. minimises ||x - c||^2; on exact ties the
-// lowest centroid index wins.
+// The candidates maximise <x,c> - ||c||^2/2, i.e. minimise ||x - c||^2.  The best TWO by that score are
+// kept and re-scored with fp32 sum (x - c)^2: where two centroids lie closer together than the
+// rounding of the expanded score resolves (near-duplicate centroids), the expansion alone -- which is
+// all the reference's kernels and its CPU path use -- picks either; the direct distance picks the
+// nearer.  On exact ties the lowest centroid index wins.
 template <int TQ>
 __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
     const float* __restrict__ x, int64_t n, int64_t ldx, const float* __restrict__ c, int K, int64_t ldc,
@@ -43,10 +46,11 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
         const int r = (i * 256 + tid) >> 3;
         qrow[i] = (r < BQ && row0 + r < n) ? x + (row0 + r) * ldx : nullptr;
     }
-    float best[TQ];
-    int bidx[TQ];
+    float best[TQ], sec[TQ];
+    int bidx[TQ], sidx[TQ];
 #pragma unroll
-    for (int i = 0; i < TQ; ++i) { best[i] = neg_inf(); bidx[i] = 0x7fffffff; }
+    for (int i = 0; i < TQ; ++i) { best[i] = sec[i] = neg_inf(); bidx[i] = sidx[i] = 0x7fffffff; }
+    auto beats = [](float a, int ai, float b, int bi) { return a > b || (a == b && ai < bi); };
 
     for (int tile = 0; tile < K; tile += 128) {
         const void* drow[4];
@@ -65,7 +69,8 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
 #pragma unroll
                 for (int i = 0; i < TQ; ++i) {
                     const float s = acc[i][j] - hv;
-                    if (s > best[i] || (s == best[i] && col < bidx[i])) { best[i] = s; bidx[i] = col; }
+                    if (beats(s, col, best[i], bidx[i])) { sec[i] = best[i]; sidx[i] = bidx[i]; best[i] = s; bidx[i] = col; }
+                    else if (beats(s, col, sec[i], sidx[i])) { sec[i] = s; sidx[i] = col; }
                 }
             }
         }
@@ -75,12 +80,40 @@ __global__ void __launch_bounds__(256) kmeans_assign_simt_kernel(
     for (int i = 0; i < TQ; ++i) {
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(FULL_MASK, best[i], o);
-            const int oi = __shfl_xor_sync(FULL_MASK, bidx[i], o);
-            if (ob > best[i] || (ob == best[i] && oi < bidx[i])) { best[i] = ob; bidx[i] = oi; }
+            const float ob = __shfl_xor_sync(FULL_MASK, best[i], o), os = __shfl_xor_sync(FULL_MASK, sec[i], o);
+            const int oi = __shfl_xor_sync(FULL_MASK, bidx[i], o), osi = __shfl_xor_sync(FULL_MASK, sidx[i], o);
+            if (beats(ob, oi, best[i], bidx[i])) {
+                // the other side's best leads: the runner-up is this side's best or the other side's second
+                if (beats(os, osi, best[i], bidx[i])) { sec[i] = os; sidx[i] = osi; } else { sec[i] = best[i]; sidx[i] = bidx[i]; }
+                best[i] = ob; bidx[i] = oi;
+            } else if (beats(ob, oi, sec[i], sidx[i])) {
+                sec[i] = ob; sidx[i] = oi;
+            }
         }
+        // every thread of the row now holds the same two candidates: direct distances, 16 lanes across the row
         const int64_t r = row0 + ty * TQ + i;
-        if (tx == 0 && r < n) labels[r] = bidx[i];
+        int label = bidx[i];
+        if (sidx[i] != 0x7fffffff) {               // (uniform over the half warp)
+            float d1 = 0.f, d2 = 0.f;
+            if (r < n) {
+                const float* xp = x + r * ldx;
+                const float* c1 = c + (int64_t)bidx[i] * ldc;
+                const float* c2 = c + (int64_t)sidx[i] * ldc;
+                for (int t = tx; t < d; t += 16) {
+                    const float xv = __ldg(xp + t);
+                    const float e1 = xv - __ldg(c1 + t), e2 = xv - __ldg(c2 + t);
+                    d1 += e1 * e1;
+                    d2 += e2 * e2;
+                }
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+                d1 += __shfl_xor_sync(FULL_MASK, d1, o);
+                d2 += __shfl_xor_sync(FULL_MASK, d2, o);
+            }
+            if (d2 < d1 || (d2 == d1 && sidx[i] < bidx[i])) label = sidx[i];
+        }
+        if (tx == 0 && r < n) labels[r] = label;
     }
 }
 
