@@ -101,3 +101,30 @@ def test_single_process_index_and_plain_call():
     _, ref_i = oracle.knn_naive(Q.cpu().numpy(), X.cpu().numpy(), 6)
     res = parity.knn_parity(Q.cpu().numpy(), X.cpu().numpy(), d.cpu().numpy(), (i - 5).cpu().numpy(), ref_i)
     assert res["ok"], res
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_seeded_shards(seed):
+    """Seeded random sweep of the shared-seed flow on one GPU: shard counts, uneven shard sizes (rows not
+    divisible by the shard count), features, k up to 16, data sorted towards one shard or not."""
+    r = np.random.RandomState(seed)
+    world = int(r.choice([2, 3, 5, 8]))
+    m = int(r.choice([world * 300 + 1, 70_001, 200_003]))
+    d = int(r.choice([8, 64, 100, 128, 200]))
+    k = int(r.choice([1, 5, 10, 16]))
+    nq = int(r.choice([1, 129, 700]))
+    g = torch.Generator().manual_seed(40 + seed)
+    centres = 2 * torch.randn(30, d, generator=g)
+    X = centres[torch.randint(0, 30, (m,), generator=g)] + torch.randn(m, d, generator=g)
+    Q = centres[torch.randint(0, 30, (nq,), generator=g)] + torch.randn(nq, d, generator=g)
+    if r.randint(2):
+        X = X[((X - Q[0]) ** 2).sum(1).argsort()].contiguous()
+    Xd, Qd = X.cuda(), Q.cuda()
+    kern, outs, msgs = run_shards(Xd, Qd, k, world)
+    dd, ii, st = kern.merge(torch.cat(msgs), nq, k, world)
+    assert st[_lib.FL_STATUS_ERROR].item() == 0, st.tolist()
+    qd, xd = Qd.double(), Xd.double()
+    d64 = (qd * qd).sum(-1, keepdim=True) + (xd * xd).sum(-1)[None, :] - 2.0 * qd @ xd.T
+    ref_i = d64.topk(k, dim=1, largest=False).indices.cpu().numpy()
+    res = parity.knn_parity(Q.numpy(), X.numpy(), dd.cpu().numpy(), ii.cpu().numpy(), ref_i)
+    assert res["ok"], (seed, world, m, d, k, nq, res)
