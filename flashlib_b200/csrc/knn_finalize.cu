@@ -42,7 +42,7 @@ int launch_knn_finalize(const FinalizeParams& p, int64_t max_slots, cudaStream_t
 // lies below qsq - 2 (bound + eps), bound = max(u, best score that was not re-scored).
 // Otherwise (or when more than BIG_CAND entries survive) the query is queued for the exact path.
 // ------------------------------------------------------------------------------------
-constexpr int BIG_THREADS = 256, BIG_CAND = 4096, BIG_RERANK = 256, BIG_POOL = 256;
+constexpr int BIG_THREADS = 256, BIG_CAND = 2048, BIG_RERANK = 256, BIG_POOL = 256;
 
 static __device__ __forceinline__ void finalize_big_slot(const FinalizeParams& p, const int64_t slot) {
     __shared__ float s_key[BIG_CAND];
