@@ -208,7 +208,7 @@ def centroid_update_delta(x: torch.Tensor, cluster_ids: torch.Tensor, prev_ids: 
 
 # Lloyd iterations between two full recomputations of the sums when they are maintained
 # incrementally: bounds the rounding drift of adding and taking out rows.
-DELTA_REFRESH = 8
+DELTA_REFRESH = 16
 
 
 def triton_lloyd_centroid_step_euclid(x: torch.Tensor, cluster_ids: torch.Tensor, old_centroids: torch.Tensor,
