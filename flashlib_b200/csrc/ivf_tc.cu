@@ -379,6 +379,8 @@ __global__ void __launch_bounds__(128) ivf_tc_finalize_kernel(
     int* fb_list) {
     __shared__ float s_sc[4][IVF_GATHER];
     __shared__ uint32_t s_id[4][IVF_GATHER];
+    __shared__ int s_poff[4][32];
+    __shared__ int s_pool[4][32];
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int64_t qi = (int64_t)blockIdx.x * 4 + w;
     if (qi >= nq) return;
@@ -393,7 +395,7 @@ __global__ void __launch_bounds__(128) ivf_tc_finalize_kernel(
 
     // Gather: 32 pools at a time, one pool per lane for the bookkeeping (gathered row, entry count,
     // threshold: independent loads), then the pools' entries are copied to the warp's list at
-    // the offsets a prefix sum of the counts gives -- no load waits for another.
+    // the offsets a prefix sum of the counts gives, 32 entries per round trip whatever pool they sit in.
     float u = neg_inf();
     int total = 0;
     bool overflow = false;
@@ -415,19 +417,23 @@ __global__ void __launch_bounds__(128) ivf_tc_finalize_kernel(
         const int chunk_total = __shfl_sync(FULL_MASK, off, 31);
         off += total - n;                             // exclusive, from the list's start
         if (total + chunk_total > IVF_GATHER) { overflow = true; break; }
-#pragma unroll 4
-        for (int pl = 0; pl < 32; ++pl) {
-            const int np = __shfl_sync(FULL_MASK, n, pl);
-            const int op = __shfl_sync(FULL_MASK, off, pl);
-            const int rp = __shfl_sync(FULL_MASK, r, pl);
-            if (np == 0) continue;
-            const float2* pool = pools + ((int64_t)rp * 2 + ((base + pl) & 1)) * IVF_POOL;
-            for (int e = lane; e < np; e += 32) {
-                const float2 v = pool[e];
-                s_sc[w][op + e] = v.x;
-                s_id[w][op + e] = __float_as_uint(v.y);
+        // The lanes share the chunk's entries evenly (a pool holds a handful of entries, so a loop over the
+        // pools would spend one memory round trip per pool): entry idx of the list belongs to the last
+        // pool whose offset is <= idx (empty pools share the offset of the next one and sort before it).
+        s_poff[w][lane] = off;
+        s_pool[w][lane] = (int)(r >= 0 ? r * 2 + (pi & 1) : 0);
+        __syncwarp();
+        for (int idx = total + lane; idx < total + chunk_total; idx += 32) {
+            int lo = 0, hi = 31;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (s_poff[w][mid] <= idx) lo = mid; else hi = mid - 1;
             }
+            const float2 v = pools[(int64_t)s_pool[w][lo] * IVF_POOL + (idx - s_poff[w][lo])];
+            s_sc[w][idx] = v.x;
+            s_id[w][idx] = __float_as_uint(v.y);
         }
+        __syncwarp();
         total += chunk_total;
     }
 #pragma unroll
