@@ -98,15 +98,18 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             float* wsc = s_sc[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             uint32_t* wid = s_id[HAS_FILTER ? (threadIdx.x >> 5) : 0];
             float lmax = neg_inf();
+            // (the pools were written by earlier launches: read-only loads, which the compiler may
+            // issue for several pools before the first one is consumed)
+#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | ((lane + 5 * s + 16 * r) & 31);
-                    const float sc = psc[pb + e];
+                    const float sc = __ldg(psc + pb + e);
                     // (padding rows of an operand plane score -3e38: no need to look their ids up)
-                    if (pid[pb + e] != INVALID_ID) lmax = fmaxf(lmax, sc);
+                    if (__ldg(pid + pb + e) != INVALID_ID) lmax = fmaxf(lmax, sc);
                 }
             }
             int rank = 0;
@@ -120,15 +123,16 @@ __device__ __forceinline__ void finalize_slot(const FinalizeParams& p, const int
             const float f0 = __shfl_sync(FULL_MASK, lmax, __ffs(sel) - 1);
             const unsigned lt = (1u << lane) - 1u;
             int total = 0;
+#pragma unroll 4
             for (int s = 0; s < nsplit; ++s) {
                 const int64_t pb = pool_base(s);
                 if (pb < 0) continue;
 #pragma unroll
                 for (int r = 0; r < NPL1; ++r) {
                     const int e = (r << 5) | lane;
-                    const float sc = psc[pb + e];
+                    const float sc = __ldg(psc + pb + e);
                     const bool pass = sc > u && sc >= f0;
-                    const uint32_t cid = pass ? real_id(pid[pb + e]) : INVALID_ID;
+                    const uint32_t cid = pass ? real_id(__ldg(pid + pb + e)) : INVALID_ID;
                     const bool keep = pass && cid != INVALID_ID;
                     const unsigned mask = __ballot_sync(FULL_MASK, keep);
                     const int pos = total + __popc(mask & lt);
