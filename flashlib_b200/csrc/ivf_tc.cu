@@ -144,22 +144,31 @@ __global__ void ivf_tc_items_kernel(const int* __restrict__ cnt, const int* __re
 
 // Order in which the scoring kernel deals the items to its CTAs: longest list ranges first, so that the
 // round-robin deal gives every CTA a similar number of tiles (list lengths spread over a factor of
-// five around their mean).  One block sorts (tile count, item) in shared memory; entries past the
-// live items sort last and are never visited.
+// five around their mean).  An item's place is the number of items that come before it (more tiles, or
+// as many and a smaller index): eight threads per item count over an eighth of the table each, 32 items
+// per block.  Entries past the live items count -1 tiles, come last and are never visited.
 constexpr int IVF_ORDER_MAX = 4096;
-__global__ void __launch_bounds__(1024) ivf_tc_item_order_kernel(const int* __restrict__ item_t0, const int* __restrict__ item_t1,
-                                                                 const int* __restrict__ live_rows, int p2, int max_items,
-                                                                 int* __restrict__ order) {
-    __shared__ float s_key[IVF_ORDER_MAX];
-    __shared__ uint32_t s_id[IVF_ORDER_MAX];
+__global__ void __launch_bounds__(256) ivf_tc_item_order_kernel(const int* __restrict__ item_t0, const int* __restrict__ item_t1,
+                                                                const int* __restrict__ live_rows, int max_items,
+                                                                int* __restrict__ order) {
+    __shared__ int s_key[IVF_ORDER_MAX];
     const int n_items = *live_rows / IVF_TC_BQ;
-    for (int i = threadIdx.x; i < p2; i += 1024) {
-        const bool live = i < n_items && i < max_items;
-        s_key[i] = live ? (float)(item_t1[i] - item_t0[i]) : -1.f;
-        s_id[i] = (uint32_t)i;
+    for (int i = threadIdx.x; i < max_items; i += 256) s_key[i] = i < n_items ? item_t1[i] - item_t0[i] : -1;
+    __syncthreads();
+    const int i = blockIdx.x * 32 + (threadIdx.x >> 3), sub = threadIdx.x & 7;
+    const bool mine = i < max_items;
+    const int ki = mine ? s_key[i] : 0;
+    int place = 0;
+    if (mine) {
+        for (int j = sub; j < max_items; j += 8) {
+            const int kj = s_key[j];
+            place += (kj > ki || (kj == ki && j < i)) ? 1 : 0;
+        }
     }
-    block_sort_desc<1024>(s_key, s_id, p2);
-    for (int i = threadIdx.x; i < max_items && i < p2; i += 1024) order[i] = (int)s_id[i];
+    place += __shfl_xor_sync(FULL_MASK, place, 1);
+    place += __shfl_xor_sync(FULL_MASK, place, 2);
+    place += __shfl_xor_sync(FULL_MASK, place, 4);
+    if (mine && sub == 0) order[place] = i;
 }
 
 // One warp per gathered query row (grid-stride over the live rows): the bf16 row of the pair's
@@ -776,8 +785,8 @@ extern "C" int fl_ivf_fine_scan_tc_f32(const float* q, int64_t nq, int64_t ldq, 
     int* item_order = nullptr;
     if (w.max_items <= IVF_ORDER_MAX) {
         item_order = reinterpret_cast<int*>(base + w.off_item_order);
-        ivf_tc_item_order_kernel<<<1, 1024, 0, st>>>(item_t0, item_t1, live_rows, pow2_ceil((int)w.max_items), (int)w.max_items,
-                                                    item_order);
+        ivf_tc_item_order_kernel<<<(unsigned)((w.max_items + 31) / 32), 256, 0, st>>>(item_t0, item_t1, live_rows,
+                                                                                     (int)w.max_items, item_order);
         FL_CHECK_LAUNCH();
     }
     profile_mark(st);      // 2: gathered query plane
